@@ -1,0 +1,381 @@
+// Decode attention: out[h,:] = softmax(scale * q[h] . K[kv(h)]^T) . V[kv(h)] for
+// one query row per head over the valid prefix [0,ctx) of a [n_kv, kv_max, D]
+// f32 cache.  Replaces cuda::attn_decode / attn_decode_dpos and the kernels
+// tl_attn_decode_*, tl_attn_decode_split*, tl_attn_combine
+// (include/cuda.h:966-1114, kernels/tensorlib_cuda.cu:842-1061).
+//
+// Design (HBM-bound: every K and V byte is read once):
+//  * grid = (splits, kv heads).  A CTA owns one KV head and one contiguous chunk
+//    of the context and serves ALL q heads of that KV head's group from the same
+//    shared-memory tiles, so GQA costs no extra HBM or L2 traffic (the reference
+//    launches one block per q head and re-reads the cache group-size times).
+//  * K/V tiles of 32 keys are contiguous in the cache, so each is one 1-D bulk
+//    async copy (cp.async.bulk) into a 3-4 stage mbarrier ring.
+//  * 8 lanes share a key (each owns D/8 dims as 16-byte chunks -> conflict-free
+//    shared loads); a warp covers 4 keys per step and up to 4 q heads, with a
+//    per-lane online softmax that only rescales when the running max moves.
+//  * Split-K over the context with an ON-CHIP merge: each CTA writes its
+//    (m, l, acc) partial, takes a ticket on a per-KV-head counter, and the last
+//    CTA to arrive folds the partials in split order.  One launch, no second
+//    kernel, deterministic.
+//  * The device-position variant reads ctx = *d_pos + 1 and launches the
+//    capacity's split count; split boundaries are derived from ctx by the same
+//    device function in both variants, so the two are bit-identical at every
+//    position (the property check_attn64.cpp:91-102 of the reference guards).
+#include "common.cuh"
+
+namespace tlb {
+
+constexpr int AT_THREADS = 256;
+constexpr int AT_WARPS = 8;
+constexpr int AT_TK = 32;  // keys per tile
+
+struct AttnParams {
+  const float* q;
+  const float* K;
+  const float* V;
+  float* out;
+  float* partials;     // [n_q][S_cap][D+2]  (m, l, acc[D])
+  int* counters;       // [n_kv], zero between launches
+  const unsigned* d_pos;  // nullptr: use ctx
+  int ctx;
+  int n_q, n_kv, grp;
+  long long kv_stride;  // kv_max * D
+  float scale;
+  int s_cap;     // partial slots per head (= launched splits)
+  int sm2;       // 2 * SM count: split target
+  int* status;
+};
+
+// Number of splits wanted for a context length (monotone non-decreasing in ctx).
+__host__ __device__ inline int attn_splits_wanted(int n_kv, int ctx, int sm2) {
+  int s = sm2 / (n_kv > 0 ? n_kv : 1);
+  int cap = ctx / 128;
+  if (s > cap) s = cap;
+  return s < 1 ? 1 : s;
+}
+// Keys per split: ceil(ctx / wanted) rounded up to a whole tile.
+__host__ __device__ inline int attn_chunk(int n_kv, int ctx, int sm2) {
+  int s = attn_splits_wanted(n_kv, ctx, sm2);
+  int chunk = (ctx + s - 1) / s;
+  chunk = (chunk + AT_TK - 1) / AT_TK * AT_TK;
+  return chunk < AT_TK ? AT_TK : chunk;
+}
+
+// Warps across heads: ceil(grp / HW) rounded up to a divisor of the warp count.
+__host__ __device__ inline int attn_hs(int grp, int HW) {
+  int hs = (grp + HW - 1) / HW;
+  while (AT_WARPS % hs) hs++;
+  return hs;
+}
+
+template <int D, int HW>
+struct AttnCfg {
+  static constexpr int STAGES = HW >= 4 ? 4 : 3;
+  static constexpr int TILE_BYTES = AT_TK * D * 4;
+  static constexpr int CH = D / 32;  // 16-byte chunks per lane (8 lanes per key)
+};
+
+template <int D, int HW>
+size_t attn_smem_bytes(int grp) {
+  using C = AttnCfg<D, HW>;
+  int hs = attn_hs(grp, HW);
+  int ks = AT_WARPS / hs;
+  size_t b = 128;
+  b += (size_t)C::STAGES * 2 * C::TILE_BYTES;
+  b += 64;  // barriers
+  b += (size_t)ks * hs * HW * (D + 4) * sizeof(float);
+  return b;
+}
+
+template <int D, int HW>
+__global__ void __launch_bounds__(AT_THREADS, (HW >= 4 ? 1 : 2))
+    attn_decode_kernel(AttnParams p) {
+  using C = AttnCfg<D, HW>;
+  extern __shared__ unsigned char smem_raw[];
+  unsigned char* base = (unsigned char*)(((uintptr_t)smem_raw + 127) & ~(uintptr_t)127);
+  float* Kt = (float*)base;
+  float* Vt = (float*)(base + (size_t)C::STAGES * C::TILE_BYTES);
+  uint64_t* bars = (uint64_t*)(base + (size_t)C::STAGES * 2 * C::TILE_BYTES);
+  float* mrg = (float*)(bars + 8);  // barrier block padded to 64 bytes
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int kslot = lane >> 3, sub = lane & 7;
+  const int kh = blockIdx.y, sp = blockIdx.x;
+  const int hs = attn_hs(p.grp, HW);  // warps across heads
+  const int ks = AT_WARPS / hs;          // warps across keys
+  const int hslot = warp % hs, kslice = warp / hs;
+
+  if (tid == 0) {
+    for (int s = 0; s < C::STAGES; s++) mbar_init(&bars[s], 1);
+    mbar_fence_init();
+  }
+  __syncthreads();
+
+  pdl_wait();
+  pdl_launch_dependents();
+
+  const int ctx = p.d_pos ? (int)(*p.d_pos) + 1 : p.ctx;
+  const int chunk = attn_chunk(p.n_kv, ctx, p.sm2);
+  const int s_live = (ctx + chunk - 1) / chunk;
+  if (sp >= s_live) return;  // capacity-sized grid: splits past the live count do nothing
+  const int k_begin = sp * chunk;
+  const int k_end = k_begin + chunk < ctx ? k_begin + chunk : ctx;
+  const int n_tiles = (k_end - k_begin + AT_TK - 1) / AT_TK;
+
+  const float* Kh = p.K + (size_t)kh * p.kv_stride;
+  const float* Vh = p.V + (size_t)kh * p.kv_stride;
+
+  auto issue = [&](int i) {
+    const int st = i % C::STAGES;
+    const int r0 = k_begin + i * AT_TK;
+    const int rows = (k_end - r0) < AT_TK ? (k_end - r0) : AT_TK;
+    const uint32_t bytes = (uint32_t)rows * D * 4;
+    mbar_expect_tx(&bars[st], 2 * bytes);
+    bulk_load_1d((unsigned char*)Kt + (size_t)st * C::TILE_BYTES, Kh + (size_t)r0 * D, bytes,
+                 &bars[st]);
+    bulk_load_1d((unsigned char*)Vt + (size_t)st * C::TILE_BYTES, Vh + (size_t)r0 * D, bytes,
+                 &bars[st]);
+  };
+  if (tid == 0) {
+    const int pre = n_tiles < C::STAGES ? n_tiles : C::STAGES;
+    for (int i = 0; i < pre; i++) issue(i);
+  }
+
+  // q fragments: lane owns chunks {sub + 8*i}
+  float4 qf[HW][C::CH];
+#pragma unroll
+  for (int h = 0; h < HW; h++) {
+    const int hh = hslot * HW + h;
+    const bool live = hh < p.grp;
+    const float4* qp = (const float4*)(p.q + (size_t)(kh * p.grp + (live ? hh : 0)) * D);
+#pragma unroll
+    for (int i = 0; i < C::CH; i++)
+      qf[h][i] = live ? qp[sub + 8 * i] : make_float4(0.f, 0.f, 0.f, 0.f);
+  }
+  float m[HW], l[HW];
+  float4 acc[HW][C::CH];
+#pragma unroll
+  for (int h = 0; h < HW; h++) {
+    m[h] = -INFINITY;
+    l[h] = 0.f;
+#pragma unroll
+    for (int i = 0; i < C::CH; i++) acc[h][i] = make_float4(0.f, 0.f, 0.f, 0.f);
+  }
+
+  for (int it = 0; it < n_tiles; it++) {
+    const int st = it % C::STAGES;
+    if (!mbar_wait_bounded(&bars[st], (it / C::STAGES) & 1, p.status, 200 + st)) return;
+    const int r0 = k_begin + it * AT_TK;
+    const int rows = (k_end - r0) < AT_TK ? (k_end - r0) : AT_TK;
+    const float4* Ks = (const float4*)((unsigned char*)Kt + (size_t)st * C::TILE_BYTES);
+    const float4* Vs = (const float4*)((unsigned char*)Vt + (size_t)st * C::TILE_BYTES);
+    for (int step = kslice; step < AT_TK / 4; step += ks) {
+      const int row = step * 4 + kslot;
+      if (step * 4 >= rows) break;
+      const bool valid = row < rows;
+      const int rr = valid ? row : 0;
+      float4 kv[C::CH];
+#pragma unroll
+      for (int i = 0; i < C::CH; i++) kv[i] = Ks[rr * (D / 4) + sub + 8 * i];
+      float s[HW];
+#pragma unroll
+      for (int h = 0; h < HW; h++) {
+        float d = 0.f;
+#pragma unroll
+        for (int i = 0; i < C::CH; i++) {
+          d = fmaf(qf[h][i].x, kv[i].x, d);
+          d = fmaf(qf[h][i].y, kv[i].y, d);
+          d = fmaf(qf[h][i].z, kv[i].z, d);
+          d = fmaf(qf[h][i].w, kv[i].w, d);
+        }
+        d += __shfl_xor_sync(0xffffffffu, d, 1);
+        d += __shfl_xor_sync(0xffffffffu, d, 2);
+        d += __shfl_xor_sync(0xffffffffu, d, 4);
+        s[h] = d * p.scale;
+      }
+#pragma unroll
+      for (int i = 0; i < C::CH; i++) kv[i] = Vs[rr * (D / 4) + sub + 8 * i];
+      if (valid) {
+#pragma unroll
+        for (int h = 0; h < HW; h++) {
+          if (s[h] > m[h]) {
+            const float corr = __expf(m[h] - s[h]);  // exp(-inf) = 0 on the first key
+            l[h] *= corr;
+#pragma unroll
+            for (int i = 0; i < C::CH; i++) {
+              acc[h][i].x *= corr; acc[h][i].y *= corr;
+              acc[h][i].z *= corr; acc[h][i].w *= corr;
+            }
+            m[h] = s[h];
+          }
+          const float pr = __expf(s[h] - m[h]);
+          l[h] += pr;
+#pragma unroll
+          for (int i = 0; i < C::CH; i++) {
+            acc[h][i].x = fmaf(pr, kv[i].x, acc[h][i].x);
+            acc[h][i].y = fmaf(pr, kv[i].y, acc[h][i].y);
+            acc[h][i].z = fmaf(pr, kv[i].z, acc[h][i].z);
+            acc[h][i].w = fmaf(pr, kv[i].w, acc[h][i].w);
+          }
+        }
+      }
+    }
+    __syncthreads();  // every warp is done with this stage
+    if (tid == 0 && it + C::STAGES < n_tiles) issue(it + C::STAGES);
+  }
+
+  // ---- merge the 4 key slots of the warp (lanes xor 8, 16), fixed order -----
+#pragma unroll
+  for (int h = 0; h < HW; h++) {
+#pragma unroll
+    for (int o = 8; o <= 16; o <<= 1) {
+      const float mo = __shfl_xor_sync(0xffffffffu, m[h], o);
+      const float lo = __shfl_xor_sync(0xffffffffu, l[h], o);
+      const float mn = fmaxf(m[h], mo);
+      // the lower lane of each pair always plays "a" so both lanes compute the same sum
+      const bool low = (lane & o) == 0;
+      const float ma = low ? m[h] : mo, mb = low ? mo : m[h];
+      const float la = low ? l[h] : lo, lb = low ? lo : l[h];
+      const float ca = (ma == -INFINITY) ? 0.f : __expf(ma - mn);
+      const float cb = (mb == -INFINITY) ? 0.f : __expf(mb - mn);
+      l[h] = la * ca + lb * cb;
+#pragma unroll
+      for (int i = 0; i < C::CH; i++) {
+        float4 ao;
+        ao.x = __shfl_xor_sync(0xffffffffu, acc[h][i].x, o);
+        ao.y = __shfl_xor_sync(0xffffffffu, acc[h][i].y, o);
+        ao.z = __shfl_xor_sync(0xffffffffu, acc[h][i].z, o);
+        ao.w = __shfl_xor_sync(0xffffffffu, acc[h][i].w, o);
+        const float4 a = low ? acc[h][i] : ao, b = low ? ao : acc[h][i];
+        acc[h][i].x = a.x * ca + b.x * cb;
+        acc[h][i].y = a.y * ca + b.y * cb;
+        acc[h][i].z = a.z * ca + b.z * cb;
+        acc[h][i].w = a.w * ca + b.w * cb;
+      }
+      m[h] = mn;
+    }
+  }
+  // ---- per-warp partials to shared memory: mrg[kslice][head][D+2] ----------
+  const int nheads_pad = hs * HW;
+  if (kslot == 0) {
+#pragma unroll
+    for (int h = 0; h < HW; h++) {
+      // entry layout: acc[D], m, l, pad, pad (16-byte aligned stride D+4)
+      float* dst = mrg + ((size_t)kslice * nheads_pad + hslot * HW + h) * (D + 4);
+      if (sub == 0) { dst[D] = m[h]; dst[D + 1] = l[h]; }
+#pragma unroll
+      for (int i = 0; i < C::CH; i++) *(float4*)(dst + (sub + 8 * i) * 4) = acc[h][i];
+    }
+  }
+  __syncthreads();
+
+  // ---- CTA merge over key slices, then either the output or a split partial --
+  const bool single = (s_live == 1);
+  for (int idx = tid; idx < p.grp * D; idx += AT_THREADS) {
+    const int hh = idx / D, d = idx - hh * D;
+    float mm = -INFINITY;
+    for (int k2 = 0; k2 < ks; k2++)
+      mm = fmaxf(mm, mrg[((size_t)k2 * nheads_pad + hh) * (D + 4) + D]);
+    float ll = 0.f, aa = 0.f;
+    for (int k2 = 0; k2 < ks; k2++) {
+      const float* src = mrg + ((size_t)k2 * nheads_pad + hh) * (D + 4);
+      const float c = (src[D] == -INFINITY) ? 0.f : __expf(src[D] - mm);
+      ll += src[D + 1] * c;
+      aa += src[d] * c;
+    }
+    const int qh = kh * p.grp + hh;
+    if (single) {
+      p.out[(size_t)qh * D + d] = aa / ll;
+    } else {
+      float* dst = p.partials + ((size_t)qh * p.s_cap + sp) * (D + 2);
+      if (d == 0) { __stcg(&dst[0], mm); __stcg(&dst[1], ll); }
+      __stcg(&dst[2 + d], aa);
+    }
+  }
+  if (single) return;
+
+  // ---- on-chip split merge: last CTA of this KV head folds the partials ------
+  __shared__ int is_last;
+  __threadfence();
+  __syncthreads();
+  if (tid == 0) {
+    const int old = atomicAdd(&p.counters[kh], 1);
+    is_last = (old == s_live - 1);
+  }
+  __syncthreads();
+  if (!is_last) return;
+  __threadfence();
+  for (int idx = tid; idx < p.grp * D; idx += AT_THREADS) {
+    const int hh = idx / D, d = idx - hh * D;
+    const int qh = kh * p.grp + hh;
+    const float* src0 = p.partials + (size_t)qh * p.s_cap * (D + 2);
+    float mm = -INFINITY;
+    for (int s2 = 0; s2 < s_live; s2++) mm = fmaxf(mm, __ldcg(&src0[(size_t)s2 * (D + 2)]));
+    float ll = 0.f, aa = 0.f;
+    for (int s2 = 0; s2 < s_live; s2++) {
+      const float* src = src0 + (size_t)s2 * (D + 2);
+      const float c = __expf(__ldcg(&src[0]) - mm);
+      ll += __ldcg(&src[1]) * c;
+      aa += __ldcg(&src[2 + d]) * c;
+    }
+    p.out[(size_t)qh * D + d] = aa / ll;
+  }
+  if (tid == 0) p.counters[kh] = 0;
+}
+
+// ---------------------------------------------------------------------------
+// host side
+// ---------------------------------------------------------------------------
+size_t attn_partials_bytes(int n_q, int n_kv, long long kv_max, int D, int sm_count) {
+  int s = attn_splits_wanted(n_kv, (int)kv_max, 2 * sm_count);
+  return (size_t)n_q * s * (D + 2) * sizeof(float);
+}
+
+template <int D, int HW>
+static int launch_t(const AttnParams& p, int splits, cudaStream_t stream) {
+  size_t smem = attn_smem_bytes<D, HW>(p.grp);
+  static bool attr = false;
+  if (!attr) {
+    TLB_CUDA(cudaFuncSetAttribute(attn_decode_kernel<D, HW>,
+                                  cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
+    attr = true;
+  }
+  LaunchCfg lc(dim3(splits, p.n_kv), dim3(AT_THREADS), smem, stream, pdl_enabled());
+  TLB_CUDA(cudaLaunchKernelEx(&lc.cfg, attn_decode_kernel<D, HW>, p));
+  return TLB_OK;
+}
+
+// ctx >= 1 and d_pos == nullptr: host-position variant.  d_pos != nullptr: the
+// context is *d_pos + 1 and the grid is sized from kv_max.
+int attn_decode_launch(DeviceCtx* c, const float* q, const float* K, const float* V, float* out,
+                       int n_q, int n_kv, int ctx, long long kv_max, int D, float scale,
+                       const unsigned* d_pos, float* partials, int* counters,
+                       cudaStream_t stream) {
+  if (D != 64 && D != 128) return set_error(TLB_ERR_UNSUPPORTED, "attn_decode: D must be 64 or 128");
+  if (n_kv <= 0 || n_q % n_kv != 0) return set_error(TLB_ERR_ARG, "attn_decode: n_q % n_kv != 0");
+  const int grp = n_q / n_kv;
+  if (grp > 32) return set_error(TLB_ERR_UNSUPPORTED, "attn_decode: GQA group > 32");
+  if (((uintptr_t)K & 15) || ((uintptr_t)V & 15) || ((uintptr_t)q & 15))
+    return set_error(TLB_ERR_ARG, "attn_decode: q/K/V must be 16-byte aligned");
+  AttnParams p;
+  p.q = q; p.K = K; p.V = V; p.out = out; p.partials = partials; p.counters = counters;
+  p.d_pos = d_pos; p.ctx = ctx; p.n_q = n_q; p.n_kv = n_kv; p.grp = grp;
+  p.kv_stride = kv_max * D; p.scale = scale; p.sm2 = 2 * c->sm_count; p.status = c->status;
+  const int basis = d_pos ? (int)kv_max : ctx;
+  const int splits = d_pos ? attn_splits_wanted(n_kv, basis, p.sm2)
+                           : (ctx + attn_chunk(n_kv, ctx, p.sm2) - 1) / attn_chunk(n_kv, ctx, p.sm2);
+  p.s_cap = d_pos ? splits : attn_splits_wanted(n_kv, basis, p.sm2);
+  // heads per warp: the smallest of {1,2,4} such that ceil(grp/HW) divides 8
+  int HW = grp == 1 ? 1 : (grp == 2 ? 2 : 4);
+  if (D == 128) {
+    if (HW == 1) return launch_t<128, 1>(p, splits, stream);
+    if (HW == 2) return launch_t<128, 2>(p, splits, stream);
+    return launch_t<128, 4>(p, splits, stream);
+  }
+  if (HW == 1) return launch_t<64, 1>(p, splits, stream);
+  if (HW == 2) return launch_t<64, 2>(p, splits, stream);
+  return launch_t<64, 4>(p, splits, stream);
+}
+
+}  // namespace tlb

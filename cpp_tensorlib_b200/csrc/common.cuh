@@ -1,0 +1,179 @@
+// Shared device helpers (mbarrier / TMA / PDL inline PTX for sm_100a) and the
+// per-device host context of the C-ABI library.
+#pragma once
+
+#include <cuda.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include <string>
+
+#include "../../include/tlb200.h"
+
+namespace tlb {
+
+// status codes (TLB_OK, TLB_ERR_*) come from the public C header
+// Device status word indices (written by kernels whose bounded waits expire).
+enum : int { ST_WAIT_TIMEOUT = 0, ST_WAIT_WHERE = 1, ST_WORDS = 8 };
+
+int set_error(int code, const std::string& msg);
+int cuda_fail(cudaError_t e, const char* what);
+
+#define TLB_CUDA(expr)                                   \
+  do {                                                   \
+    cudaError_t _e = (expr);                             \
+    if (_e != cudaSuccess) return tlb::cuda_fail(_e, #expr); \
+  } while (0)
+
+#define TLB_REQUIRE(cond, msg)                                         \
+  do {                                                                 \
+    if (!(cond)) return tlb::set_error(TLB_ERR_ARG, std::string(msg)); \
+  } while (0)
+
+// ---------------------------------------------------------------------------
+// Per-device context: scratch owned by the library (never by a kernel launch),
+// driver entry points resolved through the runtime (nothing is linked against
+// libcuda).
+// ---------------------------------------------------------------------------
+struct DeviceCtx {
+  int device = -1;
+  int sm_count = 0;
+  int l2_bytes = 0;
+  // GEMV split-K fix-up scratch (deterministic last-arriver reduction)
+  float* gemv_partials = nullptr;  // [max_workers][2][16*8]
+  int* gemv_counters = nullptr;    // [max_row_tiles], zero between launches
+  int gemv_max_workers = 0, gemv_max_tiles = 0;
+  // attention split-KV partials for the host-ctx entry point (grown on demand)
+  float* attn_scratch = nullptr;
+  size_t attn_scratch_bytes = 0;
+  int* attn_counters = nullptr;  // [max kv-head*... ] zero between launches
+  int attn_max_counters = 0;
+  // argmax result cell (packed key) + small status block
+  unsigned long long* argmax_cell = nullptr;
+  int* status = nullptr;        // device, ST_WORDS ints
+  int* status_host = nullptr;   // pinned mirror for reads
+  // CUDA-graph capture state of the reference-style capture_begin/end API
+  cudaStream_t cap_stream = nullptr;
+  bool capturing = false;
+};
+
+int get_ctx(DeviceCtx** out);  // context of the current device (created on first use)
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
+                                  const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                                  const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+EncodeTiledFn encode_tiled_fn();
+
+// ---------------------------------------------------------------------------
+// device-side PTX wrappers
+// ---------------------------------------------------------------------------
+#ifdef __CUDACC__
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) {
+  return static_cast<uint32_t>(__cvta_generic_to_shared(p));
+}
+
+__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbar_fence_init() {
+  asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)),
+               "r"(bytes)
+               : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(smem_u32(bar)), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+// Bounded wait: gives up after `limit` polls, records where in the status block
+// and returns false; the caller must then skip the work that depended on it.
+__device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, uint32_t parity, int* status,
+                                                  int where, uint32_t limit = 20000000u) {
+  for (uint32_t i = 0; i < limit; i++) {
+    if (mbar_try_wait(bar, parity)) return true;
+  }
+  if (status) {
+    atomicExch(&status[ST_WAIT_TIMEOUT], 1);
+    atomicExch(&status[ST_WAIT_WHERE], where);
+  }
+  return false;
+}
+
+// 2-D tiled TMA load (no multicast): box lands at dst, completion on bar.
+__device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* tm, int x, int y,
+                                            uint64_t* bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, "
+      "%3}], [%4];" ::"r"(smem_u32(dst)),
+      "l"(tm), "r"(x), "r"(y), "r"(smem_u32(bar))
+      : "memory");
+}
+// 1-D bulk copy global -> shared (16-byte aligned addresses and size).
+__device__ __forceinline__ void bulk_load_1d(void* dst, const void* src, uint32_t bytes,
+                                             uint64_t* bar) {
+  asm volatile(
+      "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
+          smem_u32(dst)),
+      "l"(src), "r"(bytes), "r"(smem_u32(bar))
+      : "memory");
+}
+__device__ __forceinline__ void prefetch_tmap(const CUtensorMap* tm) {
+  asm volatile("prefetch.tensormap [%0];" ::"l"(tm) : "memory");
+}
+
+// Programmatic dependent launch: wait for the kernels this one depends on /
+// let the dependent kernel's CTAs start launching.
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_launch_dependents() {
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+}
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  return v;
+}
+
+#endif  // __CUDACC__
+
+// Launch helper: optional programmatic-dependent-launch attribute.
+struct LaunchCfg {
+  cudaLaunchConfig_t cfg{};
+  cudaLaunchAttribute attr[1];
+  LaunchCfg(dim3 grid, dim3 block, size_t smem, cudaStream_t s, bool pdl) {
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = s;
+    cfg.attrs = attr;
+    cfg.numAttrs = 0;
+    if (pdl) {
+      attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+      attr[0].val.programmaticStreamSerializationAllowed = 1;
+      cfg.numAttrs = 1;
+    }
+  }
+};
+
+bool pdl_enabled();  // process-wide switch (tlb_set_pdl)
+
+}  // namespace tlb

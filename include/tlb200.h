@@ -1,0 +1,124 @@
+/* tlb200 -- C-ABI of the B200 (sm_100a) implementation of cpp-tensorlib's
+ * quantized-decode hot path.
+ *
+ * Every entry point is plain C: raw device pointers, sizes, a CUDA stream passed
+ * as void* (NULL = the legacy default stream).  No C++ or torch types cross this
+ * boundary.  Functions return 0 on success or a non-zero tlb status code;
+ * tlb_last_error() gives the message.  Each declaration names the reference
+ * interface it replaces (paths inside the reference project; "cu.h" =
+ * include/cuda.h, ".cu" = kernels/tensorlib_cuda.cu, "arr" = include/array.h,
+ * "qm" = bench/cuda/qwen_model.h).
+ *
+ * The library links the CUDA runtime statically; consumers dlopen this one
+ * shared object and link nothing else.  There is no CPU fallback: when no
+ * usable device exists every call fails with a status code.
+ */
+#ifndef TLB200_H_
+#define TLB200_H_
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* status codes */
+#define TLB_OK 0
+#define TLB_ERR_CUDA 1
+#define TLB_ERR_ARG 2
+#define TLB_ERR_UNSUPPORTED 3
+#define TLB_ERR_DEVICE_WAIT 4
+#define TLB_ERR_STATE 5
+
+/* ---- context / memory ------------------------------------------------------ */
+/* cu.h:235-321 context::get -- bind the calling thread to `device` and create the
+ * per-device state (scratch, status block).  Called implicitly by every op for
+ * the current device. */
+int tlb_init(int device);
+int tlb_device_count(void);                 /* cu.h:493 available() (count > 0) */
+const char* tlb_last_error(void);           /* message of the last failing call on this thread */
+int tlb_version(void);
+/* Bounded device-side waits record a timeout here instead of hanging:
+ * out[0] = 1 when any wait expired since the last clear, out[1] = where. */
+int tlb_device_status(int* out2, int clear);
+int tlb_set_pdl(int enabled);               /* programmatic dependent launch on/off (default on) */
+
+int tlb_alloc(int64_t bytes, void** dptr);  /* cu.h:586-603 alloc */
+int tlb_free(void* dptr);                   /* cu.h:605-624 release */
+int tlb_h2d(void* dst, const void* src, int64_t bytes, void* stream); /* cu.h:559-580 upload */
+int tlb_d2h(void* dst, const void* src, int64_t bytes, void* stream); /* cu.h:626-637 sync_to_host */
+int tlb_memset(void* dst, int value, int64_t bytes, void* stream);
+int tlb_sync(void* stream);                 /* cu.h:501-506 flush */
+
+/* ---- int4 storage ---------------------------------------------------------- */
+int64_t tlb_q4_bytes(int64_t N, int64_t K); /* include/types.h:29-31 q4_bytes */
+/* arr:703-742 array::to_q4 on the device: w is f32 logical [K,N] row-major; q4
+ * receives packed nibbles [N][K/2] then f32 scales [N][K/32].  K % 32 == 0. */
+int tlb_to_q4(const float* w_kn, int64_t K, int64_t N, void* q4, void* stream);
+/* arr:666-684 array::to_f32 (q4 branch): out is f32 logical [K,N]. */
+int tlb_q4_to_f32(const void* q4, int64_t K, int64_t N, float* out_kn, void* stream);
+
+/* ---- int4 dequant-matmul --------------------------------------------------- */
+/* cu.h:886-905 cuda::gemv_q4 / .cu:772-796 tl_gemv_q4:  y[N] = a[K] . dequant(W).
+ * group must be 32. */
+int tlb_gemv_q4(const float* a, const void* qw, const float* scales, float* y, int64_t N,
+                int64_t K, int64_t group, void* stream);
+/* The M >= 1 contraction with the fused affine epilogue the lazy graph composes
+ * into a dot node (arr:1305-1311, arr:2109-2141; the reference routes M > 1
+ * through host dequant + tl_sgemm_rb, arr:1980-1984, .cu:310-421):
+ *   y[M,N] = (x[M,K] . dequant(W)) * alpha + beta,  x row stride ldx, y row stride ldy. */
+int tlb_gemm_q4(const float* x, int64_t M, int64_t ldx, const void* qw, const float* scales,
+                float* y, int64_t ldy, int64_t N, int64_t K, float alpha, float beta,
+                void* stream);
+/* Same contraction forced through the general-shape CUDA-core kernel (any
+ * K % 32 == 0, no alignment rules); used as an independent cross-check. */
+int tlb_gemm_q4_simt(const float* x, int64_t M, int64_t ldx, const void* qw, const float* scales,
+                     float* y, int64_t ldy, int64_t N, int64_t K, float alpha, float beta,
+                     void* stream);
+
+/* ---- decode attention ------------------------------------------------------ */
+/* cu.h:966-1009 cuda::attn_decode (f32 cache).  q,out [n_q,D]; K,V [n_kv,kv_max,D]
+ * read over [0,ctx).  Split partials live in library-owned scratch. */
+int tlb_attn_decode(const float* q, const float* K, const float* V, float* out, int64_t n_q,
+                    int64_t n_kv, int64_t ctx, int64_t kv_max, int64_t D, float scale,
+                    void* stream);
+/* cu.h:1084-1114 cuda::attn_decode_dpos: ctx = *d_pos + 1, capacity-sized grid,
+ * caller-owned partials of tlb_attn_partials_bytes() (first 256 bytes must be
+ * zero before the first call: they hold the merge counters). */
+int tlb_attn_decode_dpos(const float* q, const float* K, const float* V, float* out, int64_t n_q,
+                         int64_t n_kv, const void* d_pos, int64_t kv_max, int64_t D, float scale,
+                         void* partials, void* stream);
+int64_t tlb_attn_partials_bytes(int64_t n_q, int64_t n_kv, int64_t kv_max, int64_t D); /* cu.h:948-960 */
+
+/* ---- fused row ops --------------------------------------------------------- */
+int tlb_rmsnorm(const float* x, const float* w, float* out, int64_t n, float eps, int64_t rows,
+                void* stream);                                   /* cu.h:1287-1302 */
+int tlb_rmsnorm_res(const float* x, const float* delta, const float* w, float* xout, float* hout,
+                    int64_t n, float eps, int64_t rows, void* stream); /* cu.h:1233-1252 */
+int tlb_swiglu(const float* gu, float* out, int64_t ff, int64_t rows, void* stream); /* cu.h:1306-1319 */
+int tlb_rope(const float* x, float* out, int64_t rows, int64_t T, int64_t D, int64_t pos,
+             float base, const float* bias, void* stream);       /* cu.h:1205-1222 */
+int tlb_rope_dpos(const float* x, float* out, int64_t rows, int64_t T, int64_t D,
+                  const void* d_pos, float base, const float* bias, void* stream); /* cu.h:1018-1035 */
+int tlb_kv_append(float* Kc, float* Vc, const float* k_new, const float* v_new, int64_t pos,
+                  int64_t kv_max, int64_t n_kv, int64_t D, void* stream); /* cu.h:1118-1138 */
+int tlb_kv_append_dpos(float* Kc, float* Vc, const float* k_new, const float* v_new,
+                       const void* d_pos, int64_t kv_max, int64_t n_kv, int64_t D,
+                       void* stream);                             /* cu.h:1050-1070 */
+int tlb_incr_u32(void* d_pos, void* stream);                      /* cu.h:1038-1047 */
+/* cu.h:1261-1282 cuda::argmax: reduces on the device, synchronises the stream and
+ * returns the index (smallest index among the maxima). */
+int tlb_argmax(const float* in, int64_t n, int64_t* out_idx, void* stream);
+/* Asynchronous form: the int32 index is written to d_out (device), no sync. */
+int tlb_argmax_dev(const float* in, int64_t n, void* d_out, void* stream);
+
+/* ---- CUDA-graph capture (cu.h:512-551) ------------------------------------- */
+int tlb_capture_begin(void** stream_out);   /* capture_begin: returns the stream to launch on */
+int tlb_capture_end(void** graph_exec_out); /* capture_end */
+int tlb_graph_launch(void* graph_exec, void* stream); /* graph_launch */
+int tlb_graph_destroy(void* graph_exec);    /* graph_destroy */
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* TLB200_H_ */

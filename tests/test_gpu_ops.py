@@ -1,0 +1,276 @@
+"""GPU parity tests proper: the CUDA library, called through its C-ABI, against
+the oracle (C restatement pinned to the reference) and the committed golden
+vectors produced by the reference.  Bit-exact for the int4 layout and indices;
+1e-4 for GEMV/GEMM; 1e-3 for attention (the tolerances of the specification)."""
+import numpy as np
+import pytest
+import torch
+
+import cases
+import synth
+
+pytestmark = pytest.mark.gpu
+
+
+def relerr(a, b):
+    return float(np.max(np.abs(np.asarray(a, np.float64) - b) / (1.0 + np.abs(b))))
+
+
+def dev(a):
+    return torch.from_numpy(np.ascontiguousarray(a)).cuda()
+
+
+@pytest.fixture(scope="module")
+def tl():
+    from cpp_tensorlib_b200 import cuda as tlc
+    assert tlc.available(), "no CUDA device: the GPU tests have no fallback"
+    yield tlc
+    from cpp_tensorlib_b200 import check, lib
+    import ctypes
+    st = (ctypes.c_int * 2)()
+    check(lib().tlb_device_status(st, 0))   # no bounded wait expired during the module
+
+
+# ---------------------------------------------------------------- int4 storage
+def test_to_q4_bit_exact_small(tl, port, golden):
+    a, w, a2 = cases.ref_q4_case()
+    wq = tl.to_q4(dev(w))
+    assert np.array_equal(wq.buf.cpu().numpy(), golden("q4_small")["q4"])
+    assert np.array_equal(wq.to_f32().cpu().numpy(), golden("q4_small")["deq"])
+
+
+@pytest.mark.parametrize("K,N,std", [(896, 4864, 0.02), (32, 1, 1.0), (64, 33, 5.0), (3584, 640, 0.02)])
+def test_to_q4_bit_exact_shapes(tl, port, K, N, std):
+    w = synth.normal(50, K + N, (K, N), std)
+    w[0, 0] = 0.0
+    if K >= 64:
+        w[32:64, 0] = 0.0           # an all-zero group: scale floor 1e-8/7
+    wq = tl.to_q4(dev(w))
+    assert np.array_equal(wq.buf.cpu().numpy(), port.to_q4(w))
+    assert np.array_equal(wq.to_f32().cpu().numpy(), port.q4_to_f32(port.to_q4(w), K, N))
+
+
+def test_to_q4_rejects_bad_shapes(tl):
+    with pytest.raises(ValueError):
+        tl.to_q4(torch.zeros((48, 4), device="cuda"))
+    with pytest.raises(ValueError):
+        tl.to_q4(torch.zeros((64,), device="cuda"))
+
+
+# ---------------------------------------------------------------- GEMV / GEMM
+def test_gemv_reference_test_case(tl, golden):
+    """test/test_array.cpp:809-856 (K=256, N=48): decode GEMV and the M=2 row case."""
+    a, w, a2 = cases.ref_q4_case()
+    g = golden("q4_small")
+    wq = tl.Q4Weight.from_bytes(g["q4"], 256, 48)
+    assert relerr(tl.gemv_q4(dev(a), wq).cpu().numpy(), g["y1"][0]) < 1e-4
+    assert relerr(tl.gemm_q4(dev(a2), wq).cpu().numpy(), g["y2"]) < 1e-4
+    assert relerr(tl.gemm_q4(dev(a2), wq, simt=True).cpu().numpy(), g["y2"]) < 1e-4
+
+
+def test_gemv_cfg1_golden(tl, port, golden):
+    W, x = cases.cfg1()
+    g = golden("cfg1")
+    wq = tl.to_q4(dev(W))
+    y = tl.gemv_q4(dev(x), wq).cpu().numpy()
+    assert relerr(y, g["y"][0]) < 1e-4
+    assert np.allclose(y, g["y"][0], rtol=1e-4, atol=1e-4)
+    y2 = tl.gemm_q4(dev(x), wq, 0.5, 1.0).cpu().numpy()
+    assert np.allclose(y2, g["y_affine"], rtol=1e-4, atol=1e-4)
+    assert int(np.argmax(y)) == int(np.argmax(g["y"][0])) == tl.argmax(dev(y))
+
+
+@pytest.mark.parametrize("M,K,N", [(1, 128, 16), (1, 128, 5), (3, 384, 100), (4, 3584, 130), (5, 896, 77),
+                                   (8, 1024, 48), (11, 256, 40), (1, 4864, 896), (2, 18944, 64),
+                                   (1, 96, 7), (3, 32, 3)])
+def test_gemm_shapes_vs_oracle(tl, port, M, K, N):
+    """Ragged N (not a multiple of 16), K not a multiple of 256, K % 128 != 0 (general-shape
+    kernel), M above 8 (row blocks), with the fused affine epilogue."""
+    x, w = synth.normal(60, M * 7 + K, (M, K)), synth.normal(61, N + K, (K, N), 0.05)
+    q4 = port.to_q4(w)
+    want = port.gemm_q4(x, q4, N, 0.5, 1.0)
+    wq = tl.Q4Weight.from_bytes(q4, K, N)
+    got = tl.gemm_q4(dev(x), wq, 0.5, 1.0).cpu().numpy()
+    assert np.allclose(got, want, rtol=1e-4, atol=1e-4), np.abs(got - want).max()
+    got2 = tl.gemm_q4(dev(x), wq, 0.5, 1.0, simt=True).cpu().numpy()
+    assert np.allclose(got2, want, rtol=1e-4, atol=1e-4)
+
+
+def test_gemm_wide_dynamic_range(tl, port):
+    """Activations spanning 1e-6 .. 1e4 and one all-zero row: the power-of-two
+    normalisation and the fp16 hi/lo split must stay within 1e-4 of the oracle."""
+    K, N = 1024, 64
+    x = synth.normal(62, 1, (4, K))
+    x[0] *= 1e4
+    x[1] *= 1e-6
+    x[2] = 0.0
+    x[3, ::7] *= 300.0
+    w = synth.normal(62, 2, (K, N), 0.02)
+    q4 = port.to_q4(w)
+    want = port.gemm_q4(x, q4, N)
+    got = tl.gemm_q4(dev(x), tl.Q4Weight.from_bytes(q4, K, N)).cpu().numpy()
+    assert np.all(got[2] == 0.0)
+    for m in (0, 1, 3):
+        scale = np.abs(want[m]).max()
+        assert np.abs(got[m] - want[m]).max() <= 1e-4 * scale + 1e-30
+
+
+def test_gemm_cfg4_golden_and_linearity(tl, port, golden):
+    for M in (1, 8):
+        X, Wf = cases.cfg4(M, N=512)
+        wq = tl.to_q4(dev(Wf))
+        y = tl.gemm_q4(dev(X), wq, 0.5, 1.0).cpu().numpy()
+        assert np.allclose(y, golden(f"cfg4_M{M}_N512")["y"], rtol=1e-4, atol=1e-4)
+
+
+def test_gemm_full_size_properties(tl):
+    """BASELINE config 4 at full size (N=18944, K=3584): properties that need no
+    CPU pass over 68M weights -- M-row consistency with the M=1 kernel, the affine
+    epilogue, linearity in x, and agreement of the two independent kernels."""
+    K, N = 3584, 18944
+    g = torch.Generator(device="cuda").manual_seed(3)
+    W = torch.randn((K, N), generator=g, device="cuda") * 0.02
+    wq = tl.to_q4(W)
+    X = torch.randn((8, K), generator=g, device="cuda")
+    Y = tl.gemm_q4(X, wq)
+    for m in (0, 5):
+        assert torch.allclose(tl.gemv_q4(X[m].contiguous(), wq), Y[m], rtol=1e-5, atol=1e-5)
+    Ys = tl.gemm_q4(X, wq, simt=True)
+    assert torch.allclose(Y, Ys, rtol=1e-4, atol=1e-4)
+    Ya = tl.gemm_q4(X, wq, 0.5, 1.0)
+    assert torch.allclose(Ya, Y * 0.5 + 1.0, rtol=1e-6, atol=1e-6)
+    lin = tl.gemm_q4((X[:1] + 2.0 * X[1:2]).contiguous(), wq)
+    assert torch.allclose(lin[0], Y[0] + 2.0 * Y[1], rtol=1e-4, atol=2e-4)
+    # dequantised-f32 reference on the device for 64 sampled columns
+    Wd = wq.to_f32()
+    cols = torch.arange(0, N, N // 64, device="cuda")
+    ref = (X.double() @ Wd[:, cols].double()).float()
+    assert torch.allclose(Y[:, cols], ref, rtol=1e-4, atol=1e-4)
+    assert torch.equal(tl.gemm_q4(X, wq), Y)     # deterministic split-K fix-up
+
+
+# ---------------------------------------------------------------- attention
+def test_attn_reference_test_case(tl, golden):
+    q, K, V, sc = cases.ref_attn_case()
+    got = tl.attn_decode(dev(q), dev(K), dev(V), float(sc)).cpu().numpy()
+    assert relerr(got, golden("attn_small")["out"]) < 1e-4
+
+
+@pytest.mark.parametrize("ctx", [512, 2048])
+def test_attn_cfg2_golden(tl, golden, ctx):
+    q, K, V, sc = cases.cfg2(ctx)
+    got = tl.attn_decode(dev(q), dev(K), dev(V), float(sc)).cpu().numpy()
+    assert np.allclose(got, golden(f"cfg2_ctx{ctx}")["out"], rtol=1e-3, atol=1e-3)
+    assert relerr(got, golden(f"cfg2_ctx{ctx}")["out"]) < 1e-4
+
+
+@pytest.mark.parametrize("n_q,n_kv,D,kv_max,ctxs", [
+    (14, 2, 64, 2048, [1, 2, 31, 32, 33, 127, 128, 129, 255, 256, 257, 1000, 2047, 2048]),
+    (32, 8, 128, 600, [1, 5, 63, 64, 65, 300, 511, 600]),
+    (28, 4, 128, 4224, [1, 4096, 4097, 4224]),
+    (4, 4, 128, 300, [7, 300]), (6, 2, 64, 300, [299]), (12, 1, 64, 160, [160]), (40, 2, 64, 96, [96])])
+def test_attn_gqa_prefix_sweep(tl, port, n_q, n_kv, D, kv_max, ctxs):
+    """GQA groups 1/3/4/7/12/20, both head dims, contexts straddling every tile and
+    split boundary (bench/cuda/check/check_attn64.cpp:65-66), and the
+    device-position variant bit-identical to the host-position one
+    (check_attn64.cpp:91-102)."""
+    q, K, V = synth.normal(70, 1, (n_q, D)), synth.normal(70, 2, (n_kv, kv_max, D)), synth.normal(70, 3, (n_kv, kv_max, D))
+    dq, dK, dV = dev(q), dev(K), dev(V)
+    cache = tl.kv_cache(n_kv, kv_max, D)
+    cache.K, cache.V = dK, dV
+    d_pos = torch.zeros(1, dtype=torch.int32, device="cuda")
+    sc = float(1.0 / np.sqrt(D))
+    for ctx in ctxs:
+        want = port.attn_decode(q, K, V, sc, ctx=ctx)
+        got = tl.attn_decode(dq, dK, dV, sc, ctx=ctx)
+        assert relerr(got.cpu().numpy(), want) < 1e-4, ctx
+        d_pos.fill_(ctx - 1)
+        got2 = cache.attn_dpos(dq, d_pos, sc)
+        assert torch.equal(got, got2), ctx
+
+
+def test_attn_long_context_property(tl):
+    """BASELINE config 2 at ctx 32768: one dominant key per head must be returned
+    (softmax concentrates), and a constant V must come back unchanged."""
+    H, D, ctx = 28, 128, 32768
+    g = torch.Generator(device="cuda").manual_seed(1)
+    q = torch.randn((H, D), generator=g, device="cuda")
+    K = torch.randn((H, ctx, D), generator=g, device="cuda")
+    V = torch.randn((H, ctx, D), generator=g, device="cuda")
+    sc = 1.0 / np.sqrt(D)
+    out = tl.attn_decode(q, K, V, sc)
+    ref = torch.softmax((K @ q.unsqueeze(-1)).squeeze(-1).double() * sc, -1).unsqueeze(1) @ V.double()
+    assert torch.allclose(out, ref.squeeze(1).float(), rtol=1e-3, atol=1e-3)
+    Vc = torch.full_like(V, 0.75)
+    assert torch.allclose(tl.attn_decode(q, K, Vc, sc), torch.full_like(q, 0.75), atol=1e-5)
+
+
+# ---------------------------------------------------------------- row ops
+def test_rope_golden_and_bias(tl, port, golden):
+    g = golden("rope")
+    xr1, xr2, x64 = synth.normal(11, 1, (4, 128)), synth.normal(11, 2, (4, 5, 128)), synth.normal(11, 3, (14, 64))
+    assert relerr(tl.rope(dev(xr1), 7, 10000.0).cpu().numpy(), g["o1"]) < 1e-6
+    assert relerr(tl.rope(dev(xr2), 7, 10000.0).cpu().numpy(), g["o2"]) < 1e-6
+    assert relerr(tl.rope(dev(x64), 4200, 1e6).cpu().numpy(), g["o3"]) < 1e-6
+    b = synth.normal(11, 4, (14, 64), 0.02)
+    want = port.rope(x64, 4223, 1e6, bias=b)
+    assert relerr(tl.rope(dev(x64), 4223, 1e6, bias=dev(b)).cpu().numpy(), want) < 1e-6
+    d_pos = torch.tensor([4223], dtype=torch.int32, device="cuda")
+    assert torch.equal(tl.rope_dpos(dev(x64), d_pos, 1e6, bias=dev(b)), tl.rope(dev(x64), 4223, 1e6, bias=dev(b)))
+
+
+def test_rmsnorm_swiglu_golden(tl, port, golden):
+    xn, wn = synth.normal(12, 1, (6, 512)), 1 + synth.normal(12, 2, (512,), 0.1)
+    assert relerr(tl.rmsnorm(dev(xn), dev(wn), 1e-5).cpu().numpy(), golden("rmsnorm")["o"]) < 2e-6
+    gg, u = synth.normal(13, 1, (3, 1024)), synth.normal(13, 2, (3, 1024))
+    gu = np.concatenate([gg, u], 1)
+    assert relerr(tl.swiglu(dev(gu), 1024).cpu().numpy(), golden("swiglu")["o"]) < 2e-6
+    for n in (896, 3584, 33):
+        x, d, w = synth.normal(14, n, (2, n)), synth.normal(14, n + 1, (2, n)), 1 + synth.normal(14, n + 2, (n,), 0.1)
+        xo, ho = port.add_rmsnorm(x, d, w, 1e-6)
+        gx, gh = tl.rmsnorm_res(dev(x), dev(d), dev(w), 1e-6)
+        assert np.array_equal(gx.cpu().numpy(), xo) and relerr(gh.cpu().numpy(), ho) < 2e-6
+        dx = dev(x)
+        tl.rmsnorm_res(dx, dev(d), dev(w), 1e-6, xout=dx)      # xout may alias x
+        assert np.array_equal(dx.cpu().numpy(), xo)
+
+
+def test_argmax_ties_and_sizes(tl, port):
+    for n in (1, 5, 256, 1000, 151936, 152064):
+        v = synth.normal(15, n, (n,))
+        if n > 4:
+            v[[n // 2, n // 3, n - 1]] = v.max() + 1.0       # three-way tie: smallest index wins
+        assert tl.argmax(dev(v)) == port.argmax(v)
+    v = np.full(4097, -3.0e38, np.float32)
+    assert tl.argmax(dev(v)) == 0
+
+
+def test_kv_cache_append_and_attend(tl, port):
+    n_kv, D, maxc, n_q = 2, 64, 40, 14
+    cache = tl.kv_cache(n_kv, maxc, D)
+    Kh, Vh = np.zeros((n_kv, maxc, D), np.float32), np.zeros((n_kv, maxc, D), np.float32)
+    q = synth.normal(16, 0, (n_q, D))
+    for t in range(33):
+        k, v = synth.normal(16, 10 + t, (n_kv, D)), synth.normal(16, 100 + t, (n_kv, D))
+        cache.append(dev(k), dev(v))
+        Kh[:, t], Vh[:, t] = k, v
+    assert np.array_equal(cache.K.cpu().numpy(), Kh)
+    got = cache.attn(dev(q), 0.125).cpu().numpy()
+    assert relerr(got, port.attn_decode(q, Kh, Vh, 0.125, ctx=33)) < 1e-4
+    with pytest.raises(IndexError):
+        for _ in range(10):
+            cache.append(dev(k), dev(v))
+
+
+def test_bad_arguments_raise(tl):
+    from cpp_tensorlib_b200 import TlbError
+    x = torch.zeros((1, 64), device="cuda")
+    with pytest.raises(ValueError):
+        tl.gemm_q4(x, tl.Q4Weight(torch.zeros(tl.q4_bytes(4, 32), dtype=torch.uint8, device="cuda"), 32, 4))
+    q = torch.zeros((3, 128), device="cuda")
+    K = torch.zeros((2, 8, 128), device="cuda")
+    with pytest.raises(TlbError):
+        tl.attn_decode(q, K, K, 1.0)              # 3 q heads over 2 kv heads
+    with pytest.raises(TlbError):
+        tl.attn_decode(torch.zeros((2, 96), device="cuda"), torch.zeros((2, 8, 96), device="cuda"),
+                       torch.zeros((2, 8, 96), device="cuda"), 1.0)   # D not in {64,128}
