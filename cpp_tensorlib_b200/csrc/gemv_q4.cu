@@ -109,9 +109,14 @@ __global__ void __launch_bounds__(GV_WARPS * 32, 1)
   unsigned char* myS = Sring + warp * GV_STAGES * GV_S_BYTES;
   uint64_t* mybar = bars + warp * GV_STAGES;
 
-  const unsigned Wtot = gridDim.x * GV_WARPS;
+  // Never more workers than units, so every worker's range is non-empty and the
+  // contributors of a row tile are exactly the owners of its first..last unit.
+  const unsigned Wall = gridDim.x * GV_WARPS;
+  const unsigned Wtot = Wall < p.U ? Wall : p.U;
   const unsigned wid = blockIdx.x * GV_WARPS + warp;
-  const unsigned u0 = gv_start(wid, p.U, Wtot), u1 = gv_start(wid + 1, p.U, Wtot);
+  const bool idle = wid >= Wtot;
+  const unsigned u0 = idle ? 0u : gv_start(wid, p.U, Wtot);
+  const unsigned u1 = idle ? 0u : gv_start(wid + 1, p.U, Wtot);
   const int n_units = (int)(u1 - u0);
 
   if (lane == 0) {
