@@ -49,6 +49,22 @@ SIGNATURES = {
     "tlb_capture_end": (ci, [C.POINTER(vp)]),
     "tlb_graph_launch": (ci, [vp, vp]),
     "tlb_graph_destroy": (ci, [vp]),
+    "tlb_decoder_create": (ci, [C.POINTER(i64), ci, f32, f32, C.POINTER(vp)]),
+    "tlb_decoder_destroy": (ci, [vp]),
+    "tlb_decoder_set_linear": (ci, [vp, i64, ci, vp, i64, i64]),
+    "tlb_decoder_set_vector": (ci, [vp, i64, ci, vp]),
+    "tlb_decoder_kv": (ci, [vp, i64, C.POINTER(vp), C.POINTER(vp)]),
+    "tlb_decoder_logits": (ci, [vp, C.POINTER(vp)]),
+    "tlb_decoder_set_pos": (ci, [vp, i64, vp]),
+    "tlb_decoder_set_token": (ci, [vp, i64, vp]),
+    "tlb_decoder_forward": (ci, [vp, vp]),
+    "tlb_decoder_launches_per_token": (i64, [vp]),
+    "tlb_decoder_capture": (ci, [vp]),
+    "tlb_decoder_run": (ci, [vp, i64, vp]),
+    "tlb_decoder_step": (ci, [vp, C.POINTER(C.c_int32), C.POINTER(C.c_int32), vp]),
+    "tlb_decoder_last_token": (ci, [vp, C.POINTER(C.c_int32), vp]),
+    "tlb_decoder_ipc_export": (ci, [vp, vp]),
+    "tlb_decoder_ipc_open": (ci, [vp, vp]),
 }
 
 

@@ -1,0 +1,427 @@
+// Native driver of the Qwen2.5-architecture int4 decoder: weights, KV caches,
+// scratch, the per-token launch sequence, its CUDA graph and the tensor-parallel
+// exchange.  Mirrors the structure of the reference's model driver
+// (bench/cuda/qwen_model.h: Layer/Scratch/Model :175-308, run_layers_ :673-740,
+// captured_decoder :791-905) with every linear held in the q4 layout.
+//
+// One token (all on one stream, no host sync, position and token id read from
+// device memory so one instantiated graph replays as the sequence grows):
+//   embed gather -> rmsnorm                                   (layer 0 only)
+//   per layer: qkv GEMV -> rope+bias+KV append -> attention -> wo GEMV
+//              -> residual add + rmsnorm -> gate|up GEMV -> swiglu -> down GEMV
+//              -> residual add + rmsnorm (next layer's input norm / final norm)
+//   lm_head GEMV -> argmax -> next token id, position + 1
+// Tensor parallel (column-parallel qkv / gate|up / lm_head, row-parallel wo /
+// down): the row-parallel GEMVs push their partial outputs to every rank and the
+// following add+rmsnorm reduces them (comm.cuh); the lm_head shards exchange
+// their local argmax keys.  Each rank is one process on one GPU.
+#include <cstring>
+#include <vector>
+
+#include "comm.cuh"
+
+namespace tlb {
+
+int make_q4_tensor_maps(const void* qw, const void* scales, int N, int K, CUtensorMap* tmW,
+                        CUtensorMap* tmS);
+bool gemv_q4_tma_eligible(const void* qw, const void* scales, int N, int K, int M);
+int gemv_q4_launch(DeviceCtx* c, const CUtensorMap& tmW, const CUtensorMap& tmS, const float* x,
+                   long long ldx, int M, float* y, long long ldy, int N, int K, float alpha,
+                   float beta, cudaStream_t stream, int max_ctas, const CommDev* push_comm);
+int gemv_q4_simt_launch(const float* x, long long ldx, int M, const void* qw, const void* scales,
+                        float* y, long long ldy, int N, int K, float alpha, float beta,
+                        cudaStream_t stream);
+size_t attn_partials_bytes(int n_q, int n_kv, long long kv_max, int D, int sm_count);
+int attn_decode_launch(DeviceCtx* c, const float* q, const float* K, const float* V, float* out,
+                       int n_q, int n_kv, int ctx, long long kv_max, int D, float scale,
+                       const unsigned* d_pos, float* partials, int* counters, cudaStream_t stream);
+int launch_rmsnorm(const float*, const float*, float*, int, float, int, cudaStream_t);
+int launch_add_rmsnorm(const float*, const float*, const float*, float*, float*, int, float, int,
+                       cudaStream_t);
+int launch_add_rmsnorm_ar(const float*, const float*, float*, float*, int, float, const CommDev&,
+                          int*, cudaStream_t);
+int launch_swiglu(const float*, float*, int, int, cudaStream_t);
+int launch_incr_u32(unsigned*, cudaStream_t);
+int launch_qkv_post(float*, const float*, const float*, const float*, float*, float*, int, int,
+                    int, const unsigned*, long long, float, cudaStream_t);
+int launch_embed_gather(const float*, const int*, float*, int, cudaStream_t);
+int launch_argmax(DeviceCtx*, const float*, int, int*, int*, cudaStream_t);
+int launch_argmax_tp(DeviceCtx*, const float*, int, unsigned, const CommDev&, int*, int*,
+                     cudaStream_t);
+
+struct Linear {
+  const void* q4 = nullptr;
+  int K = 0, N = 0;
+  bool tma = false;
+  CUtensorMap tmW, tmS;
+  const float* scales() const { return (const float*)((const char*)q4 + (size_t)N * K / 2); }
+};
+
+struct DecLayer {
+  Linear wqkv, wo, wgu, wd;
+  const float *bq = nullptr, *bk = nullptr, *bv = nullptr, *an = nullptr, *fn = nullptr;
+  float *Kc = nullptr, *Vc = nullptr;
+};
+
+struct Decoder {
+  // sizes local to this rank (hidden and vocab_offset are global notions)
+  int hidden = 0, n_layers = 0, n_q = 0, n_kv = 0, hd = 0, ff = 0, vocab = 0, max_ctx = 0;
+  float eps = 1e-6f, rope_base = 1e6f, scale = 1.f;
+  int tp_rank = 0, tp_size = 1;
+  unsigned vocab_offset = 0;
+  std::vector<DecLayer> layers;
+  Linear lm_head;
+  const float *embed = nullptr, *onorm = nullptr;
+  // scratch
+  float *x = nullptr, *hb = nullptr, *qkv = nullptr, *att = nullptr, *t0 = nullptr, *gu = nullptr,
+        *mb = nullptr, *logits = nullptr;
+  void* attn_partials = nullptr;
+  unsigned* d_pos = nullptr;
+  int* d_tok = nullptr;      // token consumed by the next forward; overwritten with the result
+  int* d_tok_out = nullptr;  // copy of the last result (read back by the host)
+  int *h_tok = nullptr, *h_out = nullptr;  // pinned
+  // tensor-parallel exchange
+  CommDev comm;
+  float* stage_local = nullptr;
+  unsigned* flags_local = nullptr;
+  void* peer_stage_base[TP_MAX] = {};
+  void* peer_flags_base[TP_MAX] = {};
+  bool peers_open = false;
+  // graph
+  cudaGraphExec_t graph = nullptr;
+  long long launches_per_token = 0;
+};
+
+static int set_linear(Linear& L, const void* q4, int K, int N) {
+  L.q4 = q4;
+  L.K = K;
+  L.N = N;
+  L.tma = gemv_q4_tma_eligible(q4, L.scales(), N, K, 1);
+  if (L.tma) return make_q4_tensor_maps(q4, L.scales(), N, K, &L.tmW, &L.tmS);
+  return TLB_OK;
+}
+
+static int run_linear(DeviceCtx* c, const Linear& L, const float* x, float* y, cudaStream_t s,
+                      const CommDev* push) {
+  if (!L.q4) return set_error(TLB_ERR_STATE, "decoder: a linear weight was never set");
+  if (L.tma)
+    return gemv_q4_launch(c, L.tmW, L.tmS, x, L.K, 1, y, L.N, L.N, L.K, 1.0f, 0.0f, s, 0, push);
+  if (push) return set_error(TLB_ERR_UNSUPPORTED, "decoder: tensor-parallel linears need K % 128 == 0");
+  return gemv_q4_simt_launch(x, L.K, 1, L.q4, L.scales(), y, L.N, L.N, L.K, 1.0f, 0.0f, s);
+}
+
+static int forward(Decoder* d, cudaStream_t s) {
+  DeviceCtx* c = nullptr;
+  int rc = get_ctx(&c);
+  if (rc) return rc;
+  const bool tp = d->tp_size > 1;
+  const int E = d->hidden;
+  long long n = 0;
+#define RUN(expr)        \
+  do {                   \
+    rc = (expr);         \
+    if (rc) return rc;   \
+    n++;                 \
+  } while (0)
+  if (!d->embed || !d->onorm) return set_error(TLB_ERR_STATE, "decoder: embed / final norm not set");
+  RUN(launch_embed_gather(d->embed, d->d_tok, d->x, E, s));
+  RUN(launch_rmsnorm(d->x, d->layers[0].an, d->hb, E, d->eps, 1, s));
+  for (int l = 0; l < d->n_layers; l++) {
+    DecLayer& L = d->layers[l];
+    RUN(run_linear(c, L.wqkv, d->hb, d->qkv, s, nullptr));
+    RUN(launch_qkv_post(d->qkv, L.bq, L.bk, L.bv, L.Kc, L.Vc, d->n_q, d->n_kv, d->hd, d->d_pos,
+                        d->max_ctx, d->rope_base, s));
+    RUN(attn_decode_launch(c, d->qkv, L.Kc, L.Vc, d->att, d->n_q, d->n_kv, 0, d->max_ctx, d->hd,
+                           d->scale, d->d_pos, (float*)((char*)d->attn_partials + 256),
+                           (int*)d->attn_partials, s));
+    if (tp) {
+      RUN(run_linear(c, L.wo, d->att, nullptr, s, &d->comm));
+      RUN(launch_add_rmsnorm_ar(d->x, L.fn, d->x, d->hb, E, d->eps, d->comm, c->status, s));
+    } else {
+      RUN(run_linear(c, L.wo, d->att, d->t0, s, nullptr));
+      RUN(launch_add_rmsnorm(d->x, d->t0, L.fn, d->x, d->hb, E, d->eps, 1, s));
+    }
+    RUN(run_linear(c, L.wgu, d->hb, d->gu, s, nullptr));
+    RUN(launch_swiglu(d->gu, d->mb, d->ff, 1, s));
+    const float* nextw = (l + 1 < d->n_layers) ? d->layers[l + 1].an : d->onorm;
+    if (tp) {
+      RUN(run_linear(c, L.wd, d->mb, nullptr, s, &d->comm));
+      RUN(launch_add_rmsnorm_ar(d->x, nextw, d->x, d->hb, E, d->eps, d->comm, c->status, s));
+    } else {
+      RUN(run_linear(c, L.wd, d->mb, d->t0, s, nullptr));
+      RUN(launch_add_rmsnorm(d->x, d->t0, nextw, d->x, d->hb, E, d->eps, 1, s));
+    }
+  }
+  RUN(run_linear(c, d->lm_head, d->hb, d->logits, s, nullptr));
+  if (tp) {
+    RUN(launch_argmax_tp(c, d->logits, d->vocab, d->vocab_offset, d->comm, d->d_tok, d->d_tok_out, s));
+    n++;  // two kernels
+  } else {
+    RUN(launch_argmax(c, d->logits, d->vocab, d->d_tok, d->d_tok_out, s));
+  }
+  RUN(launch_incr_u32(d->d_pos, s));
+#undef RUN
+  d->launches_per_token = n;
+  return TLB_OK;
+}
+
+}  // namespace tlb
+
+using namespace tlb;
+
+extern "C" {
+
+// cfg: hidden, n_layers, n_q, n_kv, hd, ff, vocab, max_ctx (sizes LOCAL to the
+// rank except hidden), then tp_rank, tp_size, vocab_offset.
+int tlb_decoder_create(const int64_t* cfg, int n_cfg, float eps, float rope_base, void** out) {
+  TLB_REQUIRE(cfg && out && n_cfg >= 11, "tlb_decoder_create: bad arguments");
+  DeviceCtx* c = nullptr;
+  int rc = get_ctx(&c);
+  if (rc) return rc;
+  auto* d = new Decoder();
+  d->hidden = (int)cfg[0]; d->n_layers = (int)cfg[1]; d->n_q = (int)cfg[2]; d->n_kv = (int)cfg[3];
+  d->hd = (int)cfg[4]; d->ff = (int)cfg[5]; d->vocab = (int)cfg[6]; d->max_ctx = (int)cfg[7];
+  d->tp_rank = (int)cfg[8]; d->tp_size = (int)cfg[9]; d->vocab_offset = (unsigned)cfg[10];
+  d->eps = eps; d->rope_base = rope_base; d->scale = 1.0f / sqrtf((float)d->hd);
+  TLB_REQUIRE(d->hd == 64 || d->hd == 128, "tlb_decoder_create: head_dim must be 64 or 128");
+  TLB_REQUIRE(d->n_kv > 0 && d->n_q % d->n_kv == 0 && d->n_kv <= 64, "tlb_decoder_create: bad head counts");
+  TLB_REQUIRE(d->tp_size >= 1 && d->tp_size <= TP_MAX && d->tp_rank >= 0 && d->tp_rank < d->tp_size,
+              "tlb_decoder_create: bad tensor-parallel rank/size");
+  TLB_REQUIRE(d->n_layers > 0 && d->hidden > 0 && d->max_ctx > 0, "tlb_decoder_create: bad sizes");
+  d->layers.resize(d->n_layers);
+  const size_t kvb = (size_t)d->n_kv * d->max_ctx * d->hd * sizeof(float);
+  for (auto& L : d->layers) {
+    TLB_CUDA(cudaMalloc(&L.Kc, kvb));
+    TLB_CUDA(cudaMalloc(&L.Vc, kvb));
+    TLB_CUDA(cudaMemset(L.Kc, 0, kvb));
+    TLB_CUDA(cudaMemset(L.Vc, 0, kvb));
+  }
+  auto fa = [&](float** p, size_t n) { return cudaMalloc(p, n * sizeof(float)); };
+  TLB_CUDA(fa(&d->x, d->hidden));
+  TLB_CUDA(fa(&d->hb, d->hidden));
+  TLB_CUDA(fa(&d->qkv, (size_t)(d->n_q + 2 * d->n_kv) * d->hd));
+  TLB_CUDA(fa(&d->att, (size_t)d->n_q * d->hd));
+  TLB_CUDA(fa(&d->t0, d->hidden));
+  TLB_CUDA(fa(&d->gu, (size_t)2 * d->ff));
+  TLB_CUDA(fa(&d->mb, d->ff));
+  TLB_CUDA(fa(&d->logits, d->vocab));
+  size_t pb = 256 + attn_partials_bytes(d->n_q, d->n_kv, d->max_ctx, d->hd, c->sm_count);
+  TLB_CUDA(cudaMalloc(&d->attn_partials, pb));
+  TLB_CUDA(cudaMemset(d->attn_partials, 0, pb));
+  TLB_CUDA(cudaMalloc(&d->d_pos, 16));
+  TLB_CUDA(cudaMemset(d->d_pos, 0, 16));
+  TLB_CUDA(cudaMalloc(&d->d_tok, 16));
+  TLB_CUDA(cudaMemset(d->d_tok, 0, 16));
+  d->d_tok_out = d->d_tok + 1;
+  TLB_CUDA(cudaMallocHost(&d->h_tok, 64));
+  d->h_out = d->h_tok + 4;
+  // exchange buffers (allocated even at tp_size 1: tiny)
+  d->comm.rank = d->tp_rank;
+  d->comm.size = d->tp_size;
+  d->comm.slot_floats = (d->hidden + 3) & ~3;
+  const size_t sb = (size_t)2 * d->tp_size * d->comm.slot_floats * sizeof(float);
+  TLB_CUDA(cudaMalloc(&d->stage_local, sb));
+  TLB_CUDA(cudaMemset(d->stage_local, 0, sb));
+  TLB_CUDA(cudaMalloc(&d->flags_local, 256));
+  TLB_CUDA(cudaMemset(d->flags_local, 0, 256));
+  d->comm.stage[d->tp_rank] = d->stage_local;
+  d->comm.flags[d->tp_rank] = d->flags_local;
+  d->comm.seq = d->flags_local + 32;   // same allocation, words 32 and 33
+  d->comm.done = d->flags_local + 33;
+  TLB_CUDA(cudaDeviceSynchronize());
+  *out = d;
+  return TLB_OK;
+}
+
+int tlb_decoder_destroy(void* h) {
+  auto* d = (Decoder*)h;
+  if (!d) return TLB_OK;
+  cudaDeviceSynchronize();
+  if (d->graph) cudaGraphExecDestroy(d->graph);
+  if (d->peers_open)
+    for (int r = 0; r < d->tp_size; r++)
+      if (r != d->tp_rank) {
+        if (d->peer_stage_base[r]) cudaIpcCloseMemHandle(d->peer_stage_base[r]);
+        if (d->peer_flags_base[r]) cudaIpcCloseMemHandle(d->peer_flags_base[r]);
+      }
+  for (auto& L : d->layers) { cudaFree(L.Kc); cudaFree(L.Vc); }
+  float* bufs[] = {d->x, d->hb, d->qkv, d->att, d->t0, d->gu, d->mb, d->logits, d->stage_local};
+  for (float* b : bufs) cudaFree(b);
+  cudaFree(d->attn_partials); cudaFree(d->d_pos); cudaFree(d->d_tok); cudaFree(d->flags_local);
+  cudaFreeHost(d->h_tok);
+  delete d;
+  return TLB_OK;
+}
+
+// which: 0 wqkv [hidden -> (n_q+2n_kv)hd]  1 wo [n_q*hd -> hidden]  2 wgu [hidden -> 2ff]
+//        3 wd [ff -> hidden]  4 lm_head [hidden -> vocab] (layer ignored).
+// q4 is a DEVICE pointer to a buffer in the q4 layout, borrowed for the decoder's life.
+int tlb_decoder_set_linear(void* h, int64_t layer, int which, const void* q4, int64_t K, int64_t N) {
+  auto* d = (Decoder*)h;
+  TLB_REQUIRE(d && q4 && K > 0 && N > 0 && K % 32 == 0, "tlb_decoder_set_linear: bad arguments");
+  const int E = d->hidden, QKV = (d->n_q + 2 * d->n_kv) * d->hd;
+  Linear* L = nullptr;
+  int64_t wantK = 0, wantN = 0;
+  if (which == 4) { L = &d->lm_head; wantK = E; wantN = d->vocab; }
+  else {
+    TLB_REQUIRE(layer >= 0 && layer < d->n_layers, "tlb_decoder_set_linear: layer out of range");
+    DecLayer& Y = d->layers[layer];
+    if (which == 0) { L = &Y.wqkv; wantK = E; wantN = QKV; }
+    else if (which == 1) { L = &Y.wo; wantK = (int64_t)d->n_q * d->hd; wantN = E; }
+    else if (which == 2) { L = &Y.wgu; wantK = E; wantN = 2 * d->ff; }
+    else if (which == 3) { L = &Y.wd; wantK = d->ff; wantN = E; }
+    else return set_error(TLB_ERR_ARG, "tlb_decoder_set_linear: unknown weight id");
+  }
+  TLB_REQUIRE(K == wantK && N == wantN, "tlb_decoder_set_linear: shape does not match the config");
+  return set_linear(*L, q4, (int)K, (int)N);
+}
+
+// which: 0 attn norm  1 ffn norm  2 bq  3 bk  4 bv (may be NULL: no bias)  5 final norm
+//        6 embedding table [vocab_total, hidden] (layer ignored for 5 and 6). Device pointers.
+int tlb_decoder_set_vector(void* h, int64_t layer, int which, const float* v) {
+  auto* d = (Decoder*)h;
+  TLB_REQUIRE(d, "tlb_decoder_set_vector: null decoder");
+  if (which == 5) { d->onorm = v; return TLB_OK; }
+  if (which == 6) { d->embed = v; return TLB_OK; }
+  TLB_REQUIRE(layer >= 0 && layer < d->n_layers, "tlb_decoder_set_vector: layer out of range");
+  DecLayer& L = d->layers[layer];
+  if (which == 0) L.an = v; else if (which == 1) L.fn = v; else if (which == 2) L.bq = v;
+  else if (which == 3) L.bk = v; else if (which == 4) L.bv = v;
+  else return set_error(TLB_ERR_ARG, "tlb_decoder_set_vector: unknown vector id");
+  return TLB_OK;
+}
+
+// Device pointers of one layer's K and V cache ([n_kv, max_ctx, hd] f32) so the
+// caller can pre-fill a context.
+int tlb_decoder_kv(void* h, int64_t layer, void** K, void** V) {
+  auto* d = (Decoder*)h;
+  TLB_REQUIRE(d && K && V && layer >= 0 && layer < d->n_layers, "tlb_decoder_kv: bad arguments");
+  *K = d->layers[layer].Kc;
+  *V = d->layers[layer].Vc;
+  return TLB_OK;
+}
+int tlb_decoder_logits(void* h, void** logits) {
+  auto* d = (Decoder*)h;
+  TLB_REQUIRE(d && logits, "tlb_decoder_logits: bad arguments");
+  *logits = d->logits;
+  return TLB_OK;
+}
+int tlb_decoder_set_pos(void* h, int64_t pos, void* stream) {
+  auto* d = (Decoder*)h;
+  TLB_REQUIRE(d && pos >= 0 && pos < d->max_ctx, "tlb_decoder_set_pos: position outside the cache");
+  d->h_tok[8] = (int)pos;
+  TLB_CUDA(cudaMemcpyAsync(d->d_pos, &d->h_tok[8], 4, cudaMemcpyHostToDevice, (cudaStream_t)stream));
+  TLB_CUDA(cudaStreamSynchronize((cudaStream_t)stream));
+  return TLB_OK;
+}
+int tlb_decoder_set_token(void* h, int64_t token, void* stream) {
+  auto* d = (Decoder*)h;
+  TLB_REQUIRE(d && token >= 0, "tlb_decoder_set_token: bad token");
+  d->h_tok[0] = (int)token;
+  TLB_CUDA(cudaMemcpyAsync(d->d_tok, d->h_tok, 4, cudaMemcpyHostToDevice, (cudaStream_t)stream));
+  TLB_CUDA(cudaStreamSynchronize((cudaStream_t)stream));
+  return TLB_OK;
+}
+
+// Enqueue one token's launches on `stream` (capturable: no sync, no allocation).
+int tlb_decoder_forward(void* h, void* stream) {
+  auto* d = (Decoder*)h;
+  TLB_REQUIRE(d, "tlb_decoder_forward: null decoder");
+  return forward(d, (cudaStream_t)stream);
+}
+int64_t tlb_decoder_launches_per_token(void* h) {
+  auto* d = (Decoder*)h;
+  return d ? d->launches_per_token : 0;
+}
+
+// Capture one forward into an executable graph owned by the decoder
+// (qwen_model.h:791-905 captured_decoder::init_).
+int tlb_decoder_capture(void* h) {
+  auto* d = (Decoder*)h;
+  TLB_REQUIRE(d, "tlb_decoder_capture: null decoder");
+  if (d->graph) { cudaGraphExecDestroy(d->graph); d->graph = nullptr; }
+  cudaStream_t s;
+  TLB_CUDA(cudaStreamCreateWithFlags(&s, cudaStreamNonBlocking));
+  TLB_CUDA(cudaStreamBeginCapture(s, cudaStreamCaptureModeThreadLocal));
+  int rc = forward(d, s);
+  cudaGraph_t g = nullptr;
+  cudaError_t e = cudaStreamEndCapture(s, &g);
+  cudaStreamDestroy(s);
+  if (rc) { if (g) cudaGraphDestroy(g); return rc; }
+  if (e != cudaSuccess) return cuda_fail(e, "cudaStreamEndCapture");
+  e = cudaGraphInstantiate(&d->graph, g, 0);
+  cudaGraphDestroy(g);
+  if (e != cudaSuccess) return cuda_fail(e, "cudaGraphInstantiate");
+  return TLB_OK;
+}
+
+// Replay the captured token `n` times back to back; the token id feeds back on
+// the device (greedy decoding with no host round trip).
+int tlb_decoder_run(void* h, int64_t n, void* stream) {
+  auto* d = (Decoder*)h;
+  TLB_REQUIRE(d && d->graph, "tlb_decoder_run: capture the decoder first");
+  for (int64_t i = 0; i < n; i++) TLB_CUDA(cudaGraphLaunch(d->graph, (cudaStream_t)stream));
+  return TLB_OK;
+}
+
+// End-to-end step with HOST buffers: token id in (host), next token id out (host).
+// H2D of the id, one graph replay (or eager launches when not captured), D2H of
+// the result, stream synchronised.  token_in < 0 keeps the device-resident token.
+int tlb_decoder_step(void* h, const int32_t* token_in, int32_t* token_out, void* stream) {
+  auto* d = (Decoder*)h;
+  TLB_REQUIRE(d && token_out, "tlb_decoder_step: bad arguments");
+  cudaStream_t s = (cudaStream_t)stream;
+  if (token_in && *token_in >= 0) {
+    d->h_tok[0] = *token_in;
+    TLB_CUDA(cudaMemcpyAsync(d->d_tok, d->h_tok, 4, cudaMemcpyHostToDevice, s));
+  }
+  if (d->graph) TLB_CUDA(cudaGraphLaunch(d->graph, s));
+  else {
+    int rc = forward(d, s);
+    if (rc) return rc;
+  }
+  TLB_CUDA(cudaMemcpyAsync(d->h_out, d->d_tok_out, 4, cudaMemcpyDeviceToHost, s));
+  TLB_CUDA(cudaStreamSynchronize(s));
+  *token_out = d->h_out[0];
+  return TLB_OK;
+}
+int tlb_decoder_last_token(void* h, int32_t* token_out, void* stream) {
+  auto* d = (Decoder*)h;
+  TLB_REQUIRE(d && token_out, "tlb_decoder_last_token: bad arguments");
+  TLB_CUDA(cudaMemcpyAsync(d->h_out, d->d_tok_out, 4, cudaMemcpyDeviceToHost, (cudaStream_t)stream));
+  TLB_CUDA(cudaStreamSynchronize((cudaStream_t)stream));
+  *token_out = d->h_out[0];
+  return TLB_OK;
+}
+
+// ---- tensor-parallel wiring: exchange 128-byte records between the ranks (any
+// host channel), then open the peers' buffers.  Record = two CUDA IPC handles.
+int tlb_decoder_ipc_export(void* h, void* record128) {
+  auto* d = (Decoder*)h;
+  TLB_REQUIRE(d && record128, "tlb_decoder_ipc_export: bad arguments");
+  cudaIpcMemHandle_t a, b;
+  TLB_CUDA(cudaIpcGetMemHandle(&a, d->stage_local));
+  TLB_CUDA(cudaIpcGetMemHandle(&b, d->flags_local));
+  memcpy(record128, &a, 64);
+  memcpy((char*)record128 + 64, &b, 64);
+  return TLB_OK;
+}
+// records: tp_size consecutive 128-byte records, index = rank.
+int tlb_decoder_ipc_open(void* h, const void* records) {
+  auto* d = (Decoder*)h;
+  TLB_REQUIRE(d && records, "tlb_decoder_ipc_open: bad arguments");
+  for (int r = 0; r < d->tp_size; r++) {
+    if (r == d->tp_rank) continue;
+    cudaIpcMemHandle_t a, b;
+    memcpy(&a, (const char*)records + (size_t)r * 128, 64);
+    memcpy(&b, (const char*)records + (size_t)r * 128 + 64, 64);
+    TLB_CUDA(cudaIpcOpenMemHandle(&d->peer_stage_base[r], a, cudaIpcMemLazyEnablePeerAccess));
+    TLB_CUDA(cudaIpcOpenMemHandle(&d->peer_flags_base[r], b, cudaIpcMemLazyEnablePeerAccess));
+    d->comm.stage[r] = (float*)d->peer_stage_base[r];
+    d->comm.flags[r] = (unsigned*)d->peer_flags_base[r];
+  }
+  d->peers_open = true;
+  return TLB_OK;
+}
+
+}  // extern "C"

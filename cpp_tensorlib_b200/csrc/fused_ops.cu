@@ -3,7 +3,7 @@
 // row gather.  Each is HBM/latency bound and a few KB per launch; all are
 // programmatic-dependent-launch aware (griddepcontrol.wait first) so they can be
 // chained in a CUDA graph without full kernel-boundary drains.
-#include "common.cuh"
+#include "comm.cuh"
 
 namespace tlb {
 
@@ -281,6 +281,107 @@ __global__ void q4_to_f32_kernel(const unsigned char* __restrict__ q4, int K, in
 }
 
 // ---------------------------------------------------------------------------
+// Tensor-parallel consumers of the one-shot exchange (see comm.cuh).
+// ---------------------------------------------------------------------------
+
+// xout = a + sum_r partial_r ; hout = rmsnorm(xout) * w, for one row.  The
+// partials are the row-parallel GEMV outputs every rank pushed into this rank's
+// staging buffer; they are summed in rank order so all ranks compute identical
+// bits.  Fuses the all-reduce's reduction, the residual add and the norm
+// (the tl_add_rmsnorm seam of the single-GPU path).
+__global__ void add_rmsnorm_ar_kernel(const float* a, const float* __restrict__ w, float* xout,
+                                      float* hout, int n, float eps, CommDev comm, int* status) {
+  __shared__ float sm[32];
+  pdl_wait();
+  pdl_launch_dependents();
+  const unsigned seq = *(volatile unsigned*)comm.seq;
+  const unsigned par = seq & 1u;
+  if ((int)threadIdx.x < comm.size)
+    wait_flag_bounded(&comm.flags[comm.rank][par * comm.size + threadIdx.x], seq + 1u, status,
+                      300 + threadIdx.x);
+  __syncthreads();
+  const float* st = comm.stage[comm.rank] + (size_t)par * comm.size * comm.slot_floats;
+  float acc = 0.f;
+  for (int i = threadIdx.x; i < n; i += blockDim.x) {
+    float d = 0.f;
+    for (int r = 0; r < comm.size; r++) d += __ldcg(&st[(size_t)r * comm.slot_floats + i]);
+    float v = a[i] + d;
+    xout[i] = v;
+    acc += v * v;
+  }
+  const float tot = block_sum(acc, sm);
+  const float inv = 1.0f / sqrtf(tot / (float)n + eps);
+  for (int i = threadIdx.x; i < n; i += blockDim.x) hout[i] = xout[i] * inv * w[i];
+  if (threadIdx.x == 0) *comm.seq = seq + 1u;
+}
+
+// Vocabulary-parallel argmax: each rank reduces its logits shard to a packed key
+// (ordered float bits, inverted GLOBAL index), the last block pushes the key to
+// every rank, and argmax_finish_kernel takes the maximum over ranks.
+__global__ void argmax_push_kernel(const float* __restrict__ in, int n, unsigned vocab_offset,
+                                   unsigned long long* cell, CommDev comm) {
+  __shared__ unsigned long long sm[32];
+  pdl_wait();
+  pdl_launch_dependents();
+  float best = -3.402823466e+38f;
+  unsigned besti = 0;
+  for (unsigned i = blockIdx.x * blockDim.x + threadIdx.x; i < (unsigned)n;
+       i += gridDim.x * blockDim.x) {
+    float v = in[i];
+    if (v > best) { best = v; besti = i; }
+  }
+  unsigned long long key = argmax_key(best, besti + vocab_offset);
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    unsigned long long other = __shfl_xor_sync(0xffffffffu, key, o);
+    key = other > key ? other : key;
+  }
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  if (lane == 0) sm[warp] = key;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    for (int w = 1; w < (int)(blockDim.x >> 5); w++) key = sm[w] > key ? sm[w] : key;
+    atomicMax(&cell[0], key);
+    __threadfence();
+    unsigned ticket = atomicAdd((unsigned*)&cell[1], 1u);
+    if (ticket == gridDim.x - 1) {
+      __threadfence();
+      unsigned long long k = atomicExch(&cell[0], 0ull);
+      *(unsigned*)&cell[1] = 0u;
+      const unsigned seq = *(volatile unsigned*)comm.seq;
+      const size_t off = ((size_t)(seq & 1u) * comm.size + comm.rank) * (size_t)comm.slot_floats;
+      for (int r = 0; r < comm.size; r++) *(unsigned long long*)(comm.stage[r] + off) = k;
+      __threadfence_system();
+      for (int r = 0; r < comm.size; r++)
+        st_release_sys(&comm.flags[r][(seq & 1u) * comm.size + comm.rank], seq + 1u);
+    }
+  }
+}
+
+__global__ void argmax_finish_kernel(CommDev comm, int* out_idx, int* out_idx2, int* status) {
+  pdl_wait();
+  pdl_launch_dependents();
+  const unsigned seq = *(volatile unsigned*)comm.seq;
+  const unsigned par = seq & 1u;
+  if ((int)threadIdx.x < comm.size)
+    wait_flag_bounded(&comm.flags[comm.rank][par * comm.size + threadIdx.x], seq + 1u, status,
+                      400 + threadIdx.x);
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    const float* st = comm.stage[comm.rank] + (size_t)par * comm.size * comm.slot_floats;
+    unsigned long long best = 0ull;
+    for (int r = 0; r < comm.size; r++) {
+      unsigned long long k = __ldcg((const unsigned long long*)(st + (size_t)r * comm.slot_floats));
+      best = k > best ? k : best;
+    }
+    const int idx = (int)(0xFFFFFFFFu - (unsigned)(best & 0xFFFFFFFFull));
+    *out_idx = idx;
+    if (out_idx2) *out_idx2 = idx;
+    *comm.seq = seq + 1u;
+  }
+}
+
+// ---------------------------------------------------------------------------
 // launchers
 // ---------------------------------------------------------------------------
 static int row_threads(int n) {
@@ -356,6 +457,24 @@ int launch_q4_to_f32(const unsigned char* q4, int K, int N, float* out, cudaStre
   size_t tot = (size_t)K * N;
   q4_to_f32_kernel<<<(unsigned)((tot + 255) / 256), 256, 0, s>>>(q4, K, N, out);
   TLB_CUDA(cudaGetLastError());
+  return TLB_OK;
+}
+
+int launch_add_rmsnorm_ar(const float* a, const float* w, float* xout, float* hout, int n,
+                          float eps, const CommDev& comm, int* status, cudaStream_t s) {
+  LaunchCfg lc(dim3(1), dim3(row_threads(n)), 0, s, pdl_enabled());
+  TLB_CUDA(cudaLaunchKernelEx(&lc.cfg, add_rmsnorm_ar_kernel, a, w, xout, hout, n, eps, comm, status));
+  return TLB_OK;
+}
+int launch_argmax_tp(DeviceCtx* c, const float* in, int n, unsigned vocab_offset,
+                     const CommDev& comm, int* out_idx, int* out_idx2, cudaStream_t s) {
+  int blocks = (n + 1023) / 1024;
+  if (blocks > c->sm_count) blocks = c->sm_count;
+  if (blocks < 1) blocks = 1;
+  LaunchCfg lc(dim3(blocks), dim3(256), 0, s, pdl_enabled());
+  TLB_CUDA(cudaLaunchKernelEx(&lc.cfg, argmax_push_kernel, in, n, vocab_offset, c->argmax_cell, comm));
+  LaunchCfg lf(dim3(1), dim3(32), 0, s, pdl_enabled());
+  TLB_CUDA(cudaLaunchKernelEx(&lf.cfg, argmax_finish_kernel, comm, out_idx, out_idx2, c->status));
   return TLB_OK;
 }
 

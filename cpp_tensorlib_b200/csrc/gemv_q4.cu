@@ -26,7 +26,7 @@
 //  * Split-K falls out of the unit ranges; partial row tiles are combined by the
 //    last-arriving warp in a fixed order (deterministic, no float atomics, no
 //    spin-wait on another CTA).
-#include "common.cuh"
+#include "comm.cuh"
 
 namespace tlb {
 
@@ -49,6 +49,8 @@ struct GemvParams {
   int RT, SL;       // row tiles (16 rows), k slabs (256 k)
   unsigned U;       // RT * SL
   int x_vec_ok;     // x rows are 16-byte aligned
+  int push;         // tensor-parallel: store y (M == 1) into every rank's staging slot
+  CommDev comm;
 };
 
 __device__ __forceinline__ unsigned gv_start(unsigned w, unsigned U, unsigned W) {
@@ -221,6 +223,18 @@ __global__ void __launch_bounds__(GV_WARPS * 32, 1)
   for (int nt = 0; nt < NT; nt++) use_b[nt] = (8 * nt + g) < NCU;
   const unsigned g7x4 = (unsigned)(g & 7) * 4u;
 
+  unsigned ar_seq = 0;
+  if (p.push) ar_seq = *(volatile unsigned*)p.comm.seq;
+  const size_t ar_off =
+      ((size_t)(ar_seq & 1u) * p.comm.size + p.comm.rank) * (size_t)p.comm.slot_floats;
+  auto emit = [&](int m, int n, float v) {
+    v = v * p.alpha + p.beta;
+    if (p.push) {
+      for (int r = 0; r < p.comm.size; r++) p.comm.stage[r][ar_off + n] = v;
+    } else {
+      p.y[(long long)m * p.ldy + n] = v;
+    }
+  };
   auto flush = [&](int rt) {
     const unsigned t0 = (unsigned)rt * p.SL, t1 = t0 + p.SL;
     const bool complete = (u0 <= t0) && (u1 >= t1);
@@ -230,9 +244,8 @@ __global__ void __launch_bounds__(GV_WARPS * 32, 1)
       for (int nt = 0; nt < NT; nt++) {
         int m = 4 * nt + t;
         if (m < p.M) {
-          if (r0 + g < p.N) p.y[(long long)m * p.ldy + r0 + g] = acc[nt][0] * p.alpha + p.beta;
-          if (r0 + g + 8 < p.N)
-            p.y[(long long)m * p.ldy + r0 + g + 8] = acc[nt][1] * p.alpha + p.beta;
+          if (r0 + g < p.N) emit(m, r0 + g, acc[nt][0]);
+          if (r0 + g + 8 < p.N) emit(m, r0 + g + 8, acc[nt][1]);
         }
       }
       return;
@@ -271,9 +284,8 @@ __global__ void __launch_bounds__(GV_WARPS * 32, 1)
     for (int nt = 0; nt < NT; nt++) {
       int m = 4 * nt + t;
       if (m < p.M) {
-        if (r0 + g < p.N) p.y[(long long)m * p.ldy + r0 + g] = sum[nt][0] * p.alpha + p.beta;
-        if (r0 + g + 8 < p.N)
-          p.y[(long long)m * p.ldy + r0 + g + 8] = sum[nt][1] * p.alpha + p.beta;
+        if (r0 + g < p.N) emit(m, r0 + g, sum[nt][0]);
+        if (r0 + g + 8 < p.N) emit(m, r0 + g + 8, sum[nt][1]);
       }
     }
     if (lane == 0) p.counters[rt] = 0;  // leave the counter clean for the next launch
@@ -322,6 +334,22 @@ __global__ void __launch_bounds__(GV_WARPS * 32, 1)
     if (lane == 0 && i + GV_STAGES < n_units) issue(i + GV_STAGES);
   }
   if (cur_rt >= 0) flush(cur_rt);
+
+  // Tensor-parallel push: when the last worker of this rank has stored its tiles,
+  // publish the sequence number in every rank's flag word.
+  if (p.push && !idle) {
+    __threadfence_system();
+    __syncwarp();
+    if (lane == 0) {
+      const unsigned old = atomicAdd(p.comm.done, 1u);
+      if (old == Wtot - 1) {
+        *p.comm.done = 0u;
+        __threadfence_system();
+        for (int r = 0; r < p.comm.size; r++)
+          st_release_sys(&p.comm.flags[r][(ar_seq & 1u) * p.comm.size + p.comm.rank], ar_seq + 1u);
+      }
+    }
+  }
 }
 
 // ---------------------------------------------------------------------------
@@ -392,8 +420,13 @@ bool gemv_q4_tma_eligible(const void* qw, const void* scales, int N, int K, int 
 // Launch with ready tensor maps (the decoder caches them per weight).
 int gemv_q4_launch(DeviceCtx* c, const CUtensorMap& tmW, const CUtensorMap& tmS, const float* x,
                    long long ldx, int M, float* y, long long ldy, int N, int K, float alpha,
-                   float beta, cudaStream_t stream, int max_ctas) {
+                   float beta, cudaStream_t stream, int max_ctas, const CommDev* push_comm) {
   GemvParams p;
+  p.push = push_comm ? 1 : 0;
+  if (push_comm) {
+    if (M != 1) return set_error(TLB_ERR_ARG, "gemv_q4: the tensor-parallel push needs M == 1");
+    p.comm = *push_comm;
+  }
   p.x = x; p.ldx = ldx; p.y = y; p.ldy = ldy; p.M = M; p.N = N; p.K = K;
   p.alpha = alpha; p.beta = beta;
   p.partials = c->gemv_partials; p.counters = c->gemv_counters; p.status = c->status;

@@ -118,6 +118,35 @@ int tlb_capture_end(void** graph_exec_out); /* capture_end */
 int tlb_graph_launch(void* graph_exec, void* stream); /* graph_launch */
 int tlb_graph_destroy(void* graph_exec);    /* graph_destroy */
 
+/* ---- Qwen2.5-architecture int4 decoder (native driver) ----------------------
+ * Replaces the model driver of qm:175-308 (Layer/Scratch/Model), qm:673-740
+ * (run_layers_) and qm:791-905 (captured_decoder) with every linear in the q4
+ * layout, plus the tensor-parallel path the reference does not have.
+ * cfg[0..10] = hidden, n_layers, n_q, n_kv, head_dim, ff, vocab, max_ctx (sizes
+ * local to the rank, hidden global), tp_rank, tp_size, vocab_offset. */
+int tlb_decoder_create(const int64_t* cfg, int n_cfg, float eps, float rope_base, void** out);
+int tlb_decoder_destroy(void* dec);
+/* which: 0 wqkv 1 wo 2 wgu 3 wd 4 lm_head; q4 = device pointer, borrowed (qm:85-153). */
+int tlb_decoder_set_linear(void* dec, int64_t layer, int which, const void* q4, int64_t K, int64_t N);
+/* which: 0 attn norm 1 ffn norm 2 bq 3 bk 4 bv 5 final norm 6 embedding table (device f32). */
+int tlb_decoder_set_vector(void* dec, int64_t layer, int which, const float* v);
+int tlb_decoder_kv(void* dec, int64_t layer, void** K, void** V);     /* cu.h:1326-1346 kv_cache K,V */
+int tlb_decoder_logits(void* dec, void** logits);                      /* qm Scratch.logitsb */
+int tlb_decoder_set_pos(void* dec, int64_t pos, void* stream);         /* qm:877-885 feed / cu.h:559 upload_u32 */
+int tlb_decoder_set_token(void* dec, int64_t token, void* stream);
+int tlb_decoder_forward(void* dec, void* stream);                      /* qm:673-740 run_layers_ + argmax */
+int64_t tlb_decoder_launches_per_token(void* dec);
+int tlb_decoder_capture(void* dec);                                    /* qm:791-860 captured_decoder::init_ */
+int tlb_decoder_run(void* dec, int64_t n_tokens, void* stream);        /* qm:862-905 step, device-resident ids */
+/* qm:747-752 step_imperative with HOST buffers: token id in, next id out. */
+int tlb_decoder_step(void* dec, const int32_t* token_in, int32_t* token_out, void* stream);
+int tlb_decoder_last_token(void* dec, int32_t* token_out, void* stream);
+/* Tensor-parallel wiring (no counterpart in the reference, which is single-device):
+ * each rank exports a 128-byte record, the ranks exchange them over any host
+ * channel, and every rank opens the others' exchange buffers. */
+int tlb_decoder_ipc_export(void* dec, void* record128);
+int tlb_decoder_ipc_open(void* dec, const void* records);
+
 #ifdef __cplusplus
 }
 #endif

@@ -1,0 +1,125 @@
+"""The native decoder through the C-ABI against the golden vectors the reference
+produced and against the oracle: greedy token ids exact, logits within 1e-3
+(bench/cuda/check/check_llm_decode.cpp:241-277 allows 2e-3)."""
+import numpy as np
+import pytest
+import torch
+
+import cases
+import oracle
+import synth
+
+pytestmark = pytest.mark.gpu
+
+
+def relerr(a, b):
+    return float(np.max(np.abs(np.asarray(a, np.float64) - b) / (1.0 + np.abs(b))))
+
+
+def make(cfg, seed, max_ctx, wts=None):
+    from cpp_tensorlib_b200.decoder import Q4Decoder
+    wts = wts or cases.decoder_weights(cfg, seed)
+    d = Q4Decoder(cfg, max_ctx)
+    d.load(wts)
+    return d, wts
+
+
+def port_decoder(port, cfg, wts, max_ctx):
+    o = oracle.PortDecoder(port, cfg, max_ctx)
+    o.set_embed(wts["embed"]); o.set_vector(0, 5, wts["onorm"]); o.set_linear(0, 4, port.to_q4(wts["lm_head"]))
+    for l, L in enumerate(wts["layers"]):
+        for k, i in cases.LINEAR_IDS.items():
+            o.set_linear(l, i, port.to_q4(L[k]))
+        for k, i in cases.VECTOR_IDS.items():
+            o.set_vector(l, i, L[k])
+    return o
+
+
+@pytest.mark.parametrize("name,cfg,seed", [("dec_tiny", cases.TINY, 21), ("dec_tiny64", cases.TINY64, 22)])
+@pytest.mark.parametrize("captured", [False, True])
+def test_decoder_matches_reference_golden(golden, name, cfg, seed, captured):
+    g = golden(name)
+    d, _ = make(cfg, seed, 64)
+    d.set_pos(0)
+    if captured:
+        d.capture()
+    prompt, nxt = list(g["prompt"]), 0
+    for i in range(len(g["next_tokens"])):
+        tid = prompt[i] if i < len(prompt) else nxt
+        nxt = d.step(int(tid))
+        assert relerr(d.logits().cpu().numpy(), g["logits"][i]) < 1e-3, i
+        assert nxt == int(g["next_tokens"][i]), i
+    d.close()
+
+
+def test_device_resident_feedback_equals_host_loop():
+    cfg = cases.TINY64
+    d, wts = make(cfg, 22, 64)
+    d.set_pos(0)
+    d.capture()
+    tok, host = 5, []
+    for _ in range(20):
+        tok = d.step(tok)
+        host.append(tok)
+    lg_host = d.logits().clone()
+    d.set_pos(0)
+    d.set_token(5)
+    d.run(20)
+    assert d.last_token() == host[-1]
+    assert torch.equal(d.logits(), lg_host)          # same kernels, same order: bit-identical
+    d.close()
+
+
+def test_half_billion_shape_two_layers(port):
+    """BASELINE config 3's architecture (hidden 896, 14q/2kv, hd 64, ff 4864, full 151936
+    vocabulary, eps 1e-6, rope base 1e6) with 2 of its 24 layers: 12 prompt ids then
+    12 greedy steps against the oracle."""
+    cfg = dict(cases.QWEN05, layers=2)
+    d, wts = make(cfg, 2, 64)
+    o = port_decoder(port, cfg, wts, 64)
+    d.set_pos(0)
+    d.capture()
+    prompt = [int(t) for t in synth.token_ids(2, 99, 12, cfg["vocab"])]
+    nxt = 0
+    for i in range(24):
+        tid = prompt[i] if i < 12 else nxt
+        nxt = d.step(tid)
+        want, lg = o.step(tid, i)
+        assert np.allclose(d.logits().cpu().numpy(), lg, rtol=1e-3, atol=1e-3), i
+        assert nxt == want, i
+    d.close(); o.close()
+
+
+def test_seven_billion_shape_one_layer_prefilled(port):
+    """BASELINE config 5's layer shape (hidden 3584, 28q/4kv, hd 128, ff 18944) with one
+    layer and a 32000-row vocabulary, KV pre-filled to ctx 4096 with N(0,1): 4 greedy
+    steps at positions 4096.. against the oracle."""
+    cfg = dict(cases.QWEN7, layers=1, vocab=32000)
+    d, wts = make(cfg, 4, 4200)
+    o = port_decoder(port, cfg, wts, 4200)
+    K, V = synth.normal(4, 900, (4, 4096, 128)), synth.normal(4, 901, (4, 4096, 128))
+    d.fill_kv(0, torch.from_numpy(K).cuda(), torch.from_numpy(V).cuda())
+    o.fill_kv(0, K, V)
+    d.set_pos(4096)
+    d.capture()
+    tok = 7
+    for i in range(4):
+        nxt = d.step(tok)
+        want, lg = o.step(tok, 4096 + i)
+        assert np.allclose(d.logits().cpu().numpy(), lg, rtol=1e-3, atol=1e-3), i
+        assert nxt == want, i
+        tok = nxt
+    d.close(); o.close()
+
+
+def test_decoder_argument_errors():
+    from cpp_tensorlib_b200 import TlbError
+    from cpp_tensorlib_b200.decoder import Q4Decoder
+    with pytest.raises(TlbError):
+        Q4Decoder(dict(cases.TINY, hd=96), 16)
+    d = Q4Decoder(cases.TINY64, 16)
+    with pytest.raises(TlbError):
+        d.set_pos(16)                      # outside the cache
+    with pytest.raises(TlbError):
+        d.step(1)                          # weights never set
+    d.close()
