@@ -15,7 +15,8 @@ int make_q4_tensor_maps(const void* qw, const void* scales, int N, int K, CUtens
 bool gemv_q4_tma_eligible(const void* qw, const void* scales, int N, int K, int M);
 int gemv_q4_launch(DeviceCtx* c, const CUtensorMap& tmW, const CUtensorMap& tmS, const float* x,
                    long long ldx, int M, float* y, long long ldy, int N, int K, float alpha,
-                   float beta, cudaStream_t stream, int max_ctas, const CommDev* push_comm);
+                   float beta, cudaStream_t stream, int max_ctas, const CommDev* push_comm,
+                   int act);
 int gemv_q4_simt_launch(const float* x, long long ldx, int M, const void* qw, const void* scales,
                         float* y, long long ldy, int N, int K, float alpha, float beta,
                         cudaStream_t stream);
@@ -227,7 +228,7 @@ int tlb_gemm_q4(const float* x, int64_t M, int64_t ldx, const void* qw, const fl
       int mb = (int)((M - m0) < 8 ? (M - m0) : 8);
       while (mb > 1 && !gemv_q4_tma_eligible(qw, scales, (int)N, (int)K, mb)) mb = (mb + 1) / 2;
       rc = gemv_q4_launch(c, tmW, tmS, x + m0 * ldx, ldx, mb, y + m0 * ldy, ldy, (int)N, (int)K,
-                          alpha, beta, S(stream), 0, nullptr);
+                          alpha, beta, S(stream), 0, nullptr, 0);
       if (rc) return rc;
       m0 += mb;
     }

@@ -306,20 +306,45 @@ __global__ void __launch_bounds__(AT_THREADS, (HW >= 4 ? 1 : 2))
   __syncthreads();
   if (!is_last) return;
   __threadfence();
-  for (int idx = tid; idx < p.grp * D; idx += AT_THREADS) {
-    const int hh = idx / D, d = idx - hh * D;
+  // Phase 1 (one warp per head): rescale coefficients c_s = exp(m_s - max m) and the
+  // denominator, splits spread over the lanes.  The tile ring is free by now and
+  // holds the coefficients.
+  float* cw = Kt;                       // [grp][s_live]
+  float* lden = Kt + p.grp * s_live;    // [grp]
+  for (int hh = warp; hh < p.grp; hh += AT_WARPS) {
     const int qh = kh * p.grp + hh;
     const float* src0 = p.partials + (size_t)qh * p.s_cap * (D + 2);
     float mm = -INFINITY;
-    for (int s2 = 0; s2 < s_live; s2++) mm = fmaxf(mm, __ldcg(&src0[(size_t)s2 * (D + 2)]));
-    float ll = 0.f, aa = 0.f;
-    for (int s2 = 0; s2 < s_live; s2++) {
-      const float* src = src0 + (size_t)s2 * (D + 2);
-      const float c = __expf(__ldcg(&src[0]) - mm);
-      ll += __ldcg(&src[1]) * c;
-      aa += __ldcg(&src[2 + d]) * c;
+    for (int s2 = lane; s2 < s_live; s2 += 32) mm = fmaxf(mm, __ldcg(&src0[(size_t)s2 * (D + 2)]));
+    mm = warp_max(mm);
+    float ll = 0.f;
+    for (int s2 = lane; s2 < s_live; s2 += 32) {
+      const float c = __expf(__ldcg(&src0[(size_t)s2 * (D + 2)]) - mm);
+      cw[hh * s_live + s2] = c;
+      ll += __ldcg(&src0[(size_t)s2 * (D + 2) + 1]) * c;
     }
-    p.out[(size_t)qh * D + d] = aa / ll;
+    // fixed-order sum over lanes: butterfly adds are order-independent per lane pair
+    ll = warp_sum(ll);
+    if (lane == 0) lden[hh] = ll;
+  }
+  __syncthreads();
+  // Phase 2: one thread per (head, dim); 16 independent partial loads in flight.
+  for (int idx = tid; idx < p.grp * D; idx += AT_THREADS) {
+    const int hh = idx / D, d = idx - hh * D;
+    const int qh = kh * p.grp + hh;
+    const float* src0 = p.partials + (size_t)qh * p.s_cap * (D + 2) + 2 + d;
+    const float* cwh = cw + hh * s_live;
+    float aa = 0.f;
+    for (int s0 = 0; s0 < s_live; s0 += 16) {
+      float v[16];
+#pragma unroll
+      for (int k2 = 0; k2 < 16; k2++)
+        v[k2] = (s0 + k2 < s_live) ? __ldcg(&src0[(size_t)(s0 + k2) * (D + 2)]) : 0.f;
+#pragma unroll
+      for (int k2 = 0; k2 < 16; k2++)
+        if (s0 + k2 < s_live) aa = fmaf(v[k2], cwh[s0 + k2], aa);
+    }
+    p.out[(size_t)qh * D + d] = aa / lden[hh];
   }
   if (tid == 0) p.counters[kh] = 0;
 }

@@ -27,7 +27,8 @@ int make_q4_tensor_maps(const void* qw, const void* scales, int N, int K, CUtens
 bool gemv_q4_tma_eligible(const void* qw, const void* scales, int N, int K, int M);
 int gemv_q4_launch(DeviceCtx* c, const CUtensorMap& tmW, const CUtensorMap& tmS, const float* x,
                    long long ldx, int M, float* y, long long ldy, int N, int K, float alpha,
-                   float beta, cudaStream_t stream, int max_ctas, const CommDev* push_comm);
+                   float beta, cudaStream_t stream, int max_ctas, const CommDev* push_comm,
+                   int act);
 int gemv_q4_simt_launch(const float* x, long long ldx, int M, const void* qw, const void* scales,
                         float* y, long long ldy, int N, int K, float alpha, float beta,
                         cudaStream_t stream);
@@ -102,10 +103,12 @@ static int set_linear(Linear& L, const void* q4, int K, int N) {
 }
 
 static int run_linear(DeviceCtx* c, const Linear& L, const float* x, float* y, cudaStream_t s,
-                      const CommDev* push) {
+                      const CommDev* push, int act = 0) {
   if (!L.q4) return set_error(TLB_ERR_STATE, "decoder: a linear weight was never set");
   if (L.tma)
-    return gemv_q4_launch(c, L.tmW, L.tmS, x, L.K, 1, y, L.N, L.N, L.K, 1.0f, 0.0f, s, 0, push);
+    return gemv_q4_launch(c, L.tmW, L.tmS, x, act ? 2 * L.K : L.K, 1, y, L.N, L.N, L.K, 1.0f, 0.0f,
+                          s, 0, push, act);
+  if (act) return set_error(TLB_ERR_UNSUPPORTED, "decoder: the fused SwiGLU needs ff % 128 == 0");
   if (push) return set_error(TLB_ERR_UNSUPPORTED, "decoder: tensor-parallel linears need K % 128 == 0");
   return gemv_q4_simt_launch(x, L.K, 1, L.q4, L.scales(), y, L.N, L.N, L.K, 1.0f, 0.0f, s);
 }
@@ -142,13 +145,14 @@ static int forward(Decoder* d, cudaStream_t s) {
       RUN(launch_add_rmsnorm(d->x, d->t0, L.fn, d->x, d->hb, E, d->eps, 1, s));
     }
     RUN(run_linear(c, L.wgu, d->hb, d->gu, s, nullptr));
-    RUN(launch_swiglu(d->gu, d->mb, d->ff, 1, s));
+    const bool fuse_act = L.wd.tma;  // SwiGLU inside the down projection's activation prep
+    if (!fuse_act) RUN(launch_swiglu(d->gu, d->mb, d->ff, 1, s));
     const float* nextw = (l + 1 < d->n_layers) ? d->layers[l + 1].an : d->onorm;
     if (tp) {
-      RUN(run_linear(c, L.wd, d->mb, nullptr, s, &d->comm));
+      RUN(run_linear(c, L.wd, fuse_act ? d->gu : d->mb, nullptr, s, &d->comm, fuse_act ? 1 : 0));
       RUN(launch_add_rmsnorm_ar(d->x, nextw, d->x, d->hb, E, d->eps, d->comm, c->status, s));
     } else {
-      RUN(run_linear(c, L.wd, d->mb, d->t0, s, nullptr));
+      RUN(run_linear(c, L.wd, fuse_act ? d->gu : d->mb, d->t0, s, nullptr, fuse_act ? 1 : 0));
       RUN(launch_add_rmsnorm(d->x, d->t0, nextw, d->x, d->hb, E, d->eps, 1, s));
     }
   }

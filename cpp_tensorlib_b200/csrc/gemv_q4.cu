@@ -30,8 +30,6 @@
 
 namespace tlb {
 
-constexpr int GV_WARPS = 8;
-constexpr int GV_STAGES = 6;
 constexpr int GV_W_BYTES = 2048;  // 16 rows x 128 B
 constexpr int GV_S_BYTES = 512;   // 16 rows x 8 f32
 constexpr int GV_MAXM = 8;
@@ -49,19 +47,38 @@ struct GemvParams {
   int RT, SL;       // row tiles (16 rows), k slabs (256 k)
   unsigned U;       // RT * SL
   int x_vec_ok;     // x rows are 16-byte aligned
+  int act;          // 0: x as given; 1: x row = [gate(K) | up(K)], activation silu(gate)*up
   int push;         // tensor-parallel: store y (M == 1) into every rank's staging slot
   CommDev comm;
 };
 
-__device__ __forceinline__ unsigned gv_start(unsigned w, unsigned U, unsigned W) {
-  return (unsigned)(((unsigned long long)w * U) / W);
+// Unit ranges: with q = U / W and r = U % W, worker w owns q+1 units when w < r,
+// else q, contiguously.  start(w) needs no division; owner(u) needs one 32-bit one.
+struct GvSplit {
+  unsigned q, r;
+};
+__device__ __forceinline__ unsigned gv_start(unsigned w, GvSplit sp) {
+  return w * sp.q + (w < sp.r ? w : sp.r);
 }
-__device__ __forceinline__ unsigned gv_owner(unsigned u, unsigned U, unsigned W) {
-  unsigned w = (unsigned)(((unsigned long long)u * W) / U);
-  while (w + 1 < W && gv_start(w + 1, U, W) <= u) w++;
-  return w;
+__device__ __forceinline__ unsigned gv_owner(unsigned u, GvSplit sp) {
+  const unsigned big = sp.r * (sp.q + 1u);
+  return u < big ? u / (sp.q + 1u) : sp.r + (u - big) / sp.q;
+}
+__device__ __forceinline__ unsigned atom_add_acq_rel(int* p, int v) {
+  int old;
+  asm volatile("atom.add.acq_rel.gpu.global.s32 %0, [%1], %2;" : "=r"(old) : "l"(p), "r"(v) : "memory");
+  return (unsigned)old;
 }
 
+// D = A*B (first MMA of a group: zero accumulator input)
+__device__ __forceinline__ void mma16816_z(float (&c)[4], unsigned a0, unsigned a1, unsigned a2,
+                                           unsigned a3, unsigned b0, unsigned b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
+      "{%10,%10,%10,%10};"
+      : "=f"(c[0]), "=f"(c[1]), "=f"(c[2]), "=f"(c[3])
+      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "f"(0.f));
+}
 __device__ __forceinline__ void mma16816(float (&c)[4], unsigned a0, unsigned a1, unsigned a2,
                                          unsigned a3, unsigned b0, unsigned b1) {
   asm volatile(
@@ -75,20 +92,32 @@ __device__ __forceinline__ unsigned pack_h2(__half a, __half b) {
   return (unsigned)__half_as_ushort(a) | ((unsigned)__half_as_ushort(b) << 16);
 }
 
-size_t gemv_smem_bytes(int M, int K) {
-  int SL = (K + 255) / 256, G = SL * 8;
-  int NT = M <= 4 ? 1 : 2;
-  size_t b = 1024;  // alignment slack
-  b += (size_t)GV_WARPS * GV_STAGES * (GV_W_BYTES + GV_S_BYTES);
-  b += (size_t)GV_WARPS * GV_STAGES * 8;
-  b += 64 * sizeof(float);                     // amax reduce
-  b += (size_t)G * (4 * NT) * sizeof(float2);  // PQ
-  b += (size_t)G * (2 * M) * 4 * sizeof(uint4);  // Bfrag
-  return b;
+// Shared-memory carve-up (host and device agree through this one function).
+struct GemvSmem {
+  size_t w_ring, s_ring, bars, pslab, q, bfrag, total;
+};
+__host__ __device__ inline GemvSmem gemv_smem_layout(int warps, int stages, int M, int K) {
+  const int SL = (K + 255) / 256, G = SL * 8;
+  GemvSmem L;
+  size_t o = 0;
+  L.w_ring = o; o += (size_t)warps * stages * GV_W_BYTES;
+  L.s_ring = o; o += (size_t)warps * stages * GV_S_BYTES;
+  L.bars = o;   o += (size_t)warps * stages * 8;
+  o = (o + 15) & ~(size_t)15;
+  L.pslab = o;  o += (size_t)GV_MAXM * SL * sizeof(float);
+  o = (o + 15) & ~(size_t)15;
+  L.q = o;      o += (size_t)GV_MAXM * G * sizeof(float);
+  o = (o + 15) & ~(size_t)15;
+  L.bfrag = o;  o += (size_t)G * (2 * M) * 4 * sizeof(uint4);
+  L.total = o + 1024;  // slack for the 1 KB alignment of the dynamic base
+  return L;
 }
 
-template <int NT>
-__global__ void __launch_bounds__(GV_WARPS * 32, 1)
+// WARPS x STAGES: 8 x 4 (two CTAs per SM, for K up to ~6K) or 16 x 3 (one CTA per
+// SM, large K whose activation fragments need more shared memory).  Either way
+// 16 warps per SM hide the fixed latencies of the LDS -> LOP -> MMA -> FMA chain.
+template <int NT, int WARPS, int STAGES, bool M1>
+__global__ void __launch_bounds__(WARPS * 32, (WARPS == 8 ? 2 : 1))
     gemv_q4_mma_kernel(const __grid_constant__ CUtensorMap tmW,
                        const __grid_constant__ CUtensorMap tmS, GemvParams p) {
   extern __shared__ unsigned char smem_raw[];
@@ -96,132 +125,130 @@ __global__ void __launch_bounds__(GV_WARPS * 32, 1)
       (unsigned char*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int g = lane >> 2, t = lane & 3;
-  constexpr int MPAD = 4 * NT;
-  const int G = p.SL * 8;
+  const int SL = p.SL, G = SL * 8;
   const int NCU = 2 * p.M;
+  const GemvSmem L = gemv_smem_layout(WARPS, STAGES, p.M, p.K);
 
-  unsigned char* Wring = base;
-  unsigned char* Sring = Wring + GV_WARPS * GV_STAGES * GV_W_BYTES;
-  uint64_t* bars = (uint64_t*)(Sring + GV_WARPS * GV_STAGES * GV_S_BYTES);
-  float* red = (float*)(bars + GV_WARPS * GV_STAGES);
-  float2* PQ = (float2*)(red + 64);
-  uint4* Bfrag = (uint4*)(PQ + (size_t)G * MPAD);
+  uint64_t* bars = (uint64_t*)(base + L.bars);
+  float* Pslab = (float*)(base + L.pslab);   // [m][SL]   2^(12+e) of the slab
+  float* Qg = (float*)(base + L.q);          // [m][G]    8 * sum of the group's activations
+  uint4* Bfrag = (uint4*)(base + L.bfrag);   // [G][2M][4]
 
-  unsigned char* myW = Wring + warp * GV_STAGES * GV_W_BYTES;
-  unsigned char* myS = Sring + warp * GV_STAGES * GV_S_BYTES;
-  uint64_t* mybar = bars + warp * GV_STAGES;
+  unsigned char* myW = base + L.w_ring + (size_t)warp * STAGES * GV_W_BYTES;
+  unsigned char* myS = base + L.s_ring + (size_t)warp * STAGES * GV_S_BYTES;
+  uint64_t* mybar = bars + warp * STAGES;
 
   // Never more workers than units, so every worker's range is non-empty and the
   // contributors of a row tile are exactly the owners of its first..last unit.
-  const unsigned Wall = gridDim.x * GV_WARPS;
+  const unsigned Wall = gridDim.x * WARPS;
   const unsigned Wtot = Wall < p.U ? Wall : p.U;
-  const unsigned wid = blockIdx.x * GV_WARPS + warp;
+  const unsigned wid = blockIdx.x * WARPS + warp;
   const bool idle = wid >= Wtot;
-  const unsigned u0 = idle ? 0u : gv_start(wid, p.U, Wtot);
-  const unsigned u1 = idle ? 0u : gv_start(wid + 1, p.U, Wtot);
+  const GvSplit sp = {p.U / Wtot, p.U % Wtot};
+  const unsigned u0 = idle ? 0u : gv_start(wid, sp);
+  const unsigned u1 = idle ? 0u : gv_start(wid + 1, sp);
   const int n_units = (int)(u1 - u0);
 
   if (lane == 0) {
-    for (int s = 0; s < GV_STAGES; s++) mbar_init(&mybar[s], 1);
+    for (int s = 0; s < STAGES; s++) mbar_init(&mybar[s], 1);
     mbar_fence_init();
   }
   __syncwarp();
 
-  auto issue = [&](int i) {
-    unsigned u = u0 + i;
-    int rt = u / p.SL, s = u - rt * p.SL;
-    int st = i % GV_STAGES;
-    mbar_expect_tx(&mybar[st], GV_W_BYTES + GV_S_BYTES);
-    tma_load_2d(myW + st * GV_W_BYTES, &tmW, s * 32, rt * 16, &mybar[st]);
-    tma_load_2d(myS + st * GV_S_BYTES, &tmS, s * 8, rt * 16, &mybar[st]);
+  // producer cursor (lane 0 issues; every lane tracks it, no divisions in the loop)
+  int irt = (int)(u0 / (unsigned)SL), is = (int)(u0 - (unsigned)irt * SL), istage = 0;
+  auto issue_next = [&]() {
+    if (lane == 0) {
+      mbar_expect_tx(&mybar[istage], GV_W_BYTES + GV_S_BYTES);
+      tma_load_2d(myW + istage * GV_W_BYTES, &tmW, is * 32, irt * 16, &mybar[istage]);
+      tma_load_2d(myS + istage * GV_S_BYTES, &tmS, is * 8, irt * 16, &mybar[istage]);
+    }
+    if (++is == SL) { is = 0; irt++; }
+    if (++istage == STAGES) istage = 0;
   };
   // Weights do not depend on the previous kernel: start streaming them before
   // waiting for it.
-  if (lane == 0) {
-    int pre = n_units < GV_STAGES ? n_units : GV_STAGES;
-    for (int i = 0; i < pre; i++) issue(i);
+  {
+    const int pre = n_units < STAGES ? n_units : STAGES;
+    for (int i = 0; i < pre; i++) issue_next();
   }
 
   pdl_wait();  // activations and the fix-up scratch are valid from here
 
-  // ---- activation prep: per-row power-of-two normalisation, fp16 hi/lo split,
-  // B-fragment order.  Slot (m, j, t) covers x[m][32j+8t .. +8).
-  {
-    for (int m = 0; m < p.M; m++) {
-      float mx = 0.f;
-      const float* xr = p.x + (long long)m * p.ldx;
-      for (int k = tid; k < p.K; k += blockDim.x) mx = fmaxf(mx, fabsf(xr[k]));
-      mx = warp_max(mx);
-      if (lane == 0) red[m * GV_WARPS + warp] = mx;
-    }
-    __syncthreads();
-    const int slots = p.M * G * 4;
-    for (int slot = tid; slot < ((slots + 3) & ~3); slot += blockDim.x) {
-      const bool live = slot < slots;
-      int m = live ? slot / (G * 4) : 0;
-      int rem = slot - m * (G * 4);
-      int j = rem >> 2, tt = rem & 3;
-      float mx = 0.f;
-#pragma unroll
-      for (int w = 0; w < GV_WARPS; w++) mx = fmaxf(mx, red[m * GV_WARPS + w]);
-      int e = (int)((__float_as_uint(mx) >> 23) & 0xff) - 126;  // mx < 2^e
-      e = mx > 0.f ? (e < -100 ? -100 : (e > 100 ? 100 : e)) : 0;
-      const float s12 = __uint_as_float((unsigned)(127 + 12 - e) << 23);
-      const float s8 = __uint_as_float((unsigned)(127 + 8 - e) << 23);
-      const float P = __uint_as_float((unsigned)(127 + 12 + e) << 23);
-      float v[8];
-      const int k0 = j * 32 + tt * 8;
-      const float* xr = p.x + (long long)m * p.ldx + k0;
-      if (live && k0 + 8 <= p.K) {
+  // ---- activation prep.  One warp per (row m, slab of 256 k): power-of-two
+  // normalisation by the slab's max (no block-wide reduction), exact fp16 hi/lo
+  // split, B-fragment order.  Lane l covers x[m][256*slab + 8*l .. +8) = group
+  // jj = l/4, quad slot tt = l%4.
+  for (int job = warp; job < p.M * SL; job += WARPS) {
+    const int m = job / SL, sl = job - m * SL;
+    const int k0 = sl * 256 + lane * 8;
+    const float* xr = p.x + (long long)m * p.ldx + k0;
+    float v[8];
+    auto load8 = [&](const float* src, float (&o)[8]) {
+      if (k0 + 8 <= p.K) {
         if (p.x_vec_ok) {
-          float4 a = *(const float4*)xr, b = *(const float4*)(xr + 4);
-          v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w;
-          v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+          const float4 a = *(const float4*)src, b = *(const float4*)(src + 4);
+          o[0] = a.x; o[1] = a.y; o[2] = a.z; o[3] = a.w;
+          o[4] = b.x; o[5] = b.y; o[6] = b.z; o[7] = b.w;
         } else {
 #pragma unroll
-          for (int i = 0; i < 8; i++) v[i] = xr[i];
+          for (int i = 0; i < 8; i++) o[i] = src[i];
         }
       } else {
 #pragma unroll
-        for (int i = 0; i < 8; i++) v[i] = (live && k0 + i < p.K) ? xr[i] : 0.f;
+        for (int i = 0; i < 8; i++) o[i] = (k0 + i < p.K) ? src[i] : 0.f;
       }
-      float sum = ((v[0] + v[1]) + (v[2] + v[3])) + ((v[4] + v[5]) + (v[6] + v[7]));
-      sum += __shfl_xor_sync(0xffffffffu, sum, 1);
-      sum += __shfl_xor_sync(0xffffffffu, sum, 2);
-      if (live) {
-        __half hi[8], lo[8];
+    };
+    load8(xr, v);
+    if (p.act == 1) {
+      // fused SwiGLU (kernels/tensorlib_cuda.cu:185-192 of the reference): the row
+      // holds gate then up; same expression g / (1 + exp(-g)) * u
+      float u[8];
+      load8(xr + p.K, u);
 #pragma unroll
-        for (int i = 0; i < 8; i++) {
-          float f = v[i] * ((i & 1) ? s8 : s12);
-          hi[i] = __float2half_rn(f);
-          lo[i] = __float2half_rn(f - __half2float(hi[i]));
-        }
-        uint4 fh, fl;
-        fh.x = pack_h2(hi[0], hi[4]); fh.y = pack_h2(hi[1], hi[5]);
-        fh.z = pack_h2(hi[2], hi[6]); fh.w = pack_h2(hi[3], hi[7]);
-        fl.x = pack_h2(lo[0], lo[4]); fl.y = pack_h2(lo[1], lo[5]);
-        fl.z = pack_h2(lo[2], lo[6]); fl.w = pack_h2(lo[3], lo[7]);
-        Bfrag[((size_t)j * NCU + 2 * m) * 4 + tt] = fh;
-        Bfrag[((size_t)j * NCU + 2 * m + 1) * 4 + tt] = fl;
-        if (tt == 0) PQ[(size_t)j * MPAD + m] = make_float2(P, 8.0f * sum);
-      }
+      for (int i = 0; i < 8; i++) v[i] = (v[i] / (1.0f + expf(-v[i]))) * u[i];
     }
-    for (int i = tid; i < G * MPAD; i += blockDim.x) {
-      int m = i % MPAD;
-      if (m >= p.M) PQ[i] = make_float2(0.f, 0.f);
+    float mx = 0.f;
+#pragma unroll
+    for (int i = 0; i < 8; i++) mx = fmaxf(mx, fabsf(v[i]));
+    mx = warp_max(mx);
+    int e = (int)((__float_as_uint(mx) >> 23) & 0xff) - 126;  // mx < 2^e
+    e = mx > 0.f ? (e < -100 ? -100 : (e > 100 ? 100 : e)) : 0;
+    const float s12 = __uint_as_float((unsigned)(127 + 12 - e) << 23);
+    const float s8 = __uint_as_float((unsigned)(127 + 8 - e) << 23);
+    float sum = ((v[0] + v[1]) + (v[2] + v[3])) + ((v[4] + v[5]) + (v[6] + v[7]));
+    sum += __shfl_xor_sync(0xffffffffu, sum, 1);
+    sum += __shfl_xor_sync(0xffffffffu, sum, 2);
+    __half hi[8], lo[8];
+#pragma unroll
+    for (int i = 0; i < 8; i++) {
+      const float f = v[i] * ((i & 1) ? s8 : s12);
+      hi[i] = __float2half_rn(f);
+      lo[i] = __float2half_rn(f - __half2float(hi[i]));
     }
-    __syncthreads();
+    uint4 fh, fl;
+    fh.x = pack_h2(hi[0], hi[4]); fh.y = pack_h2(hi[1], hi[5]);
+    fh.z = pack_h2(hi[2], hi[6]); fh.w = pack_h2(hi[3], hi[7]);
+    fl.x = pack_h2(lo[0], lo[4]); fl.y = pack_h2(lo[1], lo[5]);
+    fl.z = pack_h2(lo[2], lo[6]); fl.w = pack_h2(lo[3], lo[7]);
+    const int j = sl * 8 + (lane >> 2), tt = lane & 3;
+    Bfrag[((size_t)j * NCU + 2 * m) * 4 + tt] = fh;
+    Bfrag[((size_t)j * NCU + 2 * m + 1) * 4 + tt] = fl;
+    if (tt == 0) Qg[(size_t)m * G + j] = 8.0f * sum;
+    if (lane == 0) Pslab[m * SL + sl] = __uint_as_float((unsigned)(127 + 12 + e) << 23);
   }
+  __syncthreads();
   pdl_launch_dependents();
 
   // ---- streaming loop ------------------------------------------------------
-  float acc[NT][2];
+  float acc[NT][2], corr[NT][2];
 #pragma unroll
-  for (int nt = 0; nt < NT; nt++) acc[nt][0] = acc[nt][1] = 0.f;
+  for (int nt = 0; nt < NT; nt++) acc[nt][0] = acc[nt][1] = corr[nt][0] = corr[nt][1] = 0.f;
   bool use_b[NT];
 #pragma unroll
   for (int nt = 0; nt < NT; nt++) use_b[nt] = (8 * nt + g) < NCU;
   const unsigned g7x4 = (unsigned)(g & 7) * 4u;
+  const unsigned wbase = (unsigned)g * 32u + (unsigned)t;
 
   unsigned ar_seq = 0;
   if (p.push) ar_seq = *(volatile unsigned*)p.comm.seq;
@@ -236,53 +263,81 @@ __global__ void __launch_bounds__(GV_WARPS * 32, 1)
     }
   };
   auto flush = [&](int rt) {
-    const unsigned t0 = (unsigned)rt * p.SL, t1 = t0 + p.SL;
+    // fold the -8*sum(x_g) correction in; on the M == 1 path it is spread over the
+    // four lanes of a quad and summed here
+    float val[NT][2];
+#pragma unroll
+    for (int nt = 0; nt < NT; nt++) {
+#pragma unroll
+      for (int r = 0; r < 2; r++) {
+        float cr = corr[nt][r];
+        if (M1) {
+          cr += __shfl_xor_sync(0xffffffffu, cr, 1);
+          cr += __shfl_xor_sync(0xffffffffu, cr, 2);
+        }
+        val[nt][r] = acc[nt][r] - cr;
+      }
+    }
+    const unsigned t0 = (unsigned)rt * SL, t1 = t0 + SL;
     const bool complete = (u0 <= t0) && (u1 >= t1);
     const int r0 = rt * 16;
     if (complete) {
 #pragma unroll
       for (int nt = 0; nt < NT; nt++) {
-        int m = 4 * nt + t;
+        const int m = 4 * nt + t;
         if (m < p.M) {
-          if (r0 + g < p.N) emit(m, r0 + g, acc[nt][0]);
-          if (r0 + g + 8 < p.N) emit(m, r0 + g + 8, acc[nt][1]);
+          if (r0 + g < p.N) emit(m, r0 + g, val[nt][0]);
+          if (r0 + g + 8 < p.N) emit(m, r0 + g + 8, val[nt][1]);
         }
       }
       return;
     }
     // partial: slot 0 when this tile holds the worker's first unit, else slot 1
-    const int slot = ((int)(u0 / p.SL) == rt) ? 0 : 1;
+    const int slot = (u0 >= t0) ? 0 : 1;
     float* mine = p.partials + ((size_t)wid * 2 + slot) * 128;
 #pragma unroll
     for (int nt = 0; nt < NT; nt++) {
-      int m = 4 * nt + t;
-      __stcg(&mine[m * 16 + g], acc[nt][0]);
-      __stcg(&mine[m * 16 + g + 8], acc[nt][1]);
+      const int m = 4 * nt + t;
+      __stcg(&mine[m * 16 + g], val[nt][0]);
+      __stcg(&mine[m * 16 + g + 8], val[nt][1]);
     }
-    __threadfence();
     __syncwarp();
-    const unsigned wf = gv_owner(t0, p.U, Wtot), wl = gv_owner(t1 - 1, p.U, Wtot);
+    const unsigned wf = gv_owner(t0, sp), wl = gv_owner(t1 - 1, sp);
     int old = 0;
-    if (lane == 0) old = atomicAdd(&p.counters[rt], 1);
+    if (lane == 0) old = (int)atom_add_acq_rel(&p.counters[rt], 1);  // releases the warp's stores
     old = __shfl_sync(0xffffffffu, old, 0);
     if (old != (int)(wl - wf)) return;  // not the last contributor
-    __threadfence();
+    // Last contributor: fold the partials in worker order.  Loads are issued four
+    // workers at a time before any add so their latencies overlap.
     float sum[NT][2];
 #pragma unroll
     for (int nt = 0; nt < NT; nt++) sum[nt][0] = sum[nt][1] = 0.f;
-    for (unsigned w = wf; w <= wl; w++) {
-      const int sl = ((int)(gv_start(w, p.U, Wtot) / p.SL) == rt) ? 0 : 1;
-      const float* src = p.partials + ((size_t)w * 2 + sl) * 128;
+    for (unsigned w = wf; w <= wl; w += 4) {
+      float v[4][NT][2];
 #pragma unroll
-      for (int nt = 0; nt < NT; nt++) {
-        int m = 4 * nt + t;
-        sum[nt][0] += __ldcg(&src[m * 16 + g]);
-        sum[nt][1] += __ldcg(&src[m * 16 + g + 8]);
+      for (int k = 0; k < 4; k++) {
+        const unsigned ww = w + k;
+        const bool on = ww <= wl;
+        const int sl = (gv_start(on ? ww : wl, sp) >= t0) ? 0 : 1;  // started inside this tile
+        const float* src = p.partials + ((size_t)(on ? ww : wl) * 2 + sl) * 128;
+#pragma unroll
+        for (int nt = 0; nt < NT; nt++) {
+          const int m = 4 * nt + t;
+          v[k][nt][0] = on ? __ldcg(&src[m * 16 + g]) : 0.f;
+          v[k][nt][1] = on ? __ldcg(&src[m * 16 + g + 8]) : 0.f;
+        }
       }
+#pragma unroll
+      for (int k = 0; k < 4; k++)
+#pragma unroll
+        for (int nt = 0; nt < NT; nt++) {
+          sum[nt][0] += v[k][nt][0];
+          sum[nt][1] += v[k][nt][1];
+        }
     }
 #pragma unroll
     for (int nt = 0; nt < NT; nt++) {
-      int m = 4 * nt + t;
+      const int m = 4 * nt + t;
       if (m < p.M) {
         if (r0 + g < p.N) emit(m, r0 + g, sum[nt][0]);
         if (r0 + g + 8 < p.N) emit(m, r0 + g + 8, sum[nt][1]);
@@ -291,27 +346,26 @@ __global__ void __launch_bounds__(GV_WARPS * 32, 1)
     if (lane == 0) p.counters[rt] = 0;  // leave the counter clean for the next launch
   };
 
-  int cur_rt = n_units > 0 ? (int)(u0 / p.SL) : -1;
+  int rt = (int)(u0 / (unsigned)SL), s = (int)(u0 - (unsigned)rt * SL);
+  int st = 0;
+  unsigned phase = 0;
   for (int i = 0; i < n_units; i++) {
-    const unsigned u = u0 + i;
-    const int rt = u / p.SL, s = u - rt * p.SL;
-    if (rt != cur_rt) {
-      flush(cur_rt);
-#pragma unroll
-      for (int nt = 0; nt < NT; nt++) acc[nt][0] = acc[nt][1] = 0.f;
-      cur_rt = rt;
-    }
-    const int st = i % GV_STAGES;
-    if (!mbar_wait_bounded(&mybar[st], (i / GV_STAGES) & 1, p.status, 100 + st)) return;
+    if (!mbar_wait_bounded(&mybar[st], phase, p.status, 100 + st)) return;
     const unsigned* Wst = (const unsigned*)(myW + st * GV_W_BYTES);
     const float* Sst = (const float*)(myS + st * GV_S_BYTES);
     const uint4* Bu = Bfrag + (size_t)(s * 8) * NCU * 4;
-    const float2* PQu = PQ + (size_t)(s * 8) * MPAD;
+    // the 8 group scales of rows g and g+8
+    const float4 sa0 = *(const float4*)(Sst + g * 8), sa1 = *(const float4*)(Sst + g * 8 + 4);
+    const float4 sb0 = *(const float4*)(Sst + (g + 8) * 8), sb1 = *(const float4*)(Sst + (g + 8) * 8 + 4);
+    const float sc0[8] = {sa0.x, sa0.y, sa0.z, sa0.w, sa1.x, sa1.y, sa1.z, sa1.w};
+    const float sc1[8] = {sb0.x, sb0.y, sb0.z, sb0.w, sb1.x, sb1.y, sb1.z, sb1.w};
+    float ua[NT][2];
+#pragma unroll
+    for (int nt = 0; nt < NT; nt++) ua[nt][0] = ua[nt][1] = 0.f;
 #pragma unroll
     for (int jj = 0; jj < 8; jj++) {
-      const unsigned wo = (unsigned)g * 32u + (((unsigned)jj * 4u) ^ g7x4) + (unsigned)t;
+      const unsigned wo = wbase + (((unsigned)jj * 4u) ^ g7x4);
       unsigned w0 = Wst[wo], w1 = Wst[wo + 256];
-      const float sc0 = Sst[g * 8 + jj], sc1 = Sst[(g + 8) * 8 + jj];
       const unsigned a0 = w0 & 0x000f000fu, a2 = w0 & 0x00f000f0u;
       const unsigned a1 = w1 & 0x000f000fu, a3 = w1 & 0x00f000f0u;
       w0 >>= 8;
@@ -322,18 +376,45 @@ __global__ void __launch_bounds__(GV_WARPS * 32, 1)
       for (int nt = 0; nt < NT; nt++) {
         uint4 b = make_uint4(0u, 0u, 0u, 0u);
         if (use_b[nt]) b = Bu[((size_t)jj * NCU + 8 * nt + g) * 4 + t];
-        float c[4] = {0.f, 0.f, 0.f, 0.f};
-        mma16816(c, a0, a1, a2, a3, b.x, b.y);
+        float c[4];
+        mma16816_z(c, a0, a1, a2, a3, b.x, b.y);
         mma16816(c, a4, a5, a6, a7, b.z, b.w);
-        const float2 pq = PQu[jj * MPAD + 4 * nt + t];
-        acc[nt][0] = fmaf(sc0, fmaf(pq.x, c[0] + c[1], -pq.y), acc[nt][0]);
-        acc[nt][1] = fmaf(sc1, fmaf(pq.x, c[2] + c[3], -pq.y), acc[nt][1]);
+        ua[nt][0] = fmaf(sc0[jj], c[0] + c[1], ua[nt][0]);
+        ua[nt][1] = fmaf(sc1[jj], c[2] + c[3], ua[nt][1]);
+        if (!M1) {
+          const float q = Qg[(size_t)(4 * nt + t) * G + s * 8 + jj];
+          corr[nt][0] = fmaf(sc0[jj], q, corr[nt][0]);
+          corr[nt][1] = fmaf(sc1[jj], q, corr[nt][1]);
+        }
       }
     }
+    if (M1) {
+      // lane t of the quad handles groups 2t, 2t+1 of the correction term
+      const float2 q = *(const float2*)(Qg + s * 8 + 2 * t);
+      const float2 c0 = *(const float2*)(Sst + g * 8 + 2 * t);
+      const float2 c1 = *(const float2*)(Sst + (g + 8) * 8 + 2 * t);
+      corr[0][0] = fmaf(c0.x, q.x, fmaf(c0.y, q.y, corr[0][0]));
+      corr[0][1] = fmaf(c1.x, q.x, fmaf(c1.y, q.y, corr[0][1]));
+    }
+#pragma unroll
+    for (int nt = 0; nt < NT; nt++) {
+      const int m = M1 ? 0 : 4 * nt + t;
+      const float P = Pslab[m * SL + s];
+      acc[nt][0] = fmaf(P, ua[nt][0], acc[nt][0]);
+      acc[nt][1] = fmaf(P, ua[nt][1], acc[nt][1]);
+    }
     __syncwarp();
-    if (lane == 0 && i + GV_STAGES < n_units) issue(i + GV_STAGES);
+    if (i + STAGES < n_units) issue_next();
+    if (++st == STAGES) { st = 0; phase ^= 1u; }
+    if (++s == SL) {
+      flush(rt);
+#pragma unroll
+      for (int nt = 0; nt < NT; nt++) acc[nt][0] = acc[nt][1] = corr[nt][0] = corr[nt][1] = 0.f;
+      s = 0;
+      rt++;
+    }
   }
-  if (cur_rt >= 0) flush(cur_rt);
+  if (n_units > 0 && s != 0) flush(rt);
 
   // Tensor-parallel push: when the last worker of this rank has stored its tiles,
   // publish the sequence number in every rank's flag word.
@@ -410,18 +491,44 @@ int make_q4_tensor_maps(const void* qw, const void* scales, int N, int K, CUtens
   return TLB_OK;
 }
 
+// Kernel shape for a problem: 8 warps x 4 stages when two CTAs fit on an SM,
+// else 16 warps x 3 stages.
+static void gemv_pick(int M, int K, int* warps, int* stages) {
+  const size_t small = gemv_smem_layout(8, 4, M, K).total;
+  if (small <= 113 * 1024) { *warps = 8; *stages = 4; }
+  else { *warps = 16; *stages = 3; }
+}
+
 bool gemv_q4_tma_eligible(const void* qw, const void* scales, int N, int K, int M) {
   if (K % 128 != 0 || M < 1 || M > GV_MAXM) return false;
   if (((uintptr_t)qw & 15) || ((uintptr_t)scales & 15)) return false;
-  if (gemv_smem_bytes(M, K) > 227 * 1024) return false;
+  int w, st;
+  gemv_pick(M, K, &w, &st);
+  if (gemv_smem_layout(w, st, M, K).total > 227 * 1024) return false;
   return N > 0;
+}
+
+template <int NT, int WARPS, int STAGES, bool M1>
+static int gemv_launch_t(const CUtensorMap& tmW, const CUtensorMap& tmS, const GemvParams& p,
+                         int ctas, size_t smem, cudaStream_t stream) {
+  static bool attr = false;
+  if (!attr) {
+    TLB_CUDA(cudaFuncSetAttribute(gemv_q4_mma_kernel<NT, WARPS, STAGES, M1>,
+                                  cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
+    attr = true;
+  }
+  LaunchCfg lc(dim3(ctas), dim3(WARPS * 32), smem, stream, pdl_enabled());
+  TLB_CUDA(cudaLaunchKernelEx(&lc.cfg, gemv_q4_mma_kernel<NT, WARPS, STAGES, M1>, tmW, tmS, p));
+  return TLB_OK;
 }
 
 // Launch with ready tensor maps (the decoder caches them per weight).
 int gemv_q4_launch(DeviceCtx* c, const CUtensorMap& tmW, const CUtensorMap& tmS, const float* x,
                    long long ldx, int M, float* y, long long ldy, int N, int K, float alpha,
-                   float beta, cudaStream_t stream, int max_ctas, const CommDev* push_comm) {
+                   float beta, cudaStream_t stream, int max_ctas, const CommDev* push_comm,
+                   int act) {
   GemvParams p;
+  p.act = act;
   p.push = push_comm ? 1 : 0;
   if (push_comm) {
     if (M != 1) return set_error(TLB_ERR_ARG, "gemv_q4: the tensor-parallel push needs M == 1");
@@ -432,33 +539,24 @@ int gemv_q4_launch(DeviceCtx* c, const CUtensorMap& tmW, const CUtensorMap& tmS,
   p.partials = c->gemv_partials; p.counters = c->gemv_counters; p.status = c->status;
   p.RT = (N + 15) / 16; p.SL = (K + 255) / 256;
   p.U = (unsigned)p.RT * (unsigned)p.SL;
-  p.x_vec_ok = (((uintptr_t)x & 15) == 0 && (ldx % 4) == 0) ? 1 : 0;
+  p.x_vec_ok = (((uintptr_t)x & 15) == 0 && (ldx % 4) == 0 && (K % 4) == 0) ? 1 : 0;
   if (p.RT > c->gemv_max_tiles)
     return set_error(TLB_ERR_UNSUPPORTED, "gemv_q4: N exceeds the fix-up counter capacity");
-  int ctas = max_ctas > 0 ? max_ctas : c->sm_count;
-  int need = (int)((p.U + GV_WARPS - 1) / GV_WARPS);
+  int warps, stages;
+  gemv_pick(M, K, &warps, &stages);
+  int ctas = max_ctas > 0 ? max_ctas : c->sm_count * (warps == 8 ? 2 : 1);
+  const int need = (int)((p.U + warps - 1) / warps);
   if (ctas > need) ctas = need;
-  if (ctas * GV_WARPS > c->gemv_max_workers) ctas = c->gemv_max_workers / GV_WARPS;
-  size_t smem = gemv_smem_bytes(M, K);
-  LaunchCfg lc(dim3(ctas), dim3(GV_WARPS * 32), smem, stream, pdl_enabled());
-  if (M <= 4) {
-    static bool attr1 = false;
-    if (!attr1) {
-      TLB_CUDA(cudaFuncSetAttribute(gemv_q4_mma_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                    227 * 1024));
-      attr1 = true;
-    }
-    TLB_CUDA(cudaLaunchKernelEx(&lc.cfg, gemv_q4_mma_kernel<1>, tmW, tmS, p));
-  } else {
-    static bool attr2 = false;
-    if (!attr2) {
-      TLB_CUDA(cudaFuncSetAttribute(gemv_q4_mma_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                    227 * 1024));
-      attr2 = true;
-    }
-    TLB_CUDA(cudaLaunchKernelEx(&lc.cfg, gemv_q4_mma_kernel<2>, tmW, tmS, p));
+  if (ctas * warps > c->gemv_max_workers) ctas = c->gemv_max_workers / warps;
+  const size_t smem = gemv_smem_layout(warps, stages, M, K).total;
+  if (warps == 8) {
+    if (M == 1) return gemv_launch_t<1, 8, 4, true>(tmW, tmS, p, ctas, smem, stream);
+    if (M <= 4) return gemv_launch_t<1, 8, 4, false>(tmW, tmS, p, ctas, smem, stream);
+    return gemv_launch_t<2, 8, 4, false>(tmW, tmS, p, ctas, smem, stream);
   }
-  return TLB_OK;
+  if (M == 1) return gemv_launch_t<1, 16, 3, true>(tmW, tmS, p, ctas, smem, stream);
+  if (M <= 4) return gemv_launch_t<1, 16, 3, false>(tmW, tmS, p, ctas, smem, stream);
+  return gemv_launch_t<2, 16, 3, false>(tmW, tmS, p, ctas, smem, stream);
 }
 
 int gemv_q4_simt_launch(const float* x, long long ldx, int M, const void* qw, const void* scales,

@@ -71,6 +71,18 @@ def attn(a):
                           working_set_MB=a.copies * nbytes / 1e6)))
 
 
+def rmsnorm(a):
+    x = torch.randn((1, a.n), device="cuda")
+    w = torch.ones(a.n, device="cuda")
+    out = torch.empty_like(x)
+
+    def one_pass():
+        for _ in range(a.copies):
+            tl.rmsnorm(x, w, 1e-6, out=out)
+    ms = _time_graph(one_pass, a.iters) / a.copies
+    print(json.dumps(dict(op="rmsnorm", n=a.n, us_per_launch=ms * 1e3, pdl=a.pdl)))
+
+
 def main():
     ap = argparse.ArgumentParser()
     sub = ap.add_subparsers(dest="op", required=True)
@@ -83,11 +95,16 @@ def main():
     t.add_argument("--kv-heads", type=int, default=28)
     t.add_argument("--ctx", type=int, default=4096)
     t.add_argument("--D", type=int, default=128)
-    for p in (g, t):
+    r = sub.add_parser("rmsnorm")
+    r.add_argument("--n", type=int, default=3584)
+    for p in (g, t, r):
         p.add_argument("--copies", type=int, default=4)
         p.add_argument("--iters", type=int, default=20)
+        p.add_argument("--pdl", type=int, default=1, help="programmatic dependent launch on/off")
     a = ap.parse_args()
-    {"gemv": gemv, "attn": attn}[a.op](a)
+    from ._lib import check, lib
+    check(lib().tlb_set_pdl(a.pdl))
+    {"gemv": gemv, "attn": attn, "rmsnorm": rmsnorm}[a.op](a)
 
 
 if __name__ == "__main__":
