@@ -35,7 +35,7 @@ struct AttnParams {
   const float* K;
   const float* V;
   float* out;
-  float* partials;     // [n_q][S_cap][D+2]  (m, l, acc[D])
+  float* partials;     // [n_q][S_cap][D+4]  (acc[D], m, l, pad, pad)
   int* counters;       // [n_kv], zero between launches
   const unsigned* d_pos;  // nullptr: use ctx
   int ctx;
@@ -52,6 +52,7 @@ __host__ __device__ inline int attn_splits_wanted(int n_kv, int ctx, int sm2) {
   int s = sm2 / (n_kv > 0 ? n_kv : 1);
   int cap = ctx / 128;
   if (s > cap) s = cap;
+  if (s > 96) s = 96;  // the merge keeps (m, l) of at most 3 splits per lane
   return s < 1 ? 1 : s;
 }
 // Keys per split: ceil(ctx / wanted) rounded up to a whole tile.
@@ -288,9 +289,10 @@ __global__ void __launch_bounds__(AT_THREADS, (HW >= 4 ? 1 : 2))
     if (single) {
       p.out[(size_t)qh * D + d] = aa / ll;
     } else {
-      float* dst = p.partials + ((size_t)qh * p.s_cap + sp) * (D + 2);
-      if (d == 0) { __stcg(&dst[0], mm); __stcg(&dst[1], ll); }
-      __stcg(&dst[2 + d], aa);
+      // global partial entry: acc[D], m, l, pad, pad  (stride D+4 floats, 16-byte aligned)
+      float* dst = p.partials + ((size_t)qh * p.s_cap + sp) * (D + 4);
+      if (d == 0) { __stcg(&dst[D], mm); __stcg(&dst[D + 1], ll); }
+      __stcg(&dst[d], aa);
     }
   }
   if (single) return;
@@ -313,38 +315,54 @@ __global__ void __launch_bounds__(AT_THREADS, (HW >= 4 ? 1 : 2))
   float* lden = Kt + p.grp * s_live;    // [grp]
   for (int hh = warp; hh < p.grp; hh += AT_WARPS) {
     const int qh = kh * p.grp + hh;
-    const float* src0 = p.partials + (size_t)qh * p.s_cap * (D + 2);
-    float mm = -INFINITY;
-    for (int s2 = lane; s2 < s_live; s2 += 32) mm = fmaxf(mm, __ldcg(&src0[(size_t)s2 * (D + 2)]));
-    mm = warp_max(mm);
-    float ll = 0.f;
-    for (int s2 = lane; s2 < s_live; s2 += 32) {
-      const float c = __expf(__ldcg(&src0[(size_t)s2 * (D + 2)]) - mm);
-      cw[hh * s_live + s2] = c;
-      ll += __ldcg(&src0[(size_t)s2 * (D + 2) + 1]) * c;
+    const float* src0 = p.partials + (size_t)qh * p.s_cap * (D + 4) + D;
+    // one round trip: every lane fetches (m, l) of its splits (up to 3 per lane)
+    float2 ml[3];
+#pragma unroll
+    for (int k2 = 0; k2 < 3; k2++) {
+      const int s2 = lane + 32 * k2;
+      ml[k2] = s2 < s_live ? __ldcg((const float2*)(src0 + (size_t)s2 * (D + 4)))
+                           : make_float2(-INFINITY, 0.f);
     }
-    // fixed-order sum over lanes: butterfly adds are order-independent per lane pair
+    float mm = warp_max(fmaxf(ml[0].x, fmaxf(ml[1].x, ml[2].x)));
+    float ll = 0.f;
+#pragma unroll
+    for (int k2 = 0; k2 < 3; k2++) {
+      const int s2 = lane + 32 * k2;
+      if (s2 < s_live) {
+        const float c = __expf(ml[k2].x - mm);
+        cw[hh * s_live + s2] = c;
+        ll += ml[k2].y * c;
+      }
+    }
     ll = warp_sum(ll);
     if (lane == 0) lden[hh] = ll;
   }
   __syncthreads();
-  // Phase 2: one thread per (head, dim); 16 independent partial loads in flight.
-  for (int idx = tid; idx < p.grp * D; idx += AT_THREADS) {
-    const int hh = idx / D, d = idx - hh * D;
+  // Phase 2: one thread per (head, 4 dims); 16 independent 16-byte loads in flight.
+  for (int idx = tid; idx < p.grp * (D / 4); idx += AT_THREADS) {
+    const int hh = idx / (D / 4), d4 = idx - hh * (D / 4);
     const int qh = kh * p.grp + hh;
-    const float* src0 = p.partials + (size_t)qh * p.s_cap * (D + 2) + 2 + d;
+    const float* src0 = p.partials + (size_t)qh * p.s_cap * (D + 4) + d4 * 4;
     const float* cwh = cw + hh * s_live;
-    float aa = 0.f;
+    float4 aa = make_float4(0.f, 0.f, 0.f, 0.f);
     for (int s0 = 0; s0 < s_live; s0 += 16) {
-      float v[16];
+      float4 v[16];
 #pragma unroll
       for (int k2 = 0; k2 < 16; k2++)
-        v[k2] = (s0 + k2 < s_live) ? __ldcg(&src0[(size_t)(s0 + k2) * (D + 2)]) : 0.f;
+        v[k2] = (s0 + k2 < s_live) ? __ldcg((const float4*)(src0 + (size_t)(s0 + k2) * (D + 4)))
+                                   : make_float4(0.f, 0.f, 0.f, 0.f);
 #pragma unroll
       for (int k2 = 0; k2 < 16; k2++)
-        if (s0 + k2 < s_live) aa = fmaf(v[k2], cwh[s0 + k2], aa);
+        if (s0 + k2 < s_live) {
+          const float c = cwh[s0 + k2];
+          aa.x = fmaf(v[k2].x, c, aa.x); aa.y = fmaf(v[k2].y, c, aa.y);
+          aa.z = fmaf(v[k2].z, c, aa.z); aa.w = fmaf(v[k2].w, c, aa.w);
+        }
     }
-    p.out[(size_t)qh * D + d] = aa / lden[hh];
+    const float den = lden[hh];
+    *(float4*)(p.out + (size_t)qh * D + d4 * 4) =
+        make_float4(aa.x / den, aa.y / den, aa.z / den, aa.w / den);
   }
   if (tid == 0) p.counters[kh] = 0;
 }
@@ -354,7 +372,7 @@ __global__ void __launch_bounds__(AT_THREADS, (HW >= 4 ? 1 : 2))
 // ---------------------------------------------------------------------------
 size_t attn_partials_bytes(int n_q, int n_kv, long long kv_max, int D, int sm_count) {
   int s = attn_splits_wanted(n_kv, (int)kv_max, 2 * sm_count);
-  return (size_t)n_q * s * (D + 2) * sizeof(float);
+  return (size_t)n_q * s * (D + 4) * sizeof(float);
 }
 
 template <int D, int HW>
@@ -381,8 +399,8 @@ int attn_decode_launch(DeviceCtx* c, const float* q, const float* K, const float
   if (n_kv <= 0 || n_q % n_kv != 0) return set_error(TLB_ERR_ARG, "attn_decode: n_q % n_kv != 0");
   const int grp = n_q / n_kv;
   if (grp > 32) return set_error(TLB_ERR_UNSUPPORTED, "attn_decode: GQA group > 32");
-  if (((uintptr_t)K & 15) || ((uintptr_t)V & 15) || ((uintptr_t)q & 15))
-    return set_error(TLB_ERR_ARG, "attn_decode: q/K/V must be 16-byte aligned");
+  if (((uintptr_t)K & 15) || ((uintptr_t)V & 15) || ((uintptr_t)q & 15) || ((uintptr_t)out & 15))
+    return set_error(TLB_ERR_ARG, "attn_decode: q/K/V/out must be 16-byte aligned");
   AttnParams p;
   p.q = q; p.K = K; p.V = V; p.out = out; p.partials = partials; p.counters = counters;
   p.d_pos = d_pos; p.ctx = ctx; p.n_q = n_q; p.n_kv = n_kv; p.grp = grp;
