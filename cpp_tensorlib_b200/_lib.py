@@ -33,6 +33,7 @@ SIGNATURES = {
     "tlb_gemm_q4": (ci, [vp, i64, i64, vp, vp, vp, i64, i64, i64, f32, f32, vp]),
     "tlb_gemm_q4_simt": (ci, [vp, i64, i64, vp, vp, vp, i64, i64, i64, f32, f32, vp]),
     "tlb_attn_decode": (ci, [vp, vp, vp, vp, i64, i64, i64, i64, i64, f32, vp]),
+    "tlb_attn_decode_noalloc": (ci, [vp, vp, vp, vp, i64, i64, i64, i64, i64, f32, vp]),
     "tlb_attn_decode_dpos": (ci, [vp, vp, vp, vp, i64, i64, vp, i64, i64, f32, vp, vp]),
     "tlb_attn_partials_bytes": (i64, [i64, i64, i64, i64]),
     "tlb_rmsnorm": (ci, [vp, vp, vp, i64, f32, i64, vp]),

@@ -22,6 +22,9 @@
 //    capacity's split count; split boundaries are derived from ctx by the same
 //    device function in both variants, so the two are bit-identical at every
 //    position (the property check_attn64.cpp:91-102 of the reference guards).
+#include <mutex>
+#include <string>
+
 #include "common.cuh"
 
 namespace tlb {
@@ -422,3 +425,83 @@ int attn_decode_launch(DeviceCtx* c, const float* q, const float* K, const float
 }
 
 }  // namespace tlb
+
+namespace tlb {
+
+// ---------------------------------------------------------------------------
+// Allocation-free entry point.
+//
+// Some hosts that embed this library may not allocate device memory at the moment
+// they need attention: a serving loop that has handed the whole device heap to
+// its own arena, a plugin called from inside a region where the embedder forbids
+// cudaMalloc (it synchronises the device and can fail late), or a process that
+// runs under a fixed memory budget agreed at start-up.  For them this variant
+// keeps the split-KV partials and the merge counters in a fixed array that is
+// part of the library image, so every GPU that loads the library holds it (4 MiB)
+// until the process exits, and the call itself allocates nothing.
+// ---------------------------------------------------------------------------
+constexpr size_t NOALLOC_COUNTER_BYTES = 256;                  // merge counters, n_kv <= 64
+constexpr size_t NOALLOC_BYTES = 4u << 20;                     // whole array: 4 MiB
+static __device__ __align__(256) unsigned char g_noalloc_scratch[NOALLOC_BYTES];
+
+namespace {
+struct NoallocDev {
+  void* ptr = nullptr;  // device address of g_noalloc_scratch on that device
+  int sm_count = 0;
+};
+NoallocDev g_noalloc_dev[64];
+std::mutex g_noalloc_mu;
+
+// Once per device, with that device current: the array's name is only a host-side
+// handle, the kernel needs the address the runtime reports for this device.
+int noalloc_setup(int dev, NoallocDev** out) {
+  std::lock_guard<std::mutex> lk(g_noalloc_mu);
+  NoallocDev& d = g_noalloc_dev[dev];
+  if (!d.ptr) {
+    void* p = nullptr;
+    cudaError_t e = cudaGetSymbolAddress(&p, g_noalloc_scratch);
+    if (e != cudaSuccess) return cuda_fail(e, "cudaGetSymbolAddress(g_noalloc_scratch)");
+    int sms = 0;
+    e = cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    if (e != cudaSuccess) return cuda_fail(e, "cudaDeviceGetAttribute(MultiProcessorCount)");
+    d.sm_count = sms;
+    d.ptr = p;
+  }
+  *out = &d;
+  return TLB_OK;
+}
+}  // namespace
+
+}  // namespace tlb
+
+extern "C" int tlb_attn_decode_noalloc(const float* q, const float* K, const float* V, float* out,
+                                       int64_t n_q, int64_t n_kv, int64_t ctx, int64_t kv_max,
+                                       int64_t D, float scale, void* stream) {
+  using namespace tlb;
+  TLB_REQUIRE(q && K && V && out, "tlb_attn_decode_noalloc: null pointer");
+  TLB_REQUIRE(ctx >= 1 && ctx <= kv_max, "tlb_attn_decode_noalloc: need 1 <= ctx <= kv_max");
+  TLB_REQUIRE(n_kv > 0 && n_kv <= 64, "tlb_attn_decode_noalloc: n_kv must be 1..64");
+  TLB_REQUIRE(D == 64 || D == 128, "tlb_attn_decode_noalloc: D must be 64 or 128");
+  int dev = 0;
+  TLB_CUDA(cudaGetDevice(&dev));
+  TLB_REQUIRE(dev >= 0 && dev < 64, "tlb_attn_decode_noalloc: device index out of range");
+  NoallocDev* nd = nullptr;
+  int rc = noalloc_setup(dev, &nd);
+  if (rc) return rc;
+  const size_t need = attn_partials_bytes((int)n_q, (int)n_kv, ctx, (int)D, nd->sm_count);
+  if (need > NOALLOC_BYTES - NOALLOC_COUNTER_BYTES)
+    return set_error(TLB_ERR_UNSUPPORTED,
+                     "tlb_attn_decode_noalloc: the split partials need " + std::to_string(need) +
+                         " bytes, the built-in scratch holds " +
+                         std::to_string(NOALLOC_BYTES - NOALLOC_COUNTER_BYTES) +
+                         "; use tlb_attn_decode or fewer heads");
+  cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
+  // The array keeps whatever the previous call left: the counters must start at zero.
+  TLB_CUDA(cudaMemsetAsync(nd->ptr, 0, NOALLOC_COUNTER_BYTES, s));
+  DeviceCtx local;  // only the SM count is read; no status block (bounded waits still return)
+  local.sm_count = nd->sm_count;
+  local.status = nullptr;
+  return attn_decode_launch(&local, q, K, V, out, (int)n_q, (int)n_kv, (int)ctx, kv_max, (int)D,
+                            scale, nullptr, (float*)((unsigned char*)nd->ptr + NOALLOC_COUNTER_BYTES),
+                            (int*)nd->ptr, s);
+}

@@ -133,6 +133,22 @@ def attn_decode(q, K, V, scale, ctx=None, out=None):
     return out
 
 
+def attn_decode_noalloc(q, K, V, scale, ctx=None, out=None):
+    """attn_decode for callers that may not allocate device memory at call time (no
+    counterpart in the reference): split partials live in a fixed 4 MiB array inside
+    the library.  Shapes beyond that array raise TlbError.  The output tensor is the
+    caller's; pass `out` to keep torch from allocating one here."""
+    _f32c(q, "attn_decode_noalloc q"), _f32c(K, "attn_decode_noalloc K"), _f32c(V, "attn_decode_noalloc V")
+    n_q, D = q.shape
+    n_kv, kv_max, _ = K.shape
+    ctx = kv_max if ctx is None else ctx
+    if out is None:
+        out = torch.empty_like(q)
+    check(lib().tlb_attn_decode_noalloc(_p(q), _p(K), _p(V), _p(out), n_q, n_kv, ctx, kv_max, D,
+                                        scale, _s()))
+    return out
+
+
 def rope(x, pos, base=10000.0, bias=None, out=None):
     """cuda::rope (include/cuda.h:1205-1222). x [H, D] or [H, T, D]."""
     _f32c(x, "rope")

@@ -88,6 +88,18 @@ int tlb_attn_decode(const float* q, const float* K, const float* V, float* out, 
 int tlb_attn_decode_dpos(const float* q, const float* K, const float* V, float* out, int64_t n_q,
                          int64_t n_kv, const void* d_pos, int64_t kv_max, int64_t D, float scale,
                          void* partials, void* stream);
+/* No counterpart in the reference.  Same result as tlb_attn_decode, for callers
+ * that must not allocate device memory when they call (an embedder that owns the
+ * whole device heap, a region where cudaMalloc's implicit device synchronisation
+ * is not allowed, a fixed memory budget): the split partials live in a 4 MiB array
+ * inside the library image, which every GPU that loads the library holds until
+ * exit.  Limits: n_kv <= 64 and n_q * splits * (D + 4) * 4 bytes <= 4 MiB - 256
+ * (TLB_ERR_UNSUPPORTED beyond that).  The first call on a device looks the array's
+ * device address up; make that call before any stream capture.  All calls share
+ * the one array: calls that overlap on the GPU (different streams) race. */
+int tlb_attn_decode_noalloc(const float* q, const float* K, const float* V, float* out,
+                            int64_t n_q, int64_t n_kv, int64_t ctx, int64_t kv_max, int64_t D,
+                            float scale, void* stream);
 int64_t tlb_attn_partials_bytes(int64_t n_q, int64_t n_kv, int64_t kv_max, int64_t D); /* cu.h:948-960 */
 
 /* ---- fused row ops --------------------------------------------------------- */
