@@ -267,6 +267,7 @@ def main():
         torch.cuda.synchronize()
 
     # ---- device-resident greedy decoding: W warm-up tokens, then exactly K timed
+    barrier()
     dec.run(W)
     barrier()
     dec.set_pos(CTX0)

@@ -44,6 +44,9 @@ __device__ __forceinline__ bool wait_flag_bounded(const unsigned* p, unsigned wa
                                                   int where) {
   const long long t0 = clock64();
   while (ld_acquire_sys(p) != want) {
+    // once any wait has expired, later ones give up at once so a broken exchange
+    // costs one timeout, not one per all-reduce
+    if (status && *(volatile int*)&status[ST_WAIT_TIMEOUT]) return false;
     if (clock64() - t0 > 2000000000ll) {
       if (status) {
         atomicExch(&status[ST_WAIT_TIMEOUT], 1);

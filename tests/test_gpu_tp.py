@@ -1,0 +1,20 @@
+"""Tensor-parallel decoder on 2 GPUs (skipped on a single-GPU box): token ids and
+logits shards against the oracle, through the peer-memory exchange."""
+import os
+import subprocess
+import sys
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+HERE = os.path.dirname(os.path.abspath(__file__))
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
+def test_two_rank_decoder_matches_oracle():
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0")
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2",
+           "--master-addr", "127.0.0.1", "--master-port", "29611", os.path.join(HERE, "tp_worker.py")]
+    r = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=600)
+    assert "TP_OK" in r.stdout, r.stdout[-2000:] + r.stderr[-2000:]
