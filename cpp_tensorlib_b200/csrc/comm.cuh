@@ -1,17 +1,19 @@
 // Tensor-parallel exchange over NVLink peer memory (plain ld/st to peer-mapped
 // buffers; no multicast of any kind).
 //
-// One-shot all-reduce of a short f32 vector, split across two kernels so that the
-// transfer overlaps the producer's compute tile by tile:
-//   * the row-parallel GEMV stores every finished output tile straight into the
-//     staging buffer of EVERY rank (its own included) and, when the last of its
-//     warps is done, publishes a sequence number in every rank's flag word;
-//   * the following residual-add + RMSNorm kernel waits (bounded) for the flags
-//     of all ranks, sums the partials in rank order -- every rank adds the same
+// One-shot all-reduce of a short f32 vector, fused into its producer and its
+// consumer so the transfer overlaps the producer's compute tile by tile:
+//   * the row-parallel GEMV stores every finished output element straight into the
+//     staging buffer of EVERY rank (its own included) as an 8-byte packet
+//     {value bits, sequence number + 1}.  An aligned 8-byte store arrives whole, so
+//     the packet validates itself: no fence, no separate flag, no completion
+//     counter -- the exchange costs one NVLink store latency after the last tile;
+//   * the following residual-add + RMSNorm kernel polls (bounded) each packet until
+//     its tag matches, sums the partials in rank order -- every rank adds the same
 //     numbers in the same order, so the replicated residual streams stay
 //     bit-identical -- and continues into the norm.
 // Staging is double-buffered by the parity of the sequence number: a rank can
-// only be one all-reduce ahead of the slowest peer, because its next push waits
+// only be one exchange ahead of the slowest peer, because its next push waits
 // for its own reduce, which needs every peer's previous push.
 #pragma once
 
@@ -23,40 +25,42 @@ constexpr int TP_MAX = 8;
 
 struct CommDev {
   int rank = 0, size = 1;
-  int slot_floats = 0;            // floats per (parity, rank) slot
-  float* stage[TP_MAX] = {};      // stage[r]: rank r's staging [2][size][slot_floats]
-  unsigned* flags[TP_MAX] = {};   // flags[r]: rank r's flag words [2][size]
+  int slot_floats = 0;            // packets per (parity, rank) slot
+  uint2* stage[TP_MAX] = {};      // stage[r]: rank r's staging [2][size][slot_floats] packets
   unsigned* seq = nullptr;        // local: number of completed exchanges
-  unsigned* done = nullptr;       // local: arrival counter of the pushing kernel
 };
 
 #ifdef __CUDACC__
-__device__ __forceinline__ void st_release_sys(unsigned* p, unsigned v) {
-  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+__device__ __forceinline__ void st_packet_sys(uint2* p, float v, unsigned tag) {
+  asm volatile("st.relaxed.sys.global.v2.u32 [%0], {%1, %2};" ::"l"(p), "r"(__float_as_uint(v)),
+               "r"(tag)
+               : "memory");
 }
-__device__ __forceinline__ unsigned ld_acquire_sys(const unsigned* p) {
-  unsigned v;
-  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+__device__ __forceinline__ uint2 ld_packet_sys(const uint2* p) {
+  uint2 v;
+  asm volatile("ld.relaxed.sys.global.v2.u32 {%0, %1}, [%2];" : "=r"(v.x), "=r"(v.y) : "l"(p) : "memory");
   return v;
 }
-// Wait until *p == want, at most ~1 s; false (and the status block set) on timeout.
-__device__ __forceinline__ bool wait_flag_bounded(const unsigned* p, unsigned want, int* status,
-                                                  int where) {
+// Poll a packet until its tag matches, at most ~1 s; on timeout the status block
+// is set, later waits give up at once, and the (stale) payload is returned.
+__device__ __forceinline__ uint2 wait_packet_bounded(const uint2* p, unsigned tag, int* status,
+                                                     int where) {
+  uint2 v = ld_packet_sys(p);
+  if (v.y == tag) return v;
   const long long t0 = clock64();
-  while (ld_acquire_sys(p) != want) {
-    // once any wait has expired, later ones give up at once so a broken exchange
-    // costs one timeout, not one per all-reduce
-    if (status && *(volatile int*)&status[ST_WAIT_TIMEOUT]) return false;
+  while (true) {
+    v = ld_packet_sys(p);
+    if (v.y == tag) return v;
+    if (status && *(volatile int*)&status[ST_WAIT_TIMEOUT]) return v;
     if (clock64() - t0 > 2000000000ll) {
       if (status) {
         atomicExch(&status[ST_WAIT_TIMEOUT], 1);
         atomicExch(&status[ST_WAIT_WHERE], where);
       }
-      return false;
+      return v;
     }
     __nanosleep(20);
   }
-  return true;
 }
 #endif
 

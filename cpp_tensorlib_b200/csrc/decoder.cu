@@ -83,8 +83,8 @@ struct Decoder {
   int *h_tok = nullptr, *h_out = nullptr;  // pinned
   // tensor-parallel exchange
   CommDev comm;
-  float* stage_local = nullptr;
-  unsigned* flags_local = nullptr;
+  uint2* stage_local = nullptr;
+  unsigned* flags_local = nullptr;  // sequence counter
   void* peer_stage_base[TP_MAX] = {};
   void* peer_flags_base[TP_MAX] = {};
   bool peers_open = false;
@@ -223,15 +223,13 @@ int tlb_decoder_create(const int64_t* cfg, int n_cfg, float eps, float rope_base
   d->comm.rank = d->tp_rank;
   d->comm.size = d->tp_size;
   d->comm.slot_floats = (d->hidden + 3) & ~3;
-  const size_t sb = (size_t)2 * d->tp_size * d->comm.slot_floats * sizeof(float);
+  const size_t sb = (size_t)2 * d->tp_size * d->comm.slot_floats * sizeof(uint2);
   TLB_CUDA(cudaMalloc(&d->stage_local, sb));
   TLB_CUDA(cudaMemset(d->stage_local, 0, sb));
   TLB_CUDA(cudaMalloc(&d->flags_local, 256));
   TLB_CUDA(cudaMemset(d->flags_local, 0, 256));
   d->comm.stage[d->tp_rank] = d->stage_local;
-  d->comm.flags[d->tp_rank] = d->flags_local;
-  d->comm.seq = d->flags_local + 32;   // same allocation, words 32 and 33
-  d->comm.done = d->flags_local + 33;
+  d->comm.seq = d->flags_local;
   TLB_CUDA(cudaDeviceSynchronize());
   *out = d;
   return TLB_OK;
@@ -249,8 +247,9 @@ int tlb_decoder_destroy(void* h) {
         if (d->peer_flags_base[r]) cudaIpcCloseMemHandle(d->peer_flags_base[r]);
       }
   for (auto& L : d->layers) { cudaFree(L.Kc); cudaFree(L.Vc); }
-  float* bufs[] = {d->x, d->hb, d->qkv, d->att, d->t0, d->gu, d->mb, d->logits, d->stage_local};
+  float* bufs[] = {d->x, d->hb, d->qkv, d->att, d->t0, d->gu, d->mb, d->logits};
   for (float* b : bufs) cudaFree(b);
+  cudaFree(d->stage_local);
   cudaFree(d->attn_partials); cudaFree(d->d_pos); cudaFree(d->d_tok); cudaFree(d->flags_local);
   cudaFreeHost(d->h_tok);
   delete d;
@@ -421,8 +420,7 @@ int tlb_decoder_ipc_open(void* h, const void* records) {
     memcpy(&b, (const char*)records + (size_t)r * 128 + 64, 64);
     TLB_CUDA(cudaIpcOpenMemHandle(&d->peer_stage_base[r], a, cudaIpcMemLazyEnablePeerAccess));
     TLB_CUDA(cudaIpcOpenMemHandle(&d->peer_flags_base[r], b, cudaIpcMemLazyEnablePeerAccess));
-    d->comm.stage[r] = (float*)d->peer_stage_base[r];
-    d->comm.flags[r] = (unsigned*)d->peer_flags_base[r];
+    d->comm.stage[r] = (uint2*)d->peer_stage_base[r];
   }
   d->peers_open = true;
   return TLB_OK;

@@ -295,17 +295,22 @@ __global__ void add_rmsnorm_ar_kernel(const float* a, const float* __restrict__ 
   pdl_wait();
   pdl_launch_dependents();
   const unsigned seq = *(volatile unsigned*)comm.seq;
-  const unsigned par = seq & 1u;
-  if ((int)threadIdx.x < comm.size)
-    wait_flag_bounded(&comm.flags[comm.rank][par * comm.size + threadIdx.x], seq + 1u, status,
-                      300 + threadIdx.x);
-  __syncthreads();
-  const float* st = comm.stage[comm.rank] + (size_t)par * comm.size * comm.slot_floats;
+  const uint2* st = comm.stage[comm.rank] + (size_t)(seq & 1u) * comm.size * comm.slot_floats;
   float acc = 0.f;
   for (int i = threadIdx.x; i < n; i += blockDim.x) {
+    uint2 pk[TP_MAX];
+#pragma unroll
+    for (int r = 0; r < TP_MAX; r++)          // all polls in flight before the first check
+      if (r < comm.size) pk[r] = ld_packet_sys(&st[(size_t)r * comm.slot_floats + i]);
     float d = 0.f;
-    for (int r = 0; r < comm.size; r++) d += __ldcg(&st[(size_t)r * comm.slot_floats + i]);
-    float v = a[i] + d;
+#pragma unroll
+    for (int r = 0; r < TP_MAX; r++)
+      if (r < comm.size) {
+        if (pk[r].y != seq + 1u)
+          pk[r] = wait_packet_bounded(&st[(size_t)r * comm.slot_floats + i], seq + 1u, status, 300 + r);
+        d += __uint_as_float(pk[r].x);
+      }
+    const float v = a[i] + d;
     xout[i] = v;
     acc += v * v;
   }
@@ -317,7 +322,7 @@ __global__ void add_rmsnorm_ar_kernel(const float* a, const float* __restrict__ 
 
 // Vocabulary-parallel argmax: each rank reduces its logits shard to a packed key
 // (ordered float bits, inverted GLOBAL index), the last block pushes the key to
-// every rank, and argmax_finish_kernel takes the maximum over ranks.
+// every rank as two tagged packets, and argmax_finish_kernel takes the maximum.
 __global__ void argmax_push_kernel(const float* __restrict__ in, int n, unsigned vocab_offset,
                                    unsigned long long* cell, CommDev comm) {
   __shared__ unsigned long long sm[32];
@@ -350,10 +355,10 @@ __global__ void argmax_push_kernel(const float* __restrict__ in, int n, unsigned
       *(unsigned*)&cell[1] = 0u;
       const unsigned seq = *(volatile unsigned*)comm.seq;
       const size_t off = ((size_t)(seq & 1u) * comm.size + comm.rank) * (size_t)comm.slot_floats;
-      for (int r = 0; r < comm.size; r++) *(unsigned long long*)(comm.stage[r] + off) = k;
-      __threadfence_system();
-      for (int r = 0; r < comm.size; r++)
-        st_release_sys(&comm.flags[r][(seq & 1u) * comm.size + comm.rank], seq + 1u);
+      for (int r = 0; r < comm.size; r++) {
+        st_packet_sys(&comm.stage[r][off], __uint_as_float((unsigned)(k & 0xFFFFFFFFull)), seq + 1u);
+        st_packet_sys(&comm.stage[r][off + 1], __uint_as_float((unsigned)(k >> 32)), seq + 1u);
+      }
     }
   }
 }
@@ -361,17 +366,14 @@ __global__ void argmax_push_kernel(const float* __restrict__ in, int n, unsigned
 __global__ void argmax_finish_kernel(CommDev comm, int* out_idx, int* out_idx2, int* status) {
   pdl_wait();
   pdl_launch_dependents();
-  const unsigned seq = *(volatile unsigned*)comm.seq;
-  const unsigned par = seq & 1u;
-  if ((int)threadIdx.x < comm.size)
-    wait_flag_bounded(&comm.flags[comm.rank][par * comm.size + threadIdx.x], seq + 1u, status,
-                      400 + threadIdx.x);
-  __syncthreads();
   if (threadIdx.x == 0) {
-    const float* st = comm.stage[comm.rank] + (size_t)par * comm.size * comm.slot_floats;
+    const unsigned seq = *(volatile unsigned*)comm.seq;
+    const uint2* st = comm.stage[comm.rank] + (size_t)(seq & 1u) * comm.size * comm.slot_floats;
     unsigned long long best = 0ull;
     for (int r = 0; r < comm.size; r++) {
-      unsigned long long k = __ldcg((const unsigned long long*)(st + (size_t)r * comm.slot_floats));
+      const uint2 lo = wait_packet_bounded(&st[(size_t)r * comm.slot_floats], seq + 1u, status, 400 + r);
+      const uint2 hi = wait_packet_bounded(&st[(size_t)r * comm.slot_floats + 1], seq + 1u, status, 400 + r);
+      const unsigned long long k = ((unsigned long long)hi.x << 32) | lo.x;
       best = k > best ? k : best;
     }
     const int idx = (int)(0xFFFFFFFFu - (unsigned)(best & 0xFFFFFFFFull));

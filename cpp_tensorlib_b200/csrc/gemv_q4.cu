@@ -257,7 +257,7 @@ __global__ void __launch_bounds__(WARPS * 32, (WARPS == 8 ? 2 : 1))
   auto emit = [&](int m, int n, float v) {
     v = v * p.alpha + p.beta;
     if (p.push) {
-      for (int r = 0; r < p.comm.size; r++) p.comm.stage[r][ar_off + n] = v;
+      for (int r = 0; r < p.comm.size; r++) st_packet_sys(&p.comm.stage[r][ar_off + n], v, ar_seq + 1u);
     } else {
       p.y[(long long)m * p.ldy + n] = v;
     }
@@ -416,21 +416,6 @@ __global__ void __launch_bounds__(WARPS * 32, (WARPS == 8 ? 2 : 1))
   }
   if (n_units > 0 && s != 0) flush(rt);
 
-  // Tensor-parallel push: when the last worker of this rank has stored its tiles,
-  // publish the sequence number in every rank's flag word.
-  if (p.push && !idle) {
-    __threadfence_system();
-    __syncwarp();
-    if (lane == 0) {
-      const unsigned old = atomicAdd(p.comm.done, 1u);
-      if (old == Wtot - 1) {
-        *p.comm.done = 0u;
-        __threadfence_system();
-        for (int r = 0; r < p.comm.size; r++)
-          st_release_sys(&p.comm.flags[r][(ar_seq & 1u) * p.comm.size + p.comm.rank], ar_seq + 1u);
-      }
-    }
-  }
 }
 
 // ---------------------------------------------------------------------------
