@@ -20,6 +20,10 @@ int gemv_q4_launch(DeviceCtx* c, const CUtensorMap& tmW, const CUtensorMap& tmS,
 int gemv_q4_simt_launch(const float* x, long long ldx, int M, const void* qw, const void* scales,
                         float* y, long long ldy, int N, int K, float alpha, float beta,
                         cudaStream_t stream);
+bool gemm_q4_tc_eligible(const void* qw, const void* scales, int N, int K, int M);
+int gemm_q4_tc_launch(DeviceCtx* c, const float* x, long long ldx, int M, const void* qw,
+                      const float* scales, float* y, long long ldy, int N, int K, float alpha,
+                      float beta, float* xsplit, cudaStream_t stream);
 size_t attn_partials_bytes(int n_q, int n_kv, long long kv_max, int D, int sm_count);
 int attn_decode_launch(DeviceCtx* c, const float* q, const float* K, const float* V, float* out,
                        int n_q, int n_kv, int ctx, long long kv_max, int D, float scale,
@@ -218,6 +222,21 @@ int tlb_gemm_q4(const float* x, int64_t M, int64_t ldx, const void* qw, const fl
   TLB_REQUIRE(ldx >= K && ldy >= N, "tlb_gemm_q4: row strides shorter than the rows");
   if (M == 0 || N == 0) return TLB_OK;
   CTX(c);
+  // Many rows: tensor-core path (tcgen05, TMEM accumulator, exact tf32 hi/lo splits).
+  if (gemm_q4_tc_eligible(qw, scales, (int)N, (int)K, (int)M)) {
+    const size_t need = (size_t)2 * M * K * sizeof(float);
+    if (need > c->xsplit_bytes) {
+      // grown between launches only; not capturable at a size never seen before
+      TLB_CUDA(cudaDeviceSynchronize());
+      if (c->xsplit) TLB_CUDA(cudaFree(c->xsplit));
+      c->xsplit = nullptr;
+      c->xsplit_bytes = 0;
+      TLB_CUDA(cudaMalloc(&c->xsplit, need));
+      c->xsplit_bytes = need;
+    }
+    return gemm_q4_tc_launch(c, x, ldx, (int)M, qw, scales, y, ldy, (int)N, (int)K, alpha, beta,
+                             c->xsplit, S(stream));
+  }
   // Skinny activations: stream the weights once per block of up to 8 rows.
   if (gemv_q4_tma_eligible(qw, scales, (int)N, (int)K, 1)) {
     CUtensorMap tmW, tmS;

@@ -50,6 +50,9 @@ struct DeviceCtx {
   int* attn_counters = nullptr;  // [max kv-head*... ] zero between launches
   int attn_max_counters = 0;
   // argmax result cell (packed key) + small status block
+  // tf32 hi/lo planes of the activations for the tensor-core GEMM (grown on demand)
+  float* xsplit = nullptr;
+  size_t xsplit_bytes = 0;
   unsigned long long* argmax_cell = nullptr;
   int* status = nullptr;        // device, ST_WORDS ints
   int* status_host = nullptr;   // pinned mirror for reads
@@ -99,12 +102,16 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
       : "memory");
   return ok != 0;
 }
-// Bounded wait: gives up after `limit` polls, records where in the status block
-// and returns false; the caller must then skip the work that depended on it.
+// Bounded wait: gives up after about one second (clock64 at ~2 GHz), records where
+// in the status block and returns false; the caller must then skip the work that
+// depended on it.
 __device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, uint32_t parity, int* status,
-                                                  int where, uint32_t limit = 20000000u) {
-  for (uint32_t i = 0; i < limit; i++) {
+                                                  int where) {
+  if (mbar_try_wait(bar, parity)) return true;
+  const long long t0 = clock64();
+  while (true) {
     if (mbar_try_wait(bar, parity)) return true;
+    if (clock64() - t0 > 2000000000ll) break;
   }
   if (status) {
     atomicExch(&status[ST_WAIT_TIMEOUT], 1);

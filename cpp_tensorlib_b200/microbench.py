@@ -49,6 +49,7 @@ def gemv(a):
     nbytes = a.N * a.K * 0.625 + 4 * a.M * a.K + 4 * a.M * a.N
     print(json.dumps(dict(op="gemv_q4", N=a.N, K=a.K, M=a.M, us_per_launch=ms * 1e3,
                           algorithmic_bytes=nbytes, GBps=nbytes / ms / 1e6,
+                          TFLOPs=2.0 * a.M * a.N * a.K / ms / 1e9,
                           working_set_MB=a.copies * a.N * a.K * 0.625 / 1e6)))
 
 

@@ -149,6 +149,44 @@ def test_gemm_full_size_properties(tl):
     assert torch.equal(tl.gemm_q4(X, wq), Y)     # deterministic split-K fix-up
 
 
+@pytest.mark.parametrize("M,K,N", [(9, 128, 16), (16, 384, 200), (64, 3584, 256), (130, 1024, 300),
+                                   (300, 512, 128), (512, 896, 130)])
+def test_gemm_tensor_core_path_vs_oracle(tl, port, M, K, N):
+    """M > 8 runs on tcgen05 with a TMEM accumulator (tf32 hi/lo splits, three MMAs per
+    k-step): ragged M (not a multiple of 16, more than one 256-row pass), ragged N (not a
+    multiple of 128), K down to one raw stage -- against the oracle at 1e-4 and against the
+    independent CUDA-core kernel."""
+    x, w = synth.normal(65, M + K, (M, K)), synth.normal(66, N + K, (K, N), 0.05)
+    q4 = port.to_q4(w)
+    want = port.gemm_q4(x, q4, N, 0.5, 1.0)
+    wq = tl.Q4Weight.from_bytes(q4, K, N)
+    got = tl.gemm_q4(dev(x), wq, 0.5, 1.0).cpu().numpy()
+    assert np.allclose(got, want, rtol=1e-4, atol=1e-4), np.abs(got - want).max()
+    got2 = tl.gemm_q4(dev(x), wq, 0.5, 1.0, simt=True).cpu().numpy()
+    assert np.allclose(got, got2, rtol=1e-4, atol=1e-4)
+
+
+@pytest.mark.parametrize("M", [64, 512])
+def test_gemm_cfg4_tensor_core_full_size(tl, M):
+    """BASELINE config 4 at full size (N=18944, K=3584, alpha=0.5, beta=1.0), M = 64 and
+    512: 96 sampled output columns against the dequantised weights in float64 on the
+    device, the M=1 kernel on two rows, and run-to-run determinism."""
+    K, N = 3584, 18944
+    g = torch.Generator(device="cuda").manual_seed(3)
+    W = torch.randn((K, N), generator=g, device="cuda") * 0.02
+    wq = tl.to_q4(W)
+    X = torch.randn((M, K), generator=g, device="cuda")
+    Y = tl.gemm_q4(X, wq, 0.5, 1.0)
+    Wd = wq.to_f32()
+    cols = torch.arange(5, N, N // 96, device="cuda")
+    ref = ((X.double() @ Wd[:, cols].double()) * 0.5 + 1.0).float()
+    assert torch.allclose(Y[:, cols], ref, rtol=1e-4, atol=1e-4), (Y[:, cols] - ref).abs().max()
+    for m in (0, M - 1):
+        y1 = tl.gemm_q4(X[m:m + 1].contiguous(), wq, 0.5, 1.0)
+        assert torch.allclose(y1[0], Y[m], rtol=1e-4, atol=1e-4)
+    assert torch.equal(tl.gemm_q4(X, wq, 0.5, 1.0), Y)
+
+
 # ---------------------------------------------------------------- attention
 def test_attn_reference_test_case(tl, golden):
     q, K, V, sc = cases.ref_attn_case()
