@@ -16,7 +16,7 @@ bool gemv_q4_tma_eligible(const void* qw, const void* scales, int N, int K, int 
 int gemv_q4_launch(DeviceCtx* c, const CUtensorMap& tmW, const CUtensorMap& tmS, const float* x,
                    long long ldx, int M, float* y, long long ldy, int N, int K, float alpha,
                    float beta, cudaStream_t stream, int max_ctas, const CommDev* push_comm,
-                   int act);
+                   int act, const float* delta, const float* nw, float* xout, float eps);
 int gemv_q4_simt_launch(const float* x, long long ldx, int M, const void* qw, const void* scales,
                         float* y, long long ldy, int N, int K, float alpha, float beta,
                         cudaStream_t stream);
@@ -41,6 +41,7 @@ int launch_argmax(DeviceCtx*, const float*, int, int*, int*, cudaStream_t);
 int launch_to_q4(const float*, int, int, unsigned char*, cudaStream_t);
 int launch_q4_to_f32(const unsigned char*, int, int, float*, cudaStream_t);
 
+extern unsigned long long* g_gemv_dbg;
 static thread_local std::string g_err;
 static std::mutex g_mu;
 static std::map<int, DeviceCtx*> g_ctx;
@@ -163,6 +164,13 @@ int tlb_device_status(int* out2, int clear) {
   return c->status_host[ST_WAIT_TIMEOUT] ? TLB_ERR_DEVICE_WAIT : TLB_OK;
 }
 
+// Undocumented diagnostic hook: device buffer of [ctas][8] u64 that the GEMV fills
+// with %globaltimer stamps of its phases (NULL switches it off).
+int tlb_debug_gemv_timing(void* dbuf) {
+  g_gemv_dbg = (unsigned long long*)dbuf;
+  return TLB_OK;
+}
+
 int tlb_alloc(int64_t bytes, void** dptr) {
   TLB_REQUIRE(dptr && bytes >= 0, "tlb_alloc: bad arguments");
   TLB_CUDA(cudaMalloc(dptr, (size_t)(bytes > 0 ? bytes : 4)));
@@ -247,7 +255,7 @@ int tlb_gemm_q4(const float* x, int64_t M, int64_t ldx, const void* qw, const fl
       int mb = (int)((M - m0) < 8 ? (M - m0) : 8);
       while (mb > 1 && !gemv_q4_tma_eligible(qw, scales, (int)N, (int)K, mb)) mb = (mb + 1) / 2;
       rc = gemv_q4_launch(c, tmW, tmS, x + m0 * ldx, ldx, mb, y + m0 * ldy, ldy, (int)N, (int)K,
-                          alpha, beta, S(stream), 0, nullptr, 0);
+                          alpha, beta, S(stream), 0, nullptr, 0, nullptr, nullptr, nullptr, 0.f);
       if (rc) return rc;
       m0 += mb;
     }

@@ -28,7 +28,7 @@ bool gemv_q4_tma_eligible(const void* qw, const void* scales, int N, int K, int 
 int gemv_q4_launch(DeviceCtx* c, const CUtensorMap& tmW, const CUtensorMap& tmS, const float* x,
                    long long ldx, int M, float* y, long long ldy, int N, int K, float alpha,
                    float beta, cudaStream_t stream, int max_ctas, const CommDev* push_comm,
-                   int act);
+                   int act, const float* delta, const float* nw, float* xout, float eps);
 int gemv_q4_simt_launch(const float* x, long long ldx, int M, const void* qw, const void* scales,
                         float* y, long long ldy, int N, int K, float alpha, float beta,
                         cudaStream_t stream);
@@ -74,8 +74,8 @@ struct Decoder {
   Linear lm_head;
   const float *embed = nullptr, *onorm = nullptr;
   // scratch
-  float *x = nullptr, *hb = nullptr, *qkv = nullptr, *att = nullptr, *t0 = nullptr, *gu = nullptr,
-        *mb = nullptr, *logits = nullptr;
+  float *x = nullptr, *xb = nullptr, *hb = nullptr, *qkv = nullptr, *att = nullptr, *t0 = nullptr,
+        *t1 = nullptr, *gu = nullptr, *mb = nullptr, *logits = nullptr;
   void* attn_partials = nullptr;
   unsigned* d_pos = nullptr;
   int* d_tok = nullptr;      // token consumed by the next forward; overwritten with the result
@@ -102,12 +102,24 @@ static int set_linear(Linear& L, const void* q4, int K, int N) {
   return TLB_OK;
 }
 
+// Fused residual add + RMSNorm in front of a linear: input = rmsnorm(x + delta) * w,
+// and x + delta is also written to xout (the next residual base).
+struct NormIn {
+  const float* delta;
+  const float* w;
+  float* xout;
+};
+
 static int run_linear(DeviceCtx* c, const Linear& L, const float* x, float* y, cudaStream_t s,
-                      const CommDev* push, int act = 0) {
+                      const CommDev* push, int act = 0, const NormIn* nm = nullptr, float eps = 0.f) {
   if (!L.q4) return set_error(TLB_ERR_STATE, "decoder: a linear weight was never set");
+  if (L.tma && nm)
+    return gemv_q4_launch(c, L.tmW, L.tmS, x, L.K, 1, y, L.N, L.N, L.K, 1.0f, 0.0f, s, 0, push, 2,
+                          nm->delta, nm->w, nm->xout, eps);
+  if (nm) return set_error(TLB_ERR_UNSUPPORTED, "decoder: the fused add+rmsnorm needs K % 128 == 0");
   if (L.tma)
     return gemv_q4_launch(c, L.tmW, L.tmS, x, act ? 2 * L.K : L.K, 1, y, L.N, L.N, L.K, 1.0f, 0.0f,
-                          s, 0, push, act);
+                          s, 0, push, act, nullptr, nullptr, nullptr, 0.f);
   if (act) return set_error(TLB_ERR_UNSUPPORTED, "decoder: the fused SwiGLU needs ff % 128 == 0");
   if (push) return set_error(TLB_ERR_UNSUPPORTED, "decoder: tensor-parallel linears need K % 128 == 0");
   return gemv_q4_simt_launch(x, L.K, 1, L.q4, L.scales(), y, L.N, L.N, L.K, 1.0f, 0.0f, s);
@@ -129,6 +141,42 @@ static int forward(Decoder* d, cudaStream_t s) {
   if (!d->embed || !d->onorm) return set_error(TLB_ERR_STATE, "decoder: embed / final norm not set");
   RUN(launch_embed_gather(d->embed, d->d_tok, d->x, E, s));
   RUN(launch_rmsnorm(d->x, d->layers[0].an, d->hb, E, d->eps, 1, s));
+  bool all_tma = d->lm_head.tma;
+  for (auto& L : d->layers) all_tma = all_tma && L.wqkv.tma && L.wo.tma && L.wgu.tma && L.wd.tma;
+  if (!tp && all_tma) {
+    // Single GPU, every linear on the TMA path: both residual adds and norms of a
+    // layer run inside the following projection's activation prep (6 launches per
+    // layer instead of 8).  The residual ping-pongs between two buffers because
+    // every CTA of the projection reads it while one CTA writes the new sum.
+    float* x = d->x;
+    float* xalt = d->xb;
+    for (int l = 0; l < d->n_layers; l++) {
+      DecLayer& L = d->layers[l];
+      if (l == 0) {
+        RUN(run_linear(c, L.wqkv, d->hb, d->qkv, s, nullptr));
+      } else {
+        NormIn nm{d->t1, L.an, xalt};
+        RUN(run_linear(c, L.wqkv, x, d->qkv, s, nullptr, 0, &nm, d->eps));
+        float* t = x; x = xalt; xalt = t;
+      }
+      RUN(launch_qkv_post(d->qkv, L.bq, L.bk, L.bv, L.Kc, L.Vc, d->n_q, d->n_kv, d->hd, d->d_pos,
+                          d->max_ctx, d->rope_base, s));
+      RUN(attn_decode_launch(c, d->qkv, L.Kc, L.Vc, d->att, d->n_q, d->n_kv, 0, d->max_ctx, d->hd,
+                             d->scale, d->d_pos, (float*)((char*)d->attn_partials + 256),
+                             (int*)d->attn_partials, s));
+      RUN(run_linear(c, L.wo, d->att, d->t0, s, nullptr));
+      NormIn nf{d->t0, L.fn, xalt};
+      RUN(run_linear(c, L.wgu, x, d->gu, s, nullptr, 0, &nf, d->eps));
+      { float* t = x; x = xalt; xalt = t; }
+      RUN(run_linear(c, L.wd, d->gu, d->t1, s, nullptr, 1));
+    }
+    NormIn no{d->t1, d->onorm, xalt};
+    RUN(run_linear(c, d->lm_head, x, d->logits, s, nullptr, 0, &no, d->eps));
+    RUN(launch_argmax(c, d->logits, d->vocab, d->d_tok, d->d_tok_out, s));
+    RUN(launch_incr_u32(d->d_pos, s));
+    d->launches_per_token = n;
+    return TLB_OK;
+  }
   for (int l = 0; l < d->n_layers; l++) {
     DecLayer& L = d->layers[l];
     RUN(run_linear(c, L.wqkv, d->hb, d->qkv, s, nullptr));
@@ -202,6 +250,8 @@ int tlb_decoder_create(const int64_t* cfg, int n_cfg, float eps, float rope_base
   }
   auto fa = [&](float** p, size_t n) { return cudaMalloc(p, n * sizeof(float)); };
   TLB_CUDA(fa(&d->x, d->hidden));
+  TLB_CUDA(fa(&d->xb, d->hidden));
+  TLB_CUDA(fa(&d->t1, d->hidden));
   TLB_CUDA(fa(&d->hb, d->hidden));
   TLB_CUDA(fa(&d->qkv, (size_t)(d->n_q + 2 * d->n_kv) * d->hd));
   TLB_CUDA(fa(&d->att, (size_t)d->n_q * d->hd));
@@ -247,7 +297,7 @@ int tlb_decoder_destroy(void* h) {
         if (d->peer_flags_base[r]) cudaIpcCloseMemHandle(d->peer_flags_base[r]);
       }
   for (auto& L : d->layers) { cudaFree(L.Kc); cudaFree(L.Vc); }
-  float* bufs[] = {d->x, d->hb, d->qkv, d->att, d->t0, d->gu, d->mb, d->logits};
+  float* bufs[] = {d->x, d->xb, d->t1, d->hb, d->qkv, d->att, d->t0, d->gu, d->mb, d->logits};
   for (float* b : bufs) cudaFree(b);
   cudaFree(d->stage_local);
   cudaFree(d->attn_partials); cudaFree(d->d_pos); cudaFree(d->d_tok); cudaFree(d->flags_local);

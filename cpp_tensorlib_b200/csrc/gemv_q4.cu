@@ -47,7 +47,13 @@ struct GemvParams {
   int RT, SL;       // row tiles (16 rows), k slabs (256 k)
   unsigned U;       // RT * SL
   int x_vec_ok;     // x rows are 16-byte aligned
-  int act;          // 0: x as given; 1: x row = [gate(K) | up(K)], activation silu(gate)*up
+  int act;          // 0: x as given; 1: x row = [gate(K) | up(K)], activation silu(gate)*up;
+                    // 2: x = rmsnorm(x + delta) * nw (M == 1), the sum also written to xout
+  const float* delta;
+  const float* nw;
+  float* xout;
+  float eps;
+  unsigned long long* dbg;  // optional phase timestamps (diagnostics), [grid][8]
   int push;         // tensor-parallel: store y (M == 1) into every rank's staging slot
   CommDev comm;
 };
@@ -94,7 +100,7 @@ __device__ __forceinline__ unsigned pack_h2(__half a, __half b) {
 
 // Shared-memory carve-up (host and device agree through this one function).
 struct GemvSmem {
-  size_t w_ring, s_ring, bars, pslab, q, bfrag, total;
+  size_t w_ring, s_ring, bars, red, pslab, q, bfrag, total;
 };
 __host__ __device__ inline GemvSmem gemv_smem_layout(int warps, int stages, int M, int K) {
   const int SL = (K + 255) / 256, G = SL * 8;
@@ -104,6 +110,7 @@ __host__ __device__ inline GemvSmem gemv_smem_layout(int warps, int stages, int 
   L.s_ring = o; o += (size_t)warps * stages * GV_S_BYTES;
   L.bars = o;   o += (size_t)warps * stages * 8;
   o = (o + 15) & ~(size_t)15;
+  L.red = o;    o += 64 * sizeof(float);
   L.pslab = o;  o += (size_t)GV_MAXM * SL * sizeof(float);
   o = (o + 15) & ~(size_t)15;
   L.q = o;      o += (size_t)GV_MAXM * G * sizeof(float);
@@ -128,6 +135,14 @@ __global__ void __launch_bounds__(WARPS * 32, (WARPS == 8 ? 2 : 1))
   const int SL = p.SL, G = SL * 8;
   const int NCU = 2 * p.M;
   const GemvSmem L = gemv_smem_layout(WARPS, STAGES, p.M, p.K);
+  auto stamp = [&](int i) {
+    if (p.dbg && tid == 0) {
+      unsigned long long t;
+      asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+      p.dbg[(size_t)blockIdx.x * 8 + i] = t;
+    }
+  };
+  stamp(0);
 
   uint64_t* bars = (uint64_t*)(base + L.bars);
   float* Pslab = (float*)(base + L.pslab);   // [m][SL]   2^(12+e) of the slab
@@ -166,79 +181,138 @@ __global__ void __launch_bounds__(WARPS * 32, (WARPS == 8 ? 2 : 1))
     if (++is == SL) { is = 0; irt++; }
     if (++istage == STAGES) istage = 0;
   };
-  // Weights do not depend on the previous kernel: start streaming them before
-  // waiting for it.
-  {
-    const int pre = n_units < STAGES ? n_units : STAGES;
-    for (int i = 0; i < pre; i++) issue_next();
-  }
+  // Weights do not depend on the previous kernel: the first stage streams before the
+  // wait.  The other stages are issued right AFTER the activation loads below, so
+  // those small loads are not queued behind ~100 KB of weight traffic per SM.
+  const int pre_total = n_units < STAGES ? n_units : STAGES;
+  if (pre_total > 0) issue_next();
 
   pdl_wait();  // activations and the fix-up scratch are valid from here
+  stamp(1);
 
   // ---- activation prep.  One warp per (row m, slab of 256 k): power-of-two
   // normalisation by the slab's max (no block-wide reduction), exact fp16 hi/lo
   // split, B-fragment order.  Lane l covers x[m][256*slab + 8*l .. +8) = group
   // jj = l/4, quad slot tt = l%4.
-  for (int job = warp; job < p.M * SL; job += WARPS) {
-    const int m = job / SL, sl = job - m * SL;
-    const int k0 = sl * 256 + lane * 8;
-    const float* xr = p.x + (long long)m * p.ldx + k0;
-    float v[8];
-    auto load8 = [&](const float* src, float (&o)[8]) {
-      if (k0 + 8 <= p.K) {
-        if (p.x_vec_ok) {
-          const float4 a = *(const float4*)src, b = *(const float4*)(src + 4);
-          o[0] = a.x; o[1] = a.y; o[2] = a.z; o[3] = a.w;
-          o[4] = b.x; o[5] = b.y; o[6] = b.z; o[7] = b.w;
+  float nrm_inv = 1.f;
+  // Jobs are taken four at a time: all global loads of a batch are issued before any
+  // of it is processed, so a warp pays the load latency once per batch, not per job.
+  constexpr int PB = 4;
+  const int n_jobs = p.M * SL;
+  // (the first pass runs in every warp, also one without jobs: it issues the rest of
+  // the warp's weight ring and takes part in the block reduction of the fused norm)
+  for (int job0 = warp; job0 < n_jobs || job0 == warp; job0 += WARPS * PB) {
+    float vv[PB][8], uu[PB][8];
+#pragma unroll
+    for (int b = 0; b < PB; b++) {
+      const int job = job0 + b * WARPS;
+      const bool on = job < n_jobs;
+      const int m = on ? job / SL : 0, sl = on ? job - m * SL : 0;
+      const int k0 = sl * 256 + lane * 8;
+      const float* xr = p.x + (long long)m * p.ldx + k0;
+      auto load8 = [&](const float* src, float (&o)[8]) {
+        if (on && k0 + 8 <= p.K) {
+          if (p.x_vec_ok) {
+            const float4 q0 = *(const float4*)src, q1 = *(const float4*)(src + 4);
+            o[0] = q0.x; o[1] = q0.y; o[2] = q0.z; o[3] = q0.w;
+            o[4] = q1.x; o[5] = q1.y; o[6] = q1.z; o[7] = q1.w;
+          } else {
+#pragma unroll
+            for (int i = 0; i < 8; i++) o[i] = src[i];
+          }
         } else {
 #pragma unroll
-          for (int i = 0; i < 8; i++) o[i] = src[i];
+          for (int i = 0; i < 8; i++) o[i] = (on && k0 + i < p.K) ? src[i] : 0.f;
         }
-      } else {
+      };
+      load8(xr, vv[b]);
+      if (p.act == 1) load8(xr + p.K, uu[b]);
+      if (p.act == 2) load8(p.delta + k0, uu[b]);
+    }
+    if (job0 == warp) {
+      // first batch: its loads are in flight, now queue the rest of the weight ring
+      for (int i = 1; i < pre_total; i++) issue_next();
+      stamp(6);
+      if (p.act == 2) {
+        // fused residual add + RMSNorm (tl_add_rmsnorm, kernels/tensorlib_cuda.cu:155-179):
+        // every CTA reduces sum((x+delta)^2) itself from the values it just loaded, in
+        // the same order everywhere, so all CTAs agree on the scale.  (The host only
+        // selects this mode when one batch covers the row.)
+        float* red = (float*)(base + L.red);
+        float sq = 0.f;
 #pragma unroll
-        for (int i = 0; i < 8; i++) o[i] = (k0 + i < p.K) ? src[i] : 0.f;
+        for (int b = 0; b < PB; b++)
+#pragma unroll
+          for (int i = 0; i < 8; i++) {
+            const float sv = vv[b][i] + uu[b][i];   // zero where the job or k is out of range
+            sq = fmaf(sv, sv, sq);
+          }
+        sq = warp_sum(sq);
+        if (lane == 0) red[warp] = sq;
+        __syncthreads();
+        float tot = 0.f;
+        for (int w = 0; w < WARPS; w++) tot += red[w];
+        nrm_inv = 1.0f / sqrtf(tot / (float)p.K + p.eps);
       }
-    };
-    load8(xr, v);
-    if (p.act == 1) {
-      // fused SwiGLU (kernels/tensorlib_cuda.cu:185-192 of the reference): the row
-      // holds gate then up; same expression g / (1 + exp(-g)) * u
-      float u[8];
-      load8(xr + p.K, u);
-#pragma unroll
-      for (int i = 0; i < 8; i++) v[i] = (v[i] / (1.0f + expf(-v[i]))) * u[i];
     }
-    float mx = 0.f;
 #pragma unroll
-    for (int i = 0; i < 8; i++) mx = fmaxf(mx, fabsf(v[i]));
-    mx = warp_max(mx);
-    int e = (int)((__float_as_uint(mx) >> 23) & 0xff) - 126;  // mx < 2^e
-    e = mx > 0.f ? (e < -100 ? -100 : (e > 100 ? 100 : e)) : 0;
-    const float s12 = __uint_as_float((unsigned)(127 + 12 - e) << 23);
-    const float s8 = __uint_as_float((unsigned)(127 + 8 - e) << 23);
-    float sum = ((v[0] + v[1]) + (v[2] + v[3])) + ((v[4] + v[5]) + (v[6] + v[7]));
-    sum += __shfl_xor_sync(0xffffffffu, sum, 1);
-    sum += __shfl_xor_sync(0xffffffffu, sum, 2);
-    __half hi[8], lo[8];
+    for (int b = 0; b < PB; b++) {
+      const int job = job0 + b * WARPS;
+      if (job >= n_jobs) break;  // warp-uniform
+      const int m = job / SL, sl = job - m * SL;
+      float v[8];
 #pragma unroll
-    for (int i = 0; i < 8; i++) {
-      const float f = v[i] * ((i & 1) ? s8 : s12);
-      hi[i] = __float2half_rn(f);
-      lo[i] = __float2half_rn(f - __half2float(hi[i]));
+      for (int i = 0; i < 8; i++) v[i] = vv[b][i];
+      if (p.act == 1) {
+        // fused SwiGLU (kernels/tensorlib_cuda.cu:185-192 of the reference): the row
+        // holds gate then up; same expression g / (1 + exp(-g)) * u
+#pragma unroll
+        for (int i = 0; i < 8; i++) v[i] = (v[i] / (1.0f + expf(-v[i]))) * uu[b][i];
+      }
+      if (p.act == 2) {
+        const int k0 = sl * 256 + lane * 8;
+#pragma unroll
+        for (int i = 0; i < 8; i++) {
+          const float sv = v[i] + uu[b][i];
+          const bool in = k0 + i < p.K;
+          if (in && blockIdx.x == 0) p.xout[k0 + i] = sv;
+          v[i] = in ? sv * nrm_inv * p.nw[k0 + i] : 0.f;
+        }
+      }
+      float mx = 0.f;
+#pragma unroll
+      for (int i = 0; i < 8; i++) mx = fmaxf(mx, fabsf(v[i]));
+      mx = warp_max(mx);
+      int e = (int)((__float_as_uint(mx) >> 23) & 0xff) - 126;  // mx < 2^e
+      e = mx > 0.f ? (e < -100 ? -100 : (e > 100 ? 100 : e)) : 0;
+      const float s12 = __uint_as_float((unsigned)(127 + 12 - e) << 23);
+      const float s8 = __uint_as_float((unsigned)(127 + 8 - e) << 23);
+      float sum = ((v[0] + v[1]) + (v[2] + v[3])) + ((v[4] + v[5]) + (v[6] + v[7]));
+      sum += __shfl_xor_sync(0xffffffffu, sum, 1);
+      sum += __shfl_xor_sync(0xffffffffu, sum, 2);
+      __half hi[8], lo[8];
+#pragma unroll
+      for (int i = 0; i < 8; i++) {
+        const float f = v[i] * ((i & 1) ? s8 : s12);
+        hi[i] = __float2half_rn(f);
+        lo[i] = __float2half_rn(f - __half2float(hi[i]));
+      }
+      uint4 fh, fl;
+      fh.x = pack_h2(hi[0], hi[4]); fh.y = pack_h2(hi[1], hi[5]);
+      fh.z = pack_h2(hi[2], hi[6]); fh.w = pack_h2(hi[3], hi[7]);
+      fl.x = pack_h2(lo[0], lo[4]); fl.y = pack_h2(lo[1], lo[5]);
+      fl.z = pack_h2(lo[2], lo[6]); fl.w = pack_h2(lo[3], lo[7]);
+      const int j = sl * 8 + (lane >> 2), tt = lane & 3;
+      Bfrag[((size_t)j * NCU + 2 * m) * 4 + tt] = fh;
+      Bfrag[((size_t)j * NCU + 2 * m + 1) * 4 + tt] = fl;
+      if (tt == 0) Qg[(size_t)m * G + j] = 8.0f * sum;
+      if (lane == 0) Pslab[m * SL + sl] = __uint_as_float((unsigned)(127 + 12 + e) << 23);
     }
-    uint4 fh, fl;
-    fh.x = pack_h2(hi[0], hi[4]); fh.y = pack_h2(hi[1], hi[5]);
-    fh.z = pack_h2(hi[2], hi[6]); fh.w = pack_h2(hi[3], hi[7]);
-    fl.x = pack_h2(lo[0], lo[4]); fl.y = pack_h2(lo[1], lo[5]);
-    fl.z = pack_h2(lo[2], lo[6]); fl.w = pack_h2(lo[3], lo[7]);
-    const int j = sl * 8 + (lane >> 2), tt = lane & 3;
-    Bfrag[((size_t)j * NCU + 2 * m) * 4 + tt] = fh;
-    Bfrag[((size_t)j * NCU + 2 * m + 1) * 4 + tt] = fl;
-    if (tt == 0) Qg[(size_t)m * G + j] = 8.0f * sum;
-    if (lane == 0) Pslab[m * SL + sl] = __uint_as_float((unsigned)(127 + 12 + e) << 23);
   }
+  stamp(7);
   __syncthreads();
   pdl_launch_dependents();
+  stamp(2);
 
   // ---- streaming loop ------------------------------------------------------
   float acc[NT][2], corr[NT][2];
@@ -351,6 +425,7 @@ __global__ void __launch_bounds__(WARPS * 32, (WARPS == 8 ? 2 : 1))
   unsigned phase = 0;
   for (int i = 0; i < n_units; i++) {
     if (!mbar_wait_bounded(&mybar[st], phase, p.status, 100 + st)) return;
+    if (i == 0) stamp(3);
     const unsigned* Wst = (const unsigned*)(myW + st * GV_W_BYTES);
     const float* Sst = (const float*)(myS + st * GV_S_BYTES);
     const uint4* Bu = Bfrag + (size_t)(s * 8) * NCU * 4;
@@ -414,7 +489,9 @@ __global__ void __launch_bounds__(WARPS * 32, (WARPS == 8 ? 2 : 1))
       rt++;
     }
   }
+  stamp(4);
   if (n_units > 0 && s != 0) flush(rt);
+  stamp(5);
 
 }
 
@@ -507,13 +584,22 @@ static int gemv_launch_t(const CUtensorMap& tmW, const CUtensorMap& tmS, const G
   return TLB_OK;
 }
 
+// Diagnostics: when set, every launch records per-CTA phase timestamps there.
+unsigned long long* g_gemv_dbg = nullptr;
+
 // Launch with ready tensor maps (the decoder caches them per weight).
 int gemv_q4_launch(DeviceCtx* c, const CUtensorMap& tmW, const CUtensorMap& tmS, const float* x,
                    long long ldx, int M, float* y, long long ldy, int N, int K, float alpha,
                    float beta, cudaStream_t stream, int max_ctas, const CommDev* push_comm,
-                   int act) {
+                   int act, const float* delta, const float* nw, float* xout, float eps) {
   GemvParams p;
   p.act = act;
+  p.delta = delta; p.nw = nw; p.xout = xout; p.eps = eps;
+  p.dbg = g_gemv_dbg;
+  if (act == 2 && (M != 1 || !delta || !nw || !xout))
+    return set_error(TLB_ERR_ARG, "gemv_q4: fused add+rmsnorm needs M == 1 and its three buffers");
+  if (act == 2 && (K + 255) / 256 > 8 * 4)
+    return set_error(TLB_ERR_UNSUPPORTED, "gemv_q4: fused add+rmsnorm needs K <= 8192");
   p.push = push_comm ? 1 : 0;
   if (push_comm) {
     if (M != 1) return set_error(TLB_ERR_ARG, "gemv_q4: the tensor-parallel push needs M == 1");

@@ -50,8 +50,43 @@ def build_reference(force=False):
     return out
 
 
+# The reference's OWN test / check programs, compiled unmodified against this
+# repository's seam headers (include/gpu.h, include/cuda.h shadow the reference's
+# by include order) so they exercise libtlb200.so through tl::use_gpu().
+REFERENCE_CHECKS = {
+    "ref_test_array": ["test/test_array.cpp", "test/test_basic.cpp"],
+    "ref_check_llm_decode": ["bench/cuda/check/check_llm_decode.cpp"],
+    "ref_check_llm_block": ["bench/shared/check/check_llm_block.cpp"],
+    "ref_check_attn64": ["bench/cuda/check/check_attn64.cpp"],
+    "ref_bench_q4_gemv": ["bench/cuda/speed/bench_q4_gemv.cpp"],
+}
+
+
+def build_reference_checks(force=False):
+    inc = os.path.join(REF_DIR, "include")
+    if not os.path.isfile(os.path.join(inc, "tensorlib.h")):
+        return []
+    seam = os.path.join(HERE, "..", "include")
+    out_dir = os.path.join(HERE, "_ref")
+    os.makedirs(out_dir, exist_ok=True)
+    deps = [os.path.join(seam, "cuda.h"), os.path.join(seam, "gpu.h")]
+    built, procs = [], []
+    for name, srcs in REFERENCE_CHECKS.items():
+        out = os.path.join(out_dir, name)
+        paths = [os.path.join(REF_DIR, s) for s in srcs]
+        built.append(out)
+        if force or _stale(out, paths + deps):
+            procs.append(subprocess.Popen(
+                ["g++", "-std=c++17", "-O2", "-DTENSORLIB_CUDA", "-I", seam, "-I", inc,
+                 "-I", os.path.join(REF_DIR, "test")] + paths + ["-o", out, "-ldl", "-lpthread"]))
+    for p in procs:
+        if p.wait():
+            raise RuntimeError("compiling a reference check against the seam headers failed")
+    return built
+
+
 def build_all(force=False):
-    return build_port(force), build_reference(force)
+    return build_port(force), build_reference(force), build_reference_checks(force)
 
 
 if __name__ == "__main__":
