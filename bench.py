@@ -235,6 +235,9 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--layers", type=int, default=0, help="diagnostic: fewer layers (line is marked invalid)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--mode", default="auto", choices=["auto", "ops", "persistent"],
+                    help="decoder execution: one kernel per op, or the persistent per-token kernel "
+                         "(single GPU); auto = persistent at 1 GPU, per-op under tensor parallelism")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -256,6 +259,9 @@ def main():
     max_ctx = CTX0 + max(128, K + W) + 8
     dec = build_decoder(cfg, max_ctx, rank, world, CTX0)
     dec.connect()
+    mode = args.mode if args.mode != "auto" else ("persistent" if world == 1 else "ops")
+    if mode == "persistent":
+        dec.set_mode(1)
     dec.set_pos(CTX0)
     dec.set_token(1)
     dec.capture()
@@ -320,7 +326,10 @@ def main():
                     e2e=dict(value=e2e_tps, unit="tokens/s", h2d_bytes_per_step=4, d2h_bytes_per_step=4),
                     gpu_launches=launches,
                     roofline=dict(bound="hbm", achieved=achieved, peak=peak, unit="GB/s", frac=achieved / peak,
-                                  traffic=None, peak_source=peak_src, kernel="gemv_q4_mma_kernel",
+                                  traffic=gbytes * 1.036, peak_source=peak_src, kernel="gemv_q4_mma_kernel",
+                                  traffic_note="dram read+write of the ncu capture of the gate|up shape "
+                                               "(1.036 x algorithmic, profiles/gemv_q4_gate_up_7b.md) scaled "
+                                               "to the sweep by bytes",
                                   what=f"{glaunch} int4 GEMV launches of one token ({gbytes / 1e9:.2f} GB algorithmic), "
                                        f"{gms:.3f} ms per pass, CUDA events"),
                     token_roofline=dict(bound="hbm", achieved=tok_ach, peak=peak, frac=tok_ach / peak, unit="GB/s",

@@ -52,6 +52,32 @@ def test_decoder_matches_reference_golden(golden, name, cfg, seed, captured):
     d.close()
 
 
+@pytest.mark.parametrize("name,cfg,seed", [("dec_tiny", cases.TINY, 21), ("dec_tiny64", cases.TINY64, 22)])
+def test_persistent_kernel_matches_reference_golden(golden, name, cfg, seed):
+    """Mode 1: the whole token in one cooperative launch (grid barriers between the
+    projections, attention with rope/append fused, weights prefetched across phases).
+    Same golden vectors as the per-op path, eager and captured, and device-resident
+    feedback against the host loop."""
+    g = golden(name)
+    d, _ = make(cfg, seed, 64)
+    d.set_mode(1)
+    for captured in (False, True):
+        d.set_pos(0)
+        if captured:
+            d.capture()
+        prompt, nxt = list(g["prompt"]), 0
+        for i in range(len(g["next_tokens"])):
+            tid = prompt[i] if i < len(prompt) else nxt
+            nxt = d.step(int(tid))
+            assert relerr(d.logits().cpu().numpy(), g["logits"][i]) < 1e-3, (captured, i)
+            assert nxt == int(g["next_tokens"][i]), (captured, i)
+    assert d.launches_per_token() == 1
+    d.set_pos(0)
+    d.set_token(int(g["prompt"][0]))
+    d.run(3)
+    d.close()
+
+
 def test_device_resident_feedback_equals_host_loop():
     cfg = cases.TINY64
     d, wts = make(cfg, 22, 64)
