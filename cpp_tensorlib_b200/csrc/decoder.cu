@@ -15,6 +15,7 @@
 // down): the row-parallel GEMVs push their partial outputs to every rank and the
 // following add+rmsnorm reduces them (comm.cuh); the lm_head shards exchange
 // their local argmax keys.  Each rank is one process on one GPU.
+#include <cstdlib>
 #include <cstring>
 #include <vector>
 
@@ -22,6 +23,8 @@
 #include "token_kernel.cuh"
 
 namespace tlb {
+
+extern unsigned long long* g_gemv_dbg;
 
 int make_q4_tensor_maps(const void* qw, const void* scales, int N, int K, CUtensorMap* tmW,
                         CUtensorMap* tmS);
@@ -155,6 +158,8 @@ static int build_token_table(Decoder* d, DeviceCtx* c) {
     h.U = (unsigned)h.RT * (unsigned)h.SL;
     h.Wtot = W < h.U ? W : h.U;
     h.q = h.U / h.Wtot; h.r = h.U % h.Wtot;
+    // fewer row tiles than warps: let CTAs own tiles and split K across their warps
+    h.cta_tiles = ((unsigned)h.RT < W && h.SL <= 2 * TK_WARPS) ? 1 : 0;
     h.act = act; h.argmax = argmax; h.map = (int)maps.size() / 2; h.x_from_embed = from_embed;
     h.x = x; h.delta = delta; h.nw = nw; h.xout = xout; h.y = y;
     maps.push_back(Lw.tmW);
@@ -177,6 +182,12 @@ static int build_token_table(Decoder* d, DeviceCtx* c) {
     gemv(L.wgu, 2, x, d->t0, L.fn, xalt, d->gu, 0, 0);
     { float* t = x; x = xalt; xalt = t; }
     gemv(L.wd, 1, d->gu, nullptr, nullptr, nullptr, d->t1, 0, 0);
+  }
+  if (const char* e = getenv("TLB_TK_EMPTY")) {  // diagnostics: phases that only run the grid barrier
+    TkPhase z;
+    memset(&z, 0, sizeof(z));
+    z.type = 2;
+    for (int i = 0; i < atoi(e); i++) ph.push_back(z);
   }
   gemv(d->lm_head, 2, x, d->t1, d->onorm, xalt, d->logits, 0, 1);
   if (d->d_phases) cudaFree(d->d_phases);
@@ -212,7 +223,8 @@ static int forward_persistent(Decoder* d, DeviceCtx* c, cudaStream_t s) {
   P.argmax_cell = c->argmax_cell;
   P.bar = d->d_bar;
   P.status = c->status;
-  int rc = token_kernel_launch(P, d->hd, d->tk_kmax, c->sm_count, s);
+  P.dbg = g_gemv_dbg;
+  int rc = token_kernel_launch(P, d->hd, d->tk_kmax, d->hidden, c->sm_count, s);
   if (rc) return rc;
   d->launches_per_token = 1;
   return TLB_OK;

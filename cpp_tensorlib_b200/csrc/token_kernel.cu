@@ -31,24 +31,26 @@ __device__ __forceinline__ unsigned ld_acquire_gpu(const unsigned* p) {
 __device__ __forceinline__ void tk_grid_barrier(unsigned* bar, unsigned& gen, int* status) {
   __syncthreads();
   if (threadIdx.x == 0) {
-    __threadfence();
-    const unsigned old = atomicAdd(&bar[0], 1u);
+    // release-arrive: the CTA's writes (ordered before this by the block barrier) become
+    // visible to whoever acquires the new generation
+    unsigned old;
+    asm volatile("atom.add.acq_rel.gpu.global.u32 %0, [%1], 1;" : "=r"(old) : "l"(&bar[0]) : "memory");
     if (old == gridDim.x - 1) {
-      bar[0] = 0u;
-      __threadfence();
-      atomicExch(&bar[1], gen + 1u);
+      asm volatile("st.relaxed.gpu.global.u32 [%0], %1;" ::"l"(&bar[0]), "r"(0u) : "memory");
+      asm volatile("st.release.gpu.global.u32 [%0], %1;" ::"l"(&bar[1]), "r"(gen + 1u) : "memory");
     } else {
       const long long t0 = clock64();
       while (ld_acquire_gpu(&bar[1]) == gen) {
-        if (*(volatile int*)&status[ST_WAIT_TIMEOUT]) break;
-        if (clock64() - t0 > 2000000000ll) {
-          atomicExch(&status[ST_WAIT_TIMEOUT], 1);
-          atomicExch(&status[ST_WAIT_WHERE], 600);
-          break;
+        if (clock64() - t0 > 200000ll) {   // only look at the slow-path conditions now and then
+          if (*(volatile int*)&status[ST_WAIT_TIMEOUT]) break;
+          if (clock64() - t0 > 2000000000ll) {
+            atomicExch(&status[ST_WAIT_TIMEOUT], 1);
+            atomicExch(&status[ST_WAIT_WHERE], 600);
+            break;
+          }
         }
       }
     }
-    __threadfence();
   }
   gen++;
   __syncthreads();
@@ -72,10 +74,13 @@ __global__ void __launch_bounds__(TK_THREADS, 1) token_kernel(TkParams P) {
   __shared__ TkSmem L;
   __shared__ int is_last_s;
   if (tid == 0) {
-    int kmax = 0;
-    for (int i = 0; i < P.n_phases; i++)
+    int kmax = 0, kin = 0;
+    for (int i = 0; i < P.n_phases; i++) {
       if (P.phases[i].type == 0 && P.phases[i].K > kmax) kmax = P.phases[i].K;
-    L = tk_smem_layout(kmax, P.hd, grp);
+      if (P.phases[i].type == 1 && i > 0 && P.phases[i - 1].type == 0 && P.phases[i - 1].K > kin)
+        kin = P.phases[i - 1].K;
+    }
+    L = tk_smem_layout(kmax, kin, P.hd, grp);
   }
   __syncthreads();
 
@@ -96,19 +101,48 @@ __global__ void __launch_bounds__(TK_THREADS, 1) token_kernel(TkParams P) {
   unsigned gen = *(volatile unsigned*)&P.bar[1];
   const int tok = *P.d_tok;
   const unsigned pos = *P.d_pos;
+  // cos/sin of this token's position for every rotary pair, once per token (double
+  // angle as in rope_kernel; every attention phase reads the table)
+  float* rope_cs = (float*)(base + L.rope);
+  if (tid < D / 2) {
+    const double theta = exp2(-2.0 * (double)tid / (double)D * log2((double)P.rope_base));
+    double sd, cd;
+    sincos((double)pos * theta, &sd, &cd);
+    rope_cs[tid] = (float)cd;
+    rope_cs[D / 2 + tid] = (float)sd;
+  }
+  __syncthreads();
 
   // ---------------- producer cursor of this warp's weight stream ----------------
   int prod_ph = -1, prod_SL = 1, prod_map = 0, prod_rt = 0, prod_s = 0, prod_stage = 0;
   unsigned prod_u = 0, prod_u1 = 0;
   int inflight = 0;
+  // Two ways to deal a projection's units to the warps (TkPhase::cta_tiles):
+  //  0  every warp of the grid owns a contiguous unit range (row-tile-major); used
+  //     when there are at least as many row tiles as warps -- no tile is shared;
+  //  1  every CTA owns whole row tiles (tile = blockIdx.x, += gridDim.x) and its 16
+  //     warps split the tile's K slabs (slab = warp, += 16); the partial sums meet
+  //     in shared memory.  Used for the small-N projections, where sharing a tile
+  //     across CTAs would need a round trip through global memory.
+  int prod_mode = 0, prod_RT = 0;
   auto prod_open = [&](int ph) -> bool {
     const TkPhase& H = P.phases[ph];
-    if (H.type != 0 || wid >= H.Wtot) return false;
+    if (H.type != 0) return false;
+    prod_SL = H.SL;
+    prod_map = H.map;
+    prod_mode = H.cta_tiles;
+    if (prod_mode == 1) {
+      prod_RT = H.RT;
+      prod_rt = (int)blockIdx.x;
+      prod_s = warp;
+      prod_u = 0;
+      prod_u1 = (prod_rt < prod_RT && prod_s < prod_SL) ? 1u : 0u;  // "has a next unit"
+      return prod_u1 != 0;
+    }
+    if (wid >= H.Wtot) return false;
     const GvSplit sp = {H.q, H.r};
     prod_u = gv_start(wid, sp);
     prod_u1 = gv_start(wid + 1, sp);
-    prod_SL = H.SL;
-    prod_map = H.map;
     prod_rt = (int)(prod_u / (unsigned)prod_SL);
     prod_s = (int)(prod_u - (unsigned)prod_rt * prod_SL);
     return prod_u1 > prod_u;
@@ -130,9 +164,15 @@ __global__ void __launch_bounds__(TK_THREADS, 1) token_kernel(TkParams P) {
         tma_load_2d(myS + prod_stage * GVU_S_BYTES, &P.maps[2 * prod_map + 1], prod_s * 8,
                     prod_rt * 16, &mybar[prod_stage]);
       }
-      if (++prod_s == prod_SL) { prod_s = 0; prod_rt++; }
+      if (prod_mode == 1) {
+        prod_s += TK_WARPS;
+        if (prod_s >= prod_SL) { prod_s = warp; prod_rt += (int)gridDim.x; }
+        if (prod_rt >= prod_RT) prod_u = prod_u1;  // exhausted
+      } else {
+        if (++prod_s == prod_SL) { prod_s = 0; prod_rt++; }
+        prod_u++;
+      }
       if (++prod_stage == TK_STAGES) prod_stage = 0;
-      prod_u++;
       inflight++;
     }
   };
@@ -140,12 +180,56 @@ __global__ void __launch_bounds__(TK_THREADS, 1) token_kernel(TkParams P) {
 
   int cons_stage = 0;
   unsigned cons_parity = 0;
-  unsigned at_ctr = 0;  // attention tiles consumed so far by this CTA (ring position)
   bool dead = false;    // a bounded wait expired: stop computing, keep the barriers going
   unsigned long long best_key = 0ull;
 
+  unsigned at_ctr = 0;  // attention tiles consumed so far by this CTA (ring position)
+  // ---- attention work plan (depends only on pos): splits, chunk, this CTA's items ----
+  const int at_ctx = (int)pos + 1;
+  int at_swant = (int)gridDim.x / P.n_kv;
+  if (at_swant > at_ctx / 128) at_swant = at_ctx / 128;
+  if (at_swant > P.attn_s_cap) at_swant = P.attn_s_cap;
+  if (at_swant > 96) at_swant = 96;
+  if (at_swant < 1) at_swant = 1;
+  int at_chunk = (at_ctx + at_swant - 1) / at_swant;
+  at_chunk = (at_chunk + TK_ATT_TK - 1) / TK_ATT_TK * TK_ATT_TK;
+  const int at_slive = (at_ctx + at_chunk - 1) / at_chunk;
+  constexpr int AT_TILE_BYTES = TK_ATT_TK * D * 4;
+  // Issue tile i of an item (rows of one KV head's cache) into the attention ring.
+  auto at_issue = [&](const float* Kc, const float* Vc, int item, int i) {
+    const int kh = item / at_slive, sp = item - kh * at_slive;
+    const int k_begin = sp * at_chunk;
+    const int k_end = k_begin + at_chunk < at_ctx ? k_begin + at_chunk : at_ctx;
+    const int k_stop = sp == at_slive - 1 ? k_end - 1 : k_end;
+    const unsigned c = at_ctr + (unsigned)i;
+    const int st = (int)(c % TK_ATT_STAGES);
+    const int r0 = k_begin + i * TK_ATT_TK;
+    const int rows = (k_stop - r0) < TK_ATT_TK ? (k_stop - r0) : TK_ATT_TK;
+    const uint32_t bytes = (uint32_t)rows * D * 4;
+    const size_t off = ((size_t)kh * P.max_ctx + r0) * D;
+    mbar_expect_tx(&at_bars[st], 2 * bytes);
+    bulk_load_1d(base + L.at_k + (size_t)st * AT_TILE_BYTES, Kc + off, bytes, &at_bars[st]);
+    bulk_load_1d(base + L.at_v + (size_t)st * AT_TILE_BYTES, Vc + off, bytes, &at_bars[st]);
+  };
+  auto at_tiles_of = [&](int item) {
+    const int sp = item % at_slive;
+    const int k_begin = sp * at_chunk;
+    const int k_end = k_begin + at_chunk < at_ctx ? k_begin + at_chunk : at_ctx;
+    const int k_stop = sp == at_slive - 1 ? k_end - 1 : k_end;
+    return (k_stop - k_begin + TK_ATT_TK - 1) / TK_ATT_TK;
+  };
+  int at_prefetched = 0;  // tiles of this CTA's first item already in flight (issued before the barrier)
+
+  auto stamp = [&](int ph, int i) {
+    if (P.dbg && blockIdx.x == 0 && tid == 0) {
+      unsigned long long tt;
+      asm volatile("mov.u64 %0, %globaltimer;" : "=l"(tt));
+      P.dbg[(size_t)ph * 4 + i] = tt;
+    }
+  };
   for (int ph = 0; ph < P.n_phases; ph++) {
     const TkPhase& H = P.phases[ph];
+    stamp(ph, 0);
     if (H.type == 0) {
       // =========================== GEMV phase ===========================
       const int SL = H.SL, G = SL * 8, K = H.K;
@@ -255,30 +339,108 @@ __global__ void __launch_bounds__(TK_THREADS, 1) token_kernel(TkParams P) {
         }
       }
       __syncthreads();
+      stamp(ph, 1);
 
       // ---- streaming loop over this warp's units of the phase ----
-      if (wid < H.Wtot && !dead) {
+      float acc0 = 0.f, acc1 = 0.f, corr0 = 0.f, corr1 = 0.f;
+      const bool use_b = g < 2;
+      const unsigned g7x4 = (unsigned)(g & 7) * 4u;
+      const unsigned wbase = (unsigned)g * 32u + (unsigned)t;
+      auto emit = [&](int n, float v) {
+        H.y[n] = v;
+        if (H.argmax) {
+          const unsigned long long k = tk_argmax_key(v, (unsigned)n);
+          best_key = k > best_key ? k : best_key;
+        }
+      };
+      // one unit (16 rows x 256 k, slab s) out of the ring into acc/corr
+      auto compute_unit = [&](int s) -> bool {
+        if (!mbar_wait_bounded(&mybar[cons_stage], cons_parity, P.status, 100 + cons_stage)) return false;
+        const unsigned* Wst = (const unsigned*)(myW + cons_stage * GVU_W_BYTES);
+        const float* Sst = (const float*)(myS + cons_stage * GVU_S_BYTES);
+        const uint4* Bu = Bfrag + (size_t)(s * 8) * 2 * 4;
+        const float4 sa0 = *(const float4*)(Sst + g * 8), sa1 = *(const float4*)(Sst + g * 8 + 4);
+        const float4 sb0 = *(const float4*)(Sst + (g + 8) * 8), sb1 = *(const float4*)(Sst + (g + 8) * 8 + 4);
+        const float sc0[8] = {sa0.x, sa0.y, sa0.z, sa0.w, sa1.x, sa1.y, sa1.z, sa1.w};
+        const float sc1[8] = {sb0.x, sb0.y, sb0.z, sb0.w, sb1.x, sb1.y, sb1.z, sb1.w};
+        float ua0 = 0.f, ua1 = 0.f;
+#pragma unroll
+        for (int jj = 0; jj < 8; jj++) {
+          const unsigned wo = wbase + (((unsigned)jj * 4u) ^ g7x4);
+          unsigned w0 = Wst[wo], w1 = Wst[wo + 256];
+          const unsigned a0 = w0 & 0x000f000fu, a2 = w0 & 0x00f000f0u;
+          const unsigned a1 = w1 & 0x000f000fu, a3 = w1 & 0x00f000f0u;
+          w0 >>= 8;
+          w1 >>= 8;
+          const unsigned a4 = w0 & 0x000f000fu, a6 = w0 & 0x00f000f0u;
+          const unsigned a5 = w1 & 0x000f000fu, a7 = w1 & 0x00f000f0u;
+          uint4 b = make_uint4(0u, 0u, 0u, 0u);
+          if (use_b) b = Bu[((size_t)jj * 2 + g) * 4 + t];
+          float c[4];
+          mma16816_z(c, a0, a1, a2, a3, b.x, b.y);
+          mma16816(c, a4, a5, a6, a7, b.z, b.w);
+          ua0 = fmaf(sc0[jj], c[0] + c[1], ua0);
+          ua1 = fmaf(sc1[jj], c[2] + c[3], ua1);
+        }
+        {
+          const float2 q = *(const float2*)(Qg + s * 8 + 2 * t);
+          const float2 c0 = *(const float2*)(Sst + g * 8 + 2 * t);
+          const float2 c1 = *(const float2*)(Sst + (g + 8) * 8 + 2 * t);
+          corr0 = fmaf(c0.x, q.x, fmaf(c0.y, q.y, corr0));
+          corr1 = fmaf(c1.x, q.x, fmaf(c1.y, q.y, corr1));
+        }
+        const float Pw = Pslab[s];
+        acc0 = fmaf(Pw, ua0, acc0);
+        acc1 = fmaf(Pw, ua1, acc1);
+        __syncwarp();
+        inflight--;
+        if (++cons_stage == TK_STAGES) { cons_stage = 0; cons_parity ^= 1u; }
+        issue_more();  // may already reach into the next projection's weights
+        return true;
+      };
+      // value of the finished accumulators (the -8*sum(x) correction folded in)
+      auto tile_value = [&](float& v0, float& v1) {
+        float c0 = corr0, c1 = corr1;
+        c0 += __shfl_xor_sync(0xffffffffu, c0, 1);
+        c0 += __shfl_xor_sync(0xffffffffu, c0, 2);
+        c1 += __shfl_xor_sync(0xffffffffu, c1, 1);
+        c1 += __shfl_xor_sync(0xffffffffu, c1, 2);
+        v0 = acc0 - c0;
+        v1 = acc1 - c1;
+        acc0 = acc1 = corr0 = corr1 = 0.f;
+      };
+
+      if (H.cta_tiles == 1) {
+        // CTA-owned row tiles; the warps' K-slab partials meet in shared memory
+        float* part = red;  // [TK_WARPS][16]
+        for (int rt = (int)blockIdx.x; rt < H.RT; rt += (int)gridDim.x) {
+          if (rt == (int)blockIdx.x) stamp(P.n_phases + ph, 0);
+          if (!dead)
+            for (int sl = warp; sl < SL; sl += TK_WARPS)
+              if (!compute_unit(sl)) { dead = true; break; }
+          if (rt == (int)blockIdx.x) stamp(P.n_phases + ph, 1);
+          float v0, v1;
+          tile_value(v0, v1);
+          if (t == 0) { part[warp * 16 + g] = v0; part[warp * 16 + g + 8] = v1; }
+          __syncthreads();
+          if (rt == (int)blockIdx.x) stamp(P.n_phases + ph, 2);
+          if (warp == 0 && lane < 16) {
+            float sum = 0.f;
+            const int nw = SL < TK_WARPS ? SL : TK_WARPS;   // warps that had a slab
+            for (int w = 0; w < nw; w++) sum += part[w * 16 + lane];
+            const int n = rt * 16 + lane;
+            if (n < H.N) emit(n, sum);
+          }
+          __syncthreads();
+          if (rt == (int)blockIdx.x) stamp(P.n_phases + ph, 3);
+        }
+      } else if (wid < H.Wtot && !dead) {
         const GvSplit sp = {H.q, H.r};
         const unsigned u0 = gv_start(wid, sp), u1 = gv_start(wid + 1, sp);
         const int n_units = (int)(u1 - u0);
-        float acc0 = 0.f, acc1 = 0.f, corr0 = 0.f, corr1 = 0.f;
-        const bool use_b = g < 2;
-        const unsigned g7x4 = (unsigned)(g & 7) * 4u;
-        const unsigned wbase = (unsigned)g * 32u + (unsigned)t;
-        auto emit = [&](int n, float v) {
-          H.y[n] = v;
-          if (H.argmax) {
-            const unsigned long long k = tk_argmax_key(v, (unsigned)n);
-            best_key = k > best_key ? k : best_key;
-          }
-        };
         auto flush = [&](int rt) {
-          float c0 = corr0, c1 = corr1;
-          c0 += __shfl_xor_sync(0xffffffffu, c0, 1);
-          c0 += __shfl_xor_sync(0xffffffffu, c0, 2);
-          c1 += __shfl_xor_sync(0xffffffffu, c1, 1);
-          c1 += __shfl_xor_sync(0xffffffffu, c1, 2);
-          const float v0 = acc0 - c0, v1 = acc1 - c1;
+          float v0, v1;
+          tile_value(v0, v1);
           const unsigned t0 = (unsigned)rt * SL, t1 = t0 + SL;
           const bool complete = (u0 <= t0) && (u1 >= t1);
           const int r0 = rt * 16;
@@ -323,61 +485,25 @@ __global__ void __launch_bounds__(TK_THREADS, 1) token_kernel(TkParams P) {
           }
           if (lane == 0) P.gemv_counters[rt] = 0;
         };
-
         int rt = (int)(u0 / (unsigned)SL), s = (int)(u0 - (unsigned)rt * SL);
         for (int i = 0; i < n_units; i++) {
-          if (!mbar_wait_bounded(&mybar[cons_stage], cons_parity, P.status, 100 + cons_stage)) {
-            dead = true;
-            break;
-          }
-          const unsigned* Wst = (const unsigned*)(myW + cons_stage * GVU_W_BYTES);
-          const float* Sst = (const float*)(myS + cons_stage * GVU_S_BYTES);
-          const uint4* Bu = Bfrag + (size_t)(s * 8) * 2 * 4;
-          const float4 sa0 = *(const float4*)(Sst + g * 8), sa1 = *(const float4*)(Sst + g * 8 + 4);
-          const float4 sb0 = *(const float4*)(Sst + (g + 8) * 8), sb1 = *(const float4*)(Sst + (g + 8) * 8 + 4);
-          const float sc0[8] = {sa0.x, sa0.y, sa0.z, sa0.w, sa1.x, sa1.y, sa1.z, sa1.w};
-          const float sc1[8] = {sb0.x, sb0.y, sb0.z, sb0.w, sb1.x, sb1.y, sb1.z, sb1.w};
-          float ua0 = 0.f, ua1 = 0.f;
-#pragma unroll
-          for (int jj = 0; jj < 8; jj++) {
-            const unsigned wo = wbase + (((unsigned)jj * 4u) ^ g7x4);
-            unsigned w0 = Wst[wo], w1 = Wst[wo + 256];
-            const unsigned a0 = w0 & 0x000f000fu, a2 = w0 & 0x00f000f0u;
-            const unsigned a1 = w1 & 0x000f000fu, a3 = w1 & 0x00f000f0u;
-            w0 >>= 8;
-            w1 >>= 8;
-            const unsigned a4 = w0 & 0x000f000fu, a6 = w0 & 0x00f000f0u;
-            const unsigned a5 = w1 & 0x000f000fu, a7 = w1 & 0x00f000f0u;
-            uint4 b = make_uint4(0u, 0u, 0u, 0u);
-            if (use_b) b = Bu[((size_t)jj * 2 + g) * 4 + t];
-            float c[4];
-            mma16816_z(c, a0, a1, a2, a3, b.x, b.y);
-            mma16816(c, a4, a5, a6, a7, b.z, b.w);
-            ua0 = fmaf(sc0[jj], c[0] + c[1], ua0);
-            ua1 = fmaf(sc1[jj], c[2] + c[3], ua1);
-          }
-          {
-            const float2 q = *(const float2*)(Qg + s * 8 + 2 * t);
-            const float2 c0 = *(const float2*)(Sst + g * 8 + 2 * t);
-            const float2 c1 = *(const float2*)(Sst + (g + 8) * 8 + 2 * t);
-            corr0 = fmaf(c0.x, q.x, fmaf(c0.y, q.y, corr0));
-            corr1 = fmaf(c1.x, q.x, fmaf(c1.y, q.y, corr1));
-          }
-          const float Pw = Pslab[s];
-          acc0 = fmaf(Pw, ua0, acc0);
-          acc1 = fmaf(Pw, ua1, acc1);
-          __syncwarp();
-          inflight--;
-          if (++cons_stage == TK_STAGES) { cons_stage = 0; cons_parity ^= 1u; }
-          issue_more();  // may already reach into the next projection's weights
+          if (!compute_unit(s)) { dead = true; break; }
           if (++s == SL) {
             flush(rt);
-            acc0 = acc1 = corr0 = corr1 = 0.f;
             s = 0;
             rt++;
           }
         }
         if (!dead && n_units > 0 && s != 0) flush(rt);
+      }
+      // The cached K/V rows are as static as the weights: start the next attention
+      // phase's first tiles now, so they cross HBM while the grid barrier is pending.
+      if (ph + 1 < P.n_phases && P.phases[ph + 1].type == 1 && (int)blockIdx.x < P.n_kv * at_slive) {
+        const int nt = at_tiles_of((int)blockIdx.x);
+        at_prefetched = nt < TK_ATT_STAGES ? nt : TK_ATT_STAGES;
+        if (tid == 0)
+          for (int i = 0; i < at_prefetched; i++)
+            at_issue(P.phases[ph + 1].Kc, P.phases[ph + 1].Vc, (int)blockIdx.x, i);
       }
       if (H.argmax) {
 #pragma unroll
@@ -387,22 +513,14 @@ __global__ void __launch_bounds__(TK_THREADS, 1) token_kernel(TkParams P) {
         }
         if (lane == 0 && best_key) atomicMax(P.argmax_cell, best_key);
       }
-    } else {
+    } else if (H.type == 1) {
       // =========================== attention phase ===========================
       // qkv holds the fused projection of this token.  Per (kv head, context split)
       // item: rope+bias the group's q heads into shared memory, the split that owns
       // the new position also ropes k, biases v, appends both to the cache and scores
       // them from shared memory; the cached prefix streams through bulk-copy tiles.
       constexpr int CH = D / 32;
-      const int ctx = (int)pos + 1;
-      int s_want = (int)gridDim.x / P.n_kv;
-      if (s_want > ctx / 128) s_want = ctx / 128;
-      if (s_want > P.attn_s_cap) s_want = P.attn_s_cap;
-      if (s_want > 96) s_want = 96;
-      if (s_want < 1) s_want = 1;
-      int chunk = (ctx + s_want - 1) / s_want;
-      chunk = (chunk + TK_ATT_TK - 1) / TK_ATT_TK * TK_ATT_TK;
-      const int s_live = (ctx + chunk - 1) / chunk;
+      const int ctx = at_ctx, chunk = at_chunk, s_live = at_slive;
       const long long kv_stride = (long long)P.max_ctx * D;
       int hs = (grp + TK_HW - 1) / TK_HW;
       while (TK_WARPS % hs) hs++;
@@ -414,7 +532,7 @@ __global__ void __launch_bounds__(TK_THREADS, 1) token_kernel(TkParams P) {
       float* qs = (float*)(base + L.at_q);
       float* newkv = (float*)(base + L.at_new);
       float* mrg = (float*)(base + L.at_mrg);
-      constexpr int TILE_BYTES = TK_ATT_TK * D * 4;
+      constexpr int TILE_BYTES = AT_TILE_BYTES;
 
       for (int item = blockIdx.x; item < P.n_kv * s_live; item += gridDim.x) {
         const int kh = item / s_live, sp = item - kh * s_live;
@@ -425,29 +543,18 @@ __global__ void __launch_bounds__(TK_THREADS, 1) token_kernel(TkParams P) {
         const int n_tiles = (k_stop - k_begin + TK_ATT_TK - 1) / TK_ATT_TK;
         const float* Kh = H.Kc + (size_t)kh * kv_stride;
         const float* Vh = H.Vc + (size_t)kh * kv_stride;
-        auto issue_tile = [&](int i) {
-          const unsigned c = at_ctr + (unsigned)i;
-          const int st = (int)(c % TK_ATT_STAGES);
-          const int r0 = k_begin + i * TK_ATT_TK;
-          const int rows = (k_stop - r0) < TK_ATT_TK ? (k_stop - r0) : TK_ATT_TK;
-          const uint32_t bytes = (uint32_t)rows * D * 4;
-          mbar_expect_tx(&at_bars[st], 2 * bytes);
-          bulk_load_1d((unsigned char*)Kt + (size_t)st * TILE_BYTES, Kh + (size_t)r0 * D, bytes, &at_bars[st]);
-          bulk_load_1d((unsigned char*)Vt + (size_t)st * TILE_BYTES, Vh + (size_t)r0 * D, bytes, &at_bars[st]);
-        };
+        auto issue_tile = [&](int i) { at_issue(H.Kc, H.Vc, item, i); };
         if (tid == 0) {
           const int pre = n_tiles < TK_ATT_STAGES ? n_tiles : TK_ATT_STAGES;
-          for (int i = 0; i < pre; i++) issue_tile(i);
+          for (int i = (item == (int)blockIdx.x ? at_prefetched : 0); i < pre; i++) issue_tile(i);
         }
+        if (item == (int)blockIdx.x) at_prefetched = 0;
         // rope(q + bq) for the group's heads (double angle, as rope_kernel)
         constexpr int half = D / 2;
         for (int idx = tid; idx < grp * half; idx += TK_THREADS) {
           const int hh = idx / half, j = idx - hh * half;
           const int qh = kh * grp + hh;
-          const double theta = exp2(-2.0 * (double)j / (double)D * log2((double)P.rope_base));
-          double sd, cd;
-          sincos((double)pos * theta, &sd, &cd);
-          const float c = (float)cd, sn = (float)sd;
+          const float c = rope_cs[j], sn = rope_cs[half + j];
           float x0 = H.qkv[(size_t)qh * D + j], x1 = H.qkv[(size_t)qh * D + j + half];
           if (H.bq) { x0 += H.bq[qh * D + j]; x1 += H.bq[qh * D + j + half]; }
           qs[hh * D + j] = x0 * c - x1 * sn;
@@ -459,10 +566,7 @@ __global__ void __launch_bounds__(TK_THREADS, 1) token_kernel(TkParams P) {
           float* kdst = H.Kc + (size_t)kh * kv_stride + (size_t)pos * D;
           float* vdst = H.Vc + (size_t)kh * kv_stride + (size_t)pos * D;
           for (int j = tid; j < half; j += TK_THREADS) {
-            const double theta = exp2(-2.0 * (double)j / (double)D * log2((double)P.rope_base));
-            double sd, cd;
-            sincos((double)pos * theta, &sd, &cd);
-            const float c = (float)cd, sn = (float)sd;
+            const float c = rope_cs[j], sn = rope_cs[half + j];
             float x0 = ksrc[j], x1 = ksrc[j + half];
             if (H.bk) { x0 += H.bk[kh * D + j]; x1 += H.bk[kh * D + j + half]; }
             const float r0 = x0 * c - x1 * sn, r1 = x0 * sn + x1 * c;
@@ -477,6 +581,7 @@ __global__ void __launch_bounds__(TK_THREADS, 1) token_kernel(TkParams P) {
           }
         }
         __syncthreads();
+        stamp(P.n_phases + ph, 0);
 
         float4 qf[TK_HW][CH];
 #pragma unroll
@@ -565,6 +670,7 @@ __global__ void __launch_bounds__(TK_THREADS, 1) token_kernel(TkParams P) {
           if (tid == 0 && it + TK_ATT_STAGES < n_tiles) issue_tile(it + TK_ATT_STAGES);
         }
         at_ctr += (unsigned)n_tiles;
+        stamp(P.n_phases + ph, 1);
         if (last && kslice == 0)  // the new token's own key/value, from shared memory
           row_step((const float4*)newkv, (const float4*)(newkv + D), kslot == 0);
 
@@ -630,6 +736,7 @@ __global__ void __launch_bounds__(TK_THREADS, 1) token_kernel(TkParams P) {
             __stcg(&dst[d], aa);
           }
         }
+        stamp(P.n_phases + ph, 2);
         if (!single) {
           __threadfence();
           __syncthreads();
@@ -692,9 +799,12 @@ __global__ void __launch_bounds__(TK_THREADS, 1) token_kernel(TkParams P) {
           }
         }
         __syncthreads();  // shared memory of this item is free again
+        stamp(P.n_phases + ph, 3);
       }
     }
+    stamp(ph, 2);
     tk_grid_barrier(P.bar, gen, P.status);
+    stamp(ph, 3);
   }
 
   // ---- the token: argmax of the last projection, position + 1 ----
@@ -710,9 +820,10 @@ __global__ void __launch_bounds__(TK_THREADS, 1) token_kernel(TkParams P) {
 // ---------------------------------------------------------------------------
 // host side: one cooperative launch of one CTA per SM
 // ---------------------------------------------------------------------------
-int token_kernel_launch(const TkParams& P, int D, int k_max, int sm_count, cudaStream_t stream) {
+int token_kernel_launch(const TkParams& P, int D, int k_max, int k_attn_in, int sm_count,
+                        cudaStream_t stream) {
   const int grp = P.n_q / P.n_kv;
-  const size_t smem = tk_smem_layout(k_max, D, grp).total;
+  const size_t smem = tk_smem_layout(k_max, k_attn_in, D, grp).total;
   if (smem > 227 * 1024 - 512)  // the kernel also has a few static shared words
     return set_error(TLB_ERR_UNSUPPORTED, "token kernel: shared memory need exceeds 227 KB");
   void* fn = D == 128 ? (void*)token_kernel<128> : (void*)token_kernel<64>;
