@@ -26,6 +26,9 @@
 //  * Split-K falls out of the unit ranges; partial row tiles are combined by the
 //    last-arriving warp in a fixed order (deterministic, no float atomics, no
 //    spin-wait on another CTA).
+#include <cstdlib>
+#include <cstring>
+
 #include "comm.cuh"
 #include "q4_mma.cuh"
 
@@ -517,6 +520,10 @@ int make_q4_tensor_maps(const void* qw, const void* scales, int N, int K, CUtens
 // Kernel shape for a problem: 8 warps x 4 stages when two CTAs fit on an SM,
 // else 16 warps x 3 stages.
 static void gemv_pick(int M, int K, int* warps, int* stages) {
+  if (const char* e = getenv("TLB_GEMV_CFG")) {  // diagnostics: "16x3" / "16x4"
+    if (!strcmp(e, "16x3")) { *warps = 16; *stages = 3; return; }
+    if (!strcmp(e, "16x4")) { *warps = 16; *stages = 4; return; }
+  }
   const size_t small = gemv_smem_layout(8, 4, M, K).total;
   if (small <= 113 * 1024) { *warps = 8; *stages = 4; }
   else { *warps = 16; *stages = 3; }
@@ -586,6 +593,7 @@ int gemv_q4_launch(DeviceCtx* c, const CUtensorMap& tmW, const CUtensorMap& tmS,
     if (M <= 4) return gemv_launch_t<1, 8, 4, false>(tmW, tmS, p, ctas, smem, stream);
     return gemv_launch_t<2, 8, 4, false>(tmW, tmS, p, ctas, smem, stream);
   }
+  if (M == 1 && stages == 4) return gemv_launch_t<1, 16, 4, true>(tmW, tmS, p, ctas, smem, stream);
   if (M == 1) return gemv_launch_t<1, 16, 3, true>(tmW, tmS, p, ctas, smem, stream);
   if (M <= 4) return gemv_launch_t<1, 16, 3, false>(tmW, tmS, p, ctas, smem, stream);
   return gemv_launch_t<2, 16, 3, false>(tmW, tmS, p, ctas, smem, stream);

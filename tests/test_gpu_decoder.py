@@ -116,6 +116,38 @@ def test_half_billion_shape_two_layers(port):
     d.close(); o.close()
 
 
+def test_half_billion_full_model_greedy_ids(port):
+    """BASELINE config 3 in full: the Qwen2.5-0.5B architecture (24 layers, hidden 896,
+    14q/2kv, hd 64, ff 4864, vocab 151936), random-init from seed 2, 128 prompt ids then
+    greedy decoding, token ids against the oracle at every step (both decoder modes on
+    the GPU).  The oracle costs ~0.1 s per token on the host cores, so the greedy tail is
+    64 steps here; the full 256 run with `TLB_CFG3_STEPS=256`."""
+    import os
+    cfg = cases.QWEN05
+    steps = int(os.environ.get("TLB_CFG3_STEPS", "64"))
+    n = 128 + steps
+    d, wts = make(cfg, 2, n + 8)
+    o = port_decoder(port, cfg, wts, n + 8)
+    prompt = [int(t) for t in synth.token_ids(2, 99, 128, cfg["vocab"])]
+    want, nxt = [], 0
+    for i in range(n):
+        tid = prompt[i] if i < 128 else nxt
+        nxt, _ = o.step(tid, i, want_logits=False)
+        want.append(nxt)
+    o.close()
+    for mode in (0, 1):
+        d.set_mode(mode)
+        d.set_pos(0)
+        d.capture()
+        got, nxt = [], 0
+        for i in range(n):
+            nxt = d.step(prompt[i] if i < 128 else nxt)
+            got.append(nxt)
+        first_bad = next((i for i in range(n) if got[i] != want[i]), None)
+        assert first_bad is None, (mode, first_bad, got[first_bad], want[first_bad])
+    d.close()
+
+
 def test_seven_billion_shape_one_layer_prefilled(port):
     """BASELINE config 5's layer shape (hidden 3584, 28q/4kv, hd 128, ff 18944) with one
     layer and a 32000-row vocabulary, KV pre-filled to ctx 4096 with N(0,1): 4 greedy
