@@ -46,6 +46,10 @@ SIGNATURES = {
     "tlb_incr_u32": (ci, [vp, vp]),
     "tlb_argmax": (ci, [vp, i64, C.POINTER(i64), vp]),
     "tlb_argmax_dev": (ci, [vp, i64, vp, vp]),
+    "tlb_split_heads": (ci, [vp, vp, vp, i64, i64, i64, i64, i64, vp]),
+    "tlb_merge_heads": (ci, [vp, vp, i64, i64, i64, vp]),
+    "tlb_kv_fill": (ci, [vp, vp, vp, vp, i64, i64, i64, i64, i64, vp]),
+    "tlb_attn_prefill": (ci, [vp, vp, vp, vp, i64, i64, i64, i64, i64, f32, i64, vp]),
     "tlb_capture_begin": (ci, [C.POINTER(vp)]),
     "tlb_capture_end": (ci, [C.POINTER(vp)]),
     "tlb_graph_launch": (ci, [vp, vp]),

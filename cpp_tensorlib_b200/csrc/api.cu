@@ -39,6 +39,11 @@ int launch_kv_append(float*, float*, const float*, const float*, unsigned, const
 int launch_incr_u32(unsigned*, cudaStream_t);
 int launch_argmax(DeviceCtx*, const float*, int, int*, int*, cudaStream_t);
 int launch_to_q4(const float*, int, int, unsigned char*, cudaStream_t);
+int launch_split_heads(const float*, const float*, float*, int, long long, long long, int, int, cudaStream_t);
+int launch_merge_heads(const float*, float*, int, int, int, cudaStream_t);
+int launch_kv_fill(float*, float*, const float*, const float*, int, long long, int, int, int, cudaStream_t);
+int launch_attn_prefill(DeviceCtx*, const float*, const float*, const float*, float*, int, int, int,
+                        long long, int, float, int, cudaStream_t);
 int launch_q4_to_f32(const unsigned char*, int, int, float*, cudaStream_t);
 
 extern unsigned long long* g_gemv_dbg;
@@ -372,6 +377,36 @@ int tlb_argmax(const float* in, int64_t n, int64_t* out_idx, void* stream) {
   TLB_CUDA(cudaStreamSynchronize(S(stream)));
   *out_idx = h;
   return TLB_OK;
+}
+
+int tlb_split_heads(const float* src, const float* bias, float* dst, int64_t T, int64_t ld,
+                    int64_t off, int64_t H, int64_t D, void* stream) {
+  TLB_REQUIRE(src && dst && T > 0 && H > 0 && D > 0 && D <= 1024 && T <= 65535, "tlb_split_heads: bad arguments");
+  return launch_split_heads(src, bias, dst, (int)T, ld, off, (int)H, (int)D, S(stream));
+}
+int tlb_merge_heads(const float* src, float* dst, int64_t T, int64_t H, int64_t D, void* stream) {
+  TLB_REQUIRE(src && dst && T > 0 && H > 0 && D > 0 && D <= 1024 && T <= 65535, "tlb_merge_heads: bad arguments");
+  return launch_merge_heads(src, dst, (int)T, (int)H, (int)D, S(stream));
+}
+int tlb_kv_fill(float* Kc, float* Vc, const float* K, const float* V, int64_t T, int64_t kv_max,
+                int64_t n_kv, int64_t D, int64_t pos0, void* stream) {
+  TLB_REQUIRE(Kc && Vc && K && V, "tlb_kv_fill: null pointer");
+  TLB_REQUIRE(T > 0 && T <= 65535 && pos0 >= 0 && pos0 + T <= kv_max, "tlb_kv_fill: rows outside the cache");
+  TLB_REQUIRE(D > 0 && D <= 1024 && n_kv > 0, "tlb_kv_fill: bad shape");
+  return launch_kv_fill(Kc, Vc, K, V, (int)T, kv_max, (int)n_kv, (int)D, (int)pos0, S(stream));
+}
+int tlb_attn_prefill(const float* q, const float* K, const float* V, float* out, int64_t n_q,
+                     int64_t n_kv, int64_t T, int64_t kv_max, int64_t D, float scale, int64_t pos0,
+                     void* stream) {
+  TLB_REQUIRE(q && K && V && out, "tlb_attn_prefill: null pointer");
+  TLB_REQUIRE(D == 64 || D == 128, "tlb_attn_prefill: D must be 64 or 128");
+  TLB_REQUIRE(n_kv > 0 && n_q % n_kv == 0, "tlb_attn_prefill: n_q % n_kv != 0");
+  TLB_REQUIRE(T > 0 && T <= 65535 && pos0 >= 0 && pos0 + T <= kv_max, "tlb_attn_prefill: chunk outside the cache");
+  TLB_REQUIRE((((uintptr_t)q | (uintptr_t)K | (uintptr_t)V | (uintptr_t)out) & 15) == 0,
+              "tlb_attn_prefill: pointers must be 16-byte aligned");
+  CTX(c);
+  return launch_attn_prefill(c, q, K, V, out, (int)n_q, (int)n_kv, (int)T, kv_max, (int)D, scale,
+                             (int)pos0, S(stream));
 }
 
 int tlb_capture_begin(void** stream_out) {

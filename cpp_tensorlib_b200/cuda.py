@@ -203,6 +203,35 @@ def swiglu(gu, ff, out=None):
     return out
 
 
+def split_heads(src, bias, T, ld, off, H, D, out=None):
+    """cuda::split_heads (include/cuda.h:848-864): [T, ld] token-major -> [H, T, D] (+ bias[H*D])."""
+    if out is None:
+        out = torch.empty((H, T, D), dtype=torch.float32, device=src.device)
+    check(lib().tlb_split_heads(_p(src), _p(bias), _p(out), T, ld, off, H, D, _s()))
+    return out
+
+
+def merge_heads(src, out=None):
+    """cuda::merge_heads (include/cuda.h:867-879): [H, T, D] -> [T, H*D]."""
+    H, T, D = src.shape
+    if out is None:
+        out = torch.empty((T, H * D), dtype=torch.float32, device=src.device)
+    check(lib().tlb_merge_heads(_p(src), _p(out), T, H, D, _s()))
+    return out
+
+
+def attn_prefill(q, K, V, scale, pos0=0, out=None):
+    """cuda::attn_prefill (include/cuda.h:1171-1201): causal attention of a prompt chunk.
+    q [n_q, T, D]; K, V caches [n_kv, kv_max, D] already holding rows [0, pos0 + T)."""
+    _f32c(q, "attn_prefill q"), _f32c(K, "attn_prefill K"), _f32c(V, "attn_prefill V")
+    n_q, T, D = q.shape
+    n_kv, kv_max, _ = K.shape
+    if out is None:
+        out = torch.empty_like(q)
+    check(lib().tlb_attn_prefill(_p(q), _p(K), _p(V), _p(out), n_q, n_kv, T, kv_max, D, scale, pos0, _s()))
+    return out
+
+
 def argmax(v):
     """cuda::argmax (include/cuda.h:1261-1282): smallest index among the maxima."""
     _f32c(v, "argmax")
@@ -234,6 +263,18 @@ class kv_cache:
 
     def attn(self, q, scale, out=None):
         return attn_decode(q, self.K, self.V, scale, ctx=self.pos, out=out)
+
+    def prefill(self, q, k_src, v_src, scale, out=None):
+        """kv_cache::prefill (include/cuda.h:1383-1398): append a block of k, v
+        ([n_kv, T, D]) at the current position and run causal attention for q [n_q, T, D]."""
+        T = k_src.shape[1]
+        if T <= 0 or self.pos + T > self.max_ctx:
+            raise IndexError("kv_cache.prefill: block does not fit the cache")
+        check(lib().tlb_kv_fill(_p(self.K), _p(self.V), _p(k_src), _p(v_src), T, self.max_ctx,
+                                self.n_kv_heads, self.D, self.pos, _s()))
+        p0 = self.pos
+        self.pos += T
+        return attn_prefill(q, self.K, self.V, scale, pos0=p0, out=out)
 
     def append_dpos(self, k_new, v_new, d_pos):
         check(lib().tlb_kv_append_dpos(_p(self.K), _p(self.V), _p(k_new), _p(v_new), _p(d_pos),

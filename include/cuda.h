@@ -12,7 +12,7 @@
 // rmsnorm, rmsnorm_res, swiglu, argmax, kv_append(+_dpos), kv_cache, incr_u32, graph
 // capture, the host/device mirror (alloc / release / sync_to_host / upload).  Ops
 // outside that path (elementwise, f32 GEMM, row reductions, f32/bf16 GEMV, prefill
-// attention) decline with `false`, which the reference evaluator answers with its
+// attention on a bf16 cache) decline with `false`, which the reference evaluator answers with its
 // own CPU code -- the same contract its stub backend uses.  A hot-path op that the
 // library refuses is NOT declined: it throws, because silently computing a decode
 // op on the CPU is exactly what this backend exists to prevent.
@@ -80,6 +80,11 @@ struct backend {
   int (*incr_u32)(void*, void*) = nullptr;
   int (*argmax)(const float*, int64_t, int64_t*, void*) = nullptr;
   int (*memset_)(void*, int, int64_t, void*) = nullptr;
+  int (*split_heads)(const float*, const float*, float*, int64_t, int64_t, int64_t, int64_t, int64_t, void*) = nullptr;
+  int (*merge_heads)(const float*, float*, int64_t, int64_t, int64_t, void*) = nullptr;
+  int (*kv_fill)(float*, float*, const float*, const float*, int64_t, int64_t, int64_t, int64_t, int64_t, void*) = nullptr;
+  int (*attn_prefill)(const float*, const float*, const float*, float*, int64_t, int64_t, int64_t, int64_t,
+                      int64_t, float, int64_t, void*) = nullptr;
   int (*capture_begin)(void**) = nullptr;
   int (*capture_end)(void**) = nullptr;
   int (*graph_launch)(void*, void*) = nullptr;
@@ -129,7 +134,9 @@ struct backend {
               bind(rope, "tlb_rope") && bind(rope_dpos, "tlb_rope_dpos") &&
               bind(kv_append, "tlb_kv_append") && bind(kv_append_dpos, "tlb_kv_append_dpos") &&
               bind(incr_u32, "tlb_incr_u32") && bind(argmax, "tlb_argmax") &&
-              bind(memset_, "tlb_memset") && bind(capture_begin, "tlb_capture_begin") &&
+              bind(memset_, "tlb_memset") && bind(split_heads, "tlb_split_heads") &&
+              bind(merge_heads, "tlb_merge_heads") && bind(kv_fill, "tlb_kv_fill") &&
+              bind(attn_prefill, "tlb_attn_prefill") && bind(capture_begin, "tlb_capture_begin") &&
               bind(capture_end, "tlb_capture_end") && bind(graph_launch, "tlb_graph_launch") &&
               bind(graph_destroy, "tlb_graph_destroy");
     if (!ok || device_count() <= 0) return;
@@ -262,8 +269,6 @@ inline bool gemv_f32(void*, void*, void*, int64_t, int64_t) { return false; }
 inline bool gemv_bf16(void*, void*, void*, int64_t, int64_t) { return false; }
 inline bool gemv_bf16_row(void*, void*, void*, int64_t, int64_t) { return false; }
 inline bool gemm_bf16_nt(void*, void*, void*, int64_t, int64_t, int64_t) { return false; }
-inline bool split_heads(void*, void*, void*, int64_t, int64_t, int64_t, int64_t, int64_t) { return false; }
-inline bool merge_heads(void*, void*, int64_t, int64_t, int64_t) { return false; }
 
 // ---- the quantized-decode path ----
 inline bool gemv_q4(void* a, void* qw, void* scales, void* y, int64_t N, int64_t K, int64_t group) {
@@ -367,11 +372,41 @@ inline bool attn_decode_dpos(void* q, void* K, void* V, void* out, int64_t n_q_h
                             n_kv_heads, d_pos, kv_max, D, scale, partials, b.stream), "attn_decode_dpos");
   return true;
 }
-// Prefill kernels are the next row of the build plan, not part of this backend yet.
-inline bool kv_fill(void*, void*, void*, void*, int64_t, int64_t, int64_t, int64_t, bool = false,
-                    int64_t = 0) { return false; }
-inline bool attn_prefill(void*, void*, void*, void*, int64_t, int64_t, int64_t, int64_t, int64_t,
-                         float, bool = false, int64_t = 0) { return false; }
+// ---- batched prefill (reference cuda.h:848-879, 1143-1201), f32 cache ----
+inline bool split_heads(void* src, void* bias, void* dst, int64_t T, int64_t ld, int64_t off,
+                        int64_t H, int64_t D) {
+  auto& b = detail::backend::get();
+  if (!b.ready || T <= 0 || H <= 0 || D <= 0) return false;
+  b.reads(src); if (bias) b.reads(bias); b.writes(dst);
+  b.must(b.split_heads(detail::f(src), detail::f(bias), detail::fw(dst), T, ld, off, H, D, b.stream), "split_heads");
+  return true;
+}
+inline bool merge_heads(void* src, void* dst, int64_t T, int64_t H, int64_t D) {
+  auto& b = detail::backend::get();
+  if (!b.ready || T <= 0 || H <= 0 || D <= 0) return false;
+  b.reads(src); b.writes(dst);
+  b.must(b.merge_heads(detail::f(src), detail::fw(dst), T, H, D, b.stream), "merge_heads");
+  return true;
+}
+inline bool kv_fill(void* Kc, void* Vc, void* K, void* V, int64_t T, int64_t kv_max,
+                    int64_t n_kv_heads, int64_t D, bool kv_bf16 = false, int64_t pos0 = 0) {
+  auto& b = detail::backend::get();
+  if (!b.ready || kv_bf16) return false;
+  b.reads(K); b.reads(V); b.reads(Kc); b.reads(Vc); b.writes(Kc); b.writes(Vc);
+  b.must(b.kv_fill(detail::fw(Kc), detail::fw(Vc), detail::f(K), detail::f(V), T, kv_max, n_kv_heads, D,
+                   pos0, b.stream), "kv_fill");
+  return true;
+}
+inline bool attn_prefill(void* q, void* K, void* V, void* out, int64_t n_q_heads, int64_t n_kv_heads,
+                         int64_t T, int64_t kv_max, int64_t D, float scale, bool kv_bf16 = false,
+                         int64_t pos0 = 0) {
+  auto& b = detail::backend::get();
+  if (!b.ready || kv_bf16) return false;
+  b.reads(q); b.reads(K); b.reads(V); b.writes(out);
+  b.must(b.attn_prefill(detail::f(q), detail::f(K), detail::f(V), detail::fw(out), n_q_heads, n_kv_heads,
+                        T, kv_max, D, scale, pos0, b.stream), "attn_prefill");
+  return true;
+}
 
 // ---- CUDA-graph capture (reference cuda.h:512-551) ----
 inline bool graph_available() { return detail::backend::get().ready; }
@@ -442,7 +477,13 @@ struct kv_cache {
     }
     return attn_decode_dpos(q, K, V, out, n_q_heads, n_kv_heads, d_pos, max_ctx, D, scale, dpos_partials);
   }
-  bool prefill(void*, void*, void*, void*, int64_t, int64_t, float) { return false; }
+  bool prefill(void* q, void* k_src, void* v_src, void* out, int64_t T, int64_t n_q_heads, float scale) {
+    if (T <= 0 || pos + T > max_ctx) return false;
+    if (!kv_fill(K, V, k_src, v_src, T, max_ctx, n_kv_heads, D, false, pos)) return false;
+    const int64_t p0 = pos;
+    pos += T;
+    return attn_prefill(q, K, V, out, n_q_heads, n_kv_heads, T, max_ctx, D, scale, false, p0);
+  }
   void destroy() {
     if (K) release(K, 0, nullptr);
     if (V) release(V, 0, nullptr);

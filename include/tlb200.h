@@ -124,6 +124,21 @@ int tlb_argmax(const float* in, int64_t n, int64_t* out_idx, void* stream);
 /* Asynchronous form: the int32 index is written to d_out (device), no sync. */
 int tlb_argmax_dev(const float* in, int64_t n, void* d_out, void* stream);
 
+/* ---- batched prefill (the "next" row: prompt chunks instead of token-by-token) ---- */
+/* cu.h:848-864 split_heads: [T, ld] token-major (column block at `off`) -> [H, T, D], + bias[H*D] */
+int tlb_split_heads(const float* src, const float* bias, float* dst, int64_t T, int64_t ld,
+                    int64_t off, int64_t H, int64_t D, void* stream);
+/* cu.h:867-879 merge_heads: [H, T, D] -> [T, H*D] */
+int tlb_merge_heads(const float* src, float* dst, int64_t T, int64_t H, int64_t D, void* stream);
+/* cu.h:1143-1164 kv_fill: k, v [n_kv, T, D] into cache rows [pos0, pos0 + T) (f32 cache) */
+int tlb_kv_fill(float* Kc, float* Vc, const float* K, const float* V, int64_t T, int64_t kv_max,
+                int64_t n_kv, int64_t D, int64_t pos0, void* stream);
+/* cu.h:1171-1201 attn_prefill: causal attention of a prompt chunk; q, out [n_q, T, D];
+ * query p is at position pos0 + p and attends keys 0..pos0+p of the cache. */
+int tlb_attn_prefill(const float* q, const float* K, const float* V, float* out, int64_t n_q,
+                     int64_t n_kv, int64_t T, int64_t kv_max, int64_t D, float scale, int64_t pos0,
+                     void* stream);
+
 /* ---- CUDA-graph capture (cu.h:512-551) ------------------------------------- */
 int tlb_capture_begin(void** stream_out);   /* capture_begin: returns the stream to launch on */
 int tlb_capture_end(void** graph_exec_out); /* capture_end */

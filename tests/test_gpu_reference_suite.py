@@ -41,14 +41,14 @@ def test_reference_llm_block():
     assert rc == 0 and "ALL OK" in out, out[-2000:]
 
 
-def test_reference_attn64_decode_and_dpos():
+def test_reference_attn64_decode_dpos_and_prefill():
     """bench/cuda/check/check_attn64.cpp: cache grown to 2047 tokens across the split
-    boundary and attn_dpos bit-equal to attn.  Its prefill sections need the tiled
-    prefill kernel, which this backend does not have yet, so only the decode lines
-    are asserted."""
+    boundary, attn_dpos bit-equal to attn, and the batched / chunked prefill sections
+    (kv_cache::prefill -> kv_fill + attn_prefill) against its CPU causal attention."""
     rc, out = run("ref_check_attn64")
     lines = [l for l in out.splitlines() if "kv cache grow" in l or "attn_dpos" in l]
     assert len(lines) == 2 and all(l.rstrip().endswith("OK") for l in lines), out[-2000:]
+    assert rc == 0 and "FAIL" not in out, out[-2000:]
 
 
 def test_reference_q4_gemv_bench_correctness():
