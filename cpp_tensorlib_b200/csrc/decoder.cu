@@ -29,6 +29,13 @@ extern unsigned long long* g_gemv_dbg;
 int make_q4_tensor_maps(const void* qw, const void* scales, int N, int K, CUtensorMap* tmW,
                         CUtensorMap* tmS);
 bool gemv_q4_tma_eligible(const void* qw, const void* scales, int N, int K, int M);
+bool gemv_q4p_supported(long long N, long long K);
+long long q4p_bytes(long long N, long long K);
+int launch_q4_pack(const void* q4, int N, int K, void* out, cudaStream_t s);
+int gemv_q4p_launch(DeviceCtx* c, const void* packed, const float* x, float* y, int N, int K,
+                    float alpha, float beta, cudaStream_t stream, int max_ctas,
+                    const CommDev* push_comm, int act, const float* delta, const float* nw,
+                    float* xout, float eps);
 int gemv_q4_launch(DeviceCtx* c, const CUtensorMap& tmW, const CUtensorMap& tmS, const float* x,
                    long long ldx, int M, float* y, long long ldy, int N, int K, float alpha,
                    float beta, cudaStream_t stream, int max_ctas, const CommDev* push_comm,
@@ -59,6 +66,7 @@ struct Linear {
   int K = 0, N = 0;
   bool tma = false;
   CUtensorMap tmW, tmS;
+  void* packed = nullptr;  // tile-packed copy for the decode GEMV (owned)
   const float* scales() const { return (const float*)((const char*)q4 + (size_t)N * K / 2); }
 };
 
@@ -110,6 +118,13 @@ static int set_linear(Linear& L, const void* q4, int K, int N) {
   L.K = K;
   L.N = N;
   L.tma = gemv_q4_tma_eligible(q4, L.scales(), N, K, 1);
+  if (L.packed) { cudaFree(L.packed); L.packed = nullptr; }
+  if (gemv_q4p_supported(N, K)) {
+    TLB_CUDA(cudaMalloc(&L.packed, (size_t)q4p_bytes(N, K)));
+    int rc = launch_q4_pack(q4, N, K, L.packed, nullptr);
+    if (rc) return rc;
+    TLB_CUDA(cudaStreamSynchronize(nullptr));
+  }
   if (L.tma) return make_q4_tensor_maps(q4, L.scales(), N, K, &L.tmW, &L.tmS);
   return TLB_OK;
 }
@@ -125,6 +140,9 @@ struct NormIn {
 static int run_linear(DeviceCtx* c, const Linear& L, const float* x, float* y, cudaStream_t s,
                       const CommDev* push, int act = 0, const NormIn* nm = nullptr, float eps = 0.f) {
   if (!L.q4) return set_error(TLB_ERR_STATE, "decoder: a linear weight was never set");
+  if (L.packed && !(nm && (L.K + 255) / 256 > 32))
+    return gemv_q4p_launch(c, L.packed, x, y, L.N, L.K, 1.0f, 0.0f, s, 0, push, nm ? 2 : act,
+                           nm ? nm->delta : nullptr, nm ? nm->w : nullptr, nm ? nm->xout : nullptr, eps);
   if (L.tma && nm)
     return gemv_q4_launch(c, L.tmW, L.tmS, x, L.K, 1, y, L.N, L.N, L.K, 1.0f, 0.0f, s, 0, push, 2,
                           nm->delta, nm->w, nm->xout, eps);
@@ -406,7 +424,11 @@ int tlb_decoder_destroy(void* h) {
         if (d->peer_stage_base[r]) cudaIpcCloseMemHandle(d->peer_stage_base[r]);
         if (d->peer_flags_base[r]) cudaIpcCloseMemHandle(d->peer_flags_base[r]);
       }
-  for (auto& L : d->layers) { cudaFree(L.Kc); cudaFree(L.Vc); }
+  for (auto& L : d->layers) {
+    cudaFree(L.Kc); cudaFree(L.Vc);
+    cudaFree(L.wqkv.packed); cudaFree(L.wo.packed); cudaFree(L.wgu.packed); cudaFree(L.wd.packed);
+  }
+  cudaFree(d->lm_head.packed);
   float* bufs[] = {d->x, d->xb, d->t1, d->hb, d->qkv, d->att, d->t0, d->gu, d->mb, d->logits};
   for (float* b : bufs) cudaFree(b);
   cudaFree(d->stage_local);

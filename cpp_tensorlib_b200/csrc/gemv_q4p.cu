@@ -1,0 +1,509 @@
+// Decode GEMV (M = 1) on the library's own tile-packed int4 layout.
+// y[n] = alpha * sum_k x[k] * sc[n,k/32] * (nib[n,k]-8) + beta -- the arithmetic of
+// tl_gemv_q4 (kernels/tensorlib_cuda.cu:772-796) on weights that were repacked once,
+// on the device, from the reference's q4 storage (include/types.h:15-31).
+//
+// Why a second layout.  Read through 2-D tensor maps, the reference layout costs one
+// TMA row request per 128 B of nibbles and per 32 B of scales; the request rate, not
+// HBM, then bounds the stream (the scales alone cost 28 of 73 us on a 152064 x 3584
+// matrix).  Packed, a work unit (16 rows x 256 k: 2048 B of nibbles + 512 B of
+// scales) is one contiguous 2560-byte block, units follow each other in the order
+// the kernel consumes them, and every warp streams its own contiguous byte range with
+// one bulk copy per unit.
+//
+// Inside a unit the nibble words are stored in the order the MMA fragments want them:
+// 16-byte chunk i of lane l = (g, t) holds {row g, row g+8} x {group 2i, group 2i+1},
+// word 4*group + t of the row's 32 words -- four conflict-free LDS.128 per unit and
+// no swizzle arithmetic.  Scales follow as [16 rows][8 groups] f32.
+//
+// Arithmetic.  A masked nibble word is read as two fp16 subnormals (nib * 2^-24, or
+// nib * 2^-20 for the odd nibble of a byte) and is the A operand of mma.sync
+// m16n8k16; the activation is the B operand.  Per slab of 256 k the activation is
+// turned into 24-bit fixed point (round to nearest, relative to the slab's power-of-
+// two bound) and split into two balanced 12-bit digits, which fp16 holds exactly: every
+// product and every partial sum inside the MMA is a small integer multiple of 2^-24,
+// so the tensor-core accumulation is exact whatever its internal rounding, and the
+// only approximation is the fixed-point step (2^-24 of the slab maximum per element,
+// the size of an f32 rounding error of the reference's own accumulation).  Per group of 32 k:
+// acc += sc * (c_hi + 2^-12 c_lo), the -8 offset as 8 * sc * sum(x_g) from the same
+// fixed-point values.
+//
+// Split-K falls out of the unit ranges; partial row tiles are combined by the
+// last-arriving warp in worker order (deterministic, no float atomics, no spin-wait
+// on another CTA).
+#include <cstdlib>
+#include <cstring>
+
+#include "comm.cuh"
+#include "q4_mma.cuh"
+
+namespace tlb {
+
+constexpr int PK_UNIT = 2560;
+constexpr int PK_WARPS = 16;
+
+long long q4p_bytes(long long N, long long K) {
+  const long long RT = (N + 15) / 16, SL = (K + 255) / 256;
+  return RT * SL * PK_UNIT;
+}
+
+// One CTA per unit: 128 threads write the nibble chunks, 128 the scales.  Rows past N
+// and k past K are filled with nibble 8 / scale 0 (weight value zero).
+__global__ void q4_pack_kernel(const unsigned char* __restrict__ q4, int N, int K, int SL,
+                               unsigned char* __restrict__ out) {
+  const int unit = blockIdx.x, rt = unit / SL, s = unit - rt * SL;
+  const int tid = threadIdx.x;
+  const unsigned* words = (const unsigned*)q4;                       // [N][K/8]
+  const float* scales = (const float*)(q4 + (size_t)N * K / 2);      // [N][K/32]
+  unsigned char* u = out + (size_t)unit * PK_UNIT;
+  if (tid < 128) {
+    const int i = tid >> 5, lane = tid & 31, g = lane >> 2, t = lane & 3;
+    unsigned w[4];
+#pragma unroll
+    for (int c = 0; c < 4; c++) {
+      const int row = rt * 16 + g + ((c & 1) ? 8 : 0);
+      const int j = s * 32 + 4 * (2 * i + (c >> 1)) + t;
+      w[c] = (row < N && j * 8 < K) ? words[(size_t)row * (K / 8) + j] : 0x88888888u;
+    }
+    ((uint4*)u)[i * 32 + lane] = make_uint4(w[0], w[1], w[2], w[3]);
+  } else {
+    const int j = tid - 128, r = j >> 3, jj = j & 7;
+    const int row = rt * 16 + r, grp = s * 8 + jj;
+    ((float*)(u + 2048))[j] = (row < N && grp * 32 < K) ? scales[(size_t)row * (K / 32) + grp] : 0.f;
+  }
+}
+
+int launch_q4_pack(const void* q4, int N, int K, void* out, cudaStream_t s) {
+  const int RT = (N + 15) / 16, SL = (K + 255) / 256;
+  q4_pack_kernel<<<RT * SL, 256, 0, s>>>((const unsigned char*)q4, N, K, SL, (unsigned char*)out);
+  TLB_CUDA(cudaGetLastError());
+  return TLB_OK;
+}
+
+struct GemvPParams {
+  const unsigned char* wp;
+  const float* x;
+  float* y;
+  int N, K, SL, RT;
+  unsigned U;
+  float alpha, beta;
+  float* partials;  // [workers][2][16]
+  int* counters;    // [row tiles]
+  int* status;
+  int x_vec_ok;
+  int act;          // 0: x as given; 1: x = [gate(K) | up(K)] -> silu(gate)*up;
+                    // 2: x = rmsnorm(x + delta) * nw, the sum also written to xout
+  const float* delta;
+  const float* nw;
+  float* xout;
+  float eps;
+  int push;         // tensor-parallel: store y into every rank's staging slot
+  CommDev comm;
+};
+
+struct GemvPSmem {
+  size_t ring, bars, red, pslab, q, bfrag, total;
+};
+__host__ __device__ inline GemvPSmem gemvp_smem_layout(int stages, int K) {
+  const int SL = (K + 255) / 256;
+  GemvPSmem L;
+  size_t o = 0;
+  L.ring = o;  o += (size_t)PK_WARPS * stages * PK_UNIT;
+  L.bars = o;  o += (size_t)PK_WARPS * stages * 8;
+  o = (o + 15) & ~(size_t)15;
+  L.red = o;   o += 32 * sizeof(float);
+  L.pslab = o; o += (size_t)((SL + 3) & ~3) * sizeof(float);
+  L.q = o;     o += (size_t)SL * 8 * sizeof(float);
+  L.bfrag = o; o += (size_t)SL * 1024;          // [SL*8 groups][hi, lo][4] uint4
+  L.total = o + 128;                            // slack for the 128-byte alignment of the base
+  return L;
+}
+
+template <int OFF>
+__device__ __forceinline__ uint4 lds128(uint32_t a) {
+  uint4 v;
+  asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4+%5];"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(a), "n"(OFF) : "memory");
+  return v;
+}
+template <int OFF>
+__device__ __forceinline__ float4 lds128f(uint32_t a) {
+  float4 v;
+  asm volatile("ld.shared.v4.f32 {%0,%1,%2,%3}, [%4+%5];"
+               : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "r"(a), "n"(OFF) : "memory");
+  return v;
+}
+template <int OFF>
+__device__ __forceinline__ float2 lds64f(uint32_t a) {
+  float2 v;
+  asm volatile("ld.shared.v2.f32 {%0,%1}, [%2+%3];" : "=f"(v.x), "=f"(v.y) : "r"(a), "n"(OFF) : "memory");
+  return v;
+}
+__device__ __forceinline__ float lds32f(uint32_t a) {
+  float v;
+  asm volatile("ld.shared.f32 %0, [%1];" : "=f"(v) : "r"(a) : "memory");
+  return v;
+}
+
+template <int STAGES>
+__global__ void __launch_bounds__(PK_WARPS * 32, 1) gemv_q4p_kernel(GemvPParams p) {
+  extern __shared__ unsigned char smem_raw[];
+  unsigned char* base = (unsigned char*)(((uintptr_t)smem_raw + 127) & ~(uintptr_t)127);
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int g = lane >> 2, t = lane & 3;
+  const int SL = p.SL;
+  const GemvPSmem L = gemvp_smem_layout(STAGES, p.K);
+  uint64_t* bars = (uint64_t*)(base + L.bars);
+  float* red = (float*)(base + L.red);
+  float* Pslab = (float*)(base + L.pslab);   // [SL]   2^(13+e) of the slab
+  float* Qg = (float*)(base + L.q);          // [SL*8] 8 * sum of the group's fixed-point activations
+  uint4* Bfrag = (uint4*)(base + L.bfrag);   // [SL*8][2][4]
+  unsigned char* myR = base + L.ring + (size_t)warp * STAGES * PK_UNIT;
+  uint64_t* mybar = bars + warp * STAGES;
+
+  // Never more workers than units, so every worker's range is non-empty and the
+  // contributors of a row tile are exactly the owners of its first..last unit.
+  const unsigned Wall = gridDim.x * PK_WARPS;
+  const unsigned Wtot = Wall < p.U ? Wall : p.U;
+  const unsigned wid = blockIdx.x * PK_WARPS + warp;
+  const bool idle = wid >= Wtot;
+  const GvSplit sp = {p.U / Wtot, p.U % Wtot};
+  const unsigned u0 = idle ? 0u : gv_start(wid, sp);
+  const unsigned u1 = idle ? 0u : gv_start(wid + 1, sp);
+  const int n_units = (int)(u1 - u0);
+
+  if (lane == 0) {
+    for (int s = 0; s < STAGES; s++) mbar_init(&mybar[s], 1);
+    mbar_fence_init();
+  }
+  __syncwarp();
+
+  // producer: lane 0 issues one 2560-byte bulk copy per unit, the warp's units are
+  // consecutive in memory
+  const unsigned char* src = p.wp + (size_t)u0 * PK_UNIT;
+  int istage = 0;
+  auto issue_next = [&]() {
+    if (lane == 0) {
+      mbar_expect_tx(&mybar[istage], PK_UNIT);
+      bulk_load_1d(myR + istage * PK_UNIT, src, PK_UNIT, &mybar[istage]);
+    }
+    src += PK_UNIT;
+    if (++istage == STAGES) istage = 0;
+  };
+  // Weights do not depend on the previous kernel: the first stage streams before the
+  // wait.  The other stages are issued right after the activation loads below, so
+  // those small loads are not queued behind the weight traffic.
+  const int pre_total = n_units < STAGES ? n_units : STAGES;
+  if (pre_total > 0) issue_next();
+
+  pdl_wait();  // activations and the fix-up scratch are valid from here
+
+  // ---- activation prep.  One warp per slab of 256 k, two slabs in flight per warp.
+  // Lane l covers x[256*slab + 8*l .. +8) = group jj = l/4, quad slot tt = l%4.
+  float nrm_inv = 1.f;
+  constexpr int PB = 2;
+  for (int job0 = warp; job0 < SL || job0 == warp; job0 += PK_WARPS * PB) {
+    float vv[PB][8], uu[PB][8];
+#pragma unroll
+    for (int b = 0; b < PB; b++) {
+      const int sl = job0 + b * PK_WARPS;
+      const int k0 = sl * 256 + lane * 8;
+      const bool on = sl < SL && k0 < p.K;   // K % 32 == 0: a lane's 8 values are all in or all out
+      auto load8 = [&](const float* s8, float (&o)[8]) {
+        if (on) {
+          if (p.x_vec_ok) {
+            const float4 q0 = *(const float4*)s8, q1 = *(const float4*)(s8 + 4);
+            o[0] = q0.x; o[1] = q0.y; o[2] = q0.z; o[3] = q0.w;
+            o[4] = q1.x; o[5] = q1.y; o[6] = q1.z; o[7] = q1.w;
+          } else {
+#pragma unroll
+            for (int i = 0; i < 8; i++) o[i] = s8[i];
+          }
+        } else {
+#pragma unroll
+          for (int i = 0; i < 8; i++) o[i] = 0.f;
+        }
+      };
+      load8(p.x + k0, vv[b]);
+      if (p.act == 1) load8(p.x + p.K + k0, uu[b]);
+      if (p.act == 2) load8(p.delta + k0, uu[b]);
+    }
+    if (job0 == warp) {
+      // first batch: its loads are in flight, now queue the rest of the weight ring
+      for (int i = 1; i < pre_total; i++) issue_next();
+      if (p.act == 2) {
+        // fused residual add + RMSNorm (tl_add_rmsnorm, kernels/tensorlib_cuda.cu:155-179):
+        // every CTA reduces sum((x+delta)^2) itself from the values it just loaded, in
+        // the same order everywhere, so all CTAs agree on the scale.  (The host only
+        // selects this mode when one batch covers the row.)
+        float sq = 0.f;
+#pragma unroll
+        for (int b = 0; b < PB; b++)
+#pragma unroll
+          for (int i = 0; i < 8; i++) {
+            const float sv = vv[b][i] + uu[b][i];
+            sq = fmaf(sv, sv, sq);
+          }
+        sq = warp_sum(sq);
+        if (lane == 0) red[warp] = sq;
+        __syncthreads();
+        float tot = 0.f;
+        for (int w = 0; w < PK_WARPS; w++) tot += red[w];
+        nrm_inv = 1.0f / sqrtf(tot / (float)p.K + p.eps);
+      }
+    }
+#pragma unroll
+    for (int b = 0; b < PB; b++) {
+      const int sl = job0 + b * PK_WARPS;
+      if (sl >= SL) break;  // warp-uniform
+      float v[8];
+#pragma unroll
+      for (int i = 0; i < 8; i++) v[i] = vv[b][i];
+      if (p.act == 1) {
+        // fused SwiGLU (kernels/tensorlib_cuda.cu:185-192 of the reference): the row
+        // holds gate then up; same expression g / (1 + exp(-g)) * u
+#pragma unroll
+        for (int i = 0; i < 8; i++) v[i] = (v[i] / (1.0f + expf(-v[i]))) * uu[b][i];
+      }
+      if (p.act == 2) {
+        const int k0 = sl * 256 + lane * 8;
+#pragma unroll
+        for (int i = 0; i < 8; i++) {
+          const float sv = v[i] + uu[b][i];
+          const bool in = k0 + i < p.K;
+          if (in && blockIdx.x == 0) p.xout[k0 + i] = sv;
+          v[i] = in ? sv * nrm_inv * p.nw[k0 + i] : 0.f;
+        }
+      }
+      float mx = 0.f;
+#pragma unroll
+      for (int i = 0; i < 8; i++) mx = fmaxf(mx, fabsf(v[i]));
+      mx = warp_max(mx);
+      int e = (int)((__float_as_uint(mx) >> 23) & 0xff) - 126;  // mx < 2^e
+      e = mx > 0.f ? (e < -100 ? -100 : (e > 100 ? 100 : e)) : 0;
+      if (!(mx < 3.0e38f)) e = 100;                              // inf / nan: keep the exponent legal
+      const float s23 = __uint_as_float((unsigned)(127 + 23 - e) << 23);
+      int isum = 0;
+      unsigned hh[8], ll[8];
+#pragma unroll
+      for (int i = 0; i < 8; i++) {
+        const int X = __float2int_rn(v[i] * s23);                // |X| <= 2^23
+        const int d1 = ((X + 2048) & 4095) - 2048;               // [-2048, 2047]
+        const int d0 = (X - d1) >> 12;                           // [-2048, 2048]
+        isum += X;
+        // the odd nibble of a byte reads as nib * 2^-20: its activation digits carry 2^-4
+        const float f = (i & 1) ? 0.0625f : 1.0f;
+        hh[i] = __half_as_ushort(__float2half_rn((float)d0 * f));
+        ll[i] = __half_as_ushort(__float2half_rn((float)d1 * f));
+      }
+      isum += __shfl_xor_sync(0xffffffffu, isum, 1);
+      isum += __shfl_xor_sync(0xffffffffu, isum, 2);
+      uint4 fh, fl;
+      fh.x = hh[0] | (hh[4] << 16); fh.y = hh[1] | (hh[5] << 16);
+      fh.z = hh[2] | (hh[6] << 16); fh.w = hh[3] | (hh[7] << 16);
+      fl.x = ll[0] | (ll[4] << 16); fl.y = ll[1] | (ll[5] << 16);
+      fl.z = ll[2] | (ll[6] << 16); fl.w = ll[3] | (ll[7] << 16);
+      const int jj = lane >> 2, tt = lane & 3;
+      Bfrag[((size_t)(sl * 8 + jj) * 2 + 0) * 4 + tt] = fh;
+      Bfrag[((size_t)(sl * 8 + jj) * 2 + 1) * 4 + tt] = fl;
+      // 8 * sum(x_g) in the same fixed point: (8 * isum) * 2^(e-23)
+      if (tt == 0) Qg[sl * 8 + jj] = (float)isum * __uint_as_float((unsigned)(127 + 3 - 23 + e) << 23);
+      // a non-finite activation makes every output of the slab NaN instead of garbage
+      if (lane == 0)
+        Pslab[sl] = (mx < 3.0e38f) ? __uint_as_float((unsigned)(127 + 13 + e) << 23) : __uint_as_float(0x7fc00000u);
+    }
+  }
+  __syncthreads();
+  pdl_launch_dependents();
+
+  // ---- streaming loop ------------------------------------------------------
+  float acc0 = 0.f, acc1 = 0.f, corr0 = 0.f, corr1 = 0.f;
+  uint4 bq[2] = {make_uint4(0u, 0u, 0u, 0u), make_uint4(0u, 0u, 0u, 0u)};
+  const bool bpred = g < 2;                  // columns 0 (hi digit) and 1 (lo digit) of B
+  const uint32_t ring32 = smem_u32(myR);
+  const uint32_t bh32 = smem_u32(Bfrag) + (uint32_t)((g & 1) * 4 + t) * 16u;
+  const uint32_t q32 = smem_u32(Qg) + (uint32_t)t * 8u, p32 = smem_u32(Pslab);
+  const uint32_t wl = (uint32_t)lane * 16u, sl_ = 2048u + (uint32_t)g * 32u;
+  const uint32_t cl = 2048u + (uint32_t)g * 32u + (uint32_t)t * 8u;
+
+  unsigned ar_seq = 0;
+  if (p.push) ar_seq = *(volatile unsigned*)p.comm.seq;
+  const size_t ar_off =
+      ((size_t)(ar_seq & 1u) * p.comm.size + p.comm.rank) * (size_t)p.comm.slot_floats;
+  auto emit = [&](int n, float v) {
+    v = v * p.alpha + p.beta;
+    if (p.push) {
+      for (int r = 0; r < p.comm.size; r++) st_packet_sys(&p.comm.stage[r][ar_off + n], v, ar_seq + 1u);
+    } else {
+      p.y[n] = v;
+    }
+  };
+  auto flush = [&](int rt) {
+    // lanes t == 0 hold the row sums; the -8*sum(x_g) correction is spread over the quad
+    float v0 = (t == 0 ? acc0 : 0.f) - corr0, v1 = (t == 0 ? acc1 : 0.f) - corr1;
+    v0 += __shfl_xor_sync(0xffffffffu, v0, 1);
+    v0 += __shfl_xor_sync(0xffffffffu, v0, 2);
+    v1 += __shfl_xor_sync(0xffffffffu, v1, 1);
+    v1 += __shfl_xor_sync(0xffffffffu, v1, 2);
+    const unsigned t0 = (unsigned)rt * SL, t1 = t0 + SL;
+    const bool complete = (u0 <= t0) && (u1 >= t1);
+    const int r0 = rt * 16;
+    if (complete) {
+      if (t == 0) {
+        if (r0 + g < p.N) emit(r0 + g, v0);
+        if (r0 + g + 8 < p.N) emit(r0 + g + 8, v1);
+      }
+      return;
+    }
+    // partial: slot 0 when this tile holds the worker's first unit, else slot 1
+    const int slot = (u0 >= t0) ? 0 : 1;
+    float* mine = p.partials + ((size_t)wid * 2 + slot) * 16;
+    if (t == 0) {
+      __stcg(&mine[g], v0);
+      __stcg(&mine[g + 8], v1);
+    }
+    __syncwarp();
+    const unsigned wf = gv_owner(t0, sp), wlast = gv_owner(t1 - 1, sp);
+    int old = 0;
+    if (lane == 0) old = (int)atom_add_acq_rel(&p.counters[rt], 1);  // releases the warp's stores
+    old = __shfl_sync(0xffffffffu, old, 0);
+    if (old != (int)(wlast - wf)) return;  // not the last contributor
+    // Last contributor: lanes 0..15 own one row each and fold the partials in worker
+    // order, four loads in flight.
+    if (lane < 16) {
+      float s = 0.f;
+      for (unsigned w = wf; w <= wlast; w += 4) {
+        float pv[4];
+#pragma unroll
+        for (int k = 0; k < 4; k++) {
+          const unsigned ww = w + k;
+          const bool on = ww <= wlast;
+          const unsigned wz = on ? ww : wlast;
+          const int sl = (gv_start(wz, sp) >= t0) ? 0 : 1;  // started inside this tile
+          pv[k] = on ? __ldcg(p.partials + ((size_t)wz * 2 + sl) * 16 + lane) : 0.f;
+        }
+#pragma unroll
+        for (int k = 0; k < 4; k++) s += pv[k];
+      }
+      if (r0 + lane < p.N) emit(r0 + lane, s);
+    }
+    if (lane == 0) p.counters[rt] = 0;  // leave the counter clean for the next launch
+  };
+
+  int rt = (int)(u0 / (unsigned)SL), s = (int)(u0 - (unsigned)rt * SL);
+  int st = 0;
+  unsigned phase = 0;
+  for (int i = 0; i < n_units; i++) {
+    if (!mbar_wait_bounded(&mybar[st], phase, p.status, 100 + st)) return;
+    const uint32_t ust = ring32 + (uint32_t)st * PK_UNIT;
+    const uint32_t wa = ust + wl, sa = ust + sl_, bs = bh32 + (uint32_t)s * 1024u;
+    // the 8 group scales of rows g and g+8
+    const float4 sa0 = lds128f<0>(sa), sa1 = lds128f<16>(sa), sb0 = lds128f<256>(sa), sb1 = lds128f<272>(sa);
+    const float sc0[8] = {sa0.x, sa0.y, sa0.z, sa0.w, sa1.x, sa1.y, sa1.z, sa1.w};
+    const float sc1[8] = {sb0.x, sb0.y, sb0.z, sb0.w, sb1.x, sb1.y, sb1.z, sb1.w};
+    uint4 w[4];
+    w[0] = lds128<0>(wa); w[1] = lds128<512>(wa); w[2] = lds128<1024>(wa); w[3] = lds128<1536>(wa);
+    float ua0 = 0.f, ua1 = 0.f;
+#define TLB_GRP(JJ, W0, W1, OFF)                                                          \
+  {                                                                                       \
+    if (bpred) bq[(JJ) & 1] = lds128<OFF>(bs);                                            \
+    unsigned w0 = (W0), w1 = (W1);                                                        \
+    float c[4];                                                                           \
+    mma16816_z(c, w0 & 0x000f000fu, w1 & 0x000f000fu, w0 & 0x00f000f0u, w1 & 0x00f000f0u, \
+               bq[(JJ) & 1].x, bq[(JJ) & 1].y);                                           \
+    w0 >>= 8;                                                                             \
+    w1 >>= 8;                                                                             \
+    mma16816(c, w0 & 0x000f000fu, w1 & 0x000f000fu, w0 & 0x00f000f0u, w1 & 0x00f000f0u,   \
+             bq[(JJ) & 1].z, bq[(JJ) & 1].w);                                             \
+    ua0 = fmaf(sc0[JJ], fmaf(c[1], 0.000244140625f, c[0]), ua0);                          \
+    ua1 = fmaf(sc1[JJ], fmaf(c[3], 0.000244140625f, c[2]), ua1);                          \
+  }
+    TLB_GRP(0, w[0].x, w[0].y, 0) TLB_GRP(1, w[0].z, w[0].w, 128)
+    TLB_GRP(2, w[1].x, w[1].y, 256) TLB_GRP(3, w[1].z, w[1].w, 384)
+    TLB_GRP(4, w[2].x, w[2].y, 512) TLB_GRP(5, w[2].z, w[2].w, 640)
+    TLB_GRP(6, w[3].x, w[3].y, 768) TLB_GRP(7, w[3].z, w[3].w, 896)
+#undef TLB_GRP
+    {
+      // lane t of the quad handles groups 2t, 2t+1 of the correction term
+      const float2 q = lds64f<0>(q32 + (uint32_t)s * 32u);
+      const float2 c0 = lds64f<0>(ust + cl), c1 = lds64f<256>(ust + cl);
+      corr0 = fmaf(c0.x, q.x, fmaf(c0.y, q.y, corr0));
+      corr1 = fmaf(c1.x, q.x, fmaf(c1.y, q.y, corr1));
+    }
+    const float P = lds32f(p32 + (uint32_t)s * 4u);
+    acc0 = fmaf(P, ua0, acc0);
+    acc1 = fmaf(P, ua1, acc1);
+    __syncwarp();
+    if (i + STAGES < n_units) issue_next();
+    if (++st == STAGES) { st = 0; phase ^= 1u; }
+    if (++s == SL) {
+      flush(rt);
+      acc0 = acc1 = corr0 = corr1 = 0.f;
+      s = 0;
+      rt++;
+    }
+  }
+  if (n_units > 0 && s != 0) flush(rt);
+}
+
+static int gemvp_stages(int K) {
+  for (int st = 4; st >= 2; st--)
+    if (gemvp_smem_layout(st, K).total <= 227 * 1024) return st;
+  return 0;
+}
+
+bool gemv_q4p_supported(long long N, long long K) {
+  return N > 0 && K > 0 && K % 32 == 0 && K <= (1 << 20) && gemvp_stages((int)K) != 0;
+}
+
+template <int STAGES>
+static int gemvp_launch_t(const GemvPParams& p, int ctas, size_t smem, cudaStream_t stream) {
+  static bool attr = false;
+  if (!attr) {
+    TLB_CUDA(cudaFuncSetAttribute(gemv_q4p_kernel<STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                  227 * 1024));
+    attr = true;
+  }
+  LaunchCfg lc(dim3(ctas), dim3(PK_WARPS * 32), smem, stream, pdl_enabled());
+  TLB_CUDA(cudaLaunchKernelEx(&lc.cfg, gemv_q4p_kernel<STAGES>, p));
+  return TLB_OK;
+}
+
+int gemv_q4p_launch(DeviceCtx* c, const void* packed, const float* x, float* y, int N, int K,
+                    float alpha, float beta, cudaStream_t stream, int max_ctas,
+                    const CommDev* push_comm, int act, const float* delta, const float* nw,
+                    float* xout, float eps) {
+  GemvPParams p;
+  memset(&p, 0, sizeof(p));
+  const int stages = gemvp_stages(K);
+  if (!stages || K % 32) return set_error(TLB_ERR_UNSUPPORTED, "gemv_q4p: K not supported");
+  p.act = act;
+  p.delta = delta; p.nw = nw; p.xout = xout; p.eps = eps;
+  if (act == 2 && (!delta || !nw || !xout))
+    return set_error(TLB_ERR_ARG, "gemv_q4p: fused add+rmsnorm needs its three buffers");
+  if (act == 2 && (K + 255) / 256 > PK_WARPS * 2)
+    return set_error(TLB_ERR_UNSUPPORTED, "gemv_q4p: fused add+rmsnorm needs K <= 8192");
+  p.push = push_comm ? 1 : 0;
+  if (push_comm) p.comm = *push_comm;
+  p.wp = (const unsigned char*)packed;
+  p.x = x; p.y = y; p.N = N; p.K = K;
+  p.alpha = alpha; p.beta = beta;
+  p.partials = c->gemv_partials; p.counters = c->gemv_counters; p.status = c->status;
+  p.RT = (N + 15) / 16; p.SL = (K + 255) / 256;
+  p.U = (unsigned)p.RT * (unsigned)p.SL;
+  bool vec = ((uintptr_t)x & 15) == 0 && (K % 4) == 0;
+  if (act == 2) vec = vec && ((uintptr_t)delta & 15) == 0;
+  p.x_vec_ok = vec ? 1 : 0;
+  if (p.RT > c->gemv_max_tiles)
+    return set_error(TLB_ERR_UNSUPPORTED, "gemv_q4p: N exceeds the fix-up counter capacity");
+  int ctas = max_ctas > 0 ? max_ctas : c->sm_count;
+  const int need = (int)((p.U + PK_WARPS - 1) / PK_WARPS);
+  if (ctas > need) ctas = need;
+  if (ctas * PK_WARPS > c->gemv_max_workers) ctas = c->gemv_max_workers / PK_WARPS;
+  const size_t smem = gemvp_smem_layout(stages, K).total;
+  if (stages == 4) return gemvp_launch_t<4>(p, ctas, smem, stream);
+  if (stages == 3) return gemvp_launch_t<3>(p, ctas, smem, stream);
+  return gemvp_launch_t<2>(p, ctas, smem, stream);
+}
+
+}  // namespace tlb

@@ -102,6 +102,31 @@ def gemv_q4(a, wq, y=None):
     return y
 
 
+class Q4Packed:
+    """A q4 matrix in the library's tile-packed layout (2560-byte units of 16 rows x
+    256 k: nibble words in MMA-fragment order, then the unit's scales).  Made once from
+    a Q4Weight; no counterpart in the reference."""
+
+    def __init__(self, wq):
+        nbytes = lib().tlb_q4p_bytes(wq.N, wq.K)
+        if nbytes < 0:
+            raise ValueError("Q4Packed: bad shape")
+        self.K, self.N = wq.K, wq.N
+        self.buf = torch.empty(nbytes, dtype=torch.uint8, device=wq.buf.device)
+        check(lib().tlb_q4_pack(wq.qw_ptr, wq.N, wq.K, _p(self.buf), _s()))
+
+
+def gemv_q4p(a, wp, alpha=1.0, beta=0.0, y=None):
+    """The decode GEMV on packed weights: y[N] = (a[K] . dequant(W)) * alpha + beta."""
+    _f32c(a, "gemv_q4p")
+    if a.numel() != wp.K:
+        raise ValueError("gemv_q4p: a must hold K elements")
+    if y is None:
+        y = torch.empty(wp.N, dtype=torch.float32, device=a.device)
+    check(lib().tlb_gemv_q4p(_p(a), _p(wp.buf), _p(y), wp.N, wp.K, alpha, beta, _s()))
+    return y
+
+
 def gemm_q4(x, wq, alpha=1.0, beta=0.0, y=None, simt=False):
     """The dot node with its fused affine epilogue (include/array.h:1305-1311,
     2109-2141): y[M,N] = (x[M,K] . dequant(Wq)) * alpha + beta, any M."""

@@ -1,6 +1,6 @@
 """Single-kernel micro-benchmarks of the hot path (CUDA events, HBM-cold rotation).
 
-  python -m cpp_tensorlib_b200.microbench gemv --N 37888 --K 3584 [--M 1] [--copies 4] [--iters 20]
+  python -m cpp_tensorlib_b200.microbench gemv --N 37888 --K 3584 [--M 1] [--packed 1] [--copies 4] [--iters 20]
   python -m cpp_tensorlib_b200.microbench attn --heads 28 --kv-heads 28 --ctx 4096 --D 128
 
 Distinct weight / cache copies are cycled so that the working set exceeds L2 and
@@ -42,12 +42,23 @@ def gemv(a):
     x = torch.randn((a.M, a.K), generator=gen, device="cuda")
     y = torch.empty((a.M, a.N), device="cuda")
 
-    def one_pass():
-        for w in ws:
-            tl.gemm_q4(x, w, y=y)
+    if a.packed:
+        if a.M != 1:
+            raise SystemExit("--packed is the M = 1 decode path")
+        ps = [tl.Q4Packed(w) for w in ws]
+        ws = None
+        xv, yv = x.reshape(-1), y.reshape(-1)
+
+        def one_pass():
+            for w in ps:
+                tl.gemv_q4p(xv, w, y=yv)
+    else:
+        def one_pass():
+            for w in ws:
+                tl.gemm_q4(x, w, y=y)
     ms = _time_graph(one_pass, a.iters) / a.copies
     nbytes = a.N * a.K * 0.625 + 4 * a.M * a.K + 4 * a.M * a.N
-    print(json.dumps(dict(op="gemv_q4", N=a.N, K=a.K, M=a.M, us_per_launch=ms * 1e3,
+    print(json.dumps(dict(op="gemv_q4p" if a.packed else "gemv_q4", N=a.N, K=a.K, M=a.M, us_per_launch=ms * 1e3,
                           algorithmic_bytes=nbytes, GBps=nbytes / ms / 1e6,
                           TFLOPs=2.0 * a.M * a.N * a.K / ms / 1e9,
                           working_set_MB=a.copies * a.N * a.K * 0.625 / 1e6)))
@@ -91,6 +102,7 @@ def main():
     g.add_argument("--N", type=int, default=37888)
     g.add_argument("--K", type=int, default=3584)
     g.add_argument("--M", type=int, default=1)
+    g.add_argument("--packed", type=int, default=0, help="1: tile-packed weights (tlb_gemv_q4p)")
     t = sub.add_parser("attn")
     t.add_argument("--heads", type=int, default=28)
     t.add_argument("--kv-heads", type=int, default=28)

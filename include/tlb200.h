@@ -59,6 +59,18 @@ int tlb_to_q4(const float* w_kn, int64_t K, int64_t N, void* q4, void* stream);
 int tlb_q4_to_f32(const void* q4, int64_t K, int64_t N, float* out_kn, void* stream);
 
 /* ---- int4 dequant-matmul --------------------------------------------------- */
+/* ---- tile-packed int4 weights: the library's own HBM layout for the decode GEMV.
+ * No counterpart in the reference.  A matrix in the reference layout (types.h:15-31) is
+ * repacked once, on the device, into 2560-byte units (16 rows x 256 k: nibble words in
+ * MMA-fragment order, then the unit's f32 scales), N padded to 16 and K to 256 with
+ * zero weights.  tlb_gemv_q4p then computes what cuda::gemv_q4 (cu.h:886-905) computes,
+ * y[n] = alpha * sum_k x[k] * dequant(W)[k,n] + beta, from one contiguous byte stream
+ * per warp. ---- */
+int64_t tlb_q4p_bytes(int64_t N, int64_t K);                 /* size of the packed copy; -1 on bad shape */
+int tlb_q4_pack(const void* q4, int64_t N, int64_t K, void* packed, void* stream);
+int tlb_gemv_q4p(const float* x, const void* packed, float* y, int64_t N, int64_t K, float alpha,
+                 float beta, void* stream);
+
 /* cu.h:886-905 cuda::gemv_q4 / .cu:772-796 tl_gemv_q4:  y[N] = a[K] . dequant(W).
  * group must be 32. */
 int tlb_gemv_q4(const float* a, const void* qw, const float* scales, float* y, int64_t N,

@@ -80,6 +80,48 @@ def test_gemv_cfg1_golden(tl, port, golden):
     assert int(np.argmax(y)) == int(np.argmax(g["y"][0])) == tl.argmax(dev(y))
 
 
+@pytest.mark.parametrize("K,N", [(32, 1), (896, 4864), (3584, 4608), (256, 16), (4864, 896), (18944, 48),
+                                 (1056, 333), (8192, 40)])
+def test_gemv_packed_vs_oracle(tl, port, K, N):
+    """The decode GEMV on tile-packed weights (padding of N to 16 and K to 256, split
+    row tiles, every ring depth) against the oracle; 1e-4 like the reference-layout GEMV."""
+    w = synth.normal(60 + K % 7, N, (K, N), std=0.02)
+    q = port.to_q4(w)
+    x = synth.normal(61, K, (K,))
+    wq = tl.Q4Weight.from_bytes(q, K, N)
+    wp = tl.Q4Packed(wq)
+    got = tl.gemv_q4p(dev(x), wp).cpu().numpy()
+    want = port.gemm_q4(x[None, :], q, N)[0]
+    assert relerr(got, want) < 1e-4
+    got2 = tl.gemv_q4p(dev(x), wp, alpha=0.5, beta=1.0).cpu().numpy()
+    assert relerr(got2, want * 0.5 + 1.0) < 1e-4
+    assert np.array_equal(got, tl.gemv_q4p(dev(x), wp).cpu().numpy())      # deterministic fix-up
+
+
+def test_gemv_packed_outliers_and_raw_nibbles(tl, port):
+    """Activations with 30-sigma outliers and weights holding every nibble value
+    (including 0, i.e. -8, which to_q4 itself never produces): the fixed-point
+    activation split keeps the error at the f32-rounding level."""
+    K, N = 3584, 512
+    rng = np.random.default_rng(5)
+    q = np.empty(N * K // 2 + N * (K // 32) * 4, np.uint8)
+    q[:N * K // 2] = rng.integers(0, 256, N * K // 2, dtype=np.uint8)
+    q[N * K // 2:] = rng.uniform(0.001, 0.01, N * (K // 32)).astype(np.float32).view(np.uint8)
+    x = synth.normal(62, 0, (K,))
+    x[::7] *= 30.0
+    wp = tl.Q4Packed(tl.Q4Weight.from_bytes(q, K, N))
+    got = tl.gemv_q4p(dev(x), wp).cpu().numpy().astype(np.float64)
+    wf = port.q4_to_f32(q, K, N).astype(np.float64)           # [K, N]
+    want = x.astype(np.float64) @ wf
+    assert relerr(got, want) < 5e-5
+
+
+def test_gemv_packed_bad_arguments(tl):
+    from cpp_tensorlib_b200 import lib
+    assert lib().tlb_q4p_bytes(16, 48) == -1
+    assert lib().tlb_q4p_bytes(17, 288) == 2 * 2 * 2560
+
+
 @pytest.mark.parametrize("M,K,N", [(1, 128, 16), (1, 128, 5), (3, 384, 100), (4, 3584, 130), (5, 896, 77),
                                    (8, 1024, 48), (11, 256, 40), (1, 4864, 896), (2, 18944, 64),
                                    (1, 96, 7), (3, 32, 3)])
