@@ -54,6 +54,7 @@ int launch_attn_prefill(DeviceCtx*, const float*, const float*, const float*, fl
 int launch_q4_to_f32(const unsigned char*, int, int, float*, cudaStream_t);
 
 extern unsigned long long* g_gemv_dbg;
+extern unsigned long long* g_attn_dbg;
 static thread_local std::string g_err;
 static std::mutex g_mu;
 static std::map<int, DeviceCtx*> g_ctx;
@@ -178,6 +179,10 @@ int tlb_device_status(int* out2, int clear) {
 
 // Undocumented diagnostic hook: device buffer of [ctas][8] u64 that the GEMV fills
 // with %globaltimer stamps of its phases (NULL switches it off).
+int tlb_debug_attn_timing(void* dbuf) {
+  g_attn_dbg = (unsigned long long*)dbuf;
+  return TLB_OK;
+}
 int tlb_debug_gemv_timing(void* dbuf) {
   g_gemv_dbg = (unsigned long long*)dbuf;
   return TLB_OK;

@@ -29,6 +29,7 @@
 
 namespace tlb {
 
+unsigned long long* g_attn_dbg = nullptr;  // LAB
 constexpr int AT_THREADS = 256;
 constexpr int AT_WARPS = 8;
 constexpr int AT_TK = 32;  // keys per tile
@@ -48,6 +49,7 @@ struct AttnParams {
   int s_cap;     // partial slots per head (= launched splits)
   int sm2;       // 2 * SM count: split target
   int* status;
+  unsigned long long* dbg;
 };
 
 // Number of splits wanted for a context length (monotone non-decreasing in ctx).
@@ -106,6 +108,14 @@ __global__ void __launch_bounds__(AT_THREADS, (HW >= 4 ? 1 : 2))
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int kslot = lane >> 3, sub = lane & 7;
   const int kh = blockIdx.y, sp = blockIdx.x;
+  auto stamp = [&](int i) {
+    if (p.dbg && tid == 0) {
+      unsigned long long tt;
+      asm volatile("mov.u64 %0, %globaltimer;" : "=l"(tt));
+      p.dbg[((size_t)blockIdx.y * gridDim.x + blockIdx.x) * 8 + i] = tt;
+    }
+  };
+  stamp(0);
   const int hs = attn_hs(p.grp, HW);  // warps across heads
   const int ks = AT_WARPS / hs;          // warps across keys
   const int hslot = warp % hs, kslice = warp / hs;
@@ -118,6 +128,7 @@ __global__ void __launch_bounds__(AT_THREADS, (HW >= 4 ? 1 : 2))
 
   pdl_wait();
   pdl_launch_dependents();
+  stamp(1);
 
   const int ctx = p.d_pos ? (int)(*p.d_pos) + 1 : p.ctx;
   const int chunk = attn_chunk(p.n_kv, ctx, p.sm2);
@@ -170,6 +181,8 @@ __global__ void __launch_bounds__(AT_THREADS, (HW >= 4 ? 1 : 2))
   for (int it = 0; it < n_tiles; it++) {
     const int st = it % C::STAGES;
     if (!mbar_wait_bounded(&bars[st], (it / C::STAGES) & 1, p.status, 200 + st)) return;
+    if (it == 0) stamp(2);
+    if (it == n_tiles - 1) stamp(7);
     const int r0 = k_begin + it * AT_TK;
     const int rows = (k_end - r0) < AT_TK ? (k_end - r0) : AT_TK;
     const float4* Ks = (const float4*)((unsigned char*)Kt + (size_t)st * C::TILE_BYTES);
@@ -185,43 +198,57 @@ __global__ void __launch_bounds__(AT_THREADS, (HW >= 4 ? 1 : 2))
       float s[HW];
 #pragma unroll
       for (int h = 0; h < HW; h++) {
-        float d = 0.f;
+        // four independent partial sums keep the FMA chain short
+        float dx = 0.f, dy = 0.f, dz = 0.f, dw = 0.f;
 #pragma unroll
         for (int i = 0; i < C::CH; i++) {
-          d = fmaf(qf[h][i].x, kv[i].x, d);
-          d = fmaf(qf[h][i].y, kv[i].y, d);
-          d = fmaf(qf[h][i].z, kv[i].z, d);
-          d = fmaf(qf[h][i].w, kv[i].w, d);
+          dx = fmaf(qf[h][i].x, kv[i].x, dx);
+          dy = fmaf(qf[h][i].y, kv[i].y, dy);
+          dz = fmaf(qf[h][i].z, kv[i].z, dz);
+          dw = fmaf(qf[h][i].w, kv[i].w, dw);
         }
+        float d = (dx + dy) + (dz + dw);
         d += __shfl_xor_sync(0xffffffffu, d, 1);
         d += __shfl_xor_sync(0xffffffffu, d, 2);
         d += __shfl_xor_sync(0xffffffffu, d, 4);
-        s[h] = d * p.scale;
+        s[h] = valid ? d * p.scale : -INFINITY;
       }
 #pragma unroll
       for (int i = 0; i < C::CH; i++) kv[i] = Vs[rr * (D / 4) + sub + 8 * i];
-      if (valid) {
+      // The four key slots of the warp share one running max per head, so the rescale
+      // branch is warp-uniform and the slots' sums can later be added without exps.
+      float sm[HW];
+      bool grow = false;
+#pragma unroll
+      for (int h = 0; h < HW; h++) {
+        sm[h] = fmaxf(s[h], __shfl_xor_sync(0xffffffffu, s[h], 8));
+        sm[h] = fmaxf(sm[h], __shfl_xor_sync(0xffffffffu, sm[h], 16));
+        grow = grow || (sm[h] > m[h]);
+      }
+      if (grow) {  // one warp-uniform branch per step, rare after the first keys
 #pragma unroll
         for (int h = 0; h < HW; h++) {
-          if (s[h] > m[h]) {
-            const float corr = __expf(m[h] - s[h]);  // exp(-inf) = 0 on the first key
-            l[h] *= corr;
-#pragma unroll
-            for (int i = 0; i < C::CH; i++) {
-              acc[h][i].x *= corr; acc[h][i].y *= corr;
-              acc[h][i].z *= corr; acc[h][i].w *= corr;
-            }
-            m[h] = s[h];
-          }
-          const float pr = __expf(s[h] - m[h]);
-          l[h] += pr;
+          const float mn = fmaxf(m[h], sm[h]);
+          const float corr = (mn == m[h]) ? 1.0f : __expf(m[h] - mn);  // exp(-inf) = 0 at the start
+          l[h] *= corr;
 #pragma unroll
           for (int i = 0; i < C::CH; i++) {
-            acc[h][i].x = fmaf(pr, kv[i].x, acc[h][i].x);
-            acc[h][i].y = fmaf(pr, kv[i].y, acc[h][i].y);
-            acc[h][i].z = fmaf(pr, kv[i].z, acc[h][i].z);
-            acc[h][i].w = fmaf(pr, kv[i].w, acc[h][i].w);
+            acc[h][i].x *= corr; acc[h][i].y *= corr;
+            acc[h][i].z *= corr; acc[h][i].w *= corr;
           }
+          m[h] = mn;
+        }
+      }
+#pragma unroll
+      for (int h = 0; h < HW; h++) {
+        const float pr = __expf(s[h] - m[h]);    // 0 for an invalid row (s = -inf)
+        l[h] += pr;
+#pragma unroll
+        for (int i = 0; i < C::CH; i++) {
+          acc[h][i].x = fmaf(pr, kv[i].x, acc[h][i].x);
+          acc[h][i].y = fmaf(pr, kv[i].y, acc[h][i].y);
+          acc[h][i].z = fmaf(pr, kv[i].z, acc[h][i].z);
+          acc[h][i].w = fmaf(pr, kv[i].w, acc[h][i].w);
         }
       }
     }
@@ -229,44 +256,16 @@ __global__ void __launch_bounds__(AT_THREADS, (HW >= 4 ? 1 : 2))
     if (tid == 0 && it + C::STAGES < n_tiles) issue(it + C::STAGES);
   }
 
-  // ---- merge the 4 key slots of the warp (lanes xor 8, 16), fixed order -----
-#pragma unroll
-  for (int h = 0; h < HW; h++) {
-#pragma unroll
-    for (int o = 8; o <= 16; o <<= 1) {
-      const float mo = __shfl_xor_sync(0xffffffffu, m[h], o);
-      const float lo = __shfl_xor_sync(0xffffffffu, l[h], o);
-      const float mn = fmaxf(m[h], mo);
-      // the lower lane of each pair always plays "a" so both lanes compute the same sum
-      const bool low = (lane & o) == 0;
-      const float ma = low ? m[h] : mo, mb = low ? mo : m[h];
-      const float la = low ? l[h] : lo, lb = low ? lo : l[h];
-      const float ca = (ma == -INFINITY) ? 0.f : __expf(ma - mn);
-      const float cb = (mb == -INFINITY) ? 0.f : __expf(mb - mn);
-      l[h] = la * ca + lb * cb;
-#pragma unroll
-      for (int i = 0; i < C::CH; i++) {
-        float4 ao;
-        ao.x = __shfl_xor_sync(0xffffffffu, acc[h][i].x, o);
-        ao.y = __shfl_xor_sync(0xffffffffu, acc[h][i].y, o);
-        ao.z = __shfl_xor_sync(0xffffffffu, acc[h][i].z, o);
-        ao.w = __shfl_xor_sync(0xffffffffu, acc[h][i].w, o);
-        const float4 a = low ? acc[h][i] : ao, b = low ? ao : acc[h][i];
-        acc[h][i].x = a.x * ca + b.x * cb;
-        acc[h][i].y = a.y * ca + b.y * cb;
-        acc[h][i].z = a.z * ca + b.z * cb;
-        acc[h][i].w = a.w * ca + b.w * cb;
-      }
-      m[h] = mn;
-    }
-  }
-  // ---- per-warp partials to shared memory: mrg[kslice][head][D+2] ----------
+  stamp(3);
+  // ---- every key slot of every warp leaves (acc, m, l) in shared memory (the tile
+  // ring is free now): entry [(kslice*4 + kslot)][head][D+4] = acc[D], m, l, pad, pad.
+  // Slots of one warp share m, so the CTA merge needs one exp per (warp, head).
   const int nheads_pad = hs * HW;
-  if (kslot == 0) {
+  float* ent = (float*)base;
+  {
 #pragma unroll
     for (int h = 0; h < HW; h++) {
-      // entry layout: acc[D], m, l, pad, pad (16-byte aligned stride D+4)
-      float* dst = mrg + ((size_t)kslice * nheads_pad + hslot * HW + h) * (D + 4);
+      float* dst = ent + ((size_t)(kslice * 4 + kslot) * nheads_pad + hslot * HW + h) * (D + 4);
       if (sub == 0) { dst[D] = m[h]; dst[D + 1] = l[h]; }
 #pragma unroll
       for (int i = 0; i < C::CH; i++) *(float4*)(dst + (sub + 8 * i) * 4) = acc[h][i];
@@ -274,46 +273,69 @@ __global__ void __launch_bounds__(AT_THREADS, (HW >= 4 ? 1 : 2))
   }
   __syncthreads();
 
-  // ---- CTA merge over key slices, then either the output or a split partial --
+  // ---- CTA merge over warps and key slots, then either the output or a split partial
   const bool single = (s_live == 1);
-  for (int idx = tid; idx < p.grp * D; idx += AT_THREADS) {
-    const int hh = idx / D, d = idx - hh * D;
+  for (int idx = tid; idx < p.grp * (D / 4); idx += AT_THREADS) {
+    const int hh = idx / (D / 4), d4 = idx - hh * (D / 4);
     float mm = -INFINITY;
     for (int k2 = 0; k2 < ks; k2++)
-      mm = fmaxf(mm, mrg[((size_t)k2 * nheads_pad + hh) * (D + 4) + D]);
-    float ll = 0.f, aa = 0.f;
+      mm = fmaxf(mm, ent[((size_t)(k2 * 4) * nheads_pad + hh) * (D + 4) + D]);
+    float ll = 0.f;
+    float4 aa = make_float4(0.f, 0.f, 0.f, 0.f);
     for (int k2 = 0; k2 < ks; k2++) {
-      const float* src = mrg + ((size_t)k2 * nheads_pad + hh) * (D + 4);
-      const float c = (src[D] == -INFINITY) ? 0.f : __expf(src[D] - mm);
-      ll += src[D + 1] * c;
-      aa += src[d] * c;
+      const float mk = ent[((size_t)(k2 * 4) * nheads_pad + hh) * (D + 4) + D];
+      const float c = (mk == -INFINITY) ? 0.f : __expf(mk - mm);
+#pragma unroll
+      for (int j = 0; j < 4; j++) {
+        const float* src = ent + ((size_t)(k2 * 4 + j) * nheads_pad + hh) * (D + 4);
+        const float4 a = *(const float4*)(src + d4 * 4);
+        ll = fmaf(src[D + 1], c, ll);
+        aa.x = fmaf(a.x, c, aa.x); aa.y = fmaf(a.y, c, aa.y);
+        aa.z = fmaf(a.z, c, aa.z); aa.w = fmaf(a.w, c, aa.w);
+      }
     }
     const int qh = kh * p.grp + hh;
     if (single) {
-      p.out[(size_t)qh * D + d] = aa / ll;
+      const float inv = 1.0f / ll;
+      *(float4*)(p.out + (size_t)qh * D + d4 * 4) = make_float4(aa.x * inv, aa.y * inv, aa.z * inv, aa.w * inv);
     } else {
       // global partial entry: acc[D], m, l, pad, pad  (stride D+4 floats, 16-byte aligned)
       float* dst = p.partials + ((size_t)qh * p.s_cap + sp) * (D + 4);
-      if (d == 0) { __stcg(&dst[D], mm); __stcg(&dst[D + 1], ll); }
-      __stcg(&dst[d], aa);
+      if (d4 == 0) __stcg((float2*)&dst[D], make_float2(mm, ll));
+      __stcg((float4*)&dst[d4 * 4], aa);
     }
   }
+  stamp(4);
   if (single) return;
 
   // ---- on-chip split merge: last CTA of this KV head folds the partials ------
+  // The barrier orders every thread's partial stores before thread 0's acq_rel ticket
+  // (release is cumulative), and the ticket's acquire side plus the second barrier
+  // orders the other CTAs' partials before this CTA's loads: no membar needed.
   __shared__ int is_last;
-  __threadfence();
   __syncthreads();
   if (tid == 0) {
-    const int old = atomicAdd(&p.counters[kh], 1);
+    int old;
+    asm volatile("atom.add.acq_rel.gpu.global.s32 %0, [%1], %2;" : "=r"(old) : "l"(&p.counters[kh]), "r"(1) : "memory");
     is_last = (old == s_live - 1);
   }
   __syncthreads();
+  stamp(5);
   if (!is_last) return;
-  __threadfence();
+  // One thread per (head, 4 dims).  The first 16 splits' accumulators are requested
+  // before the coefficient phase, so its round trip overlaps theirs.
+  const int my = tid;
+  const bool has = my < p.grp * (D / 4);
+  const int mh = has ? my / (D / 4) : 0, md4 = has ? my - mh * (D / 4) : 0;
+  const float* msrc = p.partials + (size_t)(kh * p.grp + mh) * p.s_cap * (D + 4) + md4 * 4;
+  float4 v0[16];
+#pragma unroll
+  for (int k2 = 0; k2 < 16; k2++)
+    v0[k2] = (has && k2 < s_live) ? __ldcg((const float4*)(msrc + (size_t)k2 * (D + 4)))
+                                  : make_float4(0.f, 0.f, 0.f, 0.f);
   // Phase 1 (one warp per head): rescale coefficients c_s = exp(m_s - max m) and the
   // denominator, splits spread over the lanes.  The tile ring is free by now and
-  // holds the coefficients.
+  // holds the coefficients (behind the CTA-merge entries nobody reads any more).
   float* cw = Kt;                       // [grp][s_live]
   float* lden = Kt + p.grp * s_live;    // [grp]
   for (int hh = warp; hh < p.grp; hh += AT_WARPS) {
@@ -342,11 +364,39 @@ __global__ void __launch_bounds__(AT_THREADS, (HW >= 4 ? 1 : 2))
     if (lane == 0) lden[hh] = ll;
   }
   __syncthreads();
-  // Phase 2: one thread per (head, 4 dims); 16 independent 16-byte loads in flight.
-  for (int idx = tid; idx < p.grp * (D / 4); idx += AT_THREADS) {
+  // Phase 2: fold, 16 independent 16-byte loads in flight per thread.
+  if (has) {
+    const float* cwh = cw + mh * s_live;
+    float4 aa = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+    for (int k2 = 0; k2 < 16; k2++)
+      if (k2 < s_live) {
+        const float c = cwh[k2];
+        aa.x = fmaf(v0[k2].x, c, aa.x); aa.y = fmaf(v0[k2].y, c, aa.y);
+        aa.z = fmaf(v0[k2].z, c, aa.z); aa.w = fmaf(v0[k2].w, c, aa.w);
+      }
+    for (int s0 = 16; s0 < s_live; s0 += 16) {
+      float4 v[16];
+#pragma unroll
+      for (int k2 = 0; k2 < 16; k2++)
+        v[k2] = (s0 + k2 < s_live) ? __ldcg((const float4*)(msrc + (size_t)(s0 + k2) * (D + 4)))
+                                   : make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+      for (int k2 = 0; k2 < 16; k2++)
+        if (s0 + k2 < s_live) {
+          const float c = cwh[s0 + k2];
+          aa.x = fmaf(v[k2].x, c, aa.x); aa.y = fmaf(v[k2].y, c, aa.y);
+          aa.z = fmaf(v[k2].z, c, aa.z); aa.w = fmaf(v[k2].w, c, aa.w);
+        }
+    }
+    const float inv = 1.0f / lden[mh];
+    *(float4*)(p.out + (size_t)(kh * p.grp + mh) * D + md4 * 4) =
+        make_float4(aa.x * inv, aa.y * inv, aa.z * inv, aa.w * inv);
+  }
+  // groups wider than 256 / (D/4) heads: the remaining (head, 4 dims) items
+  for (int idx = tid + AT_THREADS; idx < p.grp * (D / 4); idx += AT_THREADS) {
     const int hh = idx / (D / 4), d4 = idx - hh * (D / 4);
-    const int qh = kh * p.grp + hh;
-    const float* src0 = p.partials + (size_t)qh * p.s_cap * (D + 4) + d4 * 4;
+    const float* src0 = p.partials + (size_t)(kh * p.grp + hh) * p.s_cap * (D + 4) + d4 * 4;
     const float* cwh = cw + hh * s_live;
     float4 aa = make_float4(0.f, 0.f, 0.f, 0.f);
     for (int s0 = 0; s0 < s_live; s0 += 16) {
@@ -363,10 +413,11 @@ __global__ void __launch_bounds__(AT_THREADS, (HW >= 4 ? 1 : 2))
           aa.z = fmaf(v[k2].z, c, aa.z); aa.w = fmaf(v[k2].w, c, aa.w);
         }
     }
-    const float den = lden[hh];
-    *(float4*)(p.out + (size_t)qh * D + d4 * 4) =
-        make_float4(aa.x / den, aa.y / den, aa.z / den, aa.w / den);
+    const float inv = 1.0f / lden[hh];
+    *(float4*)(p.out + (size_t)(kh * p.grp + hh) * D + d4 * 4) =
+        make_float4(aa.x * inv, aa.y * inv, aa.z * inv, aa.w * inv);
   }
+  stamp(6);
   if (tid == 0) p.counters[kh] = 0;
 }
 
@@ -407,7 +458,7 @@ int attn_decode_launch(DeviceCtx* c, const float* q, const float* K, const float
   AttnParams p;
   p.q = q; p.K = K; p.V = V; p.out = out; p.partials = partials; p.counters = counters;
   p.d_pos = d_pos; p.ctx = ctx; p.n_q = n_q; p.n_kv = n_kv; p.grp = grp;
-  p.kv_stride = kv_max * D; p.scale = scale; p.sm2 = 2 * c->sm_count; p.status = c->status;
+  p.kv_stride = kv_max * D; p.scale = scale; p.sm2 = 2 * c->sm_count; p.status = c->status; p.dbg = g_attn_dbg;
   const int basis = d_pos ? (int)kv_max : ctx;
   const int splits = d_pos ? attn_splits_wanted(n_kv, basis, p.sm2)
                            : (ctx + attn_chunk(n_kv, ctx, p.sm2) - 1) / attn_chunk(n_kv, ctx, p.sm2);

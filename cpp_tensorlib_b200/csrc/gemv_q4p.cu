@@ -369,13 +369,13 @@ __global__ void __launch_bounds__(PK_WARPS * 32, 1) gemv_q4p_kernel(GemvPParams 
     old = __shfl_sync(0xffffffffu, old, 0);
     if (old != (int)(wlast - wf)) return;  // not the last contributor
     // Last contributor: lanes 0..15 own one row each and fold the partials in worker
-    // order, four loads in flight.
+    // order, sixteen loads in flight (one L2 round trip for up to 16 contributors).
     if (lane < 16) {
       float s = 0.f;
-      for (unsigned w = wf; w <= wlast; w += 4) {
-        float pv[4];
+      for (unsigned w = wf; w <= wlast; w += 16) {
+        float pv[16];
 #pragma unroll
-        for (int k = 0; k < 4; k++) {
+        for (int k = 0; k < 16; k++) {
           const unsigned ww = w + k;
           const bool on = ww <= wlast;
           const unsigned wz = on ? ww : wlast;
@@ -383,7 +383,7 @@ __global__ void __launch_bounds__(PK_WARPS * 32, 1) gemv_q4p_kernel(GemvPParams 
           pv[k] = on ? __ldcg(p.partials + ((size_t)wz * 2 + sl) * 16 + lane) : 0.f;
         }
 #pragma unroll
-        for (int k = 0; k < 4; k++) s += pv[k];
+        for (int k = 0; k < 16; k++) s += pv[k];
       }
       if (r0 + lane < p.N) emit(r0 + lane, s);
     }
