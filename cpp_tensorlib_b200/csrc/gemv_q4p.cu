@@ -41,6 +41,7 @@ namespace tlb {
 
 constexpr int PK_UNIT = 2560;
 constexpr int PK_WARPS = 16;
+constexpr int PK_CTA_UNITS = 64;  // most units one CTA may own in the CTA-owned-tiles mode
 
 long long q4p_bytes(long long N, long long K) {
   const long long RT = (N + 15) / 16, SL = (K + 255) / 256;
@@ -98,11 +99,12 @@ struct GemvPParams {
   float* xout;
   float eps;
   int push;         // tensor-parallel: store y into every rank's staging slot
+  int cta_tiles;    // small matrices: a CTA owns whole row tiles and reduces them in shared memory
   CommDev comm;
 };
 
 struct GemvPSmem {
-  size_t ring, bars, red, pslab, q, bfrag, total;
+  size_t ring, bars, red, ures, pslab, q, bfrag, total;
 };
 __host__ __device__ inline GemvPSmem gemvp_smem_layout(int stages, int K) {
   const int SL = (K + 255) / 256;
@@ -112,6 +114,7 @@ __host__ __device__ inline GemvPSmem gemvp_smem_layout(int stages, int K) {
   L.bars = o;  o += (size_t)PK_WARPS * stages * 8;
   o = (o + 15) & ~(size_t)15;
   L.red = o;   o += 32 * sizeof(float);
+  L.ures = o;  o += (size_t)PK_CTA_UNITS * 16 * sizeof(float);
   L.pslab = o; o += (size_t)((SL + 3) & ~3) * sizeof(float);
   L.q = o;     o += (size_t)SL * 8 * sizeof(float);
   L.bfrag = o; o += (size_t)SL * 1024;          // [SL*8 groups][hi, lo][4] uint4
@@ -168,9 +171,23 @@ __global__ void __launch_bounds__(PK_WARPS * 32, 1) gemv_q4p_kernel(GemvPParams 
   const unsigned wid = blockIdx.x * PK_WARPS + warp;
   const bool idle = wid >= Wtot;
   const GvSplit sp = {p.U / Wtot, p.U % Wtot};
-  const unsigned u0 = idle ? 0u : gv_start(wid, sp);
+  unsigned u0 = idle ? 0u : gv_start(wid, sp);
   const unsigned u1 = idle ? 0u : gv_start(wid + 1, sp);
-  const int n_units = (int)(u1 - u0);
+  int n_units = (int)(u1 - u0);
+  // Small matrices (about two row tiles per CTA or fewer): a CTA owns whole row tiles,
+  // its warps take the tiles' units round-robin and the 16-row results meet in shared
+  // memory -- no partials in global memory, no ticket, no last-arriver chain.
+  const bool own = p.cta_tiles != 0;
+  int tile_b = 0, n_loc = 0;
+  if (own) {
+    const GvSplit ct = {(unsigned)p.RT / gridDim.x, (unsigned)p.RT % gridDim.x};
+    tile_b = (int)gv_start(blockIdx.x, ct);
+    n_loc = ((int)gv_start(blockIdx.x + 1, ct) - tile_b) * SL;
+    n_units = warp < n_loc ? (n_loc - warp + PK_WARPS - 1) / PK_WARPS : 0;
+    u0 = (unsigned)(tile_b * SL + warp);
+  }
+  const unsigned src_step = own ? (unsigned)PK_WARPS * PK_UNIT : (unsigned)PK_UNIT;
+  float* ures = (float*)(base + L.ures);
 
   if (lane == 0) {
     for (int s = 0; s < STAGES; s++) mbar_init(&mybar[s], 1);
@@ -187,7 +204,7 @@ __global__ void __launch_bounds__(PK_WARPS * 32, 1) gemv_q4p_kernel(GemvPParams 
       mbar_expect_tx(&mybar[istage], PK_UNIT);
       bulk_load_1d(myR + istage * PK_UNIT, src, PK_UNIT, &mybar[istage]);
     }
-    src += PK_UNIT;
+    src += src_step;
     if (++istage == STAGES) istage = 0;
   };
   // Weights do not depend on the previous kernel: the first stage streams before the
@@ -394,7 +411,11 @@ __global__ void __launch_bounds__(PK_WARPS * 32, 1) gemv_q4p_kernel(GemvPParams 
   int st = 0;
   unsigned phase = 0;
   for (int i = 0; i < n_units; i++) {
-    if (!mbar_wait_bounded(&mybar[st], phase, p.status, 100 + st)) return;
+    if (own && i > 0) {   // next unit of this warp: PK_WARPS further on
+      s += PK_WARPS;
+      while (s >= SL) { s -= SL; rt++; }
+    }
+    if (!mbar_wait_bounded(&mybar[st], phase, p.status, 100 + st)) break;
     const uint32_t ust = ring32 + (uint32_t)st * PK_UNIT;
     const uint32_t wa = ust + wl, sa = ust + sl_, bs = bh32 + (uint32_t)s * 1024u;
     // the 8 group scales of rows g and g+8
@@ -436,12 +457,40 @@ __global__ void __launch_bounds__(PK_WARPS * 32, 1) gemv_q4p_kernel(GemvPParams 
     __syncwarp();
     if (i + STAGES < n_units) issue_next();
     if (++st == STAGES) { st = 0; phase ^= 1u; }
+    if (own) {
+      // this unit's 16 row sums go to the CTA's table, slot = unit index inside the CTA
+      float v0 = (t == 0 ? acc0 : 0.f) - corr0, v1 = (t == 0 ? acc1 : 0.f) - corr1;
+      v0 += __shfl_xor_sync(0xffffffffu, v0, 1);
+      v0 += __shfl_xor_sync(0xffffffffu, v0, 2);
+      v1 += __shfl_xor_sync(0xffffffffu, v1, 1);
+      v1 += __shfl_xor_sync(0xffffffffu, v1, 2);
+      if (t == 0) {
+        float* dst = ures + (size_t)((rt - tile_b) * SL + s) * 16;
+        dst[g] = v0;
+        dst[g + 8] = v1;
+      }
+      acc0 = acc1 = corr0 = corr1 = 0.f;
+      continue;
+    }
     if (++s == SL) {
       flush(rt);
       acc0 = acc1 = corr0 = corr1 = 0.f;
       s = 0;
       rt++;
     }
+  }
+  if (own) {
+    __syncthreads();
+    // one thread per output row: fold the row's SL unit results in slab order
+    for (int idx = tid; idx < (n_loc / SL) * 16; idx += PK_WARPS * 32) {
+      const int tl = idx >> 4, row = idx & 15;
+      const float* srcp = ures + (size_t)tl * SL * 16 + row;
+      float sum = 0.f;
+      for (int k = 0; k < SL; k++) sum += srcp[k * 16];
+      const int n = (tile_b + tl) * 16 + row;
+      if (n < p.N) emit(n, sum);
+    }
+    return;
   }
   if (n_units > 0 && s != 0) flush(rt);
 }
@@ -500,6 +549,16 @@ int gemv_q4p_launch(DeviceCtx* c, const void* packed, const float* x, float* y, 
   const int need = (int)((p.U + PK_WARPS - 1) / PK_WARPS);
   if (ctas > need) ctas = need;
   if (ctas * PK_WARPS > c->gemv_max_workers) ctas = c->gemv_max_workers / PK_WARPS;
+  {
+    // CTA-owned row tiles when that leaves every CTA at most about two units per warp
+    int cb = max_ctas > 0 ? max_ctas : c->sm_count;
+    if (cb > p.RT) cb = p.RT;
+    const int tiles_max = (p.RT + cb - 1) / cb;
+    if (tiles_max * p.SL <= PK_CTA_UNITS && tiles_max * p.SL <= 2 * PK_WARPS + PK_WARPS / 2) {
+      p.cta_tiles = 1;
+      ctas = cb;
+    }
+  }
   const size_t smem = gemvp_smem_layout(stages, K).total;
   if (stages == 4) return gemvp_launch_t<4>(p, ctas, smem, stream);
   if (stages == 3) return gemvp_launch_t<3>(p, ctas, smem, stream);
