@@ -6,6 +6,7 @@
 
 #include "../../include/tlb200.h"
 #include "comm.cuh"
+#include "gemv_q4p.cuh"
 
 namespace tlb {
 
@@ -39,13 +40,7 @@ int launch_kv_append(float*, float*, const float*, const float*, unsigned, const
 int launch_incr_u32(unsigned*, cudaStream_t);
 int launch_argmax(DeviceCtx*, const float*, int, int*, int*, cudaStream_t);
 int launch_to_q4(const float*, int, int, unsigned char*, cudaStream_t);
-bool gemv_q4p_supported(long long N, long long K);
-long long q4p_bytes(long long N, long long K);
-int launch_q4_pack(const void* q4, int N, int K, void* out, cudaStream_t s);
-int gemv_q4p_launch(DeviceCtx* c, const void* packed, const float* x, float* y, int N, int K,
-                    float alpha, float beta, cudaStream_t stream, int max_ctas,
-                    const CommDev* push_comm, int act, const float* delta, const float* nw,
-                    float* xout, float eps);
+
 int launch_split_heads(const float*, const float*, float*, int, long long, long long, int, int, cudaStream_t);
 int launch_merge_heads(const float*, float*, int, int, int, cudaStream_t);
 int launch_kv_fill(float*, float*, const float*, const float*, int, long long, int, int, int, cudaStream_t);
@@ -292,7 +287,7 @@ int tlb_q4_pack(const void* q4, int64_t N, int64_t K, void* packed, void* stream
   TLB_REQUIRE(N > 0 && K > 0 && K % 32 == 0, "tlb_q4_pack: K must be a positive multiple of 32");
   TLB_REQUIRE(N < (1ll << 31) && K <= (1ll << 20), "tlb_q4_pack: shape out of range");
   TLB_REQUIRE((((uintptr_t)q4 | (uintptr_t)packed) & 15) == 0, "tlb_q4_pack: pointers must be 16-byte aligned");
-  return launch_q4_pack(q4, (int)N, (int)K, packed, S(stream));
+  return launch_q4_pack(q4, (int)N, (int)K, packed, 0, S(stream));
 }
 
 int tlb_gemv_q4p(const float* x, const void* packed, float* y, int64_t N, int64_t K, float alpha,
@@ -303,7 +298,7 @@ int tlb_gemv_q4p(const float* x, const void* packed, float* y, int64_t N, int64_
   TLB_REQUIRE(((uintptr_t)packed & 15) == 0, "tlb_gemv_q4p: packed weights must be 16-byte aligned");
   CTX(c);
   return gemv_q4p_launch(c, packed, x, y, (int)N, (int)K, alpha, beta, S(stream), 0, nullptr, 0,
-                         nullptr, nullptr, nullptr, 0.f);
+                         nullptr, nullptr, nullptr, 0.f, nullptr);
 }
 
 int tlb_gemv_q4(const float* a, const void* qw, const float* scales, float* y, int64_t N,

@@ -20,6 +20,7 @@
 #include <vector>
 
 #include "comm.cuh"
+#include "gemv_q4p.cuh"
 #include "token_kernel.cuh"
 
 namespace tlb {
@@ -29,13 +30,7 @@ extern unsigned long long* g_gemv_dbg;
 int make_q4_tensor_maps(const void* qw, const void* scales, int N, int K, CUtensorMap* tmW,
                         CUtensorMap* tmS);
 bool gemv_q4_tma_eligible(const void* qw, const void* scales, int N, int K, int M);
-bool gemv_q4p_supported(long long N, long long K);
-long long q4p_bytes(long long N, long long K);
-int launch_q4_pack(const void* q4, int N, int K, void* out, cudaStream_t s);
-int gemv_q4p_launch(DeviceCtx* c, const void* packed, const float* x, float* y, int N, int K,
-                    float alpha, float beta, cudaStream_t stream, int max_ctas,
-                    const CommDev* push_comm, int act, const float* delta, const float* nw,
-                    float* xout, float eps);
+
 int gemv_q4_launch(DeviceCtx* c, const CUtensorMap& tmW, const CUtensorMap& tmS, const float* x,
                    long long ldx, int M, float* y, long long ldy, int N, int K, float alpha,
                    float beta, cudaStream_t stream, int max_ctas, const CommDev* push_comm,
@@ -67,6 +62,7 @@ struct Linear {
   bool tma = false;
   CUtensorMap tmW, tmS;
   void* packed = nullptr;  // tile-packed copy for the decode GEMV (owned)
+  int pair_h = 0;          // > 0: packed with rows r, r + pair_h in one thread (pair epilogues)
   const float* scales() const { return (const float*)((const char*)q4 + (size_t)N * K / 2); }
 };
 
@@ -113,15 +109,17 @@ struct Decoder {
   long long launches_per_token = 0;
 };
 
-static int set_linear(Linear& L, const void* q4, int K, int N) {
+static int set_linear(Linear& L, const void* q4, int K, int N, int pair_h = 0) {
   L.q4 = q4;
   L.K = K;
   L.N = N;
   L.tma = gemv_q4_tma_eligible(q4, L.scales(), N, K, 1);
   if (L.packed) { cudaFree(L.packed); L.packed = nullptr; }
+  L.pair_h = 0;
   if (gemv_q4p_supported(N, K)) {
+    if (pair_h > 0 && N % 16 == 0 && pair_h % 8 == 0 && N % (2 * pair_h) == 0) L.pair_h = pair_h;
     TLB_CUDA(cudaMalloc(&L.packed, (size_t)q4p_bytes(N, K)));
-    int rc = launch_q4_pack(q4, N, K, L.packed, nullptr);
+    int rc = launch_q4_pack(q4, N, K, L.packed, L.pair_h, nullptr);
     if (rc) return rc;
     TLB_CUDA(cudaStreamSynchronize(nullptr));
   }
@@ -138,11 +136,16 @@ struct NormIn {
 };
 
 static int run_linear(DeviceCtx* c, const Linear& L, const float* x, float* y, cudaStream_t s,
-                      const CommDev* push, int act = 0, const NormIn* nm = nullptr, float eps = 0.f) {
+                      const CommDev* push, int act = 0, const NormIn* nm = nullptr, float eps = 0.f,
+                      const PairEpi* epi = nullptr) {
   if (!L.q4) return set_error(TLB_ERR_STATE, "decoder: a linear weight was never set");
+  if ((epi != nullptr) != (L.pair_h > 0))
+    return set_error(TLB_ERR_STATE, "decoder: pair-packed weight and epilogue do not match");
   if (L.packed && !(nm && (L.K + 255) / 256 > 32))
     return gemv_q4p_launch(c, L.packed, x, y, L.N, L.K, 1.0f, 0.0f, s, 0, push, nm ? 2 : act,
-                           nm ? nm->delta : nullptr, nm ? nm->w : nullptr, nm ? nm->xout : nullptr, eps);
+                           nm ? nm->delta : nullptr, nm ? nm->w : nullptr, nm ? nm->xout : nullptr, eps,
+                           epi);
+  if (epi) return set_error(TLB_ERR_STATE, "decoder: pair epilogue without a packed weight");
   if (L.tma && nm)
     return gemv_q4_launch(c, L.tmW, L.tmS, x, L.K, 1, y, L.N, L.N, L.K, 1.0f, 0.0f, s, 0, push, 2,
                           nm->delta, nm->w, nm->xout, eps);
@@ -153,6 +156,19 @@ static int run_linear(DeviceCtx* c, const Linear& L, const float* x, float* y, c
   if (act) return set_error(TLB_ERR_UNSUPPORTED, "decoder: the fused SwiGLU needs ff % 128 == 0");
   if (push) return set_error(TLB_ERR_UNSUPPORTED, "decoder: tensor-parallel linears need K % 128 == 0");
   return gemv_q4_simt_launch(x, L.K, 1, L.q4, L.scales(), y, L.N, L.N, L.K, 1.0f, 0.0f, s);
+}
+
+static PairEpi qkv_epilogue(const Decoder* d, const DecLayer& L) {
+  PairEpi e;
+  e.kind = 2; e.H = d->hd / 2; e.out = d->qkv; e.Kc = L.Kc; e.Vc = L.Vc;
+  e.bq = L.bq; e.bk = L.bk; e.bv = L.bv; e.n_q = d->n_q; e.n_kv = d->n_kv; e.D = d->hd;
+  e.d_pos = d->d_pos; e.kv_stride = (long long)d->max_ctx * d->hd; e.base = d->rope_base;
+  return e;
+}
+static PairEpi swiglu_epilogue(const Decoder* d) {
+  PairEpi e;
+  e.kind = 1; e.H = d->ff; e.out = d->mb;
+  return e;
 }
 
 // Build the phase table of the persistent kernel (once; all pointers are fixed).
@@ -276,23 +292,31 @@ static int forward(Decoder* d, cudaStream_t s) {
     float* xalt = d->xb;
     for (int l = 0; l < d->n_layers; l++) {
       DecLayer& L = d->layers[l];
+      const PairEpi eq = qkv_epilogue(d, L), eg = swiglu_epilogue(d);
+      const PairEpi* pq = L.wqkv.pair_h > 0 ? &eq : nullptr;
+      const PairEpi* pg = L.wgu.pair_h > 0 ? &eg : nullptr;
       if (l == 0) {
-        RUN(run_linear(c, L.wqkv, d->hb, d->qkv, s, nullptr));
+        RUN(run_linear(c, L.wqkv, d->hb, d->qkv, s, nullptr, 0, nullptr, 0.f, pq));
       } else {
         NormIn nm{d->t1, L.an, xalt};
-        RUN(run_linear(c, L.wqkv, x, d->qkv, s, nullptr, 0, &nm, d->eps));
+        RUN(run_linear(c, L.wqkv, x, d->qkv, s, nullptr, 0, &nm, d->eps, pq));
         float* t = x; x = xalt; xalt = t;
       }
-      RUN(launch_qkv_post(d->qkv, L.bq, L.bk, L.bv, L.Kc, L.Vc, d->n_q, d->n_kv, d->hd, d->d_pos,
-                          d->max_ctx, d->rope_base, s));
+      if (!pq)
+        RUN(launch_qkv_post(d->qkv, L.bq, L.bk, L.bv, L.Kc, L.Vc, d->n_q, d->n_kv, d->hd, d->d_pos,
+                            d->max_ctx, d->rope_base, s));
       RUN(attn_decode_launch(c, d->qkv, L.Kc, L.Vc, d->att, d->n_q, d->n_kv, 0, d->max_ctx, d->hd,
                              d->scale, d->d_pos, (float*)((char*)d->attn_partials + 256),
                              (int*)d->attn_partials, s));
       RUN(run_linear(c, L.wo, d->att, d->t0, s, nullptr));
       NormIn nf{d->t0, L.fn, xalt};
-      RUN(run_linear(c, L.wgu, x, d->gu, s, nullptr, 0, &nf, d->eps));
+      RUN(run_linear(c, L.wgu, x, d->gu, s, nullptr, 0, &nf, d->eps, pg));
       { float* t = x; x = xalt; xalt = t; }
-      RUN(run_linear(c, L.wd, d->gu, d->t1, s, nullptr, 1));
+      if (pg) {
+        RUN(run_linear(c, L.wd, d->mb, d->t1, s, nullptr, 0));
+      } else {
+        RUN(run_linear(c, L.wd, d->gu, d->t1, s, nullptr, 1));
+      }
     }
     NormIn no{d->t1, d->onorm, xalt};
     RUN(run_linear(c, d->lm_head, x, d->logits, s, nullptr, 0, &no, d->eps));
@@ -303,9 +327,13 @@ static int forward(Decoder* d, cudaStream_t s) {
   }
   for (int l = 0; l < d->n_layers; l++) {
     DecLayer& L = d->layers[l];
-    RUN(run_linear(c, L.wqkv, d->hb, d->qkv, s, nullptr));
-    RUN(launch_qkv_post(d->qkv, L.bq, L.bk, L.bv, L.Kc, L.Vc, d->n_q, d->n_kv, d->hd, d->d_pos,
-                        d->max_ctx, d->rope_base, s));
+    const PairEpi eq = qkv_epilogue(d, L), eg = swiglu_epilogue(d);
+    const PairEpi* pq = L.wqkv.pair_h > 0 ? &eq : nullptr;
+    const PairEpi* pg = L.wgu.pair_h > 0 ? &eg : nullptr;
+    RUN(run_linear(c, L.wqkv, d->hb, d->qkv, s, nullptr, 0, nullptr, 0.f, pq));
+    if (!pq)
+      RUN(launch_qkv_post(d->qkv, L.bq, L.bk, L.bv, L.Kc, L.Vc, d->n_q, d->n_kv, d->hd, d->d_pos,
+                          d->max_ctx, d->rope_base, s));
     RUN(attn_decode_launch(c, d->qkv, L.Kc, L.Vc, d->att, d->n_q, d->n_kv, 0, d->max_ctx, d->hd,
                            d->scale, d->d_pos, (float*)((char*)d->attn_partials + 256),
                            (int*)d->attn_partials, s));
@@ -316,9 +344,11 @@ static int forward(Decoder* d, cudaStream_t s) {
       RUN(run_linear(c, L.wo, d->att, d->t0, s, nullptr));
       RUN(launch_add_rmsnorm(d->x, d->t0, L.fn, d->x, d->hb, E, d->eps, 1, s));
     }
-    RUN(run_linear(c, L.wgu, d->hb, d->gu, s, nullptr));
-    const bool fuse_act = L.wd.tma;  // SwiGLU inside the down projection's activation prep
-    if (!fuse_act) RUN(launch_swiglu(d->gu, d->mb, d->ff, 1, s));
+    RUN(run_linear(c, L.wgu, d->hb, d->gu, s, nullptr, 0, nullptr, 0.f, pg));
+    // SwiGLU: in the gate|up epilogue (pair-packed), else inside the down projection's
+    // activation prep, else its own kernel
+    const bool fuse_act = !pg && L.wd.tma;
+    if (!pg && !fuse_act) RUN(launch_swiglu(d->gu, d->mb, d->ff, 1, s));
     const float* nextw = (l + 1 < d->n_layers) ? d->layers[l + 1].an : d->onorm;
     if (tp) {
       RUN(run_linear(c, L.wd, fuse_act ? d->gu : d->mb, nullptr, s, &d->comm, fuse_act ? 1 : 0));
@@ -462,7 +492,10 @@ int tlb_decoder_set_linear(void* h, int64_t layer, int which, const void* q4, in
   }
   TLB_REQUIRE(K == wantK && N == wantN, "tlb_decoder_set_linear: shape does not match the config");
   d->tk_ready = false;
-  return set_linear(*L, q4, (int)K, (int)N);
+  // q/k/v rows are packed as rotary pairs and gate/up rows as (gate, up) pairs, so the
+  // projection's epilogue finishes rope / SwiGLU itself
+  const int pair_h = which == 0 ? d->hd / 2 : (which == 2 ? d->ff : 0);
+  return set_linear(*L, q4, (int)K, (int)N, pair_h);
 }
 
 // which: 0 attn norm  1 ffn norm  2 bq  3 bk  4 bv (may be NULL: no bias)  5 final norm

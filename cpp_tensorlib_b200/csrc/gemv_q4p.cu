@@ -34,7 +34,7 @@
 #include <cstdlib>
 #include <cstring>
 
-#include "comm.cuh"
+#include "gemv_q4p.cuh"
 #include "q4_mma.cuh"
 
 namespace tlb {
@@ -50,8 +50,22 @@ long long q4p_bytes(long long N, long long K) {
 
 // One CTA per unit: 128 threads write the nibble chunks, 128 the scales.  Rows past N
 // and k past K are filled with nibble 8 / scale 0 (weight value zero).
+//
+// pair_h > 0 additionally permutes the rows so that original rows r and r + pair_h of
+// every block of 2*pair_h rows (a rotary pair of a head, pair_h = D/2; a gate row and
+// its up row, pair_h = ff) become local rows g and g + 8 of one tile.  Both values of
+// a pair then end up in the same thread of the GEMV, whose epilogue can apply
+// rope / SwiGLU without another kernel.  Packed row T*16 + lr holds original row
+// (pi / H) * 2H + pi % H + (lr >> 3) * H with pi = T*8 + (lr & 7).
+__host__ __device__ inline int q4p_orig_row(int packed_row, int pair_h) {
+  if (pair_h <= 0) return packed_row;
+  const int T = packed_row >> 4, lr = packed_row & 15;
+  const int pi = T * 8 + (lr & 7);
+  return (pi / pair_h) * 2 * pair_h + pi % pair_h + (lr >> 3) * pair_h;
+}
+
 __global__ void q4_pack_kernel(const unsigned char* __restrict__ q4, int N, int K, int SL,
-                               unsigned char* __restrict__ out) {
+                               unsigned char* __restrict__ out, int pair_h) {
   const int unit = blockIdx.x, rt = unit / SL, s = unit - rt * SL;
   const int tid = threadIdx.x;
   const unsigned* words = (const unsigned*)q4;                       // [N][K/8]
@@ -62,21 +76,23 @@ __global__ void q4_pack_kernel(const unsigned char* __restrict__ q4, int N, int 
     unsigned w[4];
 #pragma unroll
     for (int c = 0; c < 4; c++) {
-      const int row = rt * 16 + g + ((c & 1) ? 8 : 0);
+      const int row = q4p_orig_row(rt * 16 + g + ((c & 1) ? 8 : 0), pair_h);
       const int j = s * 32 + 4 * (2 * i + (c >> 1)) + t;
       w[c] = (row < N && j * 8 < K) ? words[(size_t)row * (K / 8) + j] : 0x88888888u;
     }
     ((uint4*)u)[i * 32 + lane] = make_uint4(w[0], w[1], w[2], w[3]);
   } else {
     const int j = tid - 128, r = j >> 3, jj = j & 7;
-    const int row = rt * 16 + r, grp = s * 8 + jj;
+    const int row = q4p_orig_row(rt * 16 + r, pair_h), grp = s * 8 + jj;
     ((float*)(u + 2048))[j] = (row < N && grp * 32 < K) ? scales[(size_t)row * (K / 32) + grp] : 0.f;
   }
 }
 
-int launch_q4_pack(const void* q4, int N, int K, void* out, cudaStream_t s) {
+int launch_q4_pack(const void* q4, int N, int K, void* out, int pair_h, cudaStream_t s) {
   const int RT = (N + 15) / 16, SL = (K + 255) / 256;
-  q4_pack_kernel<<<RT * SL, 256, 0, s>>>((const unsigned char*)q4, N, K, SL, (unsigned char*)out);
+  if (pair_h > 0 && (N % 16 != 0 || pair_h % 8 != 0 || N % (2 * pair_h) != 0))
+    return set_error(TLB_ERR_ARG, "q4_pack: paired rows need N % 16 == 0, pair_h % 8 == 0, N % (2 pair_h) == 0");
+  q4_pack_kernel<<<RT * SL, 256, 0, s>>>((const unsigned char*)q4, N, K, SL, (unsigned char*)out, pair_h);
   TLB_CUDA(cudaGetLastError());
   return TLB_OK;
 }
@@ -99,6 +115,7 @@ struct GemvPParams {
   float* xout;
   float eps;
   int push;         // tensor-parallel: store y into every rank's staging slot
+  PairEpi epi;
   int cta_tiles;    // small matrices: a CTA owns whole row tiles and reduces them in shared memory
   CommDev comm;
 };
@@ -355,6 +372,46 @@ __global__ void __launch_bounds__(PK_WARPS * 32, 1) gemv_q4p_kernel(GemvPParams 
       p.y[n] = v;
     }
   };
+  // pair index pi of a pair-packed matrix, a = its first row's sum, b = its second's
+  auto emit_pair = [&](int pi, float a, float b) {
+    a = a * p.alpha + p.beta;
+    b = b * p.alpha + p.beta;
+    if (p.epi.kind == 1) {
+      // tl_swiglu (kernels/tensorlib_cuda.cu:185-192): silu(gate) * up, same expression
+      p.epi.out[pi] = (a / (1.0f + expf(-a))) * b;
+      return;
+    }
+    // kind 2: the seam after the fused QKV projection (bench/cuda/qwen_model.h:700-716):
+    // q <- rope(q + bq), rope(k + bk) and v + bv into cache row *d_pos.  Angle in double,
+    // like the CPU reference's trig (the f32 fast path drifts past 1e-3 on the low pairs).
+    const int half = p.epi.D >> 1, D = p.epi.D;
+    const int h = pi / half, j = pi - h * half;
+    const unsigned pos = *p.epi.d_pos;
+    if (h >= p.epi.n_q + p.epi.n_kv) {
+      const int kh = h - p.epi.n_q - p.epi.n_kv;
+      if (p.epi.bv) { a += p.epi.bv[kh * D + j]; b += p.epi.bv[kh * D + j + half]; }
+      float* dst = p.epi.Vc + (size_t)kh * p.epi.kv_stride + (size_t)pos * D;
+      dst[j] = a;
+      dst[j + half] = b;
+      return;
+    }
+    const double theta = exp2(-2.0 * (double)j / (double)D * log2((double)p.epi.base));
+    double sd, cd;
+    sincos((double)pos * theta, &sd, &cd);
+    const float c = (float)cd, sn = (float)sd;
+    if (h < p.epi.n_q) {
+      if (p.epi.bq) { a += p.epi.bq[h * D + j]; b += p.epi.bq[h * D + j + half]; }
+      float* dst = p.epi.out + (size_t)h * D;
+      dst[j] = a * c - b * sn;
+      dst[j + half] = a * sn + b * c;
+    } else {
+      const int kh = h - p.epi.n_q;
+      if (p.epi.bk) { a += p.epi.bk[kh * D + j]; b += p.epi.bk[kh * D + j + half]; }
+      float* dst = p.epi.Kc + (size_t)kh * p.epi.kv_stride + (size_t)pos * D;
+      dst[j] = a * c - b * sn;
+      dst[j + half] = a * sn + b * c;
+    }
+  };
   auto flush = [&](int rt) {
     // lanes t == 0 hold the row sums; the -8*sum(x_g) correction is spread over the quad
     float v0 = (t == 0 ? acc0 : 0.f) - corr0, v1 = (t == 0 ? acc1 : 0.f) - corr1;
@@ -367,8 +424,12 @@ __global__ void __launch_bounds__(PK_WARPS * 32, 1) gemv_q4p_kernel(GemvPParams 
     const int r0 = rt * 16;
     if (complete) {
       if (t == 0) {
-        if (r0 + g < p.N) emit(r0 + g, v0);
-        if (r0 + g + 8 < p.N) emit(r0 + g + 8, v1);
+        if (p.epi.kind) {
+          emit_pair(rt * 8 + g, v0, v1);
+        } else {
+          if (r0 + g < p.N) emit(r0 + g, v0);
+          if (r0 + g + 8 < p.N) emit(r0 + g + 8, v1);
+        }
       }
       return;
     }
@@ -387,8 +448,8 @@ __global__ void __launch_bounds__(PK_WARPS * 32, 1) gemv_q4p_kernel(GemvPParams 
     if (old != (int)(wlast - wf)) return;  // not the last contributor
     // Last contributor: lanes 0..15 own one row each and fold the partials in worker
     // order, sixteen loads in flight (one L2 round trip for up to 16 contributors).
+    float s = 0.f;
     if (lane < 16) {
-      float s = 0.f;
       for (unsigned w = wf; w <= wlast; w += 16) {
         float pv[16];
 #pragma unroll
@@ -402,7 +463,11 @@ __global__ void __launch_bounds__(PK_WARPS * 32, 1) gemv_q4p_kernel(GemvPParams 
 #pragma unroll
         for (int k = 0; k < 16; k++) s += pv[k];
       }
-      if (r0 + lane < p.N) emit(r0 + lane, s);
+      if (!p.epi.kind && r0 + lane < p.N) emit(r0 + lane, s);
+    }
+    if (p.epi.kind) {
+      const float s2 = __shfl_down_sync(0xffffffffu, s, 8);   // row lane + 8 of the tile
+      if (lane < 8) emit_pair(rt * 8 + lane, s, s2);
     }
     if (lane == 0) p.counters[rt] = 0;  // leave the counter clean for the next launch
   };
@@ -482,6 +547,17 @@ __global__ void __launch_bounds__(PK_WARPS * 32, 1) gemv_q4p_kernel(GemvPParams 
   if (own) {
     __syncthreads();
     // one thread per output row: fold the row's SL unit results in slab order
+    if (p.epi.kind) {
+      // one thread per pair: rows (lr, lr + 8) of a tile
+      for (int idx = tid; idx < (n_loc / SL) * 8; idx += PK_WARPS * 32) {
+        const int tl = idx >> 3, lr = idx & 7;
+        const float* srcp = ures + (size_t)tl * SL * 16 + lr;
+        float sa = 0.f, sb = 0.f;
+        for (int k = 0; k < SL; k++) { sa += srcp[k * 16]; sb += srcp[k * 16 + 8]; }
+        emit_pair((tile_b + tl) * 8 + lr, sa, sb);
+      }
+      return;
+    }
     for (int idx = tid; idx < (n_loc / SL) * 16; idx += PK_WARPS * 32) {
       const int tl = idx >> 4, row = idx & 15;
       const float* srcp = ures + (size_t)tl * SL * 16 + row;
@@ -521,9 +597,14 @@ static int gemvp_launch_t(const GemvPParams& p, int ctas, size_t smem, cudaStrea
 int gemv_q4p_launch(DeviceCtx* c, const void* packed, const float* x, float* y, int N, int K,
                     float alpha, float beta, cudaStream_t stream, int max_ctas,
                     const CommDev* push_comm, int act, const float* delta, const float* nw,
-                    float* xout, float eps) {
+                    float* xout, float eps, const PairEpi* epi) {
   GemvPParams p;
   memset(&p, 0, sizeof(p));
+  if (epi) {
+    p.epi = *epi;
+    if (push_comm) return set_error(TLB_ERR_ARG, "gemv_q4p: a pair epilogue cannot push");
+    if (N % 16) return set_error(TLB_ERR_ARG, "gemv_q4p: a pair epilogue needs N % 16 == 0");
+  }
   const int stages = gemvp_stages(K);
   if (!stages || K % 32) return set_error(TLB_ERR_UNSUPPORTED, "gemv_q4p: K not supported");
   p.act = act;
