@@ -28,7 +28,7 @@ int gemm_q4_tc_launch(DeviceCtx* c, const float* x, long long ldx, int M, const 
 size_t attn_partials_bytes(int n_q, int n_kv, long long kv_max, int D, int sm_count);
 int attn_decode_launch(DeviceCtx* c, const float* q, const float* K, const float* V, float* out,
                        int n_q, int n_kv, int ctx, long long kv_max, int D, float scale,
-                       const unsigned* d_pos, float* partials, int* counters, cudaStream_t stream);
+                       const unsigned* d_pos, float* partials, int* counters, cudaStream_t stream, int early_kv);
 int launch_rmsnorm(const float*, const float*, float*, int, float, int, cudaStream_t);
 int launch_add_rmsnorm(const float*, const float*, const float*, float*, float*, int, float, int,
                        cudaStream_t);
@@ -325,7 +325,7 @@ int tlb_attn_decode(const float* q, const float* K, const float* V, float* out, 
     c->attn_scratch_bytes = need;
   }
   return attn_decode_launch(c, q, K, V, out, (int)n_q, (int)n_kv, (int)ctx, kv_max, (int)D, scale,
-                            nullptr, c->attn_scratch, c->attn_counters, S(stream));
+                            nullptr, c->attn_scratch, c->attn_counters, S(stream), 0);
 }
 
 int64_t tlb_attn_partials_bytes(int64_t n_q, int64_t n_kv, int64_t kv_max, int64_t D) {
@@ -343,7 +343,7 @@ int tlb_attn_decode_dpos(const float* q, const float* K, const float* V, float* 
   CTX(c);
   return attn_decode_launch(c, q, K, V, out, (int)n_q, (int)n_kv, 0, kv_max, (int)D, scale,
                             (const unsigned*)d_pos, (float*)((char*)partials + 256),
-                            (int*)partials, S(stream));
+                            (int*)partials, S(stream), 0);
 }
 
 int tlb_rmsnorm(const float* x, const float* w, float* out, int64_t n, float eps, int64_t rows,

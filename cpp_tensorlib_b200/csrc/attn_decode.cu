@@ -22,6 +22,7 @@
 //    capacity's split count; split boundaries are derived from ctx by the same
 //    device function in both variants, so the two are bit-identical at every
 //    position (the property check_attn64.cpp:91-102 of the reference guards).
+#include <cstdlib>
 #include <mutex>
 #include <string>
 
@@ -29,7 +30,8 @@
 
 namespace tlb {
 
-unsigned long long* g_attn_dbg = nullptr;  // LAB
+// Diagnostics: when set, every launch records per-CTA phase timestamps there.
+unsigned long long* g_attn_dbg = nullptr;
 constexpr int AT_THREADS = 256;
 constexpr int AT_WARPS = 8;
 constexpr int AT_TK = 32;  // keys per tile
@@ -49,13 +51,15 @@ struct AttnParams {
   int s_cap;     // partial slots per head (= launched splits)
   int sm2;       // 2 * SM count: split target
   int* status;
+  int early_kv;  // cache rows below ctx-1 and *d_pos are older than the preceding kernel:
+                 // their tiles may be requested before the grid dependency resolves
   unsigned long long* dbg;
 };
 
 // Number of splits wanted for a context length (monotone non-decreasing in ctx).
 __host__ __device__ inline int attn_splits_wanted(int n_kv, int ctx, int sm2) {
   int s = sm2 / (n_kv > 0 ? n_kv : 1);
-  int cap = ctx / 128;
+  int cap = (ctx + 127) / 128;   // at most 128 keys (4 tiles) per split before splits grow
   if (s > cap) s = cap;
   if (s > 96) s = 96;  // the merge keeps (m, l) of at most 3 splits per lane
   return s < 1 ? 1 : s;
@@ -126,17 +130,13 @@ __global__ void __launch_bounds__(AT_THREADS, (HW >= 4 ? 1 : 2))
   }
   __syncthreads();
 
-  pdl_wait();
-  pdl_launch_dependents();
-  stamp(1);
-
   const int ctx = p.d_pos ? (int)(*p.d_pos) + 1 : p.ctx;
   const int chunk = attn_chunk(p.n_kv, ctx, p.sm2);
   const int s_live = (ctx + chunk - 1) / chunk;
-  if (sp >= s_live) return;  // capacity-sized grid: splits past the live count do nothing
+  const bool dead = sp >= s_live;  // capacity-sized grid: splits past the live count do nothing
   const int k_begin = sp * chunk;
   const int k_end = k_begin + chunk < ctx ? k_begin + chunk : ctx;
-  const int n_tiles = (k_end - k_begin + AT_TK - 1) / AT_TK;
+  const int n_tiles = dead ? 0 : (k_end - k_begin + AT_TK - 1) / AT_TK;
 
   const float* Kh = p.K + (size_t)kh * p.kv_stride;
   const float* Vh = p.V + (size_t)kh * p.kv_stride;
@@ -152,9 +152,20 @@ __global__ void __launch_bounds__(AT_THREADS, (HW >= 4 ? 1 : 2))
     bulk_load_1d((unsigned char*)Vt + (size_t)st * C::TILE_BYTES, Vh + (size_t)r0 * D, bytes,
                  &bars[st]);
   };
+  // Tiles that end below the newest row do not depend on the preceding kernel (it only
+  // appends row ctx-1): with early_kv they stream while that kernel drains.
+  const int pre = n_tiles < C::STAGES ? n_tiles : C::STAGES;
+  int early = 0;
+  if (p.early_kv && tid == 0) {
+    while (early < pre && k_begin + (early + 1) * AT_TK <= ctx - 1) issue(early++);
+  }
+
+  pdl_wait();
+  pdl_launch_dependents();
+  stamp(1);
+  if (dead) return;
   if (tid == 0) {
-    const int pre = n_tiles < C::STAGES ? n_tiles : C::STAGES;
-    for (int i = 0; i < pre; i++) issue(i);
+    for (int i = early; i < pre; i++) issue(i);
   }
 
   // q fragments: lane owns chunks {sub + 8*i}
@@ -448,7 +459,7 @@ static int launch_t(const AttnParams& p, int splits, cudaStream_t stream) {
 int attn_decode_launch(DeviceCtx* c, const float* q, const float* K, const float* V, float* out,
                        int n_q, int n_kv, int ctx, long long kv_max, int D, float scale,
                        const unsigned* d_pos, float* partials, int* counters,
-                       cudaStream_t stream) {
+                       cudaStream_t stream, int early_kv) {
   if (D != 64 && D != 128) return set_error(TLB_ERR_UNSUPPORTED, "attn_decode: D must be 64 or 128");
   if (n_kv <= 0 || n_q % n_kv != 0) return set_error(TLB_ERR_ARG, "attn_decode: n_q % n_kv != 0");
   const int grp = n_q / n_kv;
@@ -458,7 +469,7 @@ int attn_decode_launch(DeviceCtx* c, const float* q, const float* K, const float
   AttnParams p;
   p.q = q; p.K = K; p.V = V; p.out = out; p.partials = partials; p.counters = counters;
   p.d_pos = d_pos; p.ctx = ctx; p.n_q = n_q; p.n_kv = n_kv; p.grp = grp;
-  p.kv_stride = kv_max * D; p.scale = scale; p.sm2 = 2 * c->sm_count; p.status = c->status; p.dbg = g_attn_dbg;
+  p.kv_stride = kv_max * D; p.scale = scale; p.sm2 = 2 * c->sm_count; p.status = c->status; p.dbg = g_attn_dbg; p.early_kv = early_kv;
   const int basis = d_pos ? (int)kv_max : ctx;
   const int splits = d_pos ? attn_splits_wanted(n_kv, basis, p.sm2)
                            : (ctx + attn_chunk(n_kv, ctx, p.sm2) - 1) / attn_chunk(n_kv, ctx, p.sm2);
@@ -554,5 +565,5 @@ extern "C" int tlb_attn_decode_noalloc(const float* q, const float* K, const flo
   local.status = nullptr;
   return attn_decode_launch(&local, q, K, V, out, (int)n_q, (int)n_kv, (int)ctx, kv_max, (int)D,
                             scale, nullptr, (float*)((unsigned char*)nd->ptr + NOALLOC_COUNTER_BYTES),
-                            (int*)nd->ptr, s);
+                            (int*)nd->ptr, s, 0);
 }

@@ -41,7 +41,7 @@ int gemv_q4_simt_launch(const float* x, long long ldx, int M, const void* qw, co
 size_t attn_partials_bytes(int n_q, int n_kv, long long kv_max, int D, int sm_count);
 int attn_decode_launch(DeviceCtx* c, const float* q, const float* K, const float* V, float* out,
                        int n_q, int n_kv, int ctx, long long kv_max, int D, float scale,
-                       const unsigned* d_pos, float* partials, int* counters, cudaStream_t stream);
+                       const unsigned* d_pos, float* partials, int* counters, cudaStream_t stream, int early_kv);
 int launch_rmsnorm(const float*, const float*, float*, int, float, int, cudaStream_t);
 int launch_add_rmsnorm(const float*, const float*, const float*, float*, float*, int, float, int,
                        cudaStream_t);
@@ -51,7 +51,8 @@ int launch_swiglu(const float*, float*, int, int, cudaStream_t);
 int launch_incr_u32(unsigned*, cudaStream_t);
 int launch_qkv_post(float*, const float*, const float*, const float*, float*, float*, int, int,
                     int, const unsigned*, long long, float, cudaStream_t);
-int launch_embed_gather(const float*, const int*, float*, int, cudaStream_t);
+int launch_embed_gather(const float*, const int*, float*, int, float2*, const unsigned*, int, float,
+                        cudaStream_t);
 int launch_argmax(DeviceCtx*, const float*, int, int*, int*, cudaStream_t);
 int launch_argmax_tp(DeviceCtx*, const float*, int, unsigned, const CommDev&, int*, int*,
                      cudaStream_t);
@@ -86,6 +87,7 @@ struct Decoder {
         *t1 = nullptr, *gu = nullptr, *mb = nullptr, *logits = nullptr;
   void* attn_partials = nullptr;
   unsigned* d_pos = nullptr;
+  float2* rope_cs = nullptr;  // [hd/2] (cos, sin) of the current position, refreshed per token
   int* d_tok = nullptr;      // token consumed by the next forward; overwritten with the result
   int* d_tok_out = nullptr;  // copy of the last result (read back by the host)
   int *h_tok = nullptr, *h_out = nullptr;  // pinned
@@ -141,7 +143,7 @@ static int run_linear(DeviceCtx* c, const Linear& L, const float* x, float* y, c
   if (!L.q4) return set_error(TLB_ERR_STATE, "decoder: a linear weight was never set");
   if ((epi != nullptr) != (L.pair_h > 0))
     return set_error(TLB_ERR_STATE, "decoder: pair-packed weight and epilogue do not match");
-  if (L.packed && !(nm && (L.K + 255) / 256 > 32))
+  if (L.packed && !(nm && (L.K + 255) / 256 > 64))
     return gemv_q4p_launch(c, L.packed, x, y, L.N, L.K, 1.0f, 0.0f, s, 0, push, nm ? 2 : act,
                            nm ? nm->delta : nullptr, nm ? nm->w : nullptr, nm ? nm->xout : nullptr, eps,
                            epi);
@@ -163,6 +165,7 @@ static PairEpi qkv_epilogue(const Decoder* d, const DecLayer& L) {
   e.kind = 2; e.H = d->hd / 2; e.out = d->qkv; e.Kc = L.Kc; e.Vc = L.Vc;
   e.bq = L.bq; e.bk = L.bk; e.bv = L.bv; e.n_q = d->n_q; e.n_kv = d->n_kv; e.D = d->hd;
   e.d_pos = d->d_pos; e.kv_stride = (long long)d->max_ctx * d->hd; e.base = d->rope_base;
+  e.rope_cs = d->rope_cs;
   return e;
 }
 static PairEpi swiglu_epilogue(const Decoder* d) {
@@ -279,7 +282,7 @@ static int forward(Decoder* d, cudaStream_t s) {
     n++;                 \
   } while (0)
   if (!d->embed || !d->onorm) return set_error(TLB_ERR_STATE, "decoder: embed / final norm not set");
-  RUN(launch_embed_gather(d->embed, d->d_tok, d->x, E, s));
+  RUN(launch_embed_gather(d->embed, d->d_tok, d->x, E, d->rope_cs, d->d_pos, d->hd, d->rope_base, s));
   RUN(launch_rmsnorm(d->x, d->layers[0].an, d->hb, E, d->eps, 1, s));
   bool all_tma = d->lm_head.tma;
   for (auto& L : d->layers) all_tma = all_tma && L.wqkv.tma && L.wo.tma && L.wgu.tma && L.wd.tma;
@@ -307,7 +310,7 @@ static int forward(Decoder* d, cudaStream_t s) {
                             d->max_ctx, d->rope_base, s));
       RUN(attn_decode_launch(c, d->qkv, L.Kc, L.Vc, d->att, d->n_q, d->n_kv, 0, d->max_ctx, d->hd,
                              d->scale, d->d_pos, (float*)((char*)d->attn_partials + 256),
-                             (int*)d->attn_partials, s));
+                             (int*)d->attn_partials, s, 1));
       RUN(run_linear(c, L.wo, d->att, d->t0, s, nullptr));
       NormIn nf{d->t0, L.fn, xalt};
       RUN(run_linear(c, L.wgu, x, d->gu, s, nullptr, 0, &nf, d->eps, pg));
@@ -336,7 +339,7 @@ static int forward(Decoder* d, cudaStream_t s) {
                           d->max_ctx, d->rope_base, s));
     RUN(attn_decode_launch(c, d->qkv, L.Kc, L.Vc, d->att, d->n_q, d->n_kv, 0, d->max_ctx, d->hd,
                            d->scale, d->d_pos, (float*)((char*)d->attn_partials + 256),
-                           (int*)d->attn_partials, s));
+                           (int*)d->attn_partials, s, 1));
     if (tp) {
       RUN(run_linear(c, L.wo, d->att, nullptr, s, &d->comm));
       RUN(launch_add_rmsnorm_ar(d->x, L.fn, d->x, d->hb, E, d->eps, d->comm, c->status, s));
@@ -420,6 +423,7 @@ int tlb_decoder_create(const int64_t* cfg, int n_cfg, float eps, float rope_base
   size_t pb = 256 + attn_partials_bytes(d->n_q, d->n_kv, d->max_ctx, d->hd, c->sm_count);
   TLB_CUDA(cudaMalloc(&d->attn_partials, pb));
   TLB_CUDA(cudaMemset(d->attn_partials, 0, pb));
+  TLB_CUDA(cudaMalloc(&d->rope_cs, (size_t)(d->hd / 2) * sizeof(float2)));
   TLB_CUDA(cudaMalloc(&d->d_pos, 16));
   TLB_CUDA(cudaMemset(d->d_pos, 0, 16));
   TLB_CUDA(cudaMalloc(&d->d_tok, 16));
@@ -465,6 +469,7 @@ int tlb_decoder_destroy(void* h) {
   cudaFree(d->zeros); cudaFree(d->d_bar);
   if (d->d_phases) cudaFree(d->d_phases);
   if (d->d_maps) cudaFree(d->d_maps);
+  cudaFree(d->rope_cs);
   cudaFree(d->attn_partials); cudaFree(d->d_pos); cudaFree(d->d_tok); cudaFree(d->flags_local);
   cudaFreeHost(d->h_tok);
   delete d;

@@ -178,12 +178,24 @@ __global__ void qkv_post_kernel(float* qkv, const float* __restrict__ bq,
 // x0 <- embed[*d_tok]  (one block).  The reference gathers the row on the host
 // and uploads it (bench/cuda/qwen_model.h:530-535, 768-772); here the table is
 // resident in HBM and only the 4-byte token id crosses PCIe.
+// With rope_cs != NULL the block also fills the token's rotary table: (cos, sin) of
+// (*d_pos) * base^(-2j/D) for j < D/2, the double-precision expression of rope_pair,
+// so that the 28 layers' projections read 64 pairs instead of each evaluating sincos.
 __global__ void embed_gather_kernel(const float* __restrict__ embed,
-                                    const int* __restrict__ d_tok, float* __restrict__ x, int n) {
+                                    const int* __restrict__ d_tok, float* __restrict__ x, int n,
+                                    float2* __restrict__ rope_cs, const unsigned* __restrict__ d_pos,
+                                    int D, float rope_base) {
   pdl_wait();
   pdl_launch_dependents();
   const size_t base = (size_t)(*d_tok) * n;
   for (int i = threadIdx.x; i < n; i += blockDim.x) x[i] = embed[base + i];
+  if (rope_cs && (int)threadIdx.x < D / 2) {
+    const int j = threadIdx.x;
+    const double theta = exp2(-2.0 * (double)j / (double)D * log2((double)rope_base));
+    double sd, cd;
+    sincos((double)(*d_pos) * theta, &sd, &cd);
+    rope_cs[j] = make_float2((float)cd, (float)sd);
+  }
 }
 
 // ---------------------------------------------------------------------------
@@ -435,9 +447,12 @@ int launch_qkv_post(float* qkv, const float* bq, const float* bk, const float* b
                               d_pos, kv_stride, base));
   return TLB_OK;
 }
-int launch_embed_gather(const float* embed, const int* d_tok, float* x, int n, cudaStream_t s) {
-  LaunchCfg lc(dim3(1), dim3(row_threads(n)), 0, s, pdl_enabled());
-  TLB_CUDA(cudaLaunchKernelEx(&lc.cfg, embed_gather_kernel, embed, d_tok, x, n));
+int launch_embed_gather(const float* embed, const int* d_tok, float* x, int n, float2* rope_cs,
+                        const unsigned* d_pos, int D, float rope_base, cudaStream_t s) {
+  int threads = row_threads(n);
+  if (threads < D / 2) threads = D / 2;
+  LaunchCfg lc(dim3(1), dim3(threads), 0, s, pdl_enabled());
+  TLB_CUDA(cudaLaunchKernelEx(&lc.cfg, embed_gather_kernel, embed, d_tok, x, n, rope_cs, d_pos, D, rope_base));
   return TLB_OK;
 }
 int launch_argmax(DeviceCtx* c, const float* in, int n, int* out_idx, int* out_idx2,

@@ -232,7 +232,7 @@ __global__ void __launch_bounds__(PK_WARPS * 32, 1) gemv_q4p_kernel(GemvPParams 
 
   pdl_wait();  // activations and the fix-up scratch are valid from here
 
-  // ---- activation prep.  One warp per slab of 256 k, two slabs in flight per warp.
+  // ---- activation prep.  One warp per slab of 256 k, four slabs in flight per warp.
   // Lane l covers x[256*slab + 8*l .. +8) = group jj = l/4, quad slot tt = l%4.
   float nrm_inv = 1.f;
   constexpr int PB = 2;
@@ -264,6 +264,8 @@ __global__ void __launch_bounds__(PK_WARPS * 32, 1) gemv_q4p_kernel(GemvPParams 
     }
     if (job0 == warp) {
       // first batch: its loads are in flight, now queue the rest of the weight ring
+      // (an L2 prefetch of the units behind the ring was tried here and lost 4 us on the
+      // 85 MB gate|up matrix: the demand copies queue behind it)
       for (int i = 1; i < pre_total; i++) issue_next();
       if (p.act == 2) {
         // fused residual add + RMSNorm (tl_add_rmsnorm, kernels/tensorlib_cuda.cu:155-179):
@@ -395,10 +397,19 @@ __global__ void __launch_bounds__(PK_WARPS * 32, 1) gemv_q4p_kernel(GemvPParams 
       dst[j + half] = b;
       return;
     }
-    const double theta = exp2(-2.0 * (double)j / (double)D * log2((double)p.epi.base));
-    double sd, cd;
-    sincos((double)pos * theta, &sd, &cd);
-    const float c = (float)cd, sn = (float)sd;
+    float c, sn;
+    if (p.epi.rope_cs) {
+      // (cos, sin) of this position, computed once per token by the same expression
+      const float2 cs = p.epi.rope_cs[j];
+      c = cs.x;
+      sn = cs.y;
+    } else {
+      const double theta = exp2(-2.0 * (double)j / (double)D * log2((double)p.epi.base));
+      double sd, cd;
+      sincos((double)pos * theta, &sd, &cd);
+      c = (float)cd;
+      sn = (float)sd;
+    }
     if (h < p.epi.n_q) {
       if (p.epi.bq) { a += p.epi.bq[h * D + j]; b += p.epi.bq[h * D + j + half]; }
       float* dst = p.epi.out + (size_t)h * D;
@@ -611,8 +622,8 @@ int gemv_q4p_launch(DeviceCtx* c, const void* packed, const float* x, float* y, 
   p.delta = delta; p.nw = nw; p.xout = xout; p.eps = eps;
   if (act == 2 && (!delta || !nw || !xout))
     return set_error(TLB_ERR_ARG, "gemv_q4p: fused add+rmsnorm needs its three buffers");
-  if (act == 2 && (K + 255) / 256 > PK_WARPS * 2)
-    return set_error(TLB_ERR_UNSUPPORTED, "gemv_q4p: fused add+rmsnorm needs K <= 8192");
+  if (act == 2 && (K + 255) / 256 > PK_WARPS * 4)
+    return set_error(TLB_ERR_UNSUPPORTED, "gemv_q4p: fused add+rmsnorm needs K <= 16384");
   p.push = push_comm ? 1 : 0;
   if (push_comm) p.comm = *push_comm;
   p.wp = (const unsigned char*)packed;

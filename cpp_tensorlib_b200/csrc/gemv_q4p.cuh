@@ -20,6 +20,7 @@ struct PairEpi {
   const unsigned* d_pos = nullptr;
   long long kv_stride = 0;
   float base = 0.f;
+  const float2* rope_cs = nullptr;  // optional [D/2] (cos, sin) of position *d_pos
 };
 
 long long q4p_bytes(long long N, long long K);
