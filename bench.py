@@ -125,7 +125,7 @@ def build_decoder(cfg, max_ctx, rank, world, ctx0):
 
 
 def gemv_sweep(cfg, dec, reps):
-    """The int4 GEMV kernel alone over one token's weight matrices (28 x {qkv, o,
+    """The packed int4 GEMV kernel alone over one token's weight matrices (28 x {qkv, o,
     gate|up, down} + lm_head = 4.42 GB at 7B, HBM-cold because the set is far larger
     than L2), launched back to back eagerly and bracketed by CUDA events on the
     launching stream.  Returns (bytes per pass, ms per pass, launches per pass)."""
@@ -136,8 +136,9 @@ def gemv_sweep(cfg, dec, reps):
     xs = {w.K: torch.randn(w.K, device="cuda") for w in ws}
     ys = {w.N: torch.empty(w.N, device="cuda") for w in ws}
     nbytes = sum(w.N * w.K * 0.625 + 4 * w.K + 4 * w.N for w in ws)
+    ws = [tlc.Q4Packed(w) for w in ws]          # the layout the decoder's linears stream
     for w in ws:
-        tlc.gemv_q4(xs[w.K], w, ys[w.N])
+        tlc.gemv_q4p(xs[w.K], w, y=ys[w.N])
     torch.cuda.synchronize()
     # one pass recorded into a CUDA graph so host launch cost does not gate the GPU
     g = torch.cuda.CUDAGraph()
@@ -145,7 +146,7 @@ def gemv_sweep(cfg, dec, reps):
     with torch.cuda.stream(side):
         with torch.cuda.graph(g, stream=side):
             for w in ws:
-                tlc.gemv_q4(xs[w.K], w, ys[w.N])
+                tlc.gemv_q4p(xs[w.K], w, y=ys[w.N])
     torch.cuda.synchronize()
     g.replay()
     torch.cuda.synchronize()
@@ -259,8 +260,8 @@ def main():
     max_ctx = CTX0 + max(128, K + W) + 8
     dec = build_decoder(cfg, max_ctx, rank, world, CTX0)
     dec.connect()
-    # measured on B200: the two modes are within 3 % at 1 GPU (both are bound by the same
-    # per-phase chains); the per-op graph is the default everywhere
+    # the per-op CUDA graph (packed GEMV kernels) is the default everywhere; the persistent
+    # per-token kernel still streams the reference layout and is slower
     mode = args.mode if args.mode != "auto" else "ops"
     if mode == "persistent":
         dec.set_mode(1)
@@ -328,7 +329,7 @@ def main():
                     e2e=dict(value=e2e_tps, unit="tokens/s", h2d_bytes_per_step=4, d2h_bytes_per_step=4),
                     gpu_launches=launches,
                     roofline=dict(bound="hbm", achieved=achieved, peak=peak, unit="GB/s", frac=achieved / peak,
-                                  traffic=gbytes * 1.036, peak_source=peak_src, kernel="gemv_q4_mma_kernel",
+                                  traffic=gbytes * 1.036, peak_source=peak_src, kernel="gemv_q4p_kernel",
                                   traffic_note="dram read+write of the ncu capture of the gate|up shape "
                                                "(1.036 x algorithmic, profiles/gemv_q4_gate_up_7b.md) scaled "
                                                "to the sweep by bytes",
