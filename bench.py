@@ -236,9 +236,6 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--layers", type=int, default=0, help="diagnostic: fewer layers (line is marked invalid)")
     ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--mode", default="auto", choices=["auto", "ops", "persistent"],
-                    help="decoder execution: one kernel per op, or the persistent per-token kernel "
-                         "(single GPU); auto = per-op CUDA graph")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -260,11 +257,6 @@ def main():
     max_ctx = CTX0 + max(128, K + W) + 8
     dec = build_decoder(cfg, max_ctx, rank, world, CTX0)
     dec.connect()
-    # the per-op CUDA graph (packed GEMV kernels) is the default everywhere; the persistent
-    # per-token kernel still streams the reference layout and is slower
-    mode = args.mode if args.mode != "auto" else "ops"
-    if mode == "persistent":
-        dec.set_mode(1)
     dec.set_pos(CTX0)
     dec.set_token(1)
     dec.capture()

@@ -65,7 +65,6 @@ SIGNATURES = {
     "tlb_decoder_logits": (ci, [vp, C.POINTER(vp)]),
     "tlb_decoder_set_pos": (ci, [vp, i64, vp]),
     "tlb_decoder_set_token": (ci, [vp, i64, vp]),
-    "tlb_decoder_set_mode": (ci, [vp, ci]),
     "tlb_decoder_forward": (ci, [vp, vp]),
     "tlb_decoder_launches_per_token": (i64, [vp]),
     "tlb_decoder_capture": (ci, [vp]),

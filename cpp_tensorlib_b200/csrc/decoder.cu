@@ -21,7 +21,6 @@
 
 #include "comm.cuh"
 #include "gemv_q4p.cuh"
-#include "token_kernel.cuh"
 
 namespace tlb {
 
@@ -98,14 +97,6 @@ struct Decoder {
   void* peer_stage_base[TP_MAX] = {};
   void* peer_flags_base[TP_MAX] = {};
   bool peers_open = false;
-  // persistent per-token kernel (mode 1): phase table, tensor maps, grid-barrier words
-  int mode = 0;
-  bool tk_ready = false;
-  TkPhase* d_phases = nullptr;
-  CUtensorMap* d_maps = nullptr;
-  unsigned* d_bar = nullptr;
-  float* zeros = nullptr;
-  int tk_n_phases = 0, tk_kmax = 0;
   // graph
   cudaGraphExec_t graph = nullptr;
   long long launches_per_token = 0;
@@ -174,104 +165,11 @@ static PairEpi swiglu_epilogue(const Decoder* d) {
   return e;
 }
 
-// Build the phase table of the persistent kernel (once; all pointers are fixed).
-static int build_token_table(Decoder* d, DeviceCtx* c) {
-  if (d->tp_size != 1) return set_error(TLB_ERR_UNSUPPORTED, "persistent mode: single GPU only");
-  bool all_tma = d->lm_head.tma;
-  for (auto& L : d->layers) all_tma = all_tma && L.wqkv.tma && L.wo.tma && L.wgu.tma && L.wd.tma;
-  if (!all_tma) return set_error(TLB_ERR_UNSUPPORTED, "persistent mode: every linear needs K % 128 == 0");
-  if (d->hidden % 8 || d->ff % 8 || d->n_kv > 64)
-    return set_error(TLB_ERR_UNSUPPORTED, "persistent mode: shape not supported");
-  const unsigned W = (unsigned)c->sm_count * TK_WARPS;
-  if ((int)W > c->gemv_max_workers) return set_error(TLB_ERR_UNSUPPORTED, "persistent mode: worker count");
-  std::vector<TkPhase> ph;
-  std::vector<CUtensorMap> maps;
-  int kmax = 0;
-  auto gemv = [&](const Linear& Lw, int act, const float* x, const float* delta, const float* nw,
-                  float* xout, float* y, int from_embed, int argmax) {
-    TkPhase h;
-    memset(&h, 0, sizeof(h));
-    h.type = 0; h.N = Lw.N; h.K = Lw.K; h.RT = (Lw.N + 15) / 16; h.SL = (Lw.K + 255) / 256;
-    h.U = (unsigned)h.RT * (unsigned)h.SL;
-    h.Wtot = W < h.U ? W : h.U;
-    h.q = h.U / h.Wtot; h.r = h.U % h.Wtot;
-    // fewer row tiles than warps: let CTAs own tiles and split K across their warps
-    h.cta_tiles = ((unsigned)h.RT < W && h.SL <= 2 * TK_WARPS) ? 1 : 0;
-    h.act = act; h.argmax = argmax; h.map = (int)maps.size() / 2; h.x_from_embed = from_embed;
-    h.x = x; h.delta = delta; h.nw = nw; h.xout = xout; h.y = y;
-    maps.push_back(Lw.tmW);
-    maps.push_back(Lw.tmS);
-    ph.push_back(h);
-    if (Lw.K > kmax) kmax = Lw.K;
-  };
-  float* x = d->x;
-  float* xalt = d->xb;
-  for (int l = 0; l < d->n_layers; l++) {
-    DecLayer& L = d->layers[l];
-    gemv(L.wqkv, 2, x, l == 0 ? d->zeros : d->t1, L.an, xalt, d->qkv, l == 0 ? 1 : 0, 0);
-    { float* t = x; x = xalt; xalt = t; }
-    TkPhase a;
-    memset(&a, 0, sizeof(a));
-    a.type = 1; a.qkv = d->qkv; a.bq = L.bq; a.bk = L.bk; a.bv = L.bv; a.Kc = L.Kc; a.Vc = L.Vc;
-    a.att = d->att;
-    ph.push_back(a);
-    gemv(L.wo, 0, d->att, nullptr, nullptr, nullptr, d->t0, 0, 0);
-    gemv(L.wgu, 2, x, d->t0, L.fn, xalt, d->gu, 0, 0);
-    { float* t = x; x = xalt; xalt = t; }
-    gemv(L.wd, 1, d->gu, nullptr, nullptr, nullptr, d->t1, 0, 0);
-  }
-  if (const char* e = getenv("TLB_TK_EMPTY")) {  // diagnostics: phases that only run the grid barrier
-    TkPhase z;
-    memset(&z, 0, sizeof(z));
-    z.type = 2;
-    for (int i = 0; i < atoi(e); i++) ph.push_back(z);
-  }
-  gemv(d->lm_head, 2, x, d->t1, d->onorm, xalt, d->logits, 0, 1);
-  if (d->d_phases) cudaFree(d->d_phases);
-  if (d->d_maps) cudaFree(d->d_maps);
-  TLB_CUDA(cudaMalloc(&d->d_phases, ph.size() * sizeof(TkPhase)));
-  TLB_CUDA(cudaMalloc(&d->d_maps, maps.size() * sizeof(CUtensorMap)));
-  TLB_CUDA(cudaMemcpy(d->d_phases, ph.data(), ph.size() * sizeof(TkPhase), cudaMemcpyHostToDevice));
-  TLB_CUDA(cudaMemcpy(d->d_maps, maps.data(), maps.size() * sizeof(CUtensorMap), cudaMemcpyHostToDevice));
-  d->tk_n_phases = (int)ph.size();
-  d->tk_kmax = kmax;
-  d->tk_ready = true;
-  return TLB_OK;
-}
-
-static int forward_persistent(Decoder* d, DeviceCtx* c, cudaStream_t s) {
-  if (!d->embed || !d->onorm) return set_error(TLB_ERR_STATE, "decoder: embed / final norm not set");
-  if (!d->tk_ready) {
-    int rc = build_token_table(d, c);
-    if (rc) return rc;
-  }
-  TkParams P;
-  memset(&P, 0, sizeof(P));
-  P.phases = d->d_phases; P.n_phases = d->tk_n_phases; P.maps = d->d_maps;
-  P.n_q = d->n_q; P.n_kv = d->n_kv; P.hd = d->hd; P.max_ctx = d->max_ctx;
-  P.eps = d->eps; P.rope_base = d->rope_base; P.scale = d->scale;
-  P.embed = d->embed; P.d_pos = d->d_pos; P.d_tok = d->d_tok; P.d_tok_out = d->d_tok_out;
-  P.gemv_partials = c->gemv_partials; P.gemv_counters = c->gemv_counters;
-  P.attn_partials = (float*)((char*)d->attn_partials + 256);
-  P.attn_counters = (int*)d->attn_partials;
-  P.attn_s_cap = (int)(attn_partials_bytes(d->n_q, d->n_kv, d->max_ctx, d->hd, c->sm_count) /
-                       ((size_t)d->n_q * (d->hd + 4) * sizeof(float)));
-  P.sm2 = 2 * c->sm_count;
-  P.argmax_cell = c->argmax_cell;
-  P.bar = d->d_bar;
-  P.status = c->status;
-  P.dbg = g_gemv_dbg;
-  int rc = token_kernel_launch(P, d->hd, d->tk_kmax, d->hidden, c->sm_count, s);
-  if (rc) return rc;
-  d->launches_per_token = 1;
-  return TLB_OK;
-}
 
 static int forward(Decoder* d, cudaStream_t s) {
   DeviceCtx* c = nullptr;
   int rc = get_ctx(&c);
   if (rc) return rc;
-  if (d->mode == 1) return forward_persistent(d, c, s);
   const bool tp = d->tp_size > 1;
   const int E = d->hidden;
   long long n = 0;
@@ -408,10 +306,6 @@ int tlb_decoder_create(const int64_t* cfg, int n_cfg, float eps, float rope_base
   auto fa = [&](float** p, size_t n) { return cudaMalloc(p, n * sizeof(float)); };
   TLB_CUDA(fa(&d->x, d->hidden));
   TLB_CUDA(fa(&d->xb, d->hidden));
-  TLB_CUDA(fa(&d->zeros, d->hidden));
-  TLB_CUDA(cudaMemset(d->zeros, 0, d->hidden * sizeof(float)));
-  TLB_CUDA(cudaMalloc(&d->d_bar, 64));
-  TLB_CUDA(cudaMemset(d->d_bar, 0, 64));
   TLB_CUDA(fa(&d->t1, d->hidden));
   TLB_CUDA(fa(&d->hb, d->hidden));
   TLB_CUDA(fa(&d->qkv, (size_t)(d->n_q + 2 * d->n_kv) * d->hd));
@@ -466,9 +360,6 @@ int tlb_decoder_destroy(void* h) {
   float* bufs[] = {d->x, d->xb, d->t1, d->hb, d->qkv, d->att, d->t0, d->gu, d->mb, d->logits};
   for (float* b : bufs) cudaFree(b);
   cudaFree(d->stage_local);
-  cudaFree(d->zeros); cudaFree(d->d_bar);
-  if (d->d_phases) cudaFree(d->d_phases);
-  if (d->d_maps) cudaFree(d->d_maps);
   cudaFree(d->rope_cs);
   cudaFree(d->attn_partials); cudaFree(d->d_pos); cudaFree(d->d_tok); cudaFree(d->flags_local);
   cudaFreeHost(d->h_tok);
@@ -496,7 +387,6 @@ int tlb_decoder_set_linear(void* h, int64_t layer, int which, const void* q4, in
     else return set_error(TLB_ERR_ARG, "tlb_decoder_set_linear: unknown weight id");
   }
   TLB_REQUIRE(K == wantK && N == wantN, "tlb_decoder_set_linear: shape does not match the config");
-  d->tk_ready = false;
   // q/k/v rows are packed as rotary pairs and gate/up rows as (gate, up) pairs, so the
   // projection's epilogue finishes rope / SwiGLU itself
   const int pair_h = which == 0 ? d->hd / 2 : (which == 2 ? d->ff : 0);
@@ -508,7 +398,6 @@ int tlb_decoder_set_linear(void* h, int64_t layer, int which, const void* q4, in
 int tlb_decoder_set_vector(void* h, int64_t layer, int which, const float* v) {
   auto* d = (Decoder*)h;
   TLB_REQUIRE(d, "tlb_decoder_set_vector: null decoder");
-  d->tk_ready = false;
   if (which == 5) { d->onorm = v; return TLB_OK; }
   if (which == 6) { d->embed = v; return TLB_OK; }
   TLB_REQUIRE(layer >= 0 && layer < d->n_layers, "tlb_decoder_set_vector: layer out of range");
@@ -551,23 +440,6 @@ int tlb_decoder_set_token(void* h, int64_t token, void* stream) {
   return TLB_OK;
 }
 
-// mode 0: one kernel per op (works on any shape and tensor-parallel); mode 1: the
-// persistent per-token kernel (single GPU, every linear on the TMA path).  The phase
-// table is built here, outside any capture.
-int tlb_decoder_set_mode(void* h, int mode) {
-  auto* d = (Decoder*)h;
-  TLB_REQUIRE(d && (mode == 0 || mode == 1), "tlb_decoder_set_mode: bad arguments");
-  if (mode == 1 && !d->tk_ready) {
-    DeviceCtx* c = nullptr;
-    int rc = get_ctx(&c);
-    if (rc) return rc;
-    rc = build_token_table(d, c);
-    if (rc) return rc;
-  }
-  d->mode = mode;
-  if (d->graph) { cudaGraphExecDestroy(d->graph); d->graph = nullptr; }
-  return TLB_OK;
-}
 
 // Enqueue one token's launches on `stream` (capturable: no sync, no allocation).
 int tlb_decoder_forward(void* h, void* stream) {

@@ -1,4 +1,4 @@
-// Device helpers shared by the int4 GEMV kernel and the persistent token kernel:
+// Device helpers shared by the int4 GEMV kernels:
 // the unit-range split, the acq_rel ticket, the mma.sync wrappers.
 #pragma once
 

@@ -214,11 +214,6 @@ class Q4Decoder:
     def set_token(self, tok):
         check(lib().tlb_decoder_set_token(self.h, int(tok), self._stream()))
 
-    def set_mode(self, mode):
-        """0: one kernel per op; 1: the persistent per-token kernel (single GPU)."""
-        check(lib().tlb_decoder_set_mode(self.h, mode))
-        self.captured = False
-
     def forward(self):
         check(lib().tlb_decoder_forward(self.h, self._stream()))
 

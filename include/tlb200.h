@@ -173,10 +173,6 @@ int tlb_decoder_kv(void* dec, int64_t layer, void** K, void** V);     /* cu.h:13
 int tlb_decoder_logits(void* dec, void** logits);                      /* qm Scratch.logitsb */
 int tlb_decoder_set_pos(void* dec, int64_t pos, void* stream);         /* qm:877-885 feed / cu.h:559 upload_u32 */
 int tlb_decoder_set_token(void* dec, int64_t token, void* stream);
-/* 0 = one kernel per op (any shape, tensor parallel); 1 = persistent per-token kernel:
- * one cooperative launch per token (single GPU, all linears K % 128 == 0).  Replaces
- * the choice between step_imperative and captured_decoder of qm:747-905. */
-int tlb_decoder_set_mode(void* dec, int mode);
 int tlb_decoder_forward(void* dec, void* stream);                      /* qm:673-740 run_layers_ + argmax */
 int64_t tlb_decoder_launches_per_token(void* dec);
 int tlb_decoder_capture(void* dec);                                    /* qm:791-860 captured_decoder::init_ */

@@ -52,32 +52,6 @@ def test_decoder_matches_reference_golden(golden, name, cfg, seed, captured):
     d.close()
 
 
-@pytest.mark.parametrize("name,cfg,seed", [("dec_tiny", cases.TINY, 21), ("dec_tiny64", cases.TINY64, 22)])
-def test_persistent_kernel_matches_reference_golden(golden, name, cfg, seed):
-    """Mode 1: the whole token in one cooperative launch (grid barriers between the
-    projections, attention with rope/append fused, weights prefetched across phases).
-    Same golden vectors as the per-op path, eager and captured, and device-resident
-    feedback against the host loop."""
-    g = golden(name)
-    d, _ = make(cfg, seed, 64)
-    d.set_mode(1)
-    for captured in (False, True):
-        d.set_pos(0)
-        if captured:
-            d.capture()
-        prompt, nxt = list(g["prompt"]), 0
-        for i in range(len(g["next_tokens"])):
-            tid = prompt[i] if i < len(prompt) else nxt
-            nxt = d.step(int(tid))
-            assert relerr(d.logits().cpu().numpy(), g["logits"][i]) < 1e-3, (captured, i)
-            assert nxt == int(g["next_tokens"][i]), (captured, i)
-    assert d.launches_per_token() == 1
-    d.set_pos(0)
-    d.set_token(int(g["prompt"][0]))
-    d.run(3)
-    d.close()
-
-
 def test_device_resident_feedback_equals_host_loop():
     cfg = cases.TINY64
     d, wts = make(cfg, 22, 64)
@@ -119,8 +93,7 @@ def test_half_billion_shape_two_layers(port):
 def test_half_billion_full_model_greedy_ids(port):
     """BASELINE config 3 in full: the Qwen2.5-0.5B architecture (24 layers, hidden 896,
     14q/2kv, hd 64, ff 4864, vocab 151936), random-init from seed 2, 128 prompt ids then
-    greedy decoding, token ids against the oracle at every step (both decoder modes on
-    the GPU).  The oracle costs ~0.1 s per token on the host cores, so the greedy tail is
+    greedy decoding, token ids against the oracle at every step.  The oracle costs ~0.1 s per token on the host cores, so the greedy tail is
     64 steps here; the full 256 run with `TLB_CFG3_STEPS=256`."""
     import os
     cfg = cases.QWEN05
@@ -135,16 +108,14 @@ def test_half_billion_full_model_greedy_ids(port):
         nxt, _ = o.step(tid, i, want_logits=False)
         want.append(nxt)
     o.close()
-    for mode in (0, 1):
-        d.set_mode(mode)
-        d.set_pos(0)
-        d.capture()
-        got, nxt = [], 0
-        for i in range(n):
-            nxt = d.step(prompt[i] if i < 128 else nxt)
-            got.append(nxt)
-        first_bad = next((i for i in range(n) if got[i] != want[i]), None)
-        assert first_bad is None, (mode, first_bad, got[first_bad], want[first_bad])
+    d.set_pos(0)
+    d.capture()
+    got, nxt = [], 0
+    for i in range(n):
+        nxt = d.step(prompt[i] if i < 128 else nxt)
+        got.append(nxt)
+    first_bad = next((i for i in range(n) if got[i] != want[i]), None)
+    assert first_bad is None, (first_bad, got[first_bad], want[first_bad])
     d.close()
 
 
