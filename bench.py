@@ -323,7 +323,7 @@ def main():
                     roofline=dict(bound="hbm", achieved=achieved, peak=peak, unit="GB/s", frac=achieved / peak,
                                   traffic=gbytes * 1.036, peak_source=peak_src, kernel="gemv_q4p_kernel",
                                   traffic_note="dram read+write of the ncu capture of the gate|up shape "
-                                               "(1.036 x algorithmic, profiles/gemv_q4_gate_up_7b.md) scaled "
+                                               "(1.036 x algorithmic, profiles/gemv_q4p_gate_up_7b.md) scaled "
                                                "to the sweep by bytes",
                                   what=f"{glaunch} int4 GEMV launches of one token ({gbytes / 1e9:.2f} GB algorithmic), "
                                        f"{gms:.3f} ms per pass, CUDA events"),
