@@ -70,6 +70,7 @@ SIGNATURES = {
     "tlb_decoder_capture": (ci, [vp]),
     "tlb_decoder_run": (ci, [vp, i64, vp]),
     "tlb_decoder_step": (ci, [vp, C.POINTER(C.c_int32), C.POINTER(C.c_int32), vp]),
+    "tlb_decoder_prefill": (ci, [vp, C.POINTER(C.c_int32), i64, C.POINTER(C.c_int32), vp]),
     "tlb_decoder_last_token": (ci, [vp, C.POINTER(C.c_int32), vp]),
     "tlb_decoder_ipc_export": (ci, [vp, vp]),
     "tlb_decoder_ipc_open": (ci, [vp, vp]),

@@ -298,7 +298,7 @@ int tlb_gemv_q4p(const float* x, const void* packed, float* y, int64_t N, int64_
   TLB_REQUIRE(((uintptr_t)packed & 15) == 0, "tlb_gemv_q4p: packed weights must be 16-byte aligned");
   CTX(c);
   return gemv_q4p_launch(c, packed, x, y, (int)N, (int)K, alpha, beta, S(stream), 0, nullptr, 0,
-                         nullptr, nullptr, nullptr, 0.f, nullptr);
+                         nullptr, nullptr, nullptr, 0.f, nullptr, nullptr);
 }
 
 int tlb_gemv_q4(const float* a, const void* qw, const float* scales, float* y, int64_t N,

@@ -32,8 +32,6 @@ namespace tlb {
 
 // Diagnostics: when set, every launch records per-CTA phase timestamps there.
 unsigned long long* g_attn_dbg = nullptr;
-constexpr int AT_THREADS = 256;
-constexpr int AT_WARPS = 8;
 constexpr int AT_TK = 32;  // keys per tile
 
 struct AttnParams {
@@ -73,44 +71,47 @@ __host__ __device__ inline int attn_chunk(int n_kv, int ctx, int sm2) {
 }
 
 // Warps across heads: ceil(grp / HW) rounded up to a divisor of the warp count.
-__host__ __device__ inline int attn_hs(int grp, int HW) {
+__host__ __device__ inline int attn_hs(int grp, int HW, int warps) {
   int hs = (grp + HW - 1) / HW;
-  while (AT_WARPS % hs) hs++;
+  while (warps % hs) hs++;
   return hs;
 }
 
-template <int D, int HW>
+// LPK = lanes that share a key: 8 (8 warps, 4 keys per warp step) or 16 (16 warps, 2 keys
+// per step, half the per-lane state: the wide-group configuration, where 8 warps of
+// 4-head state leave the schedulers two warps each and the tile loop latency bound).
+template <int D, int HW, int LPK>
 struct AttnCfg {
   static constexpr int STAGES = HW >= 4 ? 4 : 3;
   static constexpr int TILE_BYTES = AT_TK * D * 4;
-  static constexpr int CH = D / 32;  // 16-byte chunks per lane (8 lanes per key)
+  static constexpr int CH = D / (4 * LPK);  // 16-byte chunks per lane
+  static constexpr int WARPS = LPK;
+  static constexpr int THREADS = 32 * LPK;
+  static constexpr int KPS = 32 / LPK;       // keys per warp step
 };
 
-template <int D, int HW>
-size_t attn_smem_bytes(int grp) {
-  using C = AttnCfg<D, HW>;
-  int hs = attn_hs(grp, HW);
-  int ks = AT_WARPS / hs;
+template <int D, int HW, int LPK>
+size_t attn_smem_bytes(int) {
+  using C = AttnCfg<D, HW, LPK>;
   size_t b = 128;
-  b += (size_t)C::STAGES * 2 * C::TILE_BYTES;
+  b += (size_t)C::STAGES * 2 * C::TILE_BYTES;   // the ring; the CTA merge reuses it
   b += 64;  // barriers
-  b += (size_t)ks * hs * HW * (D + 4) * sizeof(float);
   return b;
 }
 
-template <int D, int HW>
-__global__ void __launch_bounds__(AT_THREADS, (HW >= 4 ? 1 : 2))
+template <int D, int HW, int LPK>
+__global__ void __launch_bounds__(32 * LPK, ((HW >= 4 || LPK > 8) ? 1 : 2))
     attn_decode_kernel(AttnParams p) {
-  using C = AttnCfg<D, HW>;
+  using C = AttnCfg<D, HW, LPK>;
+  constexpr int AT_THREADS = C::THREADS, AT_WARPS = C::WARPS, KPS = C::KPS;
   extern __shared__ unsigned char smem_raw[];
   unsigned char* base = (unsigned char*)(((uintptr_t)smem_raw + 127) & ~(uintptr_t)127);
   float* Kt = (float*)base;
   float* Vt = (float*)(base + (size_t)C::STAGES * C::TILE_BYTES);
   uint64_t* bars = (uint64_t*)(base + (size_t)C::STAGES * 2 * C::TILE_BYTES);
-  float* mrg = (float*)(bars + 8);  // barrier block padded to 64 bytes
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const int kslot = lane >> 3, sub = lane & 7;
+  const int kslot = lane / LPK, sub = lane % LPK;
   const int kh = blockIdx.y, sp = blockIdx.x;
   auto stamp = [&](int i) {
     if (p.dbg && tid == 0) {
@@ -120,7 +121,7 @@ __global__ void __launch_bounds__(AT_THREADS, (HW >= 4 ? 1 : 2))
     }
   };
   stamp(0);
-  const int hs = attn_hs(p.grp, HW);  // warps across heads
+  const int hs = attn_hs(p.grp, HW, AT_WARPS);  // warps across heads
   const int ks = AT_WARPS / hs;          // warps across keys
   const int hslot = warp % hs, kslice = warp / hs;
 
@@ -168,7 +169,7 @@ __global__ void __launch_bounds__(AT_THREADS, (HW >= 4 ? 1 : 2))
     for (int i = early; i < pre; i++) issue(i);
   }
 
-  // q fragments: lane owns chunks {sub + 8*i}
+  // q fragments: lane owns chunks {sub + LPK*i}
   float4 qf[HW][C::CH];
 #pragma unroll
   for (int h = 0; h < HW; h++) {
@@ -177,7 +178,7 @@ __global__ void __launch_bounds__(AT_THREADS, (HW >= 4 ? 1 : 2))
     const float4* qp = (const float4*)(p.q + (size_t)(kh * p.grp + (live ? hh : 0)) * D);
 #pragma unroll
     for (int i = 0; i < C::CH; i++)
-      qf[h][i] = live ? qp[sub + 8 * i] : make_float4(0.f, 0.f, 0.f, 0.f);
+      qf[h][i] = live ? qp[sub + LPK * i] : make_float4(0.f, 0.f, 0.f, 0.f);
   }
   float m[HW], l[HW];
   float4 acc[HW][C::CH];
@@ -198,14 +199,14 @@ __global__ void __launch_bounds__(AT_THREADS, (HW >= 4 ? 1 : 2))
     const int rows = (k_end - r0) < AT_TK ? (k_end - r0) : AT_TK;
     const float4* Ks = (const float4*)((unsigned char*)Kt + (size_t)st * C::TILE_BYTES);
     const float4* Vs = (const float4*)((unsigned char*)Vt + (size_t)st * C::TILE_BYTES);
-    for (int step = kslice; step < AT_TK / 4; step += ks) {
-      const int row = step * 4 + kslot;
-      if (step * 4 >= rows) break;
+    for (int step = kslice; step < AT_TK / KPS; step += ks) {
+      const int row = step * KPS + kslot;
+      if (step * KPS >= rows) break;
       const bool valid = row < rows;
       const int rr = valid ? row : 0;
       float4 kv[C::CH];
 #pragma unroll
-      for (int i = 0; i < C::CH; i++) kv[i] = Ks[rr * (D / 4) + sub + 8 * i];
+      for (int i = 0; i < C::CH; i++) kv[i] = Ks[rr * (D / 4) + sub + LPK * i];
       float s[HW];
 #pragma unroll
       for (int h = 0; h < HW; h++) {
@@ -222,18 +223,19 @@ __global__ void __launch_bounds__(AT_THREADS, (HW >= 4 ? 1 : 2))
         d += __shfl_xor_sync(0xffffffffu, d, 1);
         d += __shfl_xor_sync(0xffffffffu, d, 2);
         d += __shfl_xor_sync(0xffffffffu, d, 4);
+        if (LPK > 8) d += __shfl_xor_sync(0xffffffffu, d, 8);
         s[h] = valid ? d * p.scale : -INFINITY;
       }
 #pragma unroll
-      for (int i = 0; i < C::CH; i++) kv[i] = Vs[rr * (D / 4) + sub + 8 * i];
+      for (int i = 0; i < C::CH; i++) kv[i] = Vs[rr * (D / 4) + sub + LPK * i];
       // The four key slots of the warp share one running max per head, so the rescale
       // branch is warp-uniform and the slots' sums can later be added without exps.
       float sm[HW];
       bool grow = false;
 #pragma unroll
       for (int h = 0; h < HW; h++) {
-        sm[h] = fmaxf(s[h], __shfl_xor_sync(0xffffffffu, s[h], 8));
-        sm[h] = fmaxf(sm[h], __shfl_xor_sync(0xffffffffu, sm[h], 16));
+        sm[h] = fmaxf(s[h], __shfl_xor_sync(0xffffffffu, s[h], 16));
+        if (LPK == 8) sm[h] = fmaxf(sm[h], __shfl_xor_sync(0xffffffffu, sm[h], 8));
         grow = grow || (sm[h] > m[h]);
       }
       if (grow) {  // one warp-uniform branch per step, rare after the first keys
@@ -276,10 +278,10 @@ __global__ void __launch_bounds__(AT_THREADS, (HW >= 4 ? 1 : 2))
   {
 #pragma unroll
     for (int h = 0; h < HW; h++) {
-      float* dst = ent + ((size_t)(kslice * 4 + kslot) * nheads_pad + hslot * HW + h) * (D + 4);
+      float* dst = ent + ((size_t)(kslice * KPS + kslot) * nheads_pad + hslot * HW + h) * (D + 4);
       if (sub == 0) { dst[D] = m[h]; dst[D + 1] = l[h]; }
 #pragma unroll
-      for (int i = 0; i < C::CH; i++) *(float4*)(dst + (sub + 8 * i) * 4) = acc[h][i];
+      for (int i = 0; i < C::CH; i++) *(float4*)(dst + (sub + LPK * i) * 4) = acc[h][i];
     }
   }
   __syncthreads();
@@ -290,15 +292,15 @@ __global__ void __launch_bounds__(AT_THREADS, (HW >= 4 ? 1 : 2))
     const int hh = idx / (D / 4), d4 = idx - hh * (D / 4);
     float mm = -INFINITY;
     for (int k2 = 0; k2 < ks; k2++)
-      mm = fmaxf(mm, ent[((size_t)(k2 * 4) * nheads_pad + hh) * (D + 4) + D]);
+      mm = fmaxf(mm, ent[((size_t)(k2 * KPS) * nheads_pad + hh) * (D + 4) + D]);
     float ll = 0.f;
     float4 aa = make_float4(0.f, 0.f, 0.f, 0.f);
     for (int k2 = 0; k2 < ks; k2++) {
-      const float mk = ent[((size_t)(k2 * 4) * nheads_pad + hh) * (D + 4) + D];
+      const float mk = ent[((size_t)(k2 * KPS) * nheads_pad + hh) * (D + 4) + D];
       const float c = (mk == -INFINITY) ? 0.f : __expf(mk - mm);
 #pragma unroll
-      for (int j = 0; j < 4; j++) {
-        const float* src = ent + ((size_t)(k2 * 4 + j) * nheads_pad + hh) * (D + 4);
+      for (int j = 0; j < KPS; j++) {
+        const float* src = ent + ((size_t)(k2 * KPS + j) * nheads_pad + hh) * (D + 4);
         const float4 a = *(const float4*)(src + d4 * 4);
         ll = fmaf(src[D + 1], c, ll);
         aa.x = fmaf(a.x, c, aa.x); aa.y = fmaf(a.y, c, aa.y);
@@ -440,17 +442,17 @@ size_t attn_partials_bytes(int n_q, int n_kv, long long kv_max, int D, int sm_co
   return (size_t)n_q * s * (D + 4) * sizeof(float);
 }
 
-template <int D, int HW>
+template <int D, int HW, int LPK>
 static int launch_t(const AttnParams& p, int splits, cudaStream_t stream) {
-  size_t smem = attn_smem_bytes<D, HW>(p.grp);
+  size_t smem = attn_smem_bytes<D, HW, LPK>(p.grp);
   static bool attr = false;
   if (!attr) {
-    TLB_CUDA(cudaFuncSetAttribute(attn_decode_kernel<D, HW>,
+    TLB_CUDA(cudaFuncSetAttribute(attn_decode_kernel<D, HW, LPK>,
                                   cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
     attr = true;
   }
-  LaunchCfg lc(dim3(splits, p.n_kv), dim3(AT_THREADS), smem, stream, pdl_enabled());
-  TLB_CUDA(cudaLaunchKernelEx(&lc.cfg, attn_decode_kernel<D, HW>, p));
+  LaunchCfg lc(dim3(splits, p.n_kv), dim3(32 * LPK), smem, stream, pdl_enabled());
+  TLB_CUDA(cudaLaunchKernelEx(&lc.cfg, attn_decode_kernel<D, HW, LPK>, p));
   return TLB_OK;
 }
 
@@ -477,13 +479,16 @@ int attn_decode_launch(DeviceCtx* c, const float* q, const float* K, const float
   // heads per warp: the smallest of {1,2,4} such that ceil(grp/HW) divides 8
   int HW = grp == 1 ? 1 : (grp == 2 ? 2 : 4);
   if (D == 128) {
-    if (HW == 1) return launch_t<128, 1>(p, splits, stream);
-    if (HW == 2) return launch_t<128, 2>(p, splits, stream);
-    return launch_t<128, 4>(p, splits, stream);
+    if (HW == 1) return launch_t<128, 1, 8>(p, splits, stream);
+    if (HW == 2) return launch_t<128, 2, 8>(p, splits, stream);
+    // wide groups: 16 lanes per key and 16 warps (TLB_ATTN_LPK=8 selects the 8-warp form)
+    static const int lpk = getenv("TLB_ATTN_LPK") ? atoi(getenv("TLB_ATTN_LPK")) : 16;
+    if (lpk == 8) return launch_t<128, 4, 8>(p, splits, stream);
+    return launch_t<128, 4, 16>(p, splits, stream);
   }
-  if (HW == 1) return launch_t<64, 1>(p, splits, stream);
-  if (HW == 2) return launch_t<64, 2>(p, splits, stream);
-  return launch_t<64, 4>(p, splits, stream);
+  if (HW == 1) return launch_t<64, 1, 8>(p, splits, stream);
+  if (HW == 2) return launch_t<64, 2, 8>(p, splits, stream);
+  return launch_t<64, 4, 8>(p, splits, stream);
 }
 
 }  // namespace tlb

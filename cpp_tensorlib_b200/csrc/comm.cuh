@@ -15,6 +15,10 @@
 // Staging is double-buffered by the parity of the sequence number: a rank can
 // only be one exchange ahead of the slowest peer, because its next push waits
 // for its own reduce, which needs every peer's previous push.
+// The sequence number of an exchange is (tokens decoded so far) * E + k: the token
+// counter lives in device memory and is advanced once per token by the last exchange
+// (the argmax), k is the exchange's fixed index inside a token and E their number, so
+// producers and consumers of any grid size derive the same tag without writing it.
 #pragma once
 
 #include "common.cuh"
@@ -27,10 +31,14 @@ struct CommDev {
   int rank = 0, size = 1;
   int slot_floats = 0;            // packets per (parity, rank) slot
   uint2* stage[TP_MAX] = {};      // stage[r]: rank r's staging [2][size][slot_floats] packets
-  unsigned* seq = nullptr;        // local: number of completed exchanges
+  unsigned* seq = nullptr;        // local: tokens decoded so far (advanced by the argmax exchange)
+  int k = 0, E = 1;               // this exchange's index inside a token, exchanges per token
 };
 
 #ifdef __CUDACC__
+__device__ __forceinline__ unsigned comm_seq(const CommDev& c) {
+  return *(volatile unsigned*)c.seq * (unsigned)c.E + (unsigned)c.k;
+}
 __device__ __forceinline__ void st_packet_sys(uint2* p, float v, unsigned tag) {
   asm volatile("st.relaxed.sys.global.v2.u32 [%0], {%1, %2};" ::"l"(p), "r"(__float_as_uint(v)),
                "r"(tag)

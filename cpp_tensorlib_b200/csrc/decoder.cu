@@ -42,6 +42,16 @@ int attn_decode_launch(DeviceCtx* c, const float* q, const float* K, const float
                        int n_q, int n_kv, int ctx, long long kv_max, int D, float scale,
                        const unsigned* d_pos, float* partials, int* counters, cudaStream_t stream, int early_kv);
 int launch_rmsnorm(const float*, const float*, float*, int, float, int, cudaStream_t);
+int launch_embed_rows(const float*, const int*, float*, int, int, cudaStream_t);
+int launch_rope(const float*, const float*, float*, int, int, int, unsigned, const unsigned*, float,
+                cudaStream_t);
+int launch_split_heads(const float*, const float*, float*, int, long long, long long, int, int,
+                       cudaStream_t);
+int launch_merge_heads(const float*, float*, int, int, int, cudaStream_t);
+int launch_kv_fill(float*, float*, const float*, const float*, int, long long, int, int, int,
+                   cudaStream_t);
+int launch_attn_prefill(DeviceCtx*, const float*, const float*, const float*, float*, int, int, int,
+                        long long, int, float, int, cudaStream_t);
 int launch_add_rmsnorm(const float*, const float*, const float*, float*, float*, int, float, int,
                        cudaStream_t);
 int launch_add_rmsnorm_ar(const float*, const float*, float*, float*, int, float, const CommDev&,
@@ -97,6 +107,9 @@ struct Decoder {
   void* peer_stage_base[TP_MAX] = {};
   void* peer_flags_base[TP_MAX] = {};
   bool peers_open = false;
+  // batched prompt pass: row-batched scratch for chunks of up to PF_CHUNK tokens
+  float* pf = nullptr;
+  int* pf_ids = nullptr;
   // graph
   cudaGraphExec_t graph = nullptr;
   long long launches_per_token = 0;
@@ -123,9 +136,10 @@ static int set_linear(Linear& L, const void* q4, int K, int N, int pair_h = 0) {
 // Fused residual add + RMSNorm in front of a linear: input = rmsnorm(x + delta) * w,
 // and x + delta is also written to xout (the next residual base).
 struct NormIn {
-  const float* delta;
+  const float* delta;   // NULL with `pull`: the delta is the sum of an exchange's partial vectors
   const float* w;
   float* xout;
+  const CommDev* pull = nullptr;
 };
 
 static int run_linear(DeviceCtx* c, const Linear& L, const float* x, float* y, cudaStream_t s,
@@ -134,11 +148,12 @@ static int run_linear(DeviceCtx* c, const Linear& L, const float* x, float* y, c
   if (!L.q4) return set_error(TLB_ERR_STATE, "decoder: a linear weight was never set");
   if ((epi != nullptr) != (L.pair_h > 0))
     return set_error(TLB_ERR_STATE, "decoder: pair-packed weight and epilogue do not match");
-  if (L.packed && !(nm && (L.K + 255) / 256 > 64))
+  if (L.packed && !(nm && (L.K + 255) / 256 > 32))
     return gemv_q4p_launch(c, L.packed, x, y, L.N, L.K, 1.0f, 0.0f, s, 0, push, nm ? 2 : act,
                            nm ? nm->delta : nullptr, nm ? nm->w : nullptr, nm ? nm->xout : nullptr, eps,
-                           epi);
+                           epi, nm ? nm->pull : nullptr);
   if (epi) return set_error(TLB_ERR_STATE, "decoder: pair epilogue without a packed weight");
+  if (nm && nm->pull) return set_error(TLB_ERR_STATE, "decoder: fused exchange without a packed weight");
   if (L.tma && nm)
     return gemv_q4_launch(c, L.tmW, L.tmS, x, L.K, 1, y, L.N, L.N, L.K, 1.0f, 0.0f, s, 0, push, 2,
                           nm->delta, nm->w, nm->xout, eps);
@@ -182,13 +197,29 @@ static int forward(Decoder* d, cudaStream_t s) {
   if (!d->embed || !d->onorm) return set_error(TLB_ERR_STATE, "decoder: embed / final norm not set");
   RUN(launch_embed_gather(d->embed, d->d_tok, d->x, E, d->rope_cs, d->d_pos, d->hd, d->rope_base, s));
   RUN(launch_rmsnorm(d->x, d->layers[0].an, d->hb, E, d->eps, 1, s));
-  bool all_tma = d->lm_head.tma;
-  for (auto& L : d->layers) all_tma = all_tma && L.wqkv.tma && L.wo.tma && L.wgu.tma && L.wd.tma;
-  if (!tp && all_tma) {
-    // Single GPU, every linear on the TMA path: both residual adds and norms of a
-    // layer run inside the following projection's activation prep (6 launches per
-    // layer instead of 8).  The residual ping-pongs between two buffers because
-    // every CTA of the projection reads it while one CTA writes the new sum.
+  bool all_tma = d->lm_head.tma && d->lm_head.packed;
+  for (auto& L : d->layers)
+    all_tma = all_tma && L.wqkv.tma && L.wo.tma && L.wgu.tma && L.wd.tma && L.wqkv.packed &&
+              L.wo.packed && L.wgu.packed && L.wd.packed;
+  // exchanges of one token: after wo and after wd of every layer, then the argmax
+  const int EX = 2 * d->n_layers + 1;
+  auto cm = [&](int k) {
+    CommDev c2 = d->comm;
+    c2.k = k;
+    c2.E = EX;
+    return c2;
+  };
+  // TLB_TP_PULL_MAX (diagnostics): largest rank count that uses the fused consumer (default 4)
+  const char* pm = getenv("TLB_TP_PULL_MAX");
+  const int pull_max = pm ? atoi(pm) : 4;
+  if (all_tma && (!tp || d->tp_size <= pull_max)) {
+    // Both residual adds and norms of a layer run inside the following projection's
+    // activation prep (5 launches per layer).  Tensor parallel (up to 4 ranks): that
+    // prologue is also the exchange's consumer -- it polls the ranks' partial vectors from
+    // this rank's staging and sums them in rank order -- so the row-parallel projection's
+    // push and the next projection are the only kernels of an all-reduce.  The residual
+    // ping-pongs between two buffers because every CTA of the projection reads it while
+    // one CTA writes the new sum.
     float* x = d->x;
     float* xalt = d->xb;
     for (int l = 0; l < d->n_layers; l++) {
@@ -196,10 +227,11 @@ static int forward(Decoder* d, cudaStream_t s) {
       const PairEpi eq = qkv_epilogue(d, L), eg = swiglu_epilogue(d);
       const PairEpi* pq = L.wqkv.pair_h > 0 ? &eq : nullptr;
       const PairEpi* pg = L.wgu.pair_h > 0 ? &eg : nullptr;
+      const CommDev c_prev = cm(2 * l - 1), c_wo = cm(2 * l), c_wd = cm(2 * l + 1);
       if (l == 0) {
         RUN(run_linear(c, L.wqkv, d->hb, d->qkv, s, nullptr, 0, nullptr, 0.f, pq));
       } else {
-        NormIn nm{d->t1, L.an, xalt};
+        NormIn nm{tp ? nullptr : d->t1, L.an, xalt, tp ? &c_prev : nullptr};
         RUN(run_linear(c, L.wqkv, x, d->qkv, s, nullptr, 0, &nm, d->eps, pq));
         float* t = x; x = xalt; xalt = t;
       }
@@ -209,19 +241,26 @@ static int forward(Decoder* d, cudaStream_t s) {
       RUN(attn_decode_launch(c, d->qkv, L.Kc, L.Vc, d->att, d->n_q, d->n_kv, 0, d->max_ctx, d->hd,
                              d->scale, d->d_pos, (float*)((char*)d->attn_partials + 256),
                              (int*)d->attn_partials, s, 1));
-      RUN(run_linear(c, L.wo, d->att, d->t0, s, nullptr));
-      NormIn nf{d->t0, L.fn, xalt};
+      RUN(run_linear(c, L.wo, d->att, tp ? nullptr : d->t0, s, tp ? &c_wo : nullptr));
+      NormIn nf{tp ? nullptr : d->t0, L.fn, xalt, tp ? &c_wo : nullptr};
       RUN(run_linear(c, L.wgu, x, d->gu, s, nullptr, 0, &nf, d->eps, pg));
       { float* t = x; x = xalt; xalt = t; }
       if (pg) {
-        RUN(run_linear(c, L.wd, d->mb, d->t1, s, nullptr, 0));
+        RUN(run_linear(c, L.wd, d->mb, tp ? nullptr : d->t1, s, tp ? &c_wd : nullptr, 0));
       } else {
-        RUN(run_linear(c, L.wd, d->gu, d->t1, s, nullptr, 1));
+        RUN(run_linear(c, L.wd, d->gu, tp ? nullptr : d->t1, s, tp ? &c_wd : nullptr, 1));
       }
     }
-    NormIn no{d->t1, d->onorm, xalt};
+    const CommDev c_last = cm(2 * d->n_layers - 1);
+    NormIn no{tp ? nullptr : d->t1, d->onorm, xalt, tp ? &c_last : nullptr};
     RUN(run_linear(c, d->lm_head, x, d->logits, s, nullptr, 0, &no, d->eps));
-    RUN(launch_argmax(c, d->logits, d->vocab, d->d_tok, d->d_tok_out, s));
+    if (tp) {
+      RUN(launch_argmax_tp(c, d->logits, d->vocab, d->vocab_offset, cm(2 * d->n_layers), d->d_tok,
+                           d->d_tok_out, s));
+      n++;  // two kernels
+    } else {
+      RUN(launch_argmax(c, d->logits, d->vocab, d->d_tok, d->d_tok_out, s));
+    }
     RUN(launch_incr_u32(d->d_pos, s));
     d->launches_per_token = n;
     return TLB_OK;
@@ -231,6 +270,7 @@ static int forward(Decoder* d, cudaStream_t s) {
     const PairEpi eq = qkv_epilogue(d, L), eg = swiglu_epilogue(d);
     const PairEpi* pq = L.wqkv.pair_h > 0 ? &eq : nullptr;
     const PairEpi* pg = L.wgu.pair_h > 0 ? &eg : nullptr;
+    const CommDev c_wo = cm(2 * l), c_wd = cm(2 * l + 1);
     RUN(run_linear(c, L.wqkv, d->hb, d->qkv, s, nullptr, 0, nullptr, 0.f, pq));
     if (!pq)
       RUN(launch_qkv_post(d->qkv, L.bq, L.bk, L.bv, L.Kc, L.Vc, d->n_q, d->n_kv, d->hd, d->d_pos,
@@ -239,8 +279,8 @@ static int forward(Decoder* d, cudaStream_t s) {
                            d->scale, d->d_pos, (float*)((char*)d->attn_partials + 256),
                            (int*)d->attn_partials, s, 1));
     if (tp) {
-      RUN(run_linear(c, L.wo, d->att, nullptr, s, &d->comm));
-      RUN(launch_add_rmsnorm_ar(d->x, L.fn, d->x, d->hb, E, d->eps, d->comm, c->status, s));
+      RUN(run_linear(c, L.wo, d->att, nullptr, s, &c_wo));
+      RUN(launch_add_rmsnorm_ar(d->x, L.fn, d->x, d->hb, E, d->eps, c_wo, c->status, s));
     } else {
       RUN(run_linear(c, L.wo, d->att, d->t0, s, nullptr));
       RUN(launch_add_rmsnorm(d->x, d->t0, L.fn, d->x, d->hb, E, d->eps, 1, s));
@@ -252,8 +292,8 @@ static int forward(Decoder* d, cudaStream_t s) {
     if (!pg && !fuse_act) RUN(launch_swiglu(d->gu, d->mb, d->ff, 1, s));
     const float* nextw = (l + 1 < d->n_layers) ? d->layers[l + 1].an : d->onorm;
     if (tp) {
-      RUN(run_linear(c, L.wd, fuse_act ? d->gu : d->mb, nullptr, s, &d->comm, fuse_act ? 1 : 0));
-      RUN(launch_add_rmsnorm_ar(d->x, nextw, d->x, d->hb, E, d->eps, d->comm, c->status, s));
+      RUN(run_linear(c, L.wd, fuse_act ? d->gu : d->mb, nullptr, s, &c_wd, fuse_act ? 1 : 0));
+      RUN(launch_add_rmsnorm_ar(d->x, nextw, d->x, d->hb, E, d->eps, c_wd, c->status, s));
     } else {
       RUN(run_linear(c, L.wd, fuse_act ? d->gu : d->mb, d->t0, s, nullptr, fuse_act ? 1 : 0));
       RUN(launch_add_rmsnorm(d->x, d->t0, nextw, d->x, d->hb, E, d->eps, 1, s));
@@ -261,7 +301,8 @@ static int forward(Decoder* d, cudaStream_t s) {
   }
   RUN(run_linear(c, d->lm_head, d->hb, d->logits, s, nullptr));
   if (tp) {
-    RUN(launch_argmax_tp(c, d->logits, d->vocab, d->vocab_offset, d->comm, d->d_tok, d->d_tok_out, s));
+    RUN(launch_argmax_tp(c, d->logits, d->vocab, d->vocab_offset, cm(2 * d->n_layers), d->d_tok,
+                         d->d_tok_out, s));
     n++;  // two kernels
   } else {
     RUN(launch_argmax(c, d->logits, d->vocab, d->d_tok, d->d_tok_out, s));
@@ -361,6 +402,7 @@ int tlb_decoder_destroy(void* h) {
   for (float* b : bufs) cudaFree(b);
   cudaFree(d->stage_local);
   cudaFree(d->rope_cs);
+  cudaFree(d->pf); cudaFree(d->pf_ids);
   cudaFree(d->attn_partials); cudaFree(d->d_pos); cudaFree(d->d_tok); cudaFree(d->flags_local);
   cudaFreeHost(d->h_tok);
   delete d;
@@ -503,6 +545,106 @@ int tlb_decoder_step(void* h, const int32_t* token_in, int32_t* token_out, void*
   *token_out = d->h_out[0];
   return TLB_OK;
 }
+// ---- batched prompt pass (bench/cuda/qwen_model.h:357-442 prefill_chunk_ / prefill_batched):
+// the same forward as the decode step with one row per prompt token -- every projection is a
+// GEMM on the int4 weights (tensor cores for more than 8 rows), attention is one tiled causal
+// pass over the cache -- in chunks of up to 256 tokens starting at the decoder's current
+// position.  Leaves the caches and the position at pos + T, the greedy next token in the
+// device-resident token cell (so tlb_decoder_run continues from there) and in *next_token.
+// Single GPU; the weights are read in the reference layout the caller handed to
+// tlb_decoder_set_linear, which must still be alive.
+int tlb_decoder_prefill(void* h, const int32_t* tokens, int64_t T, int32_t* next_token, void* stream) {
+  auto* d = (Decoder*)h;
+  TLB_REQUIRE(d && tokens && T > 0, "tlb_decoder_prefill: bad arguments");
+  if (d->tp_size != 1) return set_error(TLB_ERR_UNSUPPORTED, "tlb_decoder_prefill: single GPU only");
+  if (!d->embed || !d->onorm) return set_error(TLB_ERR_STATE, "decoder: embed / final norm not set");
+  DeviceCtx* c = nullptr;
+  int rc = get_ctx(&c);
+  if (rc) return rc;
+  cudaStream_t s = (cudaStream_t)stream;
+  constexpr int CH = 256;
+  const int E = d->hidden, D = d->hd, NQ = d->n_q, NKV = d->n_kv, FF = d->ff;
+  const int QKV = (NQ + 2 * NKV) * D;
+  unsigned pos0 = 0;
+  TLB_CUDA(cudaMemcpyAsync(&pos0, d->d_pos, 4, cudaMemcpyDeviceToHost, s));
+  TLB_CUDA(cudaStreamSynchronize(s));
+  if ((long long)pos0 + T > d->max_ctx)
+    return set_error(TLB_ERR_ARG, "tlb_decoder_prefill: the prompt does not fit the cache");
+  for (int64_t i = 0; i < T; i++)
+    if (tokens[i] < 0) return set_error(TLB_ERR_ARG, "tlb_decoder_prefill: negative token id");
+  // row-batched scratch, carved from one allocation
+  const size_t n_emb = (size_t)CH * E, n_qkv = (size_t)CH * QKV, n_att = (size_t)CH * NQ * D,
+               n_gu = (size_t)CH * 2 * FF, n_mb = (size_t)CH * FF;
+  const size_t total = 5 * n_emb /* res0 res1 h h2 md */ + 2 * n_qkv + 2 * n_att + n_gu + n_mb;
+  if (!d->pf) {
+    TLB_CUDA(cudaMalloc(&d->pf, total * sizeof(float)));
+    TLB_CUDA(cudaMalloc(&d->pf_ids, CH * sizeof(int)));
+  }
+  float* p = d->pf;
+  float* res[2] = {p, p + n_emb};
+  p += 2 * n_emb;
+  float* hrow = p; p += n_emb;
+  float* h2 = p; p += n_emb;
+  float* md = p; p += n_emb;
+  float* qkv = p; p += n_qkv;
+  float* qkvh = p; p += n_qkv;
+  float* ah = p; p += n_att;
+  float* at = p; p += n_att;
+  float* gu = p; p += n_gu;
+  float* mb = p;
+  auto gemm = [&](const Linear& L, const float* x, float* y, int rows) -> int {
+    if (!L.q4) return set_error(TLB_ERR_STATE, "decoder: a linear weight was never set");
+    return tlb_gemm_q4(x, rows, L.K, L.q4, L.scales(), y, L.N, L.N, L.K, 1.0f, 0.0f, s);
+  };
+#define PF(expr) do { rc = (expr); if (rc) return rc; } while (0)
+  int last_rows = 0;
+  for (int64_t t0 = 0; t0 < T; t0 += CH) {
+    const int rows = (int)((T - t0) < CH ? (T - t0) : CH);
+    const unsigned pos = pos0 + (unsigned)t0;
+    last_rows = rows;
+    TLB_CUDA(cudaMemcpyAsync(d->pf_ids, tokens + t0, (size_t)rows * sizeof(int), cudaMemcpyHostToDevice, s));
+    float* x = res[1];   // the chunk's embeddings; layer l writes its residual into res[l & 1]
+    PF(launch_embed_rows(d->embed, d->pf_ids, x, E, rows, s));
+    PF(launch_rmsnorm(x, d->layers[0].an, hrow, E, d->eps, rows, s));
+    for (int l = 0; l < d->n_layers; l++) {
+      DecLayer& L = d->layers[l];
+      float* ro = res[l & 1];
+      PF(gemm(L.wqkv, hrow, qkv, rows));
+      // token-major [rows, q|k|v] -> head-major [n_q + 2 n_kv, rows, D], biases riding along
+      float* kh = qkvh + (size_t)NQ * rows * D;
+      float* vh = qkvh + (size_t)(NQ + NKV) * rows * D;
+      PF(launch_split_heads(qkv, L.bq, qkvh, rows, QKV, 0, NQ, D, s));
+      PF(launch_split_heads(qkv, L.bk, kh, rows, QKV, (long long)NQ * D, NKV, D, s));
+      PF(launch_split_heads(qkv, L.bv, vh, rows, QKV, (long long)(NQ + NKV) * D, NKV, D, s));
+      // [H, rows, D] flattened: row r = h*rows + t, so rope's position is pos + r % rows
+      PF(launch_rope(qkvh, nullptr, qkvh, NQ * rows, rows, D, pos, nullptr, d->rope_base, s));
+      PF(launch_rope(kh, nullptr, kh, NKV * rows, rows, D, pos, nullptr, d->rope_base, s));
+      PF(launch_kv_fill(L.Kc, L.Vc, kh, vh, rows, d->max_ctx, NKV, D, (int)pos, s));
+      PF(launch_attn_prefill(c, qkvh, L.Kc, L.Vc, ah, NQ, NKV, rows, d->max_ctx, D, d->scale, (int)pos, s));
+      PF(launch_merge_heads(ah, at, rows, NQ, D, s));
+      PF(gemm(L.wo, at, md, rows));
+      PF(launch_add_rmsnorm(x, md, L.fn, ro, h2, E, d->eps, rows, s));
+      PF(gemm(L.wgu, h2, gu, rows));
+      PF(launch_swiglu(gu, mb, FF, rows, s));
+      PF(gemm(L.wd, mb, md, rows));
+      const float* nextw = (l + 1 < d->n_layers) ? d->layers[l + 1].an : d->onorm;
+      PF(launch_add_rmsnorm(ro, md, nextw, ro, hrow, E, d->eps, rows, s));
+      x = ro;
+    }
+  }
+  // logits only for the last row of the last chunk (hrow holds its final norm)
+  PF(run_linear(c, d->lm_head, hrow + (size_t)(last_rows - 1) * E, d->logits, s, nullptr));
+  PF(launch_argmax(c, d->logits, d->vocab, d->d_tok, d->d_tok_out, s));
+#undef PF
+  const unsigned newpos = pos0 + (unsigned)T;
+  d->h_tok[1] = (int)newpos;
+  TLB_CUDA(cudaMemcpyAsync(d->d_pos, &d->h_tok[1], 4, cudaMemcpyHostToDevice, s));
+  TLB_CUDA(cudaMemcpyAsync(d->h_out, d->d_tok_out, 4, cudaMemcpyDeviceToHost, s));
+  TLB_CUDA(cudaStreamSynchronize(s));
+  if (next_token) *next_token = d->h_out[0];
+  return TLB_OK;
+}
+
 int tlb_decoder_last_token(void* h, int32_t* token_out, void* stream) {
   auto* d = (Decoder*)h;
   TLB_REQUIRE(d && token_out, "tlb_decoder_last_token: bad arguments");

@@ -198,6 +198,15 @@ __global__ void embed_gather_kernel(const float* __restrict__ embed,
   }
 }
 
+// Batched form for the prompt pass: row t <- embed[ids[t]] (one block per row).
+__global__ void embed_rows_kernel(const float* __restrict__ embed, const int* __restrict__ ids,
+                                  float* __restrict__ x, int n) {
+  pdl_wait();
+  pdl_launch_dependents();
+  const size_t src = (size_t)ids[blockIdx.x] * n, dst = (size_t)blockIdx.x * n;
+  for (int i = threadIdx.x; i < n; i += blockDim.x) x[dst + i] = embed[src + i];
+}
+
 // ---------------------------------------------------------------------------
 // argmax: smallest index among the maxima (kernels/tensorlib_cuda.cu:90-119).
 // Multi-block: each thread keeps (value, index) with strict '>', a packed
@@ -306,7 +315,7 @@ __global__ void add_rmsnorm_ar_kernel(const float* a, const float* __restrict__ 
   __shared__ float sm[32];
   pdl_wait();
   pdl_launch_dependents();
-  const unsigned seq = *(volatile unsigned*)comm.seq;
+  const unsigned seq = comm_seq(comm);
   const uint2* st = comm.stage[comm.rank] + (size_t)(seq & 1u) * comm.size * comm.slot_floats;
   float acc = 0.f;
   for (int i = threadIdx.x; i < n; i += blockDim.x) {
@@ -329,7 +338,6 @@ __global__ void add_rmsnorm_ar_kernel(const float* a, const float* __restrict__ 
   const float tot = block_sum(acc, sm);
   const float inv = 1.0f / sqrtf(tot / (float)n + eps);
   for (int i = threadIdx.x; i < n; i += blockDim.x) hout[i] = xout[i] * inv * w[i];
-  if (threadIdx.x == 0) *comm.seq = seq + 1u;
 }
 
 // Vocabulary-parallel argmax: each rank reduces its logits shard to a packed key
@@ -365,7 +373,7 @@ __global__ void argmax_push_kernel(const float* __restrict__ in, int n, unsigned
       __threadfence();
       unsigned long long k = atomicExch(&cell[0], 0ull);
       *(unsigned*)&cell[1] = 0u;
-      const unsigned seq = *(volatile unsigned*)comm.seq;
+      const unsigned seq = comm_seq(comm);
       const size_t off = ((size_t)(seq & 1u) * comm.size + comm.rank) * (size_t)comm.slot_floats;
       for (int r = 0; r < comm.size; r++) {
         st_packet_sys(&comm.stage[r][off], __uint_as_float((unsigned)(k & 0xFFFFFFFFull)), seq + 1u);
@@ -379,7 +387,7 @@ __global__ void argmax_finish_kernel(CommDev comm, int* out_idx, int* out_idx2, 
   pdl_wait();
   pdl_launch_dependents();
   if (threadIdx.x == 0) {
-    const unsigned seq = *(volatile unsigned*)comm.seq;
+    const unsigned seq = comm_seq(comm);
     const uint2* st = comm.stage[comm.rank] + (size_t)(seq & 1u) * comm.size * comm.slot_floats;
     unsigned long long best = 0ull;
     for (int r = 0; r < comm.size; r++) {
@@ -391,7 +399,7 @@ __global__ void argmax_finish_kernel(CommDev comm, int* out_idx, int* out_idx2, 
     const int idx = (int)(0xFFFFFFFFu - (unsigned)(best & 0xFFFFFFFFull));
     *out_idx = idx;
     if (out_idx2) *out_idx2 = idx;
-    *comm.seq = seq + 1u;
+    *comm.seq = *(volatile unsigned*)comm.seq + 1u;   // the token's last exchange: advance the token counter
   }
 }
 
@@ -453,6 +461,11 @@ int launch_embed_gather(const float* embed, const int* d_tok, float* x, int n, f
   if (threads < D / 2) threads = D / 2;
   LaunchCfg lc(dim3(1), dim3(threads), 0, s, pdl_enabled());
   TLB_CUDA(cudaLaunchKernelEx(&lc.cfg, embed_gather_kernel, embed, d_tok, x, n, rope_cs, d_pos, D, rope_base));
+  return TLB_OK;
+}
+int launch_embed_rows(const float* embed, const int* ids, float* x, int n, int rows, cudaStream_t s) {
+  LaunchCfg lc(dim3(rows), dim3(row_threads(n)), 0, s, pdl_enabled());
+  TLB_CUDA(cudaLaunchKernelEx(&lc.cfg, embed_rows_kernel, embed, ids, x, n));
   return TLB_OK;
 }
 int launch_argmax(DeviceCtx* c, const float* in, int n, int* out_idx, int* out_idx2,

@@ -289,7 +289,7 @@ __global__ void __launch_bounds__(WARPS * 32, (WARPS == 8 ? 2 : 1))
   const unsigned wbase = (unsigned)g * 32u + (unsigned)t;
 
   unsigned ar_seq = 0;
-  if (p.push) ar_seq = *(volatile unsigned*)p.comm.seq;
+  if (p.push) ar_seq = comm_seq(p.comm);
   const size_t ar_off =
       ((size_t)(ar_seq & 1u) * p.comm.size + p.comm.rank) * (size_t)p.comm.slot_floats;
   auto emit = [&](int m, int n, float v) {

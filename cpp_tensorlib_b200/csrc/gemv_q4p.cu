@@ -109,12 +109,15 @@ struct GemvPParams {
   int* status;
   int x_vec_ok;
   int act;          // 0: x as given; 1: x = [gate(K) | up(K)] -> silu(gate)*up;
-                    // 2: x = rmsnorm(x + delta) * nw, the sum also written to xout
+                    // 2: x = rmsnorm(x + delta) * nw, the sum also written to xout;
+                    // 3: as 2 with delta = the ranks' partial vectors of a tensor-parallel
+                    //    exchange, polled from this rank's staging and summed in rank order
   const float* delta;
   const float* nw;
   float* xout;
   float eps;
-  int push;         // tensor-parallel: store y into every rank's staging slot
+  int push;         // tensor-parallel: store y into every rank's staging slot (comm = that exchange)
+                    // (act 3 reads comm instead: a launch pulls or pushes, never both)
   PairEpi epi;
   int cta_tiles;    // small matrices: a CTA owns whole row tiles and reduces them in shared memory
   CommDev comm;
@@ -236,6 +239,40 @@ __global__ void __launch_bounds__(PK_WARPS * 32, 1) gemv_q4p_kernel(GemvPParams 
   // Lane l covers x[256*slab + 8*l .. +8) = group jj = l/4, quad slot tt = l%4.
   float nrm_inv = 1.f;
   constexpr int PB = 2;
+  const bool normed = p.act == 2 || p.act == 3;
+  unsigned pull_seq = 0;
+  if (p.act == 3) pull_seq = comm_seq(p.comm);
+  // act 3: the exchange's reduction.  Packets validate themselves by their tag; up to four
+  // ranks' polls are in flight before the first check, the partials are added in rank
+  // order (every rank and every CTA computes the same bits).
+  auto pull8 = [&](int k0, float (&o)[8], bool on) {
+#pragma unroll
+    for (int i = 0; i < 8; i++) o[i] = 0.f;
+    if (!on) return;
+    const unsigned tag = pull_seq + 1u;
+    const uint2* stb = p.comm.stage[p.comm.rank] +
+                       (size_t)(pull_seq & 1u) * p.comm.size * p.comm.slot_floats + k0;
+    for (int r0 = 0; r0 < p.comm.size; r0 += 4) {
+      uint2 pk[4][8];
+#pragma unroll
+      for (int rr = 0; rr < 4; rr++)
+        if (r0 + rr < p.comm.size) {
+#pragma unroll
+          for (int i = 0; i < 8; i++) pk[rr][i] = ld_packet_sys(stb + (size_t)(r0 + rr) * p.comm.slot_floats + i);
+        }
+#pragma unroll
+      for (int rr = 0; rr < 4; rr++)
+        if (r0 + rr < p.comm.size) {
+#pragma unroll
+          for (int i = 0; i < 8; i++) {
+            if (pk[rr][i].y != tag)
+              pk[rr][i] = wait_packet_bounded(stb + (size_t)(r0 + rr) * p.comm.slot_floats + i, tag,
+                                              p.status, 300 + r0 + rr);
+            o[i] += __uint_as_float(pk[rr][i].x);
+          }
+        }
+    }
+  };
   for (int job0 = warp; job0 < SL || job0 == warp; job0 += PK_WARPS * PB) {
     float vv[PB][8], uu[PB][8];
 #pragma unroll
@@ -261,13 +298,14 @@ __global__ void __launch_bounds__(PK_WARPS * 32, 1) gemv_q4p_kernel(GemvPParams 
       load8(p.x + k0, vv[b]);
       if (p.act == 1) load8(p.x + p.K + k0, uu[b]);
       if (p.act == 2) load8(p.delta + k0, uu[b]);
+      if (p.act == 3) pull8(k0, uu[b], on);
     }
     if (job0 == warp) {
       // first batch: its loads are in flight, now queue the rest of the weight ring
       // (an L2 prefetch of the units behind the ring was tried here and lost 4 us on the
       // 85 MB gate|up matrix: the demand copies queue behind it)
       for (int i = 1; i < pre_total; i++) issue_next();
-      if (p.act == 2) {
+      if (normed) {
         // fused residual add + RMSNorm (tl_add_rmsnorm, kernels/tensorlib_cuda.cu:155-179):
         // every CTA reduces sum((x+delta)^2) itself from the values it just loaded, in
         // the same order everywhere, so all CTAs agree on the scale.  (The host only
@@ -301,7 +339,7 @@ __global__ void __launch_bounds__(PK_WARPS * 32, 1) gemv_q4p_kernel(GemvPParams 
 #pragma unroll
         for (int i = 0; i < 8; i++) v[i] = (v[i] / (1.0f + expf(-v[i]))) * uu[b][i];
       }
-      if (p.act == 2) {
+      if (normed) {
         const int k0 = sl * 256 + lane * 8;
 #pragma unroll
         for (int i = 0; i < 8; i++) {
@@ -363,7 +401,7 @@ __global__ void __launch_bounds__(PK_WARPS * 32, 1) gemv_q4p_kernel(GemvPParams 
   const uint32_t cl = 2048u + (uint32_t)g * 32u + (uint32_t)t * 8u;
 
   unsigned ar_seq = 0;
-  if (p.push) ar_seq = *(volatile unsigned*)p.comm.seq;
+  if (p.push) ar_seq = comm_seq(p.comm);
   const size_t ar_off =
       ((size_t)(ar_seq & 1u) * p.comm.size + p.comm.rank) * (size_t)p.comm.slot_floats;
   auto emit = [&](int n, float v) {
@@ -608,9 +646,13 @@ static int gemvp_launch_t(const GemvPParams& p, int ctas, size_t smem, cudaStrea
 int gemv_q4p_launch(DeviceCtx* c, const void* packed, const float* x, float* y, int N, int K,
                     float alpha, float beta, cudaStream_t stream, int max_ctas,
                     const CommDev* push_comm, int act, const float* delta, const float* nw,
-                    float* xout, float eps, const PairEpi* epi) {
+                    float* xout, float eps, const PairEpi* epi, const CommDev* pull_comm) {
   GemvPParams p;
   memset(&p, 0, sizeof(p));
+  if (pull_comm) {
+    if (push_comm) return set_error(TLB_ERR_ARG, "gemv_q4p: a launch pulls or pushes, not both");
+    act = 3;
+  }
   if (epi) {
     p.epi = *epi;
     if (push_comm) return set_error(TLB_ERR_ARG, "gemv_q4p: a pair epilogue cannot push");
@@ -622,10 +664,14 @@ int gemv_q4p_launch(DeviceCtx* c, const void* packed, const float* x, float* y, 
   p.delta = delta; p.nw = nw; p.xout = xout; p.eps = eps;
   if (act == 2 && (!delta || !nw || !xout))
     return set_error(TLB_ERR_ARG, "gemv_q4p: fused add+rmsnorm needs its three buffers");
-  if (act == 2 && (K + 255) / 256 > PK_WARPS * 4)
-    return set_error(TLB_ERR_UNSUPPORTED, "gemv_q4p: fused add+rmsnorm needs K <= 16384");
+  if (act == 3 && (!nw || !xout || K > pull_comm->slot_floats))
+    return set_error(TLB_ERR_ARG, "gemv_q4p: fused exchange + rmsnorm needs nw, xout and K within the staging slot");
+  // the norm's sum of squares is taken from the first batch of slabs: it must cover the row
+  if ((act == 2 || act == 3) && (K + 255) / 256 > PK_WARPS * 2)
+    return set_error(TLB_ERR_UNSUPPORTED, "gemv_q4p: fused add+rmsnorm needs K <= 8192");
   p.push = push_comm ? 1 : 0;
   if (push_comm) p.comm = *push_comm;
+  if (pull_comm) p.comm = *pull_comm;
   p.wp = (const unsigned char*)packed;
   p.x = x; p.y = y; p.N = N; p.K = K;
   p.alpha = alpha; p.beta = beta;

@@ -30,6 +30,6 @@ int launch_q4_pack(const void* q4, int N, int K, void* out, int pair_h, cudaStre
 int gemv_q4p_launch(DeviceCtx* c, const void* packed, const float* x, float* y, int N, int K,
                     float alpha, float beta, cudaStream_t stream, int max_ctas,
                     const CommDev* push_comm, int act, const float* delta, const float* nw,
-                    float* xout, float eps, const PairEpi* epi);
+                    float* xout, float eps, const PairEpi* epi, const CommDev* pull_comm);
 
 }  // namespace tlb

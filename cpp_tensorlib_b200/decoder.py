@@ -231,6 +231,15 @@ class Q4Decoder:
         check(lib().tlb_decoder_step(self.h, C.byref(tin), C.byref(tout), self._stream()))
         return int(tout.value)
 
+    def prefill(self, tokens):
+        """prefill_batched (bench/cuda/qwen_model.h:423-442): the whole prompt as row-batched
+        GEMMs + tiled causal attention from the current position; returns the greedy next
+        token, which is also left on the device for run()."""
+        ids = (C.c_int32 * len(tokens))(*[int(t) for t in tokens])
+        tout = C.c_int32(0)
+        check(lib().tlb_decoder_prefill(self.h, ids, len(tokens), C.byref(tout), self._stream()))
+        return int(tout.value)
+
     def last_token(self):
         t = C.c_int32(0)
         check(lib().tlb_decoder_last_token(self.h, C.byref(t), self._stream()))

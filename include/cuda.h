@@ -80,6 +80,9 @@ struct backend {
   int (*incr_u32)(void*, void*) = nullptr;
   int (*argmax)(const float*, int64_t, int64_t*, void*) = nullptr;
   int (*memset_)(void*, int, int64_t, void*) = nullptr;
+  int64_t (*q4p_bytes)(int64_t, int64_t) = nullptr;
+  int (*q4_pack)(const void*, int64_t, int64_t, void*, void*) = nullptr;
+  int (*gemv_q4p)(const float*, const void*, float*, int64_t, int64_t, float, float, void*) = nullptr;
   int (*split_heads)(const float*, const float*, float*, int64_t, int64_t, int64_t, int64_t, int64_t, void*) = nullptr;
   int (*merge_heads)(const float*, float*, int64_t, int64_t, int64_t, void*) = nullptr;
   int (*kv_fill)(float*, float*, const float*, const float*, int64_t, int64_t, int64_t, int64_t, int64_t, void*) = nullptr;
@@ -100,6 +103,47 @@ struct backend {
   };
   std::unordered_map<void*, twin> twins;                                  // key: device pointer
   std::unordered_map<size_t, std::vector<std::pair<void*, float*>>> pool;  // recycled, by size
+
+  // Weights seen by gemv_q4 are repacked once into the library's tile-packed layout (the
+  // fast decode GEMV reads that); key: the q4 buffer's device pointer.  An entry dies when
+  // the mirror uploads new host contents into the buffer, a kernel writes it, or it is
+  // released.  TLB200_SEAM_PACK=0 keeps the reference layout (half the weight memory).
+  struct packed_w {
+    void* dev = nullptr;
+    int64_t N = 0, K = 0;
+  };
+  std::unordered_map<void*, packed_w> packed;
+  int pack_enabled = -1;
+  void drop_packed(void* native) {
+    auto it = packed.find(native);
+    if (it == packed.end()) return;
+    sync(stream);   // a launch may still read it
+    free_(it->second.dev);
+    packed.erase(it);
+  }
+  const void* packed_for(void* qw, int64_t N, int64_t K) {
+    if (pack_enabled < 0) {
+      const char* e = std::getenv("TLB200_SEAM_PACK");
+      pack_enabled = (e && e[0] == '0') ? 0 : 1;
+    }
+    if (!pack_enabled) return nullptr;
+    auto it = packed.find(qw);
+    if (it != packed.end()) {
+      if (it->second.N == N && it->second.K == K) return it->second.dev;
+      drop_packed(qw);
+    }
+    const int64_t nb = q4p_bytes(N, K);
+    packed_w w;
+    if (nb <= 0 || alloc_(nb, &w.dev) != 0) return nullptr;
+    if (q4_pack(qw, N, K, w.dev, stream) != 0) {
+      free_(w.dev);
+      return nullptr;
+    }
+    w.N = N;
+    w.K = K;
+    packed.emplace(qw, w);
+    return w.dev;
+  }
 
   template <class F>
   bool bind(F& fn, const char* name) {
@@ -134,7 +178,8 @@ struct backend {
               bind(rope, "tlb_rope") && bind(rope_dpos, "tlb_rope_dpos") &&
               bind(kv_append, "tlb_kv_append") && bind(kv_append_dpos, "tlb_kv_append_dpos") &&
               bind(incr_u32, "tlb_incr_u32") && bind(argmax, "tlb_argmax") &&
-              bind(memset_, "tlb_memset") && bind(split_heads, "tlb_split_heads") &&
+              bind(memset_, "tlb_memset") && bind(q4p_bytes, "tlb_q4p_bytes") &&
+              bind(q4_pack, "tlb_q4_pack") && bind(gemv_q4p, "tlb_gemv_q4p") && bind(split_heads, "tlb_split_heads") &&
               bind(merge_heads, "tlb_merge_heads") && bind(kv_fill, "tlb_kv_fill") &&
               bind(attn_prefill, "tlb_attn_prefill") && bind(capture_begin, "tlb_capture_begin") &&
               bind(capture_end, "tlb_capture_end") && bind(graph_launch, "tlb_graph_launch") &&
@@ -164,10 +209,12 @@ struct backend {
     if (t && t->where == HOST) {
       if (h2d(native, t->host, (int64_t)t->bytes, stream) != 0) fail("upload");
       t->where = BOTH;
+      drop_packed(native);   // new contents: a packed copy of the old ones is stale
     }
   }
   void writes(void* native) {
     if (twin* t = find(native)) t->where = DEVICE;
+    drop_packed(native);
   }
 };
 
@@ -214,6 +261,7 @@ inline void* alloc(int64_t bytes, float** contents) {
 inline void release(void* buf, int64_t, float*) {
   auto& b = detail::backend::get();
   if (!b.ready || !buf) return;
+  b.drop_packed(buf);
   auto it = b.twins.find(buf);
   if (it == b.twins.end()) {
     b.free_(buf);
@@ -275,6 +323,14 @@ inline bool gemv_q4(void* a, void* qw, void* scales, void* y, int64_t N, int64_t
   auto& b = detail::backend::get();
   if (!b.ready) return false;
   b.reads(a); b.reads(qw); b.reads(scales); b.writes(y);
+  // scales sit inside the same buffer at qw + N*K/2 (reference array.h:1621-1622): only then
+  // is qw the whole weight, and only then may the packed copy stand in for it
+  if (group == 32 && static_cast<char*>(scales) == static_cast<char*>(qw) + N * K / 2) {
+    if (const void* pk = b.packed_for(qw, N, K)) {
+      b.must(b.gemv_q4p(detail::f(a), pk, detail::fw(y), N, K, 1.0f, 0.0f, b.stream), "gemv_q4 (packed)");
+      return true;
+    }
+  }
   b.must(b.gemv_q4(detail::f(a), qw, detail::f(scales), detail::fw(y), N, K, group, b.stream), "gemv_q4");
   return true;
 }

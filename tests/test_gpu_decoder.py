@@ -152,3 +152,36 @@ def test_decoder_argument_errors():
     with pytest.raises(TlbError):
         d.step(1)                          # weights never set
     d.close()
+
+
+@pytest.mark.parametrize("cfg,seed,T", [(cases.TINY, 21, 19), (cases.TINY64, 22, 40),
+                                        (dict(cases.QWEN05, layers=2), 2, 300)])
+def test_batched_prefill_matches_token_by_token(cfg, seed, T):
+    """The batched prompt pass (bench/cuda/qwen_model.h:357-442) against the decode loop of
+    the same decoder: same greedy token after the prompt, logits and every cache row within
+    1e-3, and identical greedy ids for the tokens decoded after it.  T = 300 spans two
+    chunks of 256 and puts the projections on the tensor-core GEMM."""
+    d1, wts = make(cfg, seed, T + 16)
+    d2, _ = make(cfg, seed, T + 16, wts)
+    prompt = [int(t) for t in synth.token_ids(seed, 7, T, cfg["vocab"])]
+    d1.set_pos(0)
+    nxt1 = 0
+    for t in prompt:
+        nxt1 = d1.step(t)
+    lg1 = d1.logits().cpu().numpy().copy()
+    d2.set_pos(0)
+    nxt2 = d2.prefill(prompt)
+    assert nxt2 == nxt1
+    assert np.allclose(d2.logits().cpu().numpy(), lg1, rtol=1e-3, atol=1e-3)
+    for l in range(cfg["layers"]):
+        K1, V1 = d1.kv(l)
+        K2, V2 = d2.kv(l)
+        assert np.allclose(K2[:, :T].cpu().numpy(), K1[:, :T].cpu().numpy(), rtol=1e-3, atol=1e-3), l
+        assert np.allclose(V2[:, :T].cpu().numpy(), V1[:, :T].cpu().numpy(), rtol=1e-3, atol=1e-3), l
+    a, b = [], []
+    t1, t2 = nxt1, nxt2
+    for _ in range(8):
+        t1 = d1.step(t1); a.append(t1)
+        t2 = d2.step(t2); b.append(t2)
+    assert a == b
+    d1.close(); d2.close()
