@@ -78,8 +78,7 @@ __host__ __device__ inline int attn_hs(int grp, int HW, int warps) {
 }
 
 // LPK = lanes that share a key: 8 (8 warps, 4 keys per warp step) or 16 (16 warps, 2 keys
-// per step, half the per-lane state: the wide-group configuration, where 8 warps of
-// 4-head state leave the schedulers two warps each and the tile loop latency bound).
+// per step, half the per-lane state; an experiment for wide groups, not the default).
 template <int D, int HW, int LPK>
 struct AttnCfg {
   static constexpr int STAGES = HW >= 4 ? 4 : 3;
@@ -481,10 +480,11 @@ int attn_decode_launch(DeviceCtx* c, const float* q, const float* K, const float
   if (D == 128) {
     if (HW == 1) return launch_t<128, 1, 8>(p, splits, stream);
     if (HW == 2) return launch_t<128, 2, 8>(p, splits, stream);
-    // wide groups: 16 lanes per key and 16 warps (TLB_ATTN_LPK=8 selects the 8-warp form)
-    static const int lpk = getenv("TLB_ATTN_LPK") ? atoi(getenv("TLB_ATTN_LPK")) : 16;
-    if (lpk == 8) return launch_t<128, 4, 8>(p, splits, stream);
-    return launch_t<128, 4, 16>(p, splits, stream);
+    // TLB_ATTN_LPK=16 selects the 16-warp form (16 lanes per key); measured 6 % slower than
+    // the 8-warp form on the 7B layer shape (14.4 vs 13.6 us), so it is not the default
+    static const int lpk = getenv("TLB_ATTN_LPK") ? atoi(getenv("TLB_ATTN_LPK")) : 8;
+    if (lpk == 16) return launch_t<128, 4, 16>(p, splits, stream);
+    return launch_t<128, 4, 8>(p, splits, stream);
   }
   if (HW == 1) return launch_t<64, 1, 8>(p, splits, stream);
   if (HW == 2) return launch_t<64, 2, 8>(p, splits, stream);

@@ -168,7 +168,9 @@ __device__ __forceinline__ float lds32f(uint32_t a) {
   return v;
 }
 
-template <int STAGES>
+// PULL: the instantiation that can consume a tensor-parallel exchange in its prologue (act 3);
+// kept out of the single-GPU kernel, whose register budget it would eat.
+template <int STAGES, bool PULL>
 __global__ void __launch_bounds__(PK_WARPS * 32, 1) gemv_q4p_kernel(GemvPParams p) {
   extern __shared__ unsigned char smem_raw[];
   unsigned char* base = (unsigned char*)(((uintptr_t)smem_raw + 127) & ~(uintptr_t)127);
@@ -239,11 +241,11 @@ __global__ void __launch_bounds__(PK_WARPS * 32, 1) gemv_q4p_kernel(GemvPParams 
   // Lane l covers x[256*slab + 8*l .. +8) = group jj = l/4, quad slot tt = l%4.
   float nrm_inv = 1.f;
   constexpr int PB = 2;
-  const bool normed = p.act == 2 || p.act == 3;
+  const bool normed = p.act == 2 || (PULL && p.act == 3);
   unsigned pull_seq = 0;
-  if (p.act == 3) pull_seq = comm_seq(p.comm);
-  // act 3: the exchange's reduction.  Packets validate themselves by their tag; up to four
-  // ranks' polls are in flight before the first check, the partials are added in rank
+  if (PULL && p.act == 3) pull_seq = comm_seq(p.comm);
+  // act 3: the exchange's reduction.  Packets validate themselves by their tag; two
+  // ranks' polls (16 packets per lane) are in flight before the first check, the partials are added in rank
   // order (every rank and every CTA computes the same bits).
   auto pull8 = [&](int k0, float (&o)[8], bool on) {
 #pragma unroll
@@ -252,16 +254,16 @@ __global__ void __launch_bounds__(PK_WARPS * 32, 1) gemv_q4p_kernel(GemvPParams 
     const unsigned tag = pull_seq + 1u;
     const uint2* stb = p.comm.stage[p.comm.rank] +
                        (size_t)(pull_seq & 1u) * p.comm.size * p.comm.slot_floats + k0;
-    for (int r0 = 0; r0 < p.comm.size; r0 += 4) {
-      uint2 pk[4][8];
+    for (int r0 = 0; r0 < p.comm.size; r0 += 2) {
+      uint2 pk[2][8];
 #pragma unroll
-      for (int rr = 0; rr < 4; rr++)
+      for (int rr = 0; rr < 2; rr++)
         if (r0 + rr < p.comm.size) {
 #pragma unroll
           for (int i = 0; i < 8; i++) pk[rr][i] = ld_packet_sys(stb + (size_t)(r0 + rr) * p.comm.slot_floats + i);
         }
 #pragma unroll
-      for (int rr = 0; rr < 4; rr++)
+      for (int rr = 0; rr < 2; rr++)
         if (r0 + rr < p.comm.size) {
 #pragma unroll
           for (int i = 0; i < 8; i++) {
@@ -298,7 +300,9 @@ __global__ void __launch_bounds__(PK_WARPS * 32, 1) gemv_q4p_kernel(GemvPParams 
       load8(p.x + k0, vv[b]);
       if (p.act == 1) load8(p.x + p.K + k0, uu[b]);
       if (p.act == 2) load8(p.delta + k0, uu[b]);
-      if (p.act == 3) pull8(k0, uu[b], on);
+      if constexpr (PULL) {
+        if (p.act == 3) pull8(k0, uu[b], on);
+      }
     }
     if (job0 == warp) {
       // first batch: its loads are in flight, now queue the rest of the weight ring
@@ -630,16 +634,16 @@ bool gemv_q4p_supported(long long N, long long K) {
   return N > 0 && K > 0 && K % 32 == 0 && K <= (1 << 20) && gemvp_stages((int)K) != 0;
 }
 
-template <int STAGES>
+template <int STAGES, bool PULL>
 static int gemvp_launch_t(const GemvPParams& p, int ctas, size_t smem, cudaStream_t stream) {
   static bool attr = false;
   if (!attr) {
-    TLB_CUDA(cudaFuncSetAttribute(gemv_q4p_kernel<STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                  227 * 1024));
+    TLB_CUDA(cudaFuncSetAttribute(gemv_q4p_kernel<STAGES, PULL>,
+                                  cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
     attr = true;
   }
   LaunchCfg lc(dim3(ctas), dim3(PK_WARPS * 32), smem, stream, pdl_enabled());
-  TLB_CUDA(cudaLaunchKernelEx(&lc.cfg, gemv_q4p_kernel<STAGES>, p));
+  TLB_CUDA(cudaLaunchKernelEx(&lc.cfg, gemv_q4p_kernel<STAGES, PULL>, p));
   return TLB_OK;
 }
 
@@ -698,9 +702,14 @@ int gemv_q4p_launch(DeviceCtx* c, const void* packed, const float* x, float* y, 
     }
   }
   const size_t smem = gemvp_smem_layout(stages, K).total;
-  if (stages == 4) return gemvp_launch_t<4>(p, ctas, smem, stream);
-  if (stages == 3) return gemvp_launch_t<3>(p, ctas, smem, stream);
-  return gemvp_launch_t<2>(p, ctas, smem, stream);
+  if (p.act == 3) {
+    if (stages == 4) return gemvp_launch_t<4, true>(p, ctas, smem, stream);
+    if (stages == 3) return gemvp_launch_t<3, true>(p, ctas, smem, stream);
+    return gemvp_launch_t<2, true>(p, ctas, smem, stream);
+  }
+  if (stages == 4) return gemvp_launch_t<4, false>(p, ctas, smem, stream);
+  if (stages == 3) return gemvp_launch_t<3, false>(p, ctas, smem, stream);
+  return gemvp_launch_t<2, false>(p, ctas, smem, stream);
 }
 
 }  // namespace tlb
