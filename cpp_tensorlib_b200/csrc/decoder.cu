@@ -209,12 +209,14 @@ static int forward(Decoder* d, cudaStream_t s) {
     c2.E = EX;
     return c2;
   };
-  // TLB_TP_PULL_MAX (diagnostics): largest rank count that uses the fused consumer (default 4)
+  // TLB_TP_PULL_MAX: largest rank count whose exchanges are consumed inside the next
+  // projection's prologue.  Default 1 = never: measured on 2 GPUs the 148 CTAs' system-scope
+  // polls cost what the two saved kernels per layer cost (582 vs 589 tok/s).
   const char* pm = getenv("TLB_TP_PULL_MAX");
-  const int pull_max = pm ? atoi(pm) : 4;
+  const int pull_max = pm ? atoi(pm) : 1;
   if (all_tma && (!tp || d->tp_size <= pull_max)) {
     // Both residual adds and norms of a layer run inside the following projection's
-    // activation prep (5 launches per layer).  Tensor parallel (up to 4 ranks): that
+    // activation prep (5 launches per layer).  Tensor parallel (opt-in, see above): that
     // prologue is also the exchange's consumer -- it polls the ranks' partial vectors from
     // this rank's staging and sums them in rank order -- so the row-parallel projection's
     // push and the next projection are the only kernels of an all-reduce.  The residual

@@ -12,8 +12,12 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 
 
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
-def test_two_rank_decoder_matches_oracle():
-    env = dict(os.environ, NCCL_NVLS_ENABLE="0")
+@pytest.mark.parametrize("pull_max", ["1", "4"])
+def test_two_rank_decoder_matches_oracle(pull_max):
+    """Two ranks on two GPUs against the oracle, with the exchange consumed by its own
+    add+rmsnorm kernel (pull_max 1, the default) and inside the next projection's
+    prologue (pull_max 4)."""
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0", TLB_TP_PULL_MAX=pull_max)
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2",
            "--master-addr", "127.0.0.1", "--master-port", "29611", os.path.join(HERE, "tp_worker.py")]
     r = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=600)
