@@ -33,8 +33,10 @@ SIGNATURES = {
     "tlb_gemm_q4": (ci, [vp, i64, i64, vp, vp, vp, i64, i64, i64, f32, f32, vp]),
     "tlb_gemm_q4_simt": (ci, [vp, i64, i64, vp, vp, vp, i64, i64, i64, f32, f32, vp]),
     "tlb_attn_decode": (ci, [vp, vp, vp, vp, i64, i64, i64, i64, i64, f32, vp]),
+    "tlb_attn_decode_bf16": (ci, [vp, vp, vp, vp, i64, i64, i64, i64, i64, f32, vp]),
     "tlb_attn_decode_noalloc": (ci, [vp, vp, vp, vp, i64, i64, i64, i64, i64, f32, vp]),
     "tlb_attn_decode_dpos": (ci, [vp, vp, vp, vp, i64, i64, vp, i64, i64, f32, vp, vp]),
+    "tlb_attn_decode_dpos_bf16": (ci, [vp, vp, vp, vp, i64, i64, vp, i64, i64, f32, vp, vp]),
     "tlb_attn_partials_bytes": (i64, [i64, i64, i64, i64]),
     "tlb_rmsnorm": (ci, [vp, vp, vp, i64, f32, i64, vp]),
     "tlb_rmsnorm_res": (ci, [vp, vp, vp, vp, vp, i64, f32, i64, vp]),
@@ -42,7 +44,9 @@ SIGNATURES = {
     "tlb_rope": (ci, [vp, vp, i64, i64, i64, i64, f32, vp, vp]),
     "tlb_rope_dpos": (ci, [vp, vp, i64, i64, i64, vp, f32, vp, vp]),
     "tlb_kv_append": (ci, [vp, vp, vp, vp, i64, i64, i64, i64, vp]),
+    "tlb_kv_append_bf16": (ci, [vp, vp, vp, vp, i64, i64, i64, i64, vp]),
     "tlb_kv_append_dpos": (ci, [vp, vp, vp, vp, vp, i64, i64, i64, vp]),
+    "tlb_kv_append_dpos_bf16": (ci, [vp, vp, vp, vp, vp, i64, i64, i64, vp]),
     "tlb_incr_u32": (ci, [vp, vp]),
     "tlb_argmax": (ci, [vp, i64, C.POINTER(i64), vp]),
     "tlb_argmax_dev": (ci, [vp, i64, vp, vp]),
@@ -52,6 +56,7 @@ SIGNATURES = {
     "tlb_split_heads": (ci, [vp, vp, vp, i64, i64, i64, i64, i64, vp]),
     "tlb_merge_heads": (ci, [vp, vp, i64, i64, i64, vp]),
     "tlb_kv_fill": (ci, [vp, vp, vp, vp, i64, i64, i64, i64, i64, vp]),
+    "tlb_kv_fill_bf16": (ci, [vp, vp, vp, vp, i64, i64, i64, i64, i64, vp]),
     "tlb_attn_prefill": (ci, [vp, vp, vp, vp, i64, i64, i64, i64, i64, f32, i64, vp]),
     "tlb_capture_begin": (ci, [C.POINTER(vp)]),
     "tlb_capture_end": (ci, [C.POINTER(vp)]),

@@ -26,24 +26,26 @@ int gemm_q4_tc_launch(DeviceCtx* c, const float* x, long long ldx, int M, const 
                       const float* scales, float* y, long long ldy, int N, int K, float alpha,
                       float beta, float* xsplit, cudaStream_t stream);
 size_t attn_partials_bytes(int n_q, int n_kv, long long kv_max, int D, int sm_count);
-int attn_decode_launch(DeviceCtx* c, const float* q, const float* K, const float* V, float* out,
+int attn_decode_launch(DeviceCtx* c, const float* q, const void* K, const void* V, float* out,
                        int n_q, int n_kv, int ctx, long long kv_max, int D, float scale,
-                       const unsigned* d_pos, float* partials, int* counters, cudaStream_t stream, int early_kv);
+                       const unsigned* d_pos, float* partials, int* counters, cudaStream_t stream,
+                       int early_kv, int kv_bf16);
 int launch_rmsnorm(const float*, const float*, float*, int, float, int, cudaStream_t);
 int launch_add_rmsnorm(const float*, const float*, const float*, float*, float*, int, float, int,
                        cudaStream_t);
 int launch_swiglu(const float*, float*, int, int, cudaStream_t);
 int launch_rope(const float*, const float*, float*, int, int, int, unsigned, const unsigned*,
                 float, cudaStream_t);
-int launch_kv_append(float*, float*, const float*, const float*, unsigned, const unsigned*,
-                     long long, int, int, cudaStream_t);
+int launch_kv_append(void*, void*, const float*, const float*, unsigned, const unsigned*, long long,
+                     int, int, int, cudaStream_t);
 int launch_incr_u32(unsigned*, cudaStream_t);
 int launch_argmax(DeviceCtx*, const float*, int, int*, int*, cudaStream_t);
 int launch_to_q4(const float*, int, int, unsigned char*, cudaStream_t);
 
 int launch_split_heads(const float*, const float*, float*, int, long long, long long, int, int, cudaStream_t);
 int launch_merge_heads(const float*, float*, int, int, int, cudaStream_t);
-int launch_kv_fill(float*, float*, const float*, const float*, int, long long, int, int, int, cudaStream_t);
+int launch_kv_fill(void*, void*, const float*, const float*, int, long long, int, int, int, int,
+                   cudaStream_t);
 int launch_attn_prefill(DeviceCtx*, const float*, const float*, const float*, float*, int, int, int,
                         long long, int, float, int, cudaStream_t);
 int launch_q4_to_f32(const unsigned char*, int, int, float*, cudaStream_t);
@@ -307,9 +309,9 @@ int tlb_gemv_q4(const float* a, const void* qw, const float* scales, float* y, i
   return tlb_gemm_q4(a, 1, K, qw, scales, y, N, N, K, 1.0f, 0.0f, stream);
 }
 
-int tlb_attn_decode(const float* q, const float* K, const float* V, float* out, int64_t n_q,
-                    int64_t n_kv, int64_t ctx, int64_t kv_max, int64_t D, float scale,
-                    void* stream) {
+static int attn_decode_any(const float* q, const void* K, const void* V, float* out, int64_t n_q,
+                           int64_t n_kv, int64_t ctx, int64_t kv_max, int64_t D, float scale,
+                           void* stream, int kv_bf16) {
   TLB_REQUIRE(q && K && V && out, "tlb_attn_decode: null pointer");
   TLB_REQUIRE(ctx >= 1 && ctx <= kv_max, "tlb_attn_decode: need 1 <= ctx <= kv_max");
   TLB_REQUIRE(n_kv > 0 && n_kv <= 1024, "tlb_attn_decode: n_kv out of range");
@@ -325,7 +327,17 @@ int tlb_attn_decode(const float* q, const float* K, const float* V, float* out, 
     c->attn_scratch_bytes = need;
   }
   return attn_decode_launch(c, q, K, V, out, (int)n_q, (int)n_kv, (int)ctx, kv_max, (int)D, scale,
-                            nullptr, c->attn_scratch, c->attn_counters, S(stream), 0);
+                            nullptr, c->attn_scratch, c->attn_counters, S(stream), 0, kv_bf16);
+}
+int tlb_attn_decode(const float* q, const float* K, const float* V, float* out, int64_t n_q,
+                    int64_t n_kv, int64_t ctx, int64_t kv_max, int64_t D, float scale,
+                    void* stream) {
+  return attn_decode_any(q, K, V, out, n_q, n_kv, ctx, kv_max, D, scale, stream, 0);
+}
+int tlb_attn_decode_bf16(const float* q, const void* K, const void* V, float* out, int64_t n_q,
+                         int64_t n_kv, int64_t ctx, int64_t kv_max, int64_t D, float scale,
+                         void* stream) {
+  return attn_decode_any(q, K, V, out, n_q, n_kv, ctx, kv_max, D, scale, stream, 1);
 }
 
 int64_t tlb_attn_partials_bytes(int64_t n_q, int64_t n_kv, int64_t kv_max, int64_t D) {
@@ -334,16 +346,26 @@ int64_t tlb_attn_partials_bytes(int64_t n_q, int64_t n_kv, int64_t kv_max, int64
   return 256 + (int64_t)attn_partials_bytes((int)n_q, (int)n_kv, kv_max, (int)D, c->sm_count);
 }
 
-int tlb_attn_decode_dpos(const float* q, const float* K, const float* V, float* out, int64_t n_q,
-                         int64_t n_kv, const void* d_pos, int64_t kv_max, int64_t D, float scale,
-                         void* partials, void* stream) {
+static int attn_decode_dpos_any(const float* q, const void* K, const void* V, float* out, int64_t n_q,
+                                int64_t n_kv, const void* d_pos, int64_t kv_max, int64_t D, float scale,
+                                void* partials, void* stream, int kv_bf16) {
   TLB_REQUIRE(q && K && V && out && d_pos && partials, "tlb_attn_decode_dpos: null pointer");
   TLB_REQUIRE(n_kv > 0 && n_kv <= 64, "tlb_attn_decode_dpos: n_kv must be 1..64");
   TLB_REQUIRE(((uintptr_t)partials & 15) == 0, "tlb_attn_decode_dpos: partials must be 16-byte aligned");
   CTX(c);
   return attn_decode_launch(c, q, K, V, out, (int)n_q, (int)n_kv, 0, kv_max, (int)D, scale,
                             (const unsigned*)d_pos, (float*)((char*)partials + 256),
-                            (int*)partials, S(stream), 0);
+                            (int*)partials, S(stream), 0, kv_bf16);
+}
+int tlb_attn_decode_dpos(const float* q, const float* K, const float* V, float* out, int64_t n_q,
+                         int64_t n_kv, const void* d_pos, int64_t kv_max, int64_t D, float scale,
+                         void* partials, void* stream) {
+  return attn_decode_dpos_any(q, K, V, out, n_q, n_kv, d_pos, kv_max, D, scale, partials, stream, 0);
+}
+int tlb_attn_decode_dpos_bf16(const float* q, const void* K, const void* V, float* out, int64_t n_q,
+                              int64_t n_kv, const void* d_pos, int64_t kv_max, int64_t D, float scale,
+                              void* partials, void* stream) {
+  return attn_decode_dpos_any(q, K, V, out, n_q, n_kv, d_pos, kv_max, D, scale, partials, stream, 1);
 }
 
 int tlb_rmsnorm(const float* x, const float* w, float* out, int64_t n, float eps, int64_t rows,
@@ -378,7 +400,15 @@ int tlb_kv_append(float* Kc, float* Vc, const float* k_new, const float* v_new, 
   TLB_REQUIRE(Kc && Vc && k_new && v_new, "tlb_kv_append: null pointer");
   TLB_REQUIRE(pos >= 0 && pos < kv_max, "tlb_kv_append: pos outside the cache");
   TLB_REQUIRE(D > 0 && D <= 1024 && n_kv > 0, "tlb_kv_append: bad shape");
-  return launch_kv_append(Kc, Vc, k_new, v_new, (unsigned)pos, nullptr, kv_max, (int)n_kv, (int)D,
+  return launch_kv_append(Kc, Vc, k_new, v_new, (unsigned)pos, nullptr, kv_max, (int)n_kv, (int)D, 0,
+                          S(stream));
+}
+int tlb_kv_append_bf16(void* Kc, void* Vc, const float* k_new, const float* v_new, int64_t pos,
+                       int64_t kv_max, int64_t n_kv, int64_t D, void* stream) {
+  TLB_REQUIRE(Kc && Vc && k_new && v_new, "tlb_kv_append_bf16: null pointer");
+  TLB_REQUIRE(pos >= 0 && pos < kv_max, "tlb_kv_append_bf16: pos outside the cache");
+  TLB_REQUIRE(D > 0 && D <= 1024 && n_kv > 0, "tlb_kv_append_bf16: bad shape");
+  return launch_kv_append(Kc, Vc, k_new, v_new, (unsigned)pos, nullptr, kv_max, (int)n_kv, (int)D, 1,
                           S(stream));
 }
 int tlb_kv_append_dpos(float* Kc, float* Vc, const float* k_new, const float* v_new,
@@ -386,7 +416,14 @@ int tlb_kv_append_dpos(float* Kc, float* Vc, const float* k_new, const float* v_
   TLB_REQUIRE(Kc && Vc && k_new && v_new && d_pos, "tlb_kv_append_dpos: null pointer");
   TLB_REQUIRE(D > 0 && D <= 1024 && n_kv > 0, "tlb_kv_append_dpos: bad shape");
   return launch_kv_append(Kc, Vc, k_new, v_new, 0u, (const unsigned*)d_pos, kv_max, (int)n_kv,
-                          (int)D, S(stream));
+                          (int)D, 0, S(stream));
+}
+int tlb_kv_append_dpos_bf16(void* Kc, void* Vc, const float* k_new, const float* v_new,
+                            const void* d_pos, int64_t kv_max, int64_t n_kv, int64_t D, void* stream) {
+  TLB_REQUIRE(Kc && Vc && k_new && v_new && d_pos, "tlb_kv_append_dpos_bf16: null pointer");
+  TLB_REQUIRE(D > 0 && D <= 1024 && n_kv > 0, "tlb_kv_append_dpos_bf16: bad shape");
+  return launch_kv_append(Kc, Vc, k_new, v_new, 0u, (const unsigned*)d_pos, kv_max, (int)n_kv,
+                          (int)D, 1, S(stream));
 }
 int tlb_incr_u32(void* d_pos, void* stream) {
   TLB_REQUIRE(d_pos, "tlb_incr_u32: null pointer");
@@ -424,7 +461,14 @@ int tlb_kv_fill(float* Kc, float* Vc, const float* K, const float* V, int64_t T,
   TLB_REQUIRE(Kc && Vc && K && V, "tlb_kv_fill: null pointer");
   TLB_REQUIRE(T > 0 && T <= 65535 && pos0 >= 0 && pos0 + T <= kv_max, "tlb_kv_fill: rows outside the cache");
   TLB_REQUIRE(D > 0 && D <= 1024 && n_kv > 0, "tlb_kv_fill: bad shape");
-  return launch_kv_fill(Kc, Vc, K, V, (int)T, kv_max, (int)n_kv, (int)D, (int)pos0, S(stream));
+  return launch_kv_fill(Kc, Vc, K, V, (int)T, kv_max, (int)n_kv, (int)D, (int)pos0, 0, S(stream));
+}
+int tlb_kv_fill_bf16(void* Kc, void* Vc, const float* K, const float* V, int64_t T, int64_t kv_max,
+                     int64_t n_kv, int64_t D, int64_t pos0, void* stream) {
+  TLB_REQUIRE(Kc && Vc && K && V, "tlb_kv_fill_bf16: null pointer");
+  TLB_REQUIRE(T > 0 && T <= 65535 && pos0 >= 0 && pos0 + T <= kv_max, "tlb_kv_fill_bf16: rows outside the cache");
+  TLB_REQUIRE(D > 0 && D <= 1024 && n_kv > 0, "tlb_kv_fill_bf16: bad shape");
+  return launch_kv_fill(Kc, Vc, K, V, (int)T, kv_max, (int)n_kv, (int)D, (int)pos0, 1, S(stream));
 }
 int tlb_attn_prefill(const float* q, const float* K, const float* V, float* out, int64_t n_q,
                      int64_t n_kv, int64_t T, int64_t kv_max, int64_t D, float scale, int64_t pos0,

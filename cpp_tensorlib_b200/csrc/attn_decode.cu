@@ -36,8 +36,8 @@ constexpr int AT_TK = 32;  // keys per tile
 
 struct AttnParams {
   const float* q;
-  const float* K;
-  const float* V;
+  const void* K;   // f32 or bf16 cache (template parameter BF of the kernel)
+  const void* V;
   float* out;
   float* partials;     // [n_q][S_cap][D+4]  (acc[D], m, l, pad, pad)
   int* counters;       // [n_kv], zero between launches
@@ -79,35 +79,67 @@ __host__ __device__ inline int attn_hs(int grp, int HW, int warps) {
 
 // LPK = lanes that share a key: 8 (8 warps, 4 keys per warp step) or 16 (16 warps, 2 keys
 // per step, half the per-lane state; an experiment for wide groups, not the default).
-template <int D, int HW, int LPK>
+// BF: the cache holds bf16 (kv_ld / kv_st of the reference, kernels/tensorlib_cuda.cu:828-831:
+// widened to f32 for the dot and the accumulate, q / out / partials stay f32).  A lane then
+// owns 16-byte chunks of 8 dims instead of 4.
+template <int D, int HW, int LPK, bool BF>
 struct AttnCfg {
   static constexpr int STAGES = HW >= 4 ? 4 : 3;
-  static constexpr int TILE_BYTES = AT_TK * D * 4;
+  static constexpr int ELT = BF ? 2 : 4;
+  static constexpr int TILE_BYTES = AT_TK * D * ELT;
   static constexpr int CH = D / (4 * LPK);  // 16-byte chunks per lane
   static constexpr int WARPS = LPK;
   static constexpr int THREADS = 32 * LPK;
   static constexpr int KPS = 32 / LPK;       // keys per warp step
 };
 
-template <int D, int HW, int LPK>
+// the ring; the CTA merge reuses it and needs WARPS * KPS * HW entries of D+4 floats
+template <int D, int HW, int LPK, bool BF>
+__host__ __device__ constexpr size_t attn_ring_bytes() {
+  using C = AttnCfg<D, HW, LPK, BF>;
+  const size_t ring = (size_t)C::STAGES * 2 * C::TILE_BYTES;
+  const size_t ent = (size_t)C::WARPS * C::KPS * HW * (D + 4) * sizeof(float);
+  return ring < ent ? ent : ring;
+}
+template <int D, int HW, int LPK, bool BF>
 size_t attn_smem_bytes(int) {
-  using C = AttnCfg<D, HW, LPK>;
-  size_t b = 128;
-  b += (size_t)C::STAGES * 2 * C::TILE_BYTES;   // the ring; the CTA merge reuses it
-  b += 64;  // barriers
-  return b;
+  return 128 + attn_ring_bytes<D, HW, LPK, BF>() + 64;  // alignment slack, ring, barriers
 }
 
-template <int D, int HW, int LPK>
+// first dim of a lane's j-th float4 of q / acc / a key row
+template <int LPK, bool BF>
+__device__ __forceinline__ int attn_dim0(int sub, int j) {
+  return BF ? 8 * (sub + LPK * (j >> 1)) + 4 * (j & 1) : 4 * (sub + LPK * j);
+}
+// the lane's CH float4 of one key row held in a tile (f32 as it is, bf16 widened)
+template <int D, int LPK, int CH, bool BF>
+__device__ __forceinline__ void attn_load_row(const unsigned char* row, int sub, float4 (&kv)[CH]) {
+  if (BF) {
+#pragma unroll
+    for (int jj = 0; jj < CH / 2; jj++) {
+      const uint4 w = *(const uint4*)(row + (size_t)(sub + LPK * jj) * 16);
+      kv[2 * jj] = make_float4(__uint_as_float(w.x << 16), __uint_as_float(w.x & 0xffff0000u),
+                               __uint_as_float(w.y << 16), __uint_as_float(w.y & 0xffff0000u));
+      kv[2 * jj + 1] = make_float4(__uint_as_float(w.z << 16), __uint_as_float(w.z & 0xffff0000u),
+                                   __uint_as_float(w.w << 16), __uint_as_float(w.w & 0xffff0000u));
+    }
+  } else {
+#pragma unroll
+    for (int j = 0; j < CH; j++) kv[j] = *(const float4*)(row + (size_t)(sub + LPK * j) * 16);
+  }
+}
+
+template <int D, int HW, int LPK, bool BF>
 __global__ void __launch_bounds__(32 * LPK, ((HW >= 4 || LPK > 8) ? 1 : 2))
     attn_decode_kernel(AttnParams p) {
-  using C = AttnCfg<D, HW, LPK>;
+  using C = AttnCfg<D, HW, LPK, BF>;
+  static_assert(!BF || C::CH % 2 == 0, "bf16 rows are read in 16-byte chunks of 8 dims");
   constexpr int AT_THREADS = C::THREADS, AT_WARPS = C::WARPS, KPS = C::KPS;
   extern __shared__ unsigned char smem_raw[];
   unsigned char* base = (unsigned char*)(((uintptr_t)smem_raw + 127) & ~(uintptr_t)127);
   float* Kt = (float*)base;
   float* Vt = (float*)(base + (size_t)C::STAGES * C::TILE_BYTES);
-  uint64_t* bars = (uint64_t*)(base + (size_t)C::STAGES * 2 * C::TILE_BYTES);
+  uint64_t* bars = (uint64_t*)(base + attn_ring_bytes<D, HW, LPK, BF>());
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int kslot = lane / LPK, sub = lane % LPK;
@@ -138,18 +170,18 @@ __global__ void __launch_bounds__(32 * LPK, ((HW >= 4 || LPK > 8) ? 1 : 2))
   const int k_end = k_begin + chunk < ctx ? k_begin + chunk : ctx;
   const int n_tiles = dead ? 0 : (k_end - k_begin + AT_TK - 1) / AT_TK;
 
-  const float* Kh = p.K + (size_t)kh * p.kv_stride;
-  const float* Vh = p.V + (size_t)kh * p.kv_stride;
+  const unsigned char* Kh = (const unsigned char*)p.K + (size_t)kh * p.kv_stride * C::ELT;
+  const unsigned char* Vh = (const unsigned char*)p.V + (size_t)kh * p.kv_stride * C::ELT;
 
   auto issue = [&](int i) {
     const int st = i % C::STAGES;
     const int r0 = k_begin + i * AT_TK;
     const int rows = (k_end - r0) < AT_TK ? (k_end - r0) : AT_TK;
-    const uint32_t bytes = (uint32_t)rows * D * 4;
+    const uint32_t bytes = (uint32_t)rows * D * C::ELT;
     mbar_expect_tx(&bars[st], 2 * bytes);
-    bulk_load_1d((unsigned char*)Kt + (size_t)st * C::TILE_BYTES, Kh + (size_t)r0 * D, bytes,
+    bulk_load_1d((unsigned char*)Kt + (size_t)st * C::TILE_BYTES, Kh + (size_t)r0 * D * C::ELT, bytes,
                  &bars[st]);
-    bulk_load_1d((unsigned char*)Vt + (size_t)st * C::TILE_BYTES, Vh + (size_t)r0 * D, bytes,
+    bulk_load_1d((unsigned char*)Vt + (size_t)st * C::TILE_BYTES, Vh + (size_t)r0 * D * C::ELT, bytes,
                  &bars[st]);
   };
   // Tiles that end below the newest row do not depend on the preceding kernel (it only
@@ -174,10 +206,10 @@ __global__ void __launch_bounds__(32 * LPK, ((HW >= 4 || LPK > 8) ? 1 : 2))
   for (int h = 0; h < HW; h++) {
     const int hh = hslot * HW + h;
     const bool live = hh < p.grp;
-    const float4* qp = (const float4*)(p.q + (size_t)(kh * p.grp + (live ? hh : 0)) * D);
+    const float* qp = p.q + (size_t)(kh * p.grp + (live ? hh : 0)) * D;
 #pragma unroll
     for (int i = 0; i < C::CH; i++)
-      qf[h][i] = live ? qp[sub + LPK * i] : make_float4(0.f, 0.f, 0.f, 0.f);
+      qf[h][i] = live ? *(const float4*)(qp + attn_dim0<LPK, BF>(sub, i)) : make_float4(0.f, 0.f, 0.f, 0.f);
   }
   float m[HW], l[HW];
   float4 acc[HW][C::CH];
@@ -196,16 +228,15 @@ __global__ void __launch_bounds__(32 * LPK, ((HW >= 4 || LPK > 8) ? 1 : 2))
     if (it == n_tiles - 1) stamp(7);
     const int r0 = k_begin + it * AT_TK;
     const int rows = (k_end - r0) < AT_TK ? (k_end - r0) : AT_TK;
-    const float4* Ks = (const float4*)((unsigned char*)Kt + (size_t)st * C::TILE_BYTES);
-    const float4* Vs = (const float4*)((unsigned char*)Vt + (size_t)st * C::TILE_BYTES);
+    const unsigned char* Ks = (const unsigned char*)Kt + (size_t)st * C::TILE_BYTES;
+    const unsigned char* Vs = (const unsigned char*)Vt + (size_t)st * C::TILE_BYTES;
     for (int step = kslice; step < AT_TK / KPS; step += ks) {
       const int row = step * KPS + kslot;
       if (step * KPS >= rows) break;
       const bool valid = row < rows;
       const int rr = valid ? row : 0;
       float4 kv[C::CH];
-#pragma unroll
-      for (int i = 0; i < C::CH; i++) kv[i] = Ks[rr * (D / 4) + sub + LPK * i];
+      attn_load_row<D, LPK, C::CH, BF>(Ks + (size_t)rr * D * C::ELT, sub, kv);
       float s[HW];
 #pragma unroll
       for (int h = 0; h < HW; h++) {
@@ -225,8 +256,7 @@ __global__ void __launch_bounds__(32 * LPK, ((HW >= 4 || LPK > 8) ? 1 : 2))
         if (LPK > 8) d += __shfl_xor_sync(0xffffffffu, d, 8);
         s[h] = valid ? d * p.scale : -INFINITY;
       }
-#pragma unroll
-      for (int i = 0; i < C::CH; i++) kv[i] = Vs[rr * (D / 4) + sub + LPK * i];
+      attn_load_row<D, LPK, C::CH, BF>(Vs + (size_t)rr * D * C::ELT, sub, kv);
       // The four key slots of the warp share one running max per head, so the rescale
       // branch is warp-uniform and the slots' sums can later be added without exps.
       float sm[HW];
@@ -280,7 +310,7 @@ __global__ void __launch_bounds__(32 * LPK, ((HW >= 4 || LPK > 8) ? 1 : 2))
       float* dst = ent + ((size_t)(kslice * KPS + kslot) * nheads_pad + hslot * HW + h) * (D + 4);
       if (sub == 0) { dst[D] = m[h]; dst[D + 1] = l[h]; }
 #pragma unroll
-      for (int i = 0; i < C::CH; i++) *(float4*)(dst + (sub + LPK * i) * 4) = acc[h][i];
+      for (int i = 0; i < C::CH; i++) *(float4*)(dst + attn_dim0<LPK, BF>(sub, i)) = acc[h][i];
     }
   }
   __syncthreads();
@@ -441,26 +471,31 @@ size_t attn_partials_bytes(int n_q, int n_kv, long long kv_max, int D, int sm_co
   return (size_t)n_q * s * (D + 4) * sizeof(float);
 }
 
-template <int D, int HW, int LPK>
-static int launch_t(const AttnParams& p, int splits, cudaStream_t stream) {
-  size_t smem = attn_smem_bytes<D, HW, LPK>(p.grp);
+template <int D, int HW, int LPK, bool BF>
+static int launch_b(const AttnParams& p, int splits, cudaStream_t stream) {
+  size_t smem = attn_smem_bytes<D, HW, LPK, BF>(p.grp);
   static bool attr = false;
   if (!attr) {
-    TLB_CUDA(cudaFuncSetAttribute(attn_decode_kernel<D, HW, LPK>,
+    TLB_CUDA(cudaFuncSetAttribute(attn_decode_kernel<D, HW, LPK, BF>,
                                   cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
     attr = true;
   }
   LaunchCfg lc(dim3(splits, p.n_kv), dim3(32 * LPK), smem, stream, pdl_enabled());
-  TLB_CUDA(cudaLaunchKernelEx(&lc.cfg, attn_decode_kernel<D, HW, LPK>, p));
+  TLB_CUDA(cudaLaunchKernelEx(&lc.cfg, attn_decode_kernel<D, HW, LPK, BF>, p));
   return TLB_OK;
+}
+template <int D, int HW, int LPK>
+static int launch_t(const AttnParams& p, int splits, cudaStream_t stream, bool bf) {
+  if (bf) return launch_b<D, HW, LPK, true>(p, splits, stream);
+  return launch_b<D, HW, LPK, false>(p, splits, stream);
 }
 
 // ctx >= 1 and d_pos == nullptr: host-position variant.  d_pos != nullptr: the
 // context is *d_pos + 1 and the grid is sized from kv_max.
-int attn_decode_launch(DeviceCtx* c, const float* q, const float* K, const float* V, float* out,
+int attn_decode_launch(DeviceCtx* c, const float* q, const void* K, const void* V, float* out,
                        int n_q, int n_kv, int ctx, long long kv_max, int D, float scale,
                        const unsigned* d_pos, float* partials, int* counters,
-                       cudaStream_t stream, int early_kv) {
+                       cudaStream_t stream, int early_kv, int kv_bf16) {
   if (D != 64 && D != 128) return set_error(TLB_ERR_UNSUPPORTED, "attn_decode: D must be 64 or 128");
   if (n_kv <= 0 || n_q % n_kv != 0) return set_error(TLB_ERR_ARG, "attn_decode: n_q % n_kv != 0");
   const int grp = n_q / n_kv;
@@ -478,17 +513,17 @@ int attn_decode_launch(DeviceCtx* c, const float* q, const float* K, const float
   // heads per warp: the smallest of {1,2,4} such that ceil(grp/HW) divides 8
   int HW = grp == 1 ? 1 : (grp == 2 ? 2 : 4);
   if (D == 128) {
-    if (HW == 1) return launch_t<128, 1, 8>(p, splits, stream);
-    if (HW == 2) return launch_t<128, 2, 8>(p, splits, stream);
+    if (HW == 1) return launch_t<128, 1, 8>(p, splits, stream, kv_bf16 != 0);
+    if (HW == 2) return launch_t<128, 2, 8>(p, splits, stream, kv_bf16 != 0);
     // TLB_ATTN_LPK=16 selects the 16-warp form (16 lanes per key); measured 6 % slower than
     // the 8-warp form on the 7B layer shape (14.4 vs 13.6 us), so it is not the default
     static const int lpk = getenv("TLB_ATTN_LPK") ? atoi(getenv("TLB_ATTN_LPK")) : 8;
-    if (lpk == 16) return launch_t<128, 4, 16>(p, splits, stream);
-    return launch_t<128, 4, 8>(p, splits, stream);
+    if (lpk == 16) return launch_t<128, 4, 16>(p, splits, stream, kv_bf16 != 0);
+    return launch_t<128, 4, 8>(p, splits, stream, kv_bf16 != 0);
   }
-  if (HW == 1) return launch_t<64, 1, 8>(p, splits, stream);
-  if (HW == 2) return launch_t<64, 2, 8>(p, splits, stream);
-  return launch_t<64, 4, 8>(p, splits, stream);
+  if (HW == 1) return launch_t<64, 1, 8>(p, splits, stream, kv_bf16 != 0);
+  if (HW == 2) return launch_t<64, 2, 8>(p, splits, stream, kv_bf16 != 0);
+  return launch_t<64, 4, 8>(p, splits, stream, kv_bf16 != 0);
 }
 
 }  // namespace tlb
@@ -570,5 +605,5 @@ extern "C" int tlb_attn_decode_noalloc(const float* q, const float* K, const flo
   local.status = nullptr;
   return attn_decode_launch(&local, q, K, V, out, (int)n_q, (int)n_kv, (int)ctx, kv_max, (int)D,
                             scale, nullptr, (float*)((unsigned char*)nd->ptr + NOALLOC_COUNTER_BYTES),
-                            (int*)nd->ptr, s, 0);
+                            (int*)nd->ptr, s, 0, 0);
 }

@@ -11,6 +11,8 @@
 // groups of a warp share each key row, K/V tiles of 32 keys arrive by bulk copy into
 // a two-stage ring.  f32 throughout (the parity bar is 1e-4 against a double CPU
 // reference); correctness-first -- a tensor-core version is future work.
+#include <cuda_bf16.h>
+
 #include "common.cuh"
 
 namespace tlb {
@@ -35,17 +37,22 @@ __global__ void merge_heads_kernel(const float* __restrict__ src, float* __restr
   dst[(size_t)t * H * D + (size_t)h * D + d] = src[((size_t)h * T + t) * D + d];
 }
 
-__global__ void kv_fill_kernel(float* __restrict__ Kc, float* __restrict__ Vc,
+__global__ void kv_fill_kernel(void* __restrict__ Kc, void* __restrict__ Vc,
                                const float* __restrict__ K, const float* __restrict__ V, int T,
-                               long long kv_stride, int pos0, int D) {
+                               long long kv_stride, int pos0, int D, int bf) {
   pdl_wait();
   pdl_launch_dependents();
   const int h = blockIdx.x, t = blockIdx.y, d = threadIdx.x;
   if (d >= D) return;
   const size_t dst = (size_t)h * kv_stride + (size_t)(pos0 + t) * D + d;
   const size_t src = ((size_t)h * T + t) * D + d;
-  Kc[dst] = K[src];
-  Vc[dst] = V[src];
+  if (bf) {   // bf16 cache: round to nearest even, like kv_st of the reference
+    ((__nv_bfloat16*)Kc)[dst] = __float2bfloat16_rn(K[src]);
+    ((__nv_bfloat16*)Vc)[dst] = __float2bfloat16_rn(V[src]);
+  } else {
+    ((float*)Kc)[dst] = K[src];
+    ((float*)Vc)[dst] = V[src];
+  }
 }
 
 constexpr int PF_THREADS = 256;
@@ -188,11 +195,11 @@ int launch_merge_heads(const float* src, float* dst, int T, int H, int D, cudaSt
   TLB_CUDA(cudaLaunchKernelEx(&lc.cfg, merge_heads_kernel, src, dst, T, H, D));
   return TLB_OK;
 }
-int launch_kv_fill(float* Kc, float* Vc, const float* K, const float* V, int T, long long kv_max,
-                   int n_kv, int D, int pos0, cudaStream_t s) {
+int launch_kv_fill(void* Kc, void* Vc, const float* K, const float* V, int T, long long kv_max,
+                   int n_kv, int D, int pos0, int bf, cudaStream_t s) {
   LaunchCfg lc(dim3(n_kv, T), dim3(D), 0, s, pdl_enabled());
   long long kv_stride = kv_max * D;
-  TLB_CUDA(cudaLaunchKernelEx(&lc.cfg, kv_fill_kernel, Kc, Vc, K, V, T, kv_stride, pos0, D));
+  TLB_CUDA(cudaLaunchKernelEx(&lc.cfg, kv_fill_kernel, Kc, Vc, K, V, T, kv_stride, pos0, D, bf));
   return TLB_OK;
 }
 int launch_attn_prefill(DeviceCtx* c, const float* q, const float* K, const float* V, float* out,

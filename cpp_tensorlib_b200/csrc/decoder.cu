@@ -38,9 +38,10 @@ int gemv_q4_simt_launch(const float* x, long long ldx, int M, const void* qw, co
                         float* y, long long ldy, int N, int K, float alpha, float beta,
                         cudaStream_t stream);
 size_t attn_partials_bytes(int n_q, int n_kv, long long kv_max, int D, int sm_count);
-int attn_decode_launch(DeviceCtx* c, const float* q, const float* K, const float* V, float* out,
+int attn_decode_launch(DeviceCtx* c, const float* q, const void* K, const void* V, float* out,
                        int n_q, int n_kv, int ctx, long long kv_max, int D, float scale,
-                       const unsigned* d_pos, float* partials, int* counters, cudaStream_t stream, int early_kv);
+                       const unsigned* d_pos, float* partials, int* counters, cudaStream_t stream,
+                       int early_kv, int kv_bf16);
 int launch_rmsnorm(const float*, const float*, float*, int, float, int, cudaStream_t);
 int launch_embed_rows(const float*, const int*, float*, int, int, cudaStream_t);
 int launch_rope(const float*, const float*, float*, int, int, int, unsigned, const unsigned*, float,
@@ -48,7 +49,7 @@ int launch_rope(const float*, const float*, float*, int, int, int, unsigned, con
 int launch_split_heads(const float*, const float*, float*, int, long long, long long, int, int,
                        cudaStream_t);
 int launch_merge_heads(const float*, float*, int, int, int, cudaStream_t);
-int launch_kv_fill(float*, float*, const float*, const float*, int, long long, int, int, int,
+int launch_kv_fill(void*, void*, const float*, const float*, int, long long, int, int, int, int,
                    cudaStream_t);
 int launch_attn_prefill(DeviceCtx*, const float*, const float*, const float*, float*, int, int, int,
                         long long, int, float, int, cudaStream_t);
@@ -242,7 +243,7 @@ static int forward(Decoder* d, cudaStream_t s) {
                             d->max_ctx, d->rope_base, s));
       RUN(attn_decode_launch(c, d->qkv, L.Kc, L.Vc, d->att, d->n_q, d->n_kv, 0, d->max_ctx, d->hd,
                              d->scale, d->d_pos, (float*)((char*)d->attn_partials + 256),
-                             (int*)d->attn_partials, s, 1));
+                             (int*)d->attn_partials, s, 1, 0));
       RUN(run_linear(c, L.wo, d->att, tp ? nullptr : d->t0, s, tp ? &c_wo : nullptr));
       NormIn nf{tp ? nullptr : d->t0, L.fn, xalt, tp ? &c_wo : nullptr};
       RUN(run_linear(c, L.wgu, x, d->gu, s, nullptr, 0, &nf, d->eps, pg));
@@ -279,7 +280,7 @@ static int forward(Decoder* d, cudaStream_t s) {
                           d->max_ctx, d->rope_base, s));
     RUN(attn_decode_launch(c, d->qkv, L.Kc, L.Vc, d->att, d->n_q, d->n_kv, 0, d->max_ctx, d->hd,
                            d->scale, d->d_pos, (float*)((char*)d->attn_partials + 256),
-                           (int*)d->attn_partials, s, 1));
+                           (int*)d->attn_partials, s, 1, 0));
     if (tp) {
       RUN(run_linear(c, L.wo, d->att, nullptr, s, &c_wo));
       RUN(launch_add_rmsnorm_ar(d->x, L.fn, d->x, d->hb, E, d->eps, c_wo, c->status, s));
@@ -621,7 +622,7 @@ int tlb_decoder_prefill(void* h, const int32_t* tokens, int64_t T, int32_t* next
       // [H, rows, D] flattened: row r = h*rows + t, so rope's position is pos + r % rows
       PF(launch_rope(qkvh, nullptr, qkvh, NQ * rows, rows, D, pos, nullptr, d->rope_base, s));
       PF(launch_rope(kh, nullptr, kh, NKV * rows, rows, D, pos, nullptr, d->rope_base, s));
-      PF(launch_kv_fill(L.Kc, L.Vc, kh, vh, rows, d->max_ctx, NKV, D, (int)pos, s));
+      PF(launch_kv_fill(L.Kc, L.Vc, kh, vh, rows, d->max_ctx, NKV, D, (int)pos, 0, s));
       PF(launch_attn_prefill(c, qkvh, L.Kc, L.Vc, ah, NQ, NKV, rows, d->max_ctx, D, d->scale, (int)pos, s));
       PF(launch_merge_heads(ah, at, rows, NQ, D, s));
       PF(gemm(L.wo, at, md, rows));

@@ -3,6 +3,8 @@
 // row gather.  Each is HBM/latency bound and a few KB per launch; all are
 // programmatic-dependent-launch aware (griddepcontrol.wait first) so they can be
 // chained in a CUDA graph without full kernel-boundary drains.
+#include <cuda_bf16.h>
+
 #include "comm.cuh"
 
 namespace tlb {
@@ -107,18 +109,25 @@ __global__ void rope_kernel(const float* x, const float* __restrict__ bias, floa
 
 // Scatter one token's k,v ([n_kv, D]) into the cache ([n_kv, kv_max, D]) at
 // row pos (or *d_pos) -- kernels/tensorlib_cuda.cu:1068-1102.
-__global__ void kv_append_kernel(float* __restrict__ Kc, float* __restrict__ Vc,
+// bf: the cache stores bf16 (kv_st of the reference, kernels/tensorlib_cuda.cu:831:
+// round to nearest even).
+__global__ void kv_append_kernel(void* __restrict__ Kc, void* __restrict__ Vc,
                                  const float* __restrict__ k, const float* __restrict__ v,
                                  unsigned pos, const unsigned* __restrict__ d_pos,
-                                 long long kv_stride, int D) {
+                                 long long kv_stride, int D, int bf) {
   pdl_wait();
   pdl_launch_dependents();
   const unsigned p0 = d_pos ? *d_pos : pos;
   const int h = blockIdx.x, d = threadIdx.x;
   if (d >= D) return;
   const size_t dst = (size_t)h * kv_stride + (size_t)p0 * D + d;
-  Kc[dst] = k[h * D + d];
-  Vc[dst] = v[h * D + d];
+  if (bf) {
+    ((__nv_bfloat16*)Kc)[dst] = __float2bfloat16_rn(k[h * D + d]);
+    ((__nv_bfloat16*)Vc)[dst] = __float2bfloat16_rn(v[h * D + d]);
+  } else {
+    ((float*)Kc)[dst] = k[h * D + d];
+    ((float*)Vc)[dst] = v[h * D + d];
+  }
 }
 
 // kernels/tensorlib_cuda.cu:1399
@@ -434,11 +443,11 @@ int launch_rope(const float* x, const float* bias, float* out, int rows, int T, 
   TLB_CUDA(cudaLaunchKernelEx(&lc.cfg, rope_kernel, x, bias, out, T, D, pos, d_pos, base));
   return TLB_OK;
 }
-int launch_kv_append(float* Kc, float* Vc, const float* k, const float* v, unsigned pos,
-                     const unsigned* d_pos, long long kv_max, int n_kv, int D, cudaStream_t s) {
+int launch_kv_append(void* Kc, void* Vc, const float* k, const float* v, unsigned pos,
+                     const unsigned* d_pos, long long kv_max, int n_kv, int D, int bf, cudaStream_t s) {
   LaunchCfg lc(dim3(n_kv), dim3(D), 0, s, pdl_enabled());
   long long kv_stride = kv_max * D;
-  TLB_CUDA(cudaLaunchKernelEx(&lc.cfg, kv_append_kernel, Kc, Vc, k, v, pos, d_pos, kv_stride, D));
+  TLB_CUDA(cudaLaunchKernelEx(&lc.cfg, kv_append_kernel, Kc, Vc, k, v, pos, d_pos, kv_stride, D, bf));
   return TLB_OK;
 }
 int launch_incr_u32(unsigned* p, cudaStream_t s) {

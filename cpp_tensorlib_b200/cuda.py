@@ -11,7 +11,7 @@ import ctypes as C
 
 import torch
 
-from ._lib import check, lib
+from ._lib import TlbError, check, lib
 
 kQ4Group = 32  # include/types.h:28
 
@@ -146,7 +146,12 @@ def attn_decode(q, K, V, scale, ctx=None, out=None):
     """cuda::attn_decode (include/cuda.h:966-1009). q [n_q, D]; K, V [n_kv, kv_max, D]
     read over the prefix [0, ctx) (ctx defaults to kv_max, the array path of
     include/array.h:1632-1651)."""
-    _f32c(q, "attn_decode q"), _f32c(K, "attn_decode K"), _f32c(V, "attn_decode V")
+    _f32c(q, "attn_decode q")
+    bf = K.dtype == torch.bfloat16           # bf16 cache (kv_cache with dtype bf16)
+    if not bf:
+        _f32c(K, "attn_decode K"), _f32c(V, "attn_decode V")
+    elif V.dtype != torch.bfloat16 or not (K.is_contiguous() and V.is_contiguous()):
+        raise ValueError("tl::attn_decode: a bf16 cache needs contiguous bf16 K and V")
     if q.dim() != 2 or K.dim() != 3 or V.shape != K.shape:
         raise ValueError("tl::attn_decode: q must be [H,D], K/V [H,ctx,D] and equal")
     n_q, D = q.shape
@@ -154,7 +159,8 @@ def attn_decode(q, K, V, scale, ctx=None, out=None):
     ctx = kv_max if ctx is None else ctx
     if out is None:
         out = torch.empty_like(q)
-    check(lib().tlb_attn_decode(_p(q), _p(K), _p(V), _p(out), n_q, n_kv, ctx, kv_max, D, scale, _s()))
+    fn = lib().tlb_attn_decode_bf16 if bf else lib().tlb_attn_decode
+    check(fn(_p(q), _p(K), _p(V), _p(out), n_q, n_kv, ctx, kv_max, D, scale, _s()))
     return out
 
 
@@ -270,20 +276,26 @@ def incr_u32(d_pos):
 
 
 class kv_cache:
-    """cuda::kv_cache (include/cuda.h:1326-1405), f32 storage: K, V
-    [n_kv_heads, max_ctx, D] plus a running position."""
+    """cuda::kv_cache (include/cuda.h:1326-1405): K, V [n_kv_heads, max_ctx, D] in f32 or
+    bf16 (kv_cache::init's dtype argument) plus a running position."""
 
-    def __init__(self, n_kv_heads, max_ctx, D, device="cuda"):
+    def __init__(self, n_kv_heads, max_ctx, D, device="cuda", dtype=torch.float32):
+        if dtype not in (torch.float32, torch.bfloat16):
+            raise ValueError("kv_cache: dtype must be float32 or bfloat16")
         self.n_kv_heads, self.max_ctx, self.D, self.pos = n_kv_heads, max_ctx, D, 0
-        self.K = torch.zeros((n_kv_heads, max_ctx, D), dtype=torch.float32, device=device)
+        self.bf16 = dtype == torch.bfloat16
+        self.K = torch.zeros((n_kv_heads, max_ctx, D), dtype=dtype, device=device)
         self.V = torch.zeros_like(self.K)
         self.dpos_partials = None
+
+    def _fn(self, name):
+        return getattr(lib(), name + ("_bf16" if self.bf16 else ""))
 
     def append(self, k_new, v_new):
         if self.pos >= self.max_ctx:
             raise IndexError("kv_cache.append: cache is full")
-        check(lib().tlb_kv_append(_p(self.K), _p(self.V), _p(k_new), _p(v_new), self.pos,
-                                  self.max_ctx, self.n_kv_heads, self.D, _s()))
+        check(self._fn("tlb_kv_append")(_p(self.K), _p(self.V), _p(k_new), _p(v_new), self.pos,
+                                        self.max_ctx, self.n_kv_heads, self.D, _s()))
         self.pos += 1
 
     def attn(self, q, scale, out=None):
@@ -295,15 +307,27 @@ class kv_cache:
         T = k_src.shape[1]
         if T <= 0 or self.pos + T > self.max_ctx:
             raise IndexError("kv_cache.prefill: block does not fit the cache")
+        if self.bf16:
+            raise TlbError("kv_cache.prefill: the tiled prefill kernel reads an f32 cache only")
         check(lib().tlb_kv_fill(_p(self.K), _p(self.V), _p(k_src), _p(v_src), T, self.max_ctx,
                                 self.n_kv_heads, self.D, self.pos, _s()))
         p0 = self.pos
         self.pos += T
         return attn_prefill(q, self.K, self.V, scale, pos0=p0, out=out)
 
+    def fill(self, k_src, v_src):
+        """cuda::kv_fill (include/cuda.h:1143-1164): a block of k, v [n_kv, T, D] into the
+        rows from the current position on (narrowed to bf16 when the cache is bf16)."""
+        T = k_src.shape[1]
+        if T <= 0 or self.pos + T > self.max_ctx:
+            raise IndexError("kv_cache.fill: block does not fit the cache")
+        check(self._fn("tlb_kv_fill")(_p(self.K), _p(self.V), _p(k_src), _p(v_src), T, self.max_ctx,
+                                      self.n_kv_heads, self.D, self.pos, _s()))
+        self.pos += T
+
     def append_dpos(self, k_new, v_new, d_pos):
-        check(lib().tlb_kv_append_dpos(_p(self.K), _p(self.V), _p(k_new), _p(v_new), _p(d_pos),
-                                       self.max_ctx, self.n_kv_heads, self.D, _s()))
+        check(self._fn("tlb_kv_append_dpos")(_p(self.K), _p(self.V), _p(k_new), _p(v_new), _p(d_pos),
+                                             self.max_ctx, self.n_kv_heads, self.D, _s()))
 
     def attn_dpos(self, q, d_pos, scale, out=None):
         n_q = q.shape[0]
@@ -312,7 +336,7 @@ class kv_cache:
             self.dpos_partials = torch.zeros(nb, dtype=torch.uint8, device=q.device)
         if out is None:
             out = torch.empty_like(q)
-        check(lib().tlb_attn_decode_dpos(_p(q), _p(self.K), _p(self.V), _p(out), n_q,
-                                         self.n_kv_heads, _p(d_pos), self.max_ctx, self.D, scale,
-                                         _p(self.dpos_partials), _s()))
+        check(self._fn("tlb_attn_decode_dpos")(_p(q), _p(self.K), _p(self.V), _p(out), n_q,
+                                               self.n_kv_heads, _p(d_pos), self.max_ctx, self.D, scale,
+                                               _p(self.dpos_partials), _s()))
         return out

@@ -9,7 +9,7 @@
 // embedded PTX, only dlopen("libtlb200.so") and the C-ABI of tlb200.h.
 //
 // Scope: the quantized-decode path -- gemv_q4, attn_decode(+_dpos), rope(+_dpos),
-// rmsnorm, rmsnorm_res, swiglu, argmax, kv_append(+_dpos), kv_cache, incr_u32, graph
+// rmsnorm, rmsnorm_res, swiglu, argmax, kv_append(+_dpos), kv_cache (f32 or bf16), incr_u32, graph
 // capture, the host/device mirror (alloc / release / sync_to_host / upload).  Ops
 // outside that path (elementwise, f32 GEMM, row reductions, f32/bf16 GEMV, prefill
 // attention on a bf16 cache) decline with `false`, which the reference evaluator answers with its
@@ -80,6 +80,12 @@ struct backend {
   int (*incr_u32)(void*, void*) = nullptr;
   int (*argmax)(const float*, int64_t, int64_t*, void*) = nullptr;
   int (*memset_)(void*, int, int64_t, void*) = nullptr;
+  int (*attn_decode_bf16)(const float*, const void*, const void*, float*, int64_t, int64_t, int64_t,
+                          int64_t, int64_t, float, void*) = nullptr;
+  int (*kv_append_bf16)(void*, void*, const float*, const float*, int64_t, int64_t, int64_t, int64_t,
+                        void*) = nullptr;
+  int (*kv_fill_bf16)(void*, void*, const float*, const float*, int64_t, int64_t, int64_t, int64_t,
+                      int64_t, void*) = nullptr;
   int64_t (*q4p_bytes)(int64_t, int64_t) = nullptr;
   int (*q4_pack)(const void*, int64_t, int64_t, void*, void*) = nullptr;
   int (*gemv_q4p)(const float*, const void*, float*, int64_t, int64_t, float, float, void*) = nullptr;
@@ -179,7 +185,9 @@ struct backend {
               bind(kv_append, "tlb_kv_append") && bind(kv_append_dpos, "tlb_kv_append_dpos") &&
               bind(incr_u32, "tlb_incr_u32") && bind(argmax, "tlb_argmax") &&
               bind(memset_, "tlb_memset") && bind(q4p_bytes, "tlb_q4p_bytes") &&
-              bind(q4_pack, "tlb_q4_pack") && bind(gemv_q4p, "tlb_gemv_q4p") && bind(split_heads, "tlb_split_heads") &&
+              bind(q4_pack, "tlb_q4_pack") && bind(gemv_q4p, "tlb_gemv_q4p") &&
+              bind(attn_decode_bf16, "tlb_attn_decode_bf16") && bind(kv_append_bf16, "tlb_kv_append_bf16") &&
+              bind(kv_fill_bf16, "tlb_kv_fill_bf16") && bind(split_heads, "tlb_split_heads") &&
               bind(merge_heads, "tlb_merge_heads") && bind(kv_fill, "tlb_kv_fill") &&
               bind(attn_prefill, "tlb_attn_prefill") && bind(capture_begin, "tlb_capture_begin") &&
               bind(capture_end, "tlb_capture_end") && bind(graph_launch, "tlb_graph_launch") &&
@@ -338,10 +346,14 @@ inline bool gemv_q4(void* a, void* qw, void* scales, void* y, int64_t N, int64_t
 inline bool attn_decode(void* q, void* K, void* V, void* out, int64_t n_q_heads, int64_t n_kv_heads,
                         int64_t ctx, int64_t kv_max, int64_t D, float scale, bool kv_bf16 = false) {
   auto& b = detail::backend::get();
-  if (!b.ready || kv_bf16) return false;  // bf16 KV storage is not part of this backend yet
+  if (!b.ready) return false;
   b.reads(q); b.reads(K); b.reads(V); b.writes(out);
-  b.must(b.attn_decode(detail::f(q), detail::f(K), detail::f(V), detail::fw(out), n_q_heads,
-                       n_kv_heads, ctx, kv_max, D, scale, b.stream), "attn_decode");
+  if (kv_bf16)
+    b.must(b.attn_decode_bf16(detail::f(q), K, V, detail::fw(out), n_q_heads, n_kv_heads, ctx, kv_max,
+                              D, scale, b.stream), "attn_decode (bf16 cache)");
+  else
+    b.must(b.attn_decode(detail::f(q), detail::f(K), detail::f(V), detail::fw(out), n_q_heads,
+                         n_kv_heads, ctx, kv_max, D, scale, b.stream), "attn_decode");
   return true;
 }
 
@@ -403,10 +415,14 @@ inline bool argmax(void* in, int64_t n, int64_t* out_idx) {
 inline bool kv_append(void* Kc, void* Vc, void* k_new, void* v_new, int64_t pos, int64_t kv_max,
                       int64_t n_kv_heads, int64_t D, bool kv_bf16 = false) {
   auto& b = detail::backend::get();
-  if (!b.ready || kv_bf16) return false;
+  if (!b.ready) return false;
   b.reads(k_new); b.reads(v_new); b.reads(Kc); b.reads(Vc); b.writes(Kc); b.writes(Vc);
-  b.must(b.kv_append(detail::fw(Kc), detail::fw(Vc), detail::f(k_new), detail::f(v_new), pos, kv_max,
-                     n_kv_heads, D, b.stream), "kv_append");
+  if (kv_bf16)
+    b.must(b.kv_append_bf16(Kc, Vc, detail::f(k_new), detail::f(v_new), pos, kv_max, n_kv_heads, D,
+                            b.stream), "kv_append (bf16 cache)");
+  else
+    b.must(b.kv_append(detail::fw(Kc), detail::fw(Vc), detail::f(k_new), detail::f(v_new), pos, kv_max,
+                       n_kv_heads, D, b.stream), "kv_append");
   return true;
 }
 inline bool kv_append_dpos(void* Kc, void* Vc, void* k_new, void* v_new, void* d_pos, int64_t kv_max,
@@ -447,10 +463,14 @@ inline bool merge_heads(void* src, void* dst, int64_t T, int64_t H, int64_t D) {
 inline bool kv_fill(void* Kc, void* Vc, void* K, void* V, int64_t T, int64_t kv_max,
                     int64_t n_kv_heads, int64_t D, bool kv_bf16 = false, int64_t pos0 = 0) {
   auto& b = detail::backend::get();
-  if (!b.ready || kv_bf16) return false;
+  if (!b.ready) return false;
   b.reads(K); b.reads(V); b.reads(Kc); b.reads(Vc); b.writes(Kc); b.writes(Vc);
-  b.must(b.kv_fill(detail::fw(Kc), detail::fw(Vc), detail::f(K), detail::f(V), T, kv_max, n_kv_heads, D,
-                   pos0, b.stream), "kv_fill");
+  if (kv_bf16)
+    b.must(b.kv_fill_bf16(Kc, Vc, detail::f(K), detail::f(V), T, kv_max, n_kv_heads, D, pos0, b.stream),
+           "kv_fill (bf16 cache)");
+  else
+    b.must(b.kv_fill(detail::fw(Kc), detail::fw(Vc), detail::f(K), detail::f(V), T, kv_max, n_kv_heads, D,
+                     pos0, b.stream), "kv_fill");
   return true;
 }
 inline bool attn_prefill(void* q, void* K, void* V, void* out, int64_t n_q_heads, int64_t n_kv_heads,
@@ -494,7 +514,8 @@ inline void graph_destroy(CUgraphExec e) {
   if (e && b.ready) b.graph_destroy(e);
 }
 
-// Persistent KV cache (reference cuda.h:1326-1405), f32 storage.
+// Persistent KV cache (reference cuda.h:1326-1405), f32 or bf16 storage.  The device-position
+// forms and the tiled prefill read an f32 cache only and decline on a bf16 one.
 struct kv_cache {
   void* K = nullptr;
   void* V = nullptr;
@@ -503,26 +524,30 @@ struct kv_cache {
   void* dpos_partials = nullptr;
 
   bool init(int64_t kv_heads, int64_t maxctx, int64_t d, dtype kv_dt = dtype::f32) {
-    if (kv_dt != dtype::f32) return false;
+    if (kv_dt != dtype::f32 && kv_dt != dtype::bf16) return false;
     n_kv_heads = kv_heads; max_ctx = maxctx; D = d; pos = 0;
-    K = alloc(n_kv_heads * max_ctx * D * 4, nullptr);
-    V = alloc(n_kv_heads * max_ctx * D * 4, nullptr);
+    kv_bf16 = (kv_dt == dtype::bf16);
+    const int64_t w = kv_bf16 ? 2 : 4;  // bytes per K/V element
+    K = alloc(n_kv_heads * max_ctx * D * w, nullptr);
+    V = alloc(n_kv_heads * max_ctx * D * w, nullptr);
     return K && V;
   }
   bool append(void* k_new, void* v_new) {
     if (pos >= max_ctx) return false;
-    if (!kv_append(K, V, k_new, v_new, pos, max_ctx, n_kv_heads, D)) return false;
+    if (!kv_append(K, V, k_new, v_new, pos, max_ctx, n_kv_heads, D, kv_bf16)) return false;
     pos++;
     return true;
   }
   bool attn(void* q, void* out, int64_t n_q_heads, float scale) {
-    return attn_decode(q, K, V, out, n_q_heads, n_kv_heads, pos, max_ctx, D, scale);
+    return attn_decode(q, K, V, out, n_q_heads, n_kv_heads, pos, max_ctx, D, scale, kv_bf16);
   }
   bool append_dpos(void* k_new, void* v_new, void* d_pos) {
+    if (kv_bf16) return false;
     return kv_append_dpos(K, V, k_new, v_new, d_pos, max_ctx, n_kv_heads, D);
   }
   bool attn_dpos(void* q, void* out, int64_t n_q_heads, void* d_pos, float scale) {
     auto& b = detail::backend::get();
+    if (kv_bf16) return false;
     if (!dpos_partials) {
       int64_t nb = b.attn_partials_bytes(n_q_heads, n_kv_heads, max_ctx, D);
       if (nb <= 0) return false;
@@ -535,10 +560,10 @@ struct kv_cache {
   }
   bool prefill(void* q, void* k_src, void* v_src, void* out, int64_t T, int64_t n_q_heads, float scale) {
     if (T <= 0 || pos + T > max_ctx) return false;
-    if (!kv_fill(K, V, k_src, v_src, T, max_ctx, n_kv_heads, D, false, pos)) return false;
+    if (!kv_fill(K, V, k_src, v_src, T, max_ctx, n_kv_heads, D, kv_bf16, pos)) return false;
     const int64_t p0 = pos;
     pos += T;
-    return attn_prefill(q, K, V, out, n_q_heads, n_kv_heads, T, max_ctx, D, scale, false, p0);
+    return attn_prefill(q, K, V, out, n_q_heads, n_kv_heads, T, max_ctx, D, scale, kv_bf16, p0);
   }
   void destroy() {
     if (K) release(K, 0, nullptr);

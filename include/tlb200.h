@@ -100,6 +100,15 @@ int tlb_attn_decode(const float* q, const float* K, const float* V, float* out, 
 int tlb_attn_decode_dpos(const float* q, const float* K, const float* V, float* out, int64_t n_q,
                          int64_t n_kv, const void* d_pos, int64_t kv_max, int64_t D, float scale,
                          void* partials, void* stream);
+/* bf16 KV cache (cu.h:1326-1346 kv_cache::init with dtype::bf16; kernels .cu:828-831 kv_ld /
+ * kv_st): K, V are bf16 [n_kv, kv_max, D], widened to f32 for the dot and the accumulate;
+ * q, out and the split partials stay f32.  Same arguments otherwise. */
+int tlb_attn_decode_bf16(const float* q, const void* K, const void* V, float* out, int64_t n_q,
+                         int64_t n_kv, int64_t ctx, int64_t kv_max, int64_t D, float scale,
+                         void* stream);
+int tlb_attn_decode_dpos_bf16(const float* q, const void* K, const void* V, float* out, int64_t n_q,
+                              int64_t n_kv, const void* d_pos, int64_t kv_max, int64_t D, float scale,
+                              void* partials, void* stream);
 /* No counterpart in the reference.  Same result as tlb_attn_decode, for callers
  * that must not allocate device memory when they call (an embedder that owns the
  * whole device heap, a region where cudaMalloc's implicit device synchronisation
@@ -129,6 +138,11 @@ int tlb_kv_append(float* Kc, float* Vc, const float* k_new, const float* v_new, 
 int tlb_kv_append_dpos(float* Kc, float* Vc, const float* k_new, const float* v_new,
                        const void* d_pos, int64_t kv_max, int64_t n_kv, int64_t D,
                        void* stream);                             /* cu.h:1050-1070 */
+/* the same two with a bf16 cache (kv_st, kernels/tensorlib_cuda.cu:831: round to nearest even) */
+int tlb_kv_append_bf16(void* Kc, void* Vc, const float* k_new, const float* v_new, int64_t pos,
+                       int64_t kv_max, int64_t n_kv, int64_t D, void* stream);
+int tlb_kv_append_dpos_bf16(void* Kc, void* Vc, const float* k_new, const float* v_new,
+                            const void* d_pos, int64_t kv_max, int64_t n_kv, int64_t D, void* stream);
 int tlb_incr_u32(void* d_pos, void* stream);                      /* cu.h:1038-1047 */
 /* cu.h:1261-1282 cuda::argmax: reduces on the device, synchronises the stream and
  * returns the index (smallest index among the maxima). */
@@ -145,6 +159,8 @@ int tlb_merge_heads(const float* src, float* dst, int64_t T, int64_t H, int64_t 
 /* cu.h:1143-1164 kv_fill: k, v [n_kv, T, D] into cache rows [pos0, pos0 + T) (f32 cache) */
 int tlb_kv_fill(float* Kc, float* Vc, const float* K, const float* V, int64_t T, int64_t kv_max,
                 int64_t n_kv, int64_t D, int64_t pos0, void* stream);
+int tlb_kv_fill_bf16(void* Kc, void* Vc, const float* K, const float* V, int64_t T, int64_t kv_max,
+                     int64_t n_kv, int64_t D, int64_t pos0, void* stream);   /* bf16 cache */
 /* cu.h:1171-1201 attn_prefill: causal attention of a prompt chunk; q, out [n_q, T, D];
  * query p is at position pos0 + p and attends keys 0..pos0+p of the cache. */
 int tlb_attn_prefill(const float* q, const float* K, const float* V, float* out, int64_t n_q,

@@ -354,3 +354,58 @@ def test_bad_arguments_raise(tl):
     with pytest.raises(TlbError):
         tl.attn_decode(torch.zeros((2, 96), device="cuda"), torch.zeros((2, 8, 96), device="cuda"),
                        torch.zeros((2, 8, 96), device="cuda"), 1.0)   # D not in {64,128}
+
+
+def bf16_round(a):
+    """f32 -> bf16 -> f32, round to nearest even (include/types.h:35-45 of the reference)."""
+    x = np.ascontiguousarray(a, np.float32).view(np.uint32).astype(np.uint64)
+    x = (x + 0x7fff + ((x >> 16) & 1)) >> 16
+    return (x.astype(np.uint32) << 16).view(np.float32).reshape(np.shape(a))
+
+
+@pytest.mark.parametrize("n_q,n_kv,D,kv_max,ctxs", [
+    (4, 4, 128, 300, (1, 31, 32, 33, 129, 300)),
+    (14, 2, 64, 700, (5, 64, 255, 650)),
+    (28, 4, 128, 2100, (127, 1024, 2047, 2100)),
+])
+def test_attn_bf16_cache_vs_oracle(tl, port, n_q, n_kv, D, kv_max, ctxs):
+    """bf16 KV cache (kernels/tensorlib_cuda.cu:828-831 kv_ld / kv_st): the kernel widens the
+    stored bf16 to f32, so the checker is the f32 oracle on the bf16-rounded cache."""
+    K = synth.normal(70, 1, (n_kv, kv_max, D))
+    V = synth.normal(70, 2, (n_kv, kv_max, D))
+    q = synth.normal(70, 3, (n_q, D))
+    Kr, Vr = bf16_round(K), bf16_round(V)
+    Kd, Vd = dev(K).to(torch.bfloat16), dev(V).to(torch.bfloat16)
+    assert np.array_equal(Kd.float().cpu().numpy(), Kr)          # torch rounds the same way
+    for ctx in ctxs:
+        got = tl.attn_decode(dev(q), Kd, Vd, D ** -0.5, ctx=ctx).cpu().numpy()
+        assert relerr(got, port.attn_decode(q, Kr, Vr, D ** -0.5, ctx=ctx)) < 1e-4, ctx
+
+
+def test_kv_cache_bf16_append_fill_and_attend(tl, port):
+    """kv_cache with dtype bf16: append / fill narrow with round-to-nearest-even (bit-equal to
+    the host converter), attention in both position forms reads them back."""
+    n_kv, D, maxc, n_q = 2, 128, 96, 8
+    cache = tl.kv_cache(n_kv, maxc, D, dtype=torch.bfloat16)
+    Kh, Vh = np.zeros((n_kv, maxc, D), np.float32), np.zeros((n_kv, maxc, D), np.float32)
+    kb, vb = synth.normal(71, 1, (n_kv, 40, D)), synth.normal(71, 2, (n_kv, 40, D))
+    cache.fill(dev(kb), dev(vb))
+    Kh[:, :40], Vh[:, :40] = kb, vb
+    d_pos = torch.tensor([40], dtype=torch.int32, device="cuda")
+    q = synth.normal(71, 3, (n_q, D))
+    for t in range(40, 45):
+        k, v = synth.normal(71, 10 + t, (n_kv, D)), synth.normal(71, 100 + t, (n_kv, D))
+        if t % 2:
+            cache.append(dev(k), dev(v))
+        else:
+            cache.append_dpos(dev(k), dev(v), d_pos)
+            cache.pos += 1
+        tl.incr_u32(d_pos)
+        Kh[:, t], Vh[:, t] = k, v
+    assert np.array_equal(cache.K.float().cpu().numpy(), bf16_round(Kh))
+    assert np.array_equal(cache.V.float().cpu().numpy(), bf16_round(Vh))
+    want = port.attn_decode(q, bf16_round(Kh), bf16_round(Vh), 0.125, ctx=45)
+    assert relerr(cache.attn(dev(q), 0.125).cpu().numpy(), want) < 1e-4
+    d_last = torch.tensor([44], dtype=torch.int32, device="cuda")
+    got = cache.attn_dpos(dev(q), d_last, 0.125).cpu().numpy()
+    assert np.array_equal(got, cache.attn(dev(q), 0.125).cpu().numpy())   # bit-identical forms
