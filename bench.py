@@ -235,6 +235,8 @@ def main():
     ap.add_argument("--warmup", type=int, default=8)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--layers", type=int, default=0, help="diagnostic: fewer layers (line is marked invalid)")
+    ap.add_argument("--prefill", type=int, default=0,
+                    help="diagnostic: time the batched prompt pass over this many tokens and exit")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
@@ -257,6 +259,23 @@ def main():
     max_ctx = CTX0 + max(128, K + W) + 8
     dec = build_decoder(cfg, max_ctx, rank, world, CTX0)
     dec.connect()
+    if args.prefill:
+        # diagnostic, not the bench line: the batched prompt pass (tensor-core int4 GEMM for
+        # the projections, tiled causal attention) from an empty cache, single GPU
+        T = args.prefill
+        ids = [int(v) for v in torch.randint(0, cfg["vocab"], (T,), generator=torch.Generator().manual_seed(SEED))]
+        times = []
+        for _ in range(3):
+            dec.set_pos(0)
+            torch.cuda.synchronize()
+            t0 = time.perf_counter()
+            dec.prefill(ids)
+            times.append(time.perf_counter() - t0)
+        best = min(times)
+        print(json.dumps(dict(diagnostic="batched prefill", T=T, layers=cfg["layers"], ms=best * 1e3,
+                              tokens_per_s=T / best, ms_per_layer=best * 1e3 / cfg["layers"])), flush=True)
+        dec.close()
+        return
     dec.set_pos(CTX0)
     dec.set_token(1)
     dec.capture()

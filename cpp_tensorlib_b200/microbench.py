@@ -69,6 +69,9 @@ def attn(a):
     q = torch.randn((a.heads, a.D), generator=gen, device="cuda")
     Ks = [torch.randn((a.kv_heads, a.ctx, a.D), generator=gen, device="cuda") for _ in range(a.copies)]
     Vs = [torch.randn((a.kv_heads, a.ctx, a.D), generator=gen, device="cuda") for _ in range(a.copies)]
+    elt = 4
+    if a.kv_bf16:
+        Ks, Vs, elt = [k.to(torch.bfloat16) for k in Ks], [v.to(torch.bfloat16) for v in Vs], 2
     out = torch.empty_like(q)
     sc = a.D ** -0.5
     tl.attn_decode(q, Ks[0], Vs[0], sc, out=out)      # grows the library scratch before capture
@@ -77,8 +80,8 @@ def attn(a):
         for K, V in zip(Ks, Vs):
             tl.attn_decode(q, K, V, sc, out=out)
     ms = _time_graph(one_pass, a.iters) / a.copies
-    nbytes = 2 * a.kv_heads * a.ctx * a.D * 4 + 2 * a.heads * a.D * 4
-    print(json.dumps(dict(op="attn_decode", heads=a.heads, kv_heads=a.kv_heads, ctx=a.ctx, D=a.D,
+    nbytes = 2 * a.kv_heads * a.ctx * a.D * elt + 2 * a.heads * a.D * 4
+    print(json.dumps(dict(op="attn_decode_bf16kv" if a.kv_bf16 else "attn_decode", heads=a.heads, kv_heads=a.kv_heads, ctx=a.ctx, D=a.D,
                           us_per_launch=ms * 1e3, algorithmic_bytes=nbytes, GBps=nbytes / ms / 1e6,
                           working_set_MB=a.copies * nbytes / 1e6)))
 
@@ -108,6 +111,7 @@ def main():
     t.add_argument("--kv-heads", type=int, default=28)
     t.add_argument("--ctx", type=int, default=4096)
     t.add_argument("--D", type=int, default=128)
+    t.add_argument("--kv-bf16", type=int, default=0, help="1: bf16 KV cache")
     r = sub.add_parser("rmsnorm")
     r.add_argument("--n", type=int, default=3584)
     for p in (g, t, r):
