@@ -47,17 +47,22 @@ struct AttnParams {
   long long kv_stride;  // kv_max * D
   float scale;
   int s_cap;     // partial slots per head (= launched splits)
-  int sm2;       // 2 * SM count: split target
+  int sm2;       // CTA target of the grid (attn_target): split count = target / kv heads
   int* status;
   int early_kv;  // cache rows below ctx-1 and *d_pos are older than the preceding kernel:
                  // their tiles may be requested before the grid dependency resolves
   unsigned long long* dbg;
 };
 
+// CTAs the grid should have: one per SM for wide groups (4 heads per warp: one CTA fits an
+// SM), two per SM otherwise.
+__host__ __device__ inline int attn_target(int grp, int sm_count) {
+  return grp >= 3 ? sm_count : 2 * sm_count;
+}
 // Number of splits wanted for a context length (monotone non-decreasing in ctx).
 __host__ __device__ inline int attn_splits_wanted(int n_kv, int ctx, int sm2) {
   int s = sm2 / (n_kv > 0 ? n_kv : 1);
-  int cap = (ctx + 127) / 128;   // at most 128 keys (4 tiles) per split before splits grow
+  int cap = (ctx + 63) / 64;     // never less than 64 keys (2 tiles) per split
   if (s > cap) s = cap;
   if (s > 96) s = 96;  // the merge keeps (m, l) of at most 3 splits per lane
   return s < 1 ? 1 : s;
@@ -467,7 +472,7 @@ __global__ void __launch_bounds__(32 * LPK, ((HW >= 4 || LPK > 8) ? 1 : 2))
 // host side
 // ---------------------------------------------------------------------------
 size_t attn_partials_bytes(int n_q, int n_kv, long long kv_max, int D, int sm_count) {
-  int s = attn_splits_wanted(n_kv, (int)kv_max, 2 * sm_count);
+  int s = attn_splits_wanted(n_kv, (int)kv_max, attn_target(n_kv > 0 ? n_q / n_kv : 1, sm_count));
   return (size_t)n_q * s * (D + 4) * sizeof(float);
 }
 
@@ -505,7 +510,7 @@ int attn_decode_launch(DeviceCtx* c, const float* q, const void* K, const void* 
   AttnParams p;
   p.q = q; p.K = K; p.V = V; p.out = out; p.partials = partials; p.counters = counters;
   p.d_pos = d_pos; p.ctx = ctx; p.n_q = n_q; p.n_kv = n_kv; p.grp = grp;
-  p.kv_stride = kv_max * D; p.scale = scale; p.sm2 = 2 * c->sm_count; p.status = c->status; p.dbg = g_attn_dbg; p.early_kv = early_kv;
+  p.kv_stride = kv_max * D; p.scale = scale; p.sm2 = attn_target(grp, c->sm_count); p.status = c->status; p.dbg = g_attn_dbg; p.early_kv = early_kv;
   const int basis = d_pos ? (int)kv_max : ctx;
   const int splits = d_pos ? attn_splits_wanted(n_kv, basis, p.sm2)
                            : (ctx + attn_chunk(n_kv, ctx, p.sm2) - 1) / attn_chunk(n_kv, ctx, p.sm2);

@@ -62,7 +62,7 @@ int launch_incr_u32(unsigned*, cudaStream_t);
 int launch_qkv_post(float*, const float*, const float*, const float*, float*, float*, int, int,
                     int, const unsigned*, long long, float, cudaStream_t);
 int launch_embed_gather(const float*, const int*, float*, int, float2*, const unsigned*, int, float,
-                        cudaStream_t);
+                        const float*, float*, float, cudaStream_t);
 int launch_argmax(DeviceCtx*, const float*, int, int*, int*, cudaStream_t);
 int launch_argmax_tp(DeviceCtx*, const float*, int, unsigned, const CommDev&, int*, int*,
                      cudaStream_t);
@@ -196,8 +196,9 @@ static int forward(Decoder* d, cudaStream_t s) {
     n++;                 \
   } while (0)
   if (!d->embed || !d->onorm) return set_error(TLB_ERR_STATE, "decoder: embed / final norm not set");
-  RUN(launch_embed_gather(d->embed, d->d_tok, d->x, E, d->rope_cs, d->d_pos, d->hd, d->rope_base, s));
-  RUN(launch_rmsnorm(d->x, d->layers[0].an, d->hb, E, d->eps, 1, s));
+  // embedding row, the token's rotary table and the first layer's attention norm in one block
+  RUN(launch_embed_gather(d->embed, d->d_tok, d->x, E, d->rope_cs, d->d_pos, d->hd, d->rope_base,
+                          d->layers[0].an, d->hb, d->eps, s));
   bool all_tma = d->lm_head.tma && d->lm_head.packed;
   for (auto& L : d->layers)
     all_tma = all_tma && L.wqkv.tma && L.wo.tma && L.wgu.tma && L.wd.tma && L.wqkv.packed &&

@@ -190,14 +190,28 @@ __global__ void qkv_post_kernel(float* qkv, const float* __restrict__ bq,
 // With rope_cs != NULL the block also fills the token's rotary table: (cos, sin) of
 // (*d_pos) * base^(-2j/D) for j < D/2, the double-precision expression of rope_pair,
 // so that the 28 layers' projections read 64 pairs instead of each evaluating sincos.
+// With nw != NULL it also leaves rmsnorm(x) * nw in hout (the first layer's attention norm,
+// same arithmetic as rmsnorm_kernel), so the token needs no separate norm launch.
 __global__ void embed_gather_kernel(const float* __restrict__ embed,
                                     const int* __restrict__ d_tok, float* __restrict__ x, int n,
                                     float2* __restrict__ rope_cs, const unsigned* __restrict__ d_pos,
-                                    int D, float rope_base) {
+                                    int D, float rope_base, const float* __restrict__ nw,
+                                    float* __restrict__ hout, float eps) {
+  __shared__ float sm[32];
   pdl_wait();
   pdl_launch_dependents();
   const size_t base = (size_t)(*d_tok) * n;
-  for (int i = threadIdx.x; i < n; i += blockDim.x) x[i] = embed[base + i];
+  float acc = 0.f;
+  for (int i = threadIdx.x; i < n; i += blockDim.x) {
+    const float v = embed[base + i];
+    x[i] = v;
+    acc += v * v;
+  }
+  if (nw) {
+    const float tot = block_sum(acc, sm);
+    const float inv = 1.0f / sqrtf(tot / (float)n + eps);
+    for (int i = threadIdx.x; i < n; i += blockDim.x) hout[i] = x[i] * inv * nw[i];
+  }
   if (rope_cs && (int)threadIdx.x < D / 2) {
     const int j = threadIdx.x;
     const double theta = exp2(-2.0 * (double)j / (double)D * log2((double)rope_base));
@@ -465,11 +479,12 @@ int launch_qkv_post(float* qkv, const float* bq, const float* bk, const float* b
   return TLB_OK;
 }
 int launch_embed_gather(const float* embed, const int* d_tok, float* x, int n, float2* rope_cs,
-                        const unsigned* d_pos, int D, float rope_base, cudaStream_t s) {
+                        const unsigned* d_pos, int D, float rope_base, const float* nw, float* hout,
+                        float eps, cudaStream_t s) {
   int threads = row_threads(n);
   if (threads < D / 2) threads = D / 2;
   LaunchCfg lc(dim3(1), dim3(threads), 0, s, pdl_enabled());
-  TLB_CUDA(cudaLaunchKernelEx(&lc.cfg, embed_gather_kernel, embed, d_tok, x, n, rope_cs, d_pos, D, rope_base));
+  TLB_CUDA(cudaLaunchKernelEx(&lc.cfg, embed_gather_kernel, embed, d_tok, x, n, rope_cs, d_pos, D, rope_base, nw, hout, eps));
   return TLB_OK;
 }
 int launch_embed_rows(const float* embed, const int* ids, float* x, int n, int rows, cudaStream_t s) {

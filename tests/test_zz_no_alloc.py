@@ -47,7 +47,7 @@ def test_noalloc_attention_matches_regular_entry_point_twice():
 
 def test_noalloc_attention_rejects_oversized_partials():
     from cpp_tensorlib_b200 import lib
-    n_q, n_kv, D, kv_max = 2048, 64, 128, 12288      # 2048 heads x 4 splits x 528 B > 4 MiB
+    n_q, n_kv, D, kv_max = 4096, 64, 128, 12288      # 4096 heads x 2 splits x 528 B > 4 MiB
     q = torch.zeros((n_q, D), device="cuda")
     K = torch.zeros((n_kv, kv_max, D), device="cuda")
     out = torch.empty_like(q)
