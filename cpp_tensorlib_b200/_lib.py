@@ -58,6 +58,7 @@ SIGNATURES = {
     "tlb_kv_fill": (ci, [vp, vp, vp, vp, i64, i64, i64, i64, i64, vp]),
     "tlb_kv_fill_bf16": (ci, [vp, vp, vp, vp, i64, i64, i64, i64, i64, vp]),
     "tlb_attn_prefill": (ci, [vp, vp, vp, vp, i64, i64, i64, i64, i64, f32, i64, vp]),
+    "tlb_attn_prefill_bf16": (ci, [vp, vp, vp, vp, i64, i64, i64, i64, i64, f32, i64, vp]),
     "tlb_capture_begin": (ci, [C.POINTER(vp)]),
     "tlb_capture_end": (ci, [C.POINTER(vp)]),
     "tlb_graph_launch": (ci, [vp, vp]),

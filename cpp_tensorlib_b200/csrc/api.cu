@@ -46,8 +46,8 @@ int launch_split_heads(const float*, const float*, float*, int, long long, long 
 int launch_merge_heads(const float*, float*, int, int, int, cudaStream_t);
 int launch_kv_fill(void*, void*, const float*, const float*, int, long long, int, int, int, int,
                    cudaStream_t);
-int launch_attn_prefill(DeviceCtx*, const float*, const float*, const float*, float*, int, int, int,
-                        long long, int, float, int, cudaStream_t);
+int launch_attn_prefill(DeviceCtx*, const float*, const void*, const void*, float*, int, int, int,
+                        long long, int, float, int, int, cudaStream_t);
 int launch_q4_to_f32(const unsigned char*, int, int, float*, cudaStream_t);
 
 extern unsigned long long* g_gemv_dbg;
@@ -470,9 +470,9 @@ int tlb_kv_fill_bf16(void* Kc, void* Vc, const float* K, const float* V, int64_t
   TLB_REQUIRE(D > 0 && D <= 1024 && n_kv > 0, "tlb_kv_fill_bf16: bad shape");
   return launch_kv_fill(Kc, Vc, K, V, (int)T, kv_max, (int)n_kv, (int)D, (int)pos0, 1, S(stream));
 }
-int tlb_attn_prefill(const float* q, const float* K, const float* V, float* out, int64_t n_q,
-                     int64_t n_kv, int64_t T, int64_t kv_max, int64_t D, float scale, int64_t pos0,
-                     void* stream) {
+static int attn_prefill_any(const float* q, const void* K, const void* V, float* out, int64_t n_q,
+                            int64_t n_kv, int64_t T, int64_t kv_max, int64_t D, float scale, int64_t pos0,
+                            void* stream, int bf) {
   TLB_REQUIRE(q && K && V && out, "tlb_attn_prefill: null pointer");
   TLB_REQUIRE(D == 64 || D == 128, "tlb_attn_prefill: D must be 64 or 128");
   TLB_REQUIRE(n_kv > 0 && n_q % n_kv == 0, "tlb_attn_prefill: n_q % n_kv != 0");
@@ -481,7 +481,17 @@ int tlb_attn_prefill(const float* q, const float* K, const float* V, float* out,
               "tlb_attn_prefill: pointers must be 16-byte aligned");
   CTX(c);
   return launch_attn_prefill(c, q, K, V, out, (int)n_q, (int)n_kv, (int)T, kv_max, (int)D, scale,
-                             (int)pos0, S(stream));
+                             (int)pos0, bf, S(stream));
+}
+int tlb_attn_prefill(const float* q, const float* K, const float* V, float* out, int64_t n_q,
+                     int64_t n_kv, int64_t T, int64_t kv_max, int64_t D, float scale, int64_t pos0,
+                     void* stream) {
+  return attn_prefill_any(q, K, V, out, n_q, n_kv, T, kv_max, D, scale, pos0, stream, 0);
+}
+int tlb_attn_prefill_bf16(const float* q, const void* K, const void* V, float* out, int64_t n_q,
+                          int64_t n_kv, int64_t T, int64_t kv_max, int64_t D, float scale, int64_t pos0,
+                          void* stream) {
+  return attn_prefill_any(q, K, V, out, n_q, n_kv, T, kv_max, D, scale, pos0, stream, 1);
 }
 
 int tlb_capture_begin(void** stream_out) {

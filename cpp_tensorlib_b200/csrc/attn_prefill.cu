@@ -13,7 +13,7 @@
 // reference); correctness-first -- a tensor-core version is future work.
 #include <cuda_bf16.h>
 
-#include "common.cuh"
+#include "attn_common.cuh"
 
 namespace tlb {
 
@@ -59,13 +59,15 @@ constexpr int PF_THREADS = 256;
 constexpr int PF_QT = 32;   // queries per CTA (8 warps x 4 row groups)
 constexpr int PF_KT = 32;   // keys per tile
 
-template <int D>
+// BF: bf16 cache (widened to f32 on load; q, out stay f32), same lane mapping as the decode kernel.
+template <int D, bool BF>
 __global__ void __launch_bounds__(PF_THREADS, 2)
-    attn_prefill_kernel(const float* __restrict__ q, const float* __restrict__ K,
-                        const float* __restrict__ V, float* __restrict__ out, int T,
+    attn_prefill_kernel(const float* __restrict__ q, const void* __restrict__ K,
+                        const void* __restrict__ V, float* __restrict__ out, int T,
                         long long kv_stride, int group, float scale, int pos0, int* status) {
   constexpr int CH = D / 32;
-  constexpr int TILE_BYTES = PF_KT * D * 4;
+  constexpr int ELT = BF ? 2 : 4;
+  constexpr int TILE_BYTES = PF_KT * D * ELT;
   extern __shared__ unsigned char smem_raw[];
   unsigned char* base = (unsigned char*)(((uintptr_t)smem_raw + 127) & ~(uintptr_t)127);
   float* Kt = (float*)base;
@@ -91,17 +93,17 @@ __global__ void __launch_bounds__(PF_THREADS, 2)
   int cta_last_key = pos0 + qt * PF_QT + PF_QT - 1;
   if (cta_last_key > pos0 + T - 1) cta_last_key = pos0 + T - 1;
   const int n_tiles = cta_last_key / PF_KT + 1;
-  const float* Kh = K + (size_t)kh * kv_stride;
-  const float* Vh = V + (size_t)kh * kv_stride;
+  const unsigned char* Kh = (const unsigned char*)K + (size_t)kh * kv_stride * ELT;
+  const unsigned char* Vh = (const unsigned char*)V + (size_t)kh * kv_stride * ELT;
 
   auto issue = [&](int i) {
     const int st = i & 1;
     const int r0 = i * PF_KT;
     const int rows = (cta_last_key + 1 - r0) < PF_KT ? (cta_last_key + 1 - r0) : PF_KT;
-    const uint32_t bytes = (uint32_t)rows * D * 4;
+    const uint32_t bytes = (uint32_t)rows * D * ELT;
     mbar_expect_tx(&bars[st], 2 * bytes);
-    bulk_load_1d((unsigned char*)Kt + (size_t)st * TILE_BYTES, Kh + (size_t)r0 * D, bytes, &bars[st]);
-    bulk_load_1d((unsigned char*)Vt + (size_t)st * TILE_BYTES, Vh + (size_t)r0 * D, bytes, &bars[st]);
+    bulk_load_1d((unsigned char*)Kt + (size_t)st * TILE_BYTES, Kh + (size_t)r0 * D * ELT, bytes, &bars[st]);
+    bulk_load_1d((unsigned char*)Vt + (size_t)st * TILE_BYTES, Vh + (size_t)r0 * D * ELT, bytes, &bars[st]);
   };
   if (tid == 0) {
     issue(0);
@@ -110,9 +112,10 @@ __global__ void __launch_bounds__(PF_THREADS, 2)
 
   float4 qf[CH];
   {
-    const float4* qp = (const float4*)(q + ((size_t)h * T + (row_ok ? row : 0)) * D);
+    const float* qp = q + ((size_t)h * T + (row_ok ? row : 0)) * D;
 #pragma unroll
-    for (int i = 0; i < CH; i++) qf[i] = row_ok ? qp[sub + 8 * i] : make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int i = 0; i < CH; i++)
+      qf[i] = row_ok ? *(const float4*)(qp + attn_dim0<8, BF>(sub, i)) : make_float4(0.f, 0.f, 0.f, 0.f);
   }
   float m = -INFINITY, l = 0.f;
   float4 acc[CH];
@@ -123,16 +126,15 @@ __global__ void __launch_bounds__(PF_THREADS, 2)
   for (int it = 0; it < n_tiles; it++) {
     const int st = it & 1;
     if (!dead && !mbar_wait_bounded(&bars[st], (it >> 1) & 1, status, 700 + st)) dead = true;
-    const float4* Ks = (const float4*)((unsigned char*)Kt + (size_t)st * TILE_BYTES);
-    const float4* Vs = (const float4*)((unsigned char*)Vt + (size_t)st * TILE_BYTES);
+    const unsigned char* Ks = (const unsigned char*)Kt + (size_t)st * TILE_BYTES;
+    const unsigned char* Vs = (const unsigned char*)Vt + (size_t)st * TILE_BYTES;
     const int k0 = it * PF_KT;
     int jmax = warp_last_key - k0 + 1;          // keys of this tile the warp needs
     if (jmax > PF_KT) jmax = PF_KT;
     if (!dead) {
       for (int j = 0; j < jmax; j++) {
         float4 kv[CH];
-#pragma unroll
-        for (int i = 0; i < CH; i++) kv[i] = Ks[j * (D / 4) + sub + 8 * i];
+        attn_load_row<D, 8, CH, BF>(Ks + (size_t)j * D * ELT, sub, kv);
         float d = 0.f;
 #pragma unroll
         for (int i = 0; i < CH; i++) {
@@ -145,8 +147,7 @@ __global__ void __launch_bounds__(PF_THREADS, 2)
         d += __shfl_xor_sync(0xffffffffu, d, 2);
         d += __shfl_xor_sync(0xffffffffu, d, 4);
         const float s = d * scale;
-#pragma unroll
-        for (int i = 0; i < CH; i++) kv[i] = Vs[j * (D / 4) + sub + 8 * i];
+        attn_load_row<D, 8, CH, BF>(Vs + (size_t)j * D * ELT, sub, kv);
         if (row_ok && k0 + j <= row_last_key) {
           if (s > m) {
             const float corr = __expf(m - s);
@@ -173,11 +174,12 @@ __global__ void __launch_bounds__(PF_THREADS, 2)
     if (tid == 0 && it + 2 < n_tiles) issue(it + 2);
   }
   if (row_ok) {
-    float4* op = (float4*)(out + ((size_t)h * T + row) * D);
+    float* op = out + ((size_t)h * T + row) * D;
     const float inv = 1.0f / l;
 #pragma unroll
     for (int i = 0; i < CH; i++)
-      op[sub + 8 * i] = make_float4(acc[i].x * inv, acc[i].y * inv, acc[i].z * inv, acc[i].w * inv);
+      *(float4*)(op + attn_dim0<8, BF>(sub, i)) =
+          make_float4(acc[i].x * inv, acc[i].y * inv, acc[i].z * inv, acc[i].w * inv);
   }
 }
 
@@ -202,29 +204,32 @@ int launch_kv_fill(void* Kc, void* Vc, const float* K, const float* V, int T, lo
   TLB_CUDA(cudaLaunchKernelEx(&lc.cfg, kv_fill_kernel, Kc, Vc, K, V, T, kv_stride, pos0, D, bf));
   return TLB_OK;
 }
-int launch_attn_prefill(DeviceCtx* c, const float* q, const float* K, const float* V, float* out,
-                        int n_q, int n_kv, int T, long long kv_max, int D, float scale, int pos0,
-                        cudaStream_t s) {
+template <int D, bool BF>
+static int launch_attn_prefill_t(DeviceCtx* c, const float* q, const void* K, const void* V, float* out,
+                                 int n_q, int n_kv, int T, long long kv_max, float scale, int pos0,
+                                 cudaStream_t s) {
   const int group = n_q / n_kv;
   long long kv_stride = kv_max * D;
-  const size_t smem = 4 * (size_t)PF_KT * D * 4 + 64 + 128;
+  const size_t smem = 4 * (size_t)PF_KT * D * (BF ? 2 : 4) + 64 + 128;
   LaunchCfg lc(dim3((T + PF_QT - 1) / PF_QT, n_q), dim3(PF_THREADS), smem, s, pdl_enabled());
-  if (D == 128) {
-    static bool attr = false;
-    if (!attr) {
-      TLB_CUDA(cudaFuncSetAttribute(attn_prefill_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, 100 * 1024));
-      attr = true;
-    }
-    TLB_CUDA(cudaLaunchKernelEx(&lc.cfg, attn_prefill_kernel<128>, q, K, V, out, T, kv_stride, group, scale, pos0, c->status));
-  } else {
-    static bool attr = false;
-    if (!attr) {
-      TLB_CUDA(cudaFuncSetAttribute(attn_prefill_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, 100 * 1024));
-      attr = true;
-    }
-    TLB_CUDA(cudaLaunchKernelEx(&lc.cfg, attn_prefill_kernel<64>, q, K, V, out, T, kv_stride, group, scale, pos0, c->status));
+  static bool attr = false;
+  if (!attr) {
+    TLB_CUDA(cudaFuncSetAttribute(attn_prefill_kernel<D, BF>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                  100 * 1024));
+    attr = true;
   }
+  TLB_CUDA(cudaLaunchKernelEx(&lc.cfg, attn_prefill_kernel<D, BF>, q, K, V, out, T, kv_stride, group, scale,
+                              pos0, c->status));
   return TLB_OK;
+}
+int launch_attn_prefill(DeviceCtx* c, const float* q, const void* K, const void* V, float* out,
+                        int n_q, int n_kv, int T, long long kv_max, int D, float scale, int pos0,
+                        int bf, cudaStream_t s) {
+  if (D == 128)
+    return bf ? launch_attn_prefill_t<128, true>(c, q, K, V, out, n_q, n_kv, T, kv_max, scale, pos0, s)
+              : launch_attn_prefill_t<128, false>(c, q, K, V, out, n_q, n_kv, T, kv_max, scale, pos0, s);
+  return bf ? launch_attn_prefill_t<64, true>(c, q, K, V, out, n_q, n_kv, T, kv_max, scale, pos0, s)
+            : launch_attn_prefill_t<64, false>(c, q, K, V, out, n_q, n_kv, T, kv_max, scale, pos0, s);
 }
 
 }  // namespace tlb

@@ -51,8 +51,8 @@ int launch_split_heads(const float*, const float*, float*, int, long long, long 
 int launch_merge_heads(const float*, float*, int, int, int, cudaStream_t);
 int launch_kv_fill(void*, void*, const float*, const float*, int, long long, int, int, int, int,
                    cudaStream_t);
-int launch_attn_prefill(DeviceCtx*, const float*, const float*, const float*, float*, int, int, int,
-                        long long, int, float, int, cudaStream_t);
+int launch_attn_prefill(DeviceCtx*, const float*, const void*, const void*, float*, int, int, int,
+                        long long, int, float, int, int, cudaStream_t);
 int launch_add_rmsnorm(const float*, const float*, const float*, float*, float*, int, float, int,
                        cudaStream_t);
 int launch_add_rmsnorm_ar(const float*, const float*, float*, float*, int, float, const CommDev&,
@@ -624,7 +624,7 @@ int tlb_decoder_prefill(void* h, const int32_t* tokens, int64_t T, int32_t* next
       PF(launch_rope(qkvh, nullptr, qkvh, NQ * rows, rows, D, pos, nullptr, d->rope_base, s));
       PF(launch_rope(kh, nullptr, kh, NKV * rows, rows, D, pos, nullptr, d->rope_base, s));
       PF(launch_kv_fill(L.Kc, L.Vc, kh, vh, rows, d->max_ctx, NKV, D, (int)pos, 0, s));
-      PF(launch_attn_prefill(c, qkvh, L.Kc, L.Vc, ah, NQ, NKV, rows, d->max_ctx, D, d->scale, (int)pos, s));
+      PF(launch_attn_prefill(c, qkvh, L.Kc, L.Vc, ah, NQ, NKV, rows, d->max_ctx, D, d->scale, (int)pos, 0, s));
       PF(launch_merge_heads(ah, at, rows, NQ, D, s));
       PF(gemm(L.wo, at, md, rows));
       PF(launch_add_rmsnorm(x, md, L.fn, ro, h2, E, d->eps, rows, s));

@@ -254,12 +254,18 @@ def merge_heads(src, out=None):
 def attn_prefill(q, K, V, scale, pos0=0, out=None):
     """cuda::attn_prefill (include/cuda.h:1171-1201): causal attention of a prompt chunk.
     q [n_q, T, D]; K, V caches [n_kv, kv_max, D] already holding rows [0, pos0 + T)."""
-    _f32c(q, "attn_prefill q"), _f32c(K, "attn_prefill K"), _f32c(V, "attn_prefill V")
+    _f32c(q, "attn_prefill q")
+    bf = K.dtype == torch.bfloat16
+    if not bf:
+        _f32c(K, "attn_prefill K"), _f32c(V, "attn_prefill V")
+    elif V.dtype != torch.bfloat16 or not (K.is_contiguous() and V.is_contiguous()):
+        raise ValueError("attn_prefill: a bf16 cache needs contiguous bf16 K and V")
     n_q, T, D = q.shape
     n_kv, kv_max, _ = K.shape
     if out is None:
         out = torch.empty_like(q)
-    check(lib().tlb_attn_prefill(_p(q), _p(K), _p(V), _p(out), n_q, n_kv, T, kv_max, D, scale, pos0, _s()))
+    fn = lib().tlb_attn_prefill_bf16 if bf else lib().tlb_attn_prefill
+    check(fn(_p(q), _p(K), _p(V), _p(out), n_q, n_kv, T, kv_max, D, scale, pos0, _s()))
     return out
 
 
@@ -307,10 +313,8 @@ class kv_cache:
         T = k_src.shape[1]
         if T <= 0 or self.pos + T > self.max_ctx:
             raise IndexError("kv_cache.prefill: block does not fit the cache")
-        if self.bf16:
-            raise TlbError("kv_cache.prefill: the tiled prefill kernel reads an f32 cache only")
-        check(lib().tlb_kv_fill(_p(self.K), _p(self.V), _p(k_src), _p(v_src), T, self.max_ctx,
-                                self.n_kv_heads, self.D, self.pos, _s()))
+        check(self._fn("tlb_kv_fill")(_p(self.K), _p(self.V), _p(k_src), _p(v_src), T, self.max_ctx,
+                                      self.n_kv_heads, self.D, self.pos, _s()))
         p0 = self.pos
         self.pos += T
         return attn_prefill(q, self.K, self.V, scale, pos0=p0, out=out)

@@ -11,8 +11,7 @@
 // Scope: the quantized-decode path -- gemv_q4, attn_decode(+_dpos), rope(+_dpos),
 // rmsnorm, rmsnorm_res, swiglu, argmax, kv_append(+_dpos), kv_cache (f32 or bf16), incr_u32, graph
 // capture, the host/device mirror (alloc / release / sync_to_host / upload).  Ops
-// outside that path (elementwise, f32 GEMM, row reductions, f32/bf16 GEMV, prefill
-// attention on a bf16 cache) decline with `false`, which the reference evaluator answers with its
+// outside that path (elementwise, f32 GEMM, row reductions, f32/bf16 GEMV) decline with `false`, which the reference evaluator answers with its
 // own CPU code -- the same contract its stub backend uses.  A hot-path op that the
 // library refuses is NOT declined: it throws, because silently computing a decode
 // op on the CPU is exactly what this backend exists to prevent.
@@ -86,6 +85,8 @@ struct backend {
                         void*) = nullptr;
   int (*kv_fill_bf16)(void*, void*, const float*, const float*, int64_t, int64_t, int64_t, int64_t,
                       int64_t, void*) = nullptr;
+  int (*attn_prefill_bf16)(const float*, const void*, const void*, float*, int64_t, int64_t, int64_t,
+                           int64_t, int64_t, float, int64_t, void*) = nullptr;
   int64_t (*q4p_bytes)(int64_t, int64_t) = nullptr;
   int (*q4_pack)(const void*, int64_t, int64_t, void*, void*) = nullptr;
   int (*gemv_q4p)(const float*, const void*, float*, int64_t, int64_t, float, float, void*) = nullptr;
@@ -187,7 +188,7 @@ struct backend {
               bind(memset_, "tlb_memset") && bind(q4p_bytes, "tlb_q4p_bytes") &&
               bind(q4_pack, "tlb_q4_pack") && bind(gemv_q4p, "tlb_gemv_q4p") &&
               bind(attn_decode_bf16, "tlb_attn_decode_bf16") && bind(kv_append_bf16, "tlb_kv_append_bf16") &&
-              bind(kv_fill_bf16, "tlb_kv_fill_bf16") && bind(split_heads, "tlb_split_heads") &&
+              bind(kv_fill_bf16, "tlb_kv_fill_bf16") && bind(attn_prefill_bf16, "tlb_attn_prefill_bf16") && bind(split_heads, "tlb_split_heads") &&
               bind(merge_heads, "tlb_merge_heads") && bind(kv_fill, "tlb_kv_fill") &&
               bind(attn_prefill, "tlb_attn_prefill") && bind(capture_begin, "tlb_capture_begin") &&
               bind(capture_end, "tlb_capture_end") && bind(graph_launch, "tlb_graph_launch") &&
@@ -477,10 +478,14 @@ inline bool attn_prefill(void* q, void* K, void* V, void* out, int64_t n_q_heads
                          int64_t T, int64_t kv_max, int64_t D, float scale, bool kv_bf16 = false,
                          int64_t pos0 = 0) {
   auto& b = detail::backend::get();
-  if (!b.ready || kv_bf16) return false;
+  if (!b.ready) return false;
   b.reads(q); b.reads(K); b.reads(V); b.writes(out);
-  b.must(b.attn_prefill(detail::f(q), detail::f(K), detail::f(V), detail::fw(out), n_q_heads, n_kv_heads,
-                        T, kv_max, D, scale, pos0, b.stream), "attn_prefill");
+  if (kv_bf16)
+    b.must(b.attn_prefill_bf16(detail::f(q), K, V, detail::fw(out), n_q_heads, n_kv_heads, T, kv_max, D,
+                               scale, pos0, b.stream), "attn_prefill (bf16 cache)");
+  else
+    b.must(b.attn_prefill(detail::f(q), detail::f(K), detail::f(V), detail::fw(out), n_q_heads, n_kv_heads,
+                          T, kv_max, D, scale, pos0, b.stream), "attn_prefill");
   return true;
 }
 
@@ -515,7 +520,7 @@ inline void graph_destroy(CUgraphExec e) {
 }
 
 // Persistent KV cache (reference cuda.h:1326-1405), f32 or bf16 storage.  The device-position
-// forms and the tiled prefill read an f32 cache only and decline on a bf16 one.
+// forms read an f32 cache only (as in the reference) and decline on a bf16 one.
 struct kv_cache {
   void* K = nullptr;
   void* V = nullptr;

@@ -166,6 +166,9 @@ int tlb_kv_fill_bf16(void* Kc, void* Vc, const float* K, const float* V, int64_t
 int tlb_attn_prefill(const float* q, const float* K, const float* V, float* out, int64_t n_q,
                      int64_t n_kv, int64_t T, int64_t kv_max, int64_t D, float scale, int64_t pos0,
                      void* stream);
+int tlb_attn_prefill_bf16(const float* q, const void* K, const void* V, float* out, int64_t n_q,
+                          int64_t n_kv, int64_t T, int64_t kv_max, int64_t D, float scale, int64_t pos0,
+                          void* stream);                          /* bf16 cache */
 
 /* ---- CUDA-graph capture (cu.h:512-551) ------------------------------------- */
 int tlb_capture_begin(void** stream_out);   /* capture_begin: returns the stream to launch on */

@@ -129,3 +129,32 @@ def test_prefill_bad_arguments(tl):
     K96 = torch.zeros((2, 8, 96), device="cuda")
     with pytest.raises(TlbError):
         tl.attn_prefill(q96, K96, K96, 0.125)           # D outside {64, 128}
+
+
+def bf16_round(a):
+    x = np.ascontiguousarray(a, np.float32).view(np.uint32).astype(np.uint64)
+    x = (x + 0x7fff + ((x >> 16) & 1)) >> 16
+    return (x.astype(np.uint32) << 16).view(np.float32).reshape(np.shape(a))
+
+
+@pytest.mark.parametrize("n_q,n_kv,D,T,pos0,kv_max", [(14, 2, 64, 37, 0, 64), (8, 2, 128, 70, 5, 128)])
+def test_attn_prefill_bf16_cache(tl, port, n_q, n_kv, D, T, pos0, kv_max):
+    """Tiled prefill on a bf16 cache: the f32 oracle on the bf16-rounded cache, 1e-4."""
+    K, V = synth.normal(80, 1, (n_kv, kv_max, D)), synth.normal(80, 2, (n_kv, kv_max, D))
+    q = synth.normal(80, 3, (n_q, T, D))
+    scale = 1.0 / np.sqrt(D)
+    got = tl.attn_prefill(dev(q), dev(K).to(torch.bfloat16), dev(V).to(torch.bfloat16), scale,
+                          pos0=pos0).cpu().numpy()
+    assert relerr(got, causal_reference(port, q, bf16_round(K), bf16_round(V), scale, pos0)) < 1e-4
+
+
+def test_kv_cache_bf16_prefill(tl, port):
+    n_q, n_kv, D, maxc, T = 14, 2, 64, 48, 33
+    cache = tl.kv_cache(n_kv, maxc, D, dtype=torch.bfloat16)
+    k, v = synth.normal(81, 1, (n_kv, T, D)), synth.normal(81, 2, (n_kv, T, D))
+    q = synth.normal(81, 3, (n_q, T, D))
+    got = cache.prefill(dev(q), dev(k), dev(v), 0.125).cpu().numpy()
+    Kh, Vh = np.zeros((n_kv, maxc, D), np.float32), np.zeros((n_kv, maxc, D), np.float32)
+    Kh[:, :T], Vh[:, :T] = bf16_round(k), bf16_round(v)
+    assert cache.pos == T
+    assert relerr(got, causal_reference(port, q, Kh, Vh, 0.125, 0)) < 1e-4
