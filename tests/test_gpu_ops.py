@@ -116,6 +116,38 @@ def test_gemv_packed_outliers_and_raw_nibbles(tl, port):
     assert relerr(got, want) < 5e-5
 
 
+def pack_q4p_host(q, K, N):
+    """The tile-packed layout restated on the host: units of 16 rows x 256 k, 2048 B of nibble
+    words in fragment order (chunk i of lane (g, t) = rows g, g+8 x groups 2i, 2i+1, word
+    4*group + t) then 512 B of scales [16][8]; N padded to 16, K to 256 with nibble 8 / scale 0."""
+    SL, RT = (K + 255) // 256, (N + 15) // 16
+    words = q[:N * K // 2].view(np.uint32).reshape(N, K // 8)
+    scales = q[N * K // 2:].view(np.float32).reshape(N, K // 32)
+    W = np.full((RT * 16, SL * 32), 0x88888888, np.uint32)
+    S = np.zeros((RT * 16, SL * 8), np.float32)
+    W[:N, :K // 8], S[:N, :K // 32] = words, scales
+    out = np.empty((RT, SL, 2560), np.uint8)
+    lane = np.arange(32)
+    g, t = lane >> 2, lane & 3
+    for rt in range(RT):
+        for s in range(SL):
+            blk = np.empty((4, 32, 4), np.uint32)
+            for i in range(4):
+                for c in range(4):
+                    blk[i, :, c] = W[rt * 16 + g + (8 if c & 1 else 0), s * 32 + 4 * (2 * i + (c >> 1)) + t]
+            out[rt, s, :2048] = blk.reshape(-1).view(np.uint8)
+            out[rt, s, 2048:] = S[rt * 16:rt * 16 + 16, s * 8:s * 8 + 8].reshape(-1).view(np.uint8)
+    return out.reshape(-1)
+
+
+@pytest.mark.parametrize("K,N", [(256, 16), (896, 40), (1056, 333)])
+def test_q4_pack_layout_bit_exact(tl, port, K, N):
+    """tlb_q4_pack against the host restatement of the layout, byte for byte (padding included)."""
+    q = port.to_q4(synth.normal(63, K + N, (K, N), std=0.02))
+    got = tl.Q4Packed(tl.Q4Weight.from_bytes(q, K, N)).buf.cpu().numpy()
+    assert np.array_equal(got, pack_q4p_host(q, K, N))
+
+
 def test_gemv_packed_bad_arguments(tl):
     from cpp_tensorlib_b200 import lib
     assert lib().tlb_q4p_bytes(16, 48) == -1
