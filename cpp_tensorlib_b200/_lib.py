@@ -50,6 +50,7 @@ SIGNATURES = {
     "tlb_incr_u32": (ci, [vp, vp]),
     "tlb_argmax": (ci, [vp, i64, C.POINTER(i64), vp]),
     "tlb_argmax_dev": (ci, [vp, i64, vp, vp]),
+    "tlb_gemv_bf16_row": (ci, [vp, vp, vp, i64, i64, vp]),
     "tlb_q4p_bytes": (i64, [i64, i64]),
     "tlb_q4_pack": (ci, [vp, i64, i64, vp, vp]),
     "tlb_gemv_q4p": (ci, [vp, vp, vp, i64, i64, f32, f32, vp]),

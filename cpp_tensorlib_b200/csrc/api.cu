@@ -42,6 +42,7 @@ int launch_incr_u32(unsigned*, cudaStream_t);
 int launch_argmax(DeviceCtx*, const float*, int, int*, int*, cudaStream_t);
 int launch_to_q4(const float*, int, int, unsigned char*, cudaStream_t);
 
+int launch_gemv_bf16_row(DeviceCtx*, const float*, const void*, float*, int, int, cudaStream_t);
 int launch_split_heads(const float*, const float*, float*, int, long long, long long, int, int, cudaStream_t);
 int launch_merge_heads(const float*, float*, int, int, int, cudaStream_t);
 int launch_kv_fill(void*, void*, const float*, const float*, int, long long, int, int, int, int,
@@ -277,6 +278,14 @@ int tlb_gemm_q4(const float* x, int64_t M, int64_t ldx, const void* qw, const fl
   }
   return gemv_q4_simt_launch(x, ldx, (int)M, qw, scales, y, ldy, (int)N, (int)K, alpha, beta,
                              S(stream));
+}
+
+int tlb_gemv_bf16_row(const float* a, const void* W, float* y, int64_t N, int64_t K, void* stream) {
+  TLB_REQUIRE(a && W && y, "tlb_gemv_bf16_row: null pointer");
+  TLB_REQUIRE(N > 0 && N < (1ll << 31) && K > 0 && K % 8 == 0, "tlb_gemv_bf16_row: K must be a positive multiple of 8");
+  TLB_REQUIRE((((uintptr_t)a | (uintptr_t)W) & 15) == 0, "tlb_gemv_bf16_row: a and W must be 16-byte aligned");
+  CTX(c);
+  return launch_gemv_bf16_row(c, a, W, y, (int)N, (int)K, S(stream));
 }
 
 int64_t tlb_q4p_bytes(int64_t N, int64_t K) {

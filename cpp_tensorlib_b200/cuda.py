@@ -102,6 +102,20 @@ def gemv_q4(a, wq, y=None):
     return y
 
 
+def gemv_bf16_row(a, W, y=None):
+    """cuda::gemv_bf16_row (include/cuda.h:770-785): y[N] = W[N, K] (bf16, row-major) . a[K]."""
+    _f32c(a, "gemv_bf16_row a")
+    if W.dtype != torch.bfloat16 or W.dim() != 2 or not W.is_contiguous() or not W.is_cuda:
+        raise ValueError("gemv_bf16_row: W must be a contiguous bf16 CUDA matrix [N, K]")
+    N, K = W.shape
+    if a.numel() != K:
+        raise ValueError("gemv_bf16_row: a must hold K elements")
+    if y is None:
+        y = torch.empty(N, dtype=torch.float32, device=a.device)
+    check(lib().tlb_gemv_bf16_row(_p(a), _p(W), _p(y), N, K, _s()))
+    return y
+
+
 class Q4Packed:
     """A q4 matrix in the library's tile-packed layout (2560-byte units of 16 rows x
     256 k: nibble words in MMA-fragment order, then the unit's scales).  Made once from

@@ -38,6 +38,19 @@ def _time_graph(fn, iters):
 
 def gemv(a):
     gen = torch.Generator(device="cuda").manual_seed(0)
+    if a.bf16:
+        Ws = [(torch.randn((a.N, a.K), generator=gen, device="cuda") * 0.02).to(torch.bfloat16)
+              for _ in range(a.copies)]
+        xv, yv = torch.randn(a.K, generator=gen, device="cuda"), torch.empty(a.N, device="cuda")
+
+        def one_pass():
+            for w in Ws:
+                tl.gemv_bf16_row(xv, w, y=yv)
+        ms = _time_graph(one_pass, a.iters) / a.copies
+        nbytes = a.N * a.K * 2 + 4 * a.K + 4 * a.N
+        print(json.dumps(dict(op="gemv_bf16_row", N=a.N, K=a.K, us_per_launch=ms * 1e3,
+                              algorithmic_bytes=nbytes, GBps=nbytes / ms / 1e6)))
+        return
     ws = [tl.to_q4(torch.randn((a.K, a.N), generator=gen, device="cuda") * 0.02) for _ in range(a.copies)]
     x = torch.randn((a.M, a.K), generator=gen, device="cuda")
     y = torch.empty((a.M, a.N), device="cuda")
@@ -106,6 +119,7 @@ def main():
     g.add_argument("--K", type=int, default=3584)
     g.add_argument("--M", type=int, default=1)
     g.add_argument("--packed", type=int, default=0, help="1: tile-packed weights (tlb_gemv_q4p)")
+    g.add_argument("--bf16", type=int, default=0, help="1: bf16 row-major weights (tlb_gemv_bf16_row)")
     t = sub.add_parser("attn")
     t.add_argument("--heads", type=int, default=28)
     t.add_argument("--kv-heads", type=int, default=28)

@@ -87,6 +87,7 @@ struct backend {
                       int64_t, void*) = nullptr;
   int (*attn_prefill_bf16)(const float*, const void*, const void*, float*, int64_t, int64_t, int64_t,
                            int64_t, int64_t, float, int64_t, void*) = nullptr;
+  int (*gemv_bf16_row_)(const float*, const void*, float*, int64_t, int64_t, void*) = nullptr;
   int64_t (*q4p_bytes)(int64_t, int64_t) = nullptr;
   int (*q4_pack)(const void*, int64_t, int64_t, void*, void*) = nullptr;
   int (*gemv_q4p)(const float*, const void*, float*, int64_t, int64_t, float, float, void*) = nullptr;
@@ -187,6 +188,7 @@ struct backend {
               bind(incr_u32, "tlb_incr_u32") && bind(argmax, "tlb_argmax") &&
               bind(memset_, "tlb_memset") && bind(q4p_bytes, "tlb_q4p_bytes") &&
               bind(q4_pack, "tlb_q4_pack") && bind(gemv_q4p, "tlb_gemv_q4p") &&
+              bind(gemv_bf16_row_, "tlb_gemv_bf16_row") &&
               bind(attn_decode_bf16, "tlb_attn_decode_bf16") && bind(kv_append_bf16, "tlb_kv_append_bf16") &&
               bind(kv_fill_bf16, "tlb_kv_fill_bf16") && bind(attn_prefill_bf16, "tlb_attn_prefill_bf16") && bind(split_heads, "tlb_split_heads") &&
               bind(merge_heads, "tlb_merge_heads") && bind(kv_fill, "tlb_kv_fill") &&
@@ -324,7 +326,15 @@ inline bool gemm(void*, int64_t, int64_t, bool, void*, int64_t, int64_t, bool, v
 inline bool row_op(kop, void*, int64_t, void*, int64_t, int64_t, int64_t, float, float) { return false; }
 inline bool gemv_f32(void*, void*, void*, int64_t, int64_t) { return false; }
 inline bool gemv_bf16(void*, void*, void*, int64_t, int64_t) { return false; }
-inline bool gemv_bf16_row(void*, void*, void*, int64_t, int64_t) { return false; }
+// bf16 row-major weights [N][K] (reference cuda.h:770-785): the decode projection of the
+// reference's bf16-weight models
+inline bool gemv_bf16_row(void* a, void* B, void* y, int64_t n, int64_t k) {
+  auto& b = detail::backend::get();
+  if (!b.ready || (k % 8) != 0) return false;
+  b.reads(a); b.reads(B); b.writes(y);
+  b.must(b.gemv_bf16_row_(detail::f(a), B, detail::fw(y), n, k, b.stream), "gemv_bf16_row");
+  return true;
+}
 inline bool gemm_bf16_nt(void*, void*, void*, int64_t, int64_t, int64_t) { return false; }
 
 // ---- the quantized-decode path ----

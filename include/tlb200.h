@@ -59,6 +59,10 @@ int tlb_to_q4(const float* w_kn, int64_t K, int64_t N, void* q4, void* stream);
 int tlb_q4_to_f32(const void* q4, int64_t K, int64_t N, float* out_kn, void* stream);
 
 /* ---- int4 dequant-matmul --------------------------------------------------- */
+/* cu.h:770-785 cuda::gemv_bf16_row: y[n] = sum_k a[k] * W[n][k], W bf16 row-major [N][K] (the
+ * decode projection of the reference's bf16-weight models); K % 8 == 0. */
+int tlb_gemv_bf16_row(const float* a, const void* W, float* y, int64_t N, int64_t K, void* stream);
+
 /* ---- tile-packed int4 weights: the library's own HBM layout for the decode GEMV.
  * No counterpart in the reference.  A matrix in the reference layout (types.h:15-31) is
  * repacked once, on the device, into 2560-byte units (16 rows x 256 k: nibble words in

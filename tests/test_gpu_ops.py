@@ -441,3 +441,17 @@ def test_kv_cache_bf16_append_fill_and_attend(tl, port):
     d_last = torch.tensor([44], dtype=torch.int32, device="cuda")
     got = cache.attn_dpos(dev(q), d_last, 0.125).cpu().numpy()
     assert np.array_equal(got, cache.attn(dev(q), 0.125).cpu().numpy())   # bit-identical forms
+
+
+@pytest.mark.parametrize("N,K", [(1, 8), (37, 264), (1152, 896), (4608, 3584), (896, 4864)])
+def test_gemv_bf16_row_vs_host(tl, N, K):
+    """cuda::gemv_bf16_row (include/cuda.h:770-785): bf16 weights widened to f32, f32 dot; the
+    checker is the double-precision dot on the bf16-rounded weights (the reference's CPU path
+    widens the same values)."""
+    W = bf16_round(synth.normal(90, N + K, (N, K), std=0.05))
+    a = synth.normal(91, K, (K,))
+    got = tl.gemv_bf16_row(dev(a), dev(W).to(torch.bfloat16)).cpu().numpy()
+    want = W.astype(np.float64) @ a.astype(np.float64)
+    assert relerr(got, want) < 1e-4
+    with pytest.raises(Exception):
+        tl.gemv_bf16_row(dev(a)[:K - 1].contiguous(), dev(W).to(torch.bfloat16))
