@@ -41,7 +41,7 @@ namespace tlb {
 
 constexpr int PK_UNIT = 2560;
 constexpr int PK_WARPS = 16;
-constexpr int PK_CTA_UNITS = 64;  // most units one CTA may own in the CTA-owned-tiles mode
+constexpr int PK_CTA_UNITS = 144; // most units one CTA may own in the CTA-owned modes
 
 long long q4p_bytes(long long N, long long K) {
   const long long RT = (N + 15) / 16, SL = (K + 255) / 256;
@@ -119,15 +119,19 @@ struct GemvPParams {
   int push;         // tensor-parallel: store y into every rank's staging slot (comm = that exchange)
                     // (act 3 reads comm instead: a launch pulls or pushes, never both)
   PairEpi epi;
-  int cta_tiles;    // small matrices: a CTA owns whole row tiles and reduces them in shared memory
+  int cta_tiles;    // 0: warps own unit ranges.  KB >= 1: CTA-owned blocks, the grid is
+                    // RB row blocks x KB slab blocks; a CTA reduces its block in shared memory.
+                    // KB == 1 (small matrices): whole rows, results final.  KB > 1 (long rows):
+                    // a CTA prepares only its own slabs of the activation; the KB partial blocks
+                    // of a row block are folded by the last CTA to arrive
+  int slabs;        // activation slabs a CTA holds in shared memory (SL, or the largest slab block)
   CommDev comm;
 };
 
 struct GemvPSmem {
   size_t ring, bars, red, ures, pslab, q, bfrag, total;
 };
-__host__ __device__ inline GemvPSmem gemvp_smem_layout(int stages, int K) {
-  const int SL = (K + 255) / 256;
+__host__ __device__ inline GemvPSmem gemvp_smem_layout(int stages, int SL) {
   GemvPSmem L;
   size_t o = 0;
   L.ring = o;  o += (size_t)PK_WARPS * stages * PK_UNIT;
@@ -170,14 +174,15 @@ __device__ __forceinline__ float lds32f(uint32_t a) {
 
 // PULL: the instantiation that can consume a tensor-parallel exchange in its prologue (act 3);
 // kept out of the single-GPU kernel, whose register budget it would eat.
-template <int STAGES, bool PULL>
+// OWN: the CTA-owned-block instantiation (p.cta_tiles != 0).
+template <int STAGES, bool PULL, bool OWN>
 __global__ void __launch_bounds__(PK_WARPS * 32, 1) gemv_q4p_kernel(GemvPParams p) {
   extern __shared__ unsigned char smem_raw[];
   unsigned char* base = (unsigned char*)(((uintptr_t)smem_raw + 127) & ~(uintptr_t)127);
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int g = lane >> 2, t = lane & 3;
   const int SL = p.SL;
-  const GemvPSmem L = gemvp_smem_layout(STAGES, p.K);
+  const GemvPSmem L = gemvp_smem_layout(STAGES, p.slabs);
   uint64_t* bars = (uint64_t*)(base + L.bars);
   float* red = (float*)(base + L.red);
   float* Pslab = (float*)(base + L.pslab);   // [SL]   2^(13+e) of the slab
@@ -199,16 +204,30 @@ __global__ void __launch_bounds__(PK_WARPS * 32, 1) gemv_q4p_kernel(GemvPParams 
   // Small matrices (about two row tiles per CTA or fewer): a CTA owns whole row tiles,
   // its warps take the tiles' units round-robin and the 16-row results meet in shared
   // memory -- no partials in global memory, no ticket, no last-arriver chain.
-  const bool own = p.cta_tiles != 0;
+  constexpr bool own = OWN;
   int tile_b = 0, n_loc = 0;
+  int s_b = 0, ks = SL;      // the slabs this CTA prepares and indexes locally: [s_b, s_b + ks)
+  int rt = 0, s = 0;         // row tile and (local) slab of the unit being consumed
+  unsigned kb = 0, rb = 0;
   if (own) {
-    const GvSplit ct = {(unsigned)p.RT / gridDim.x, (unsigned)p.RT % gridDim.x};
-    tile_b = (int)gv_start(blockIdx.x, ct);
-    n_loc = ((int)gv_start(blockIdx.x + 1, ct) - tile_b) * SL;
+    const unsigned KB = (unsigned)p.cta_tiles, RB = gridDim.x / KB;
+    rb = blockIdx.x / KB;
+    kb = blockIdx.x - rb * KB;
+    const GvSplit ct = {(unsigned)p.RT / RB, (unsigned)p.RT % RB};
+    const GvSplit cs = {(unsigned)SL / KB, (unsigned)SL % KB};
+    tile_b = (int)gv_start(rb, ct);
+    s_b = (int)gv_start(kb, cs);
+    ks = (int)gv_start(kb + 1, cs) - s_b;
+    n_loc = ((int)gv_start(rb + 1, ct) - tile_b) * ks;
     n_units = warp < n_loc ? (n_loc - warp + PK_WARPS - 1) / PK_WARPS : 0;
-    u0 = (unsigned)(tile_b * SL + warp);
+    // the block's units in (tile, slab) order, dealt round-robin: this warp starts at `warp`
+    rt = tile_b + warp / ks;
+    s = warp % ks;
+    u0 = (unsigned)(rt * SL + s_b + s);
+  } else {
+    rt = (int)(u0 / (unsigned)SL);
+    s = (int)(u0 - (unsigned)rt * SL);
   }
-  const unsigned src_step = own ? (unsigned)PK_WARPS * PK_UNIT : (unsigned)PK_UNIT;
   float* ures = (float*)(base + L.ures);
 
   if (lane == 0) {
@@ -220,13 +239,23 @@ __global__ void __launch_bounds__(PK_WARPS * 32, 1) gemv_q4p_kernel(GemvPParams 
   // producer: lane 0 issues one 2560-byte bulk copy per unit, the warp's units are
   // consecutive in memory
   const unsigned char* src = p.wp + (size_t)u0 * PK_UNIT;
-  int istage = 0;
+  int istage = 0, isl = s;
   auto issue_next = [&]() {
     if (lane == 0) {
       mbar_expect_tx(&mybar[istage], PK_UNIT);
       bulk_load_1d(myR + istage * PK_UNIT, src, PK_UNIT, &mybar[istage]);
     }
-    src += src_step;
+    if (own) {
+      // PK_WARPS units further on in the block; past the block's slabs the next tile's begin
+      isl += PK_WARPS;
+      src += (size_t)PK_WARPS * PK_UNIT;
+      while (isl >= ks) {
+        isl -= ks;
+        src += (size_t)(SL - ks) * PK_UNIT;
+      }
+    } else {
+      src += PK_UNIT;
+    }
     if (++istage == STAGES) istage = 0;
   };
   // Weights do not depend on the previous kernel: the first stage streams before the
@@ -275,13 +304,14 @@ __global__ void __launch_bounds__(PK_WARPS * 32, 1) gemv_q4p_kernel(GemvPParams 
         }
     }
   };
-  for (int job0 = warp; job0 < SL || job0 == warp; job0 += PK_WARPS * PB) {
+  // (slab indices are local to the CTA's block [s_b, s_b + ks); the whole row unless KB > 1)
+  for (int job0 = warp; job0 < ks || job0 == warp; job0 += PK_WARPS * PB) {
     float vv[PB][8], uu[PB][8];
 #pragma unroll
     for (int b = 0; b < PB; b++) {
       const int sl = job0 + b * PK_WARPS;
-      const int k0 = sl * 256 + lane * 8;
-      const bool on = sl < SL && k0 < p.K;   // K % 32 == 0: a lane's 8 values are all in or all out
+      const int k0 = (s_b + sl) * 256 + lane * 8;
+      const bool on = sl < ks && k0 < p.K;   // K % 32 == 0: a lane's 8 values are all in or all out
       auto load8 = [&](const float* s8, float (&o)[8]) {
         if (on) {
           if (p.x_vec_ok) {
@@ -333,7 +363,7 @@ __global__ void __launch_bounds__(PK_WARPS * 32, 1) gemv_q4p_kernel(GemvPParams 
 #pragma unroll
     for (int b = 0; b < PB; b++) {
       const int sl = job0 + b * PK_WARPS;
-      if (sl >= SL) break;  // warp-uniform
+      if (sl >= ks) break;  // warp-uniform
       float v[8];
 #pragma unroll
       for (int i = 0; i < 8; i++) v[i] = vv[b][i];
@@ -344,7 +374,7 @@ __global__ void __launch_bounds__(PK_WARPS * 32, 1) gemv_q4p_kernel(GemvPParams 
         for (int i = 0; i < 8; i++) v[i] = (v[i] / (1.0f + expf(-v[i]))) * uu[b][i];
       }
       if (normed) {
-        const int k0 = sl * 256 + lane * 8;
+        const int k0 = sl * 256 + lane * 8;   // (the fused norm is never combined with slab blocks)
 #pragma unroll
         for (int i = 0; i < 8; i++) {
           const float sv = v[i] + uu[b][i];
@@ -525,13 +555,12 @@ __global__ void __launch_bounds__(PK_WARPS * 32, 1) gemv_q4p_kernel(GemvPParams 
     if (lane == 0) p.counters[rt] = 0;  // leave the counter clean for the next launch
   };
 
-  int rt = (int)(u0 / (unsigned)SL), s = (int)(u0 - (unsigned)rt * SL);
   int st = 0;
   unsigned phase = 0;
   for (int i = 0; i < n_units; i++) {
     if (own && i > 0) {   // next unit of this warp: PK_WARPS further on
       s += PK_WARPS;
-      while (s >= SL) { s -= SL; rt++; }
+      while (s >= ks) { s -= ks; rt++; }
     }
     if (!mbar_wait_bounded(&mybar[st], phase, p.status, 100 + st)) break;
     const uint32_t ust = ring32 + (uint32_t)st * PK_UNIT;
@@ -583,7 +612,7 @@ __global__ void __launch_bounds__(PK_WARPS * 32, 1) gemv_q4p_kernel(GemvPParams 
       v1 += __shfl_xor_sync(0xffffffffu, v1, 1);
       v1 += __shfl_xor_sync(0xffffffffu, v1, 2);
       if (t == 0) {
-        float* dst = ures + (size_t)((rt - tile_b) * SL + s) * 16;
+        float* dst = ures + (size_t)((rt - tile_b) * ks + s) * 16;
         dst[g] = v0;
         dst[g + 8] = v1;
       }
@@ -599,52 +628,87 @@ __global__ void __launch_bounds__(PK_WARPS * 32, 1) gemv_q4p_kernel(GemvPParams 
   }
   if (own) {
     __syncthreads();
-    // one thread per output row: fold the row's SL unit results in slab order
+    const int ntl = n_loc / ks;   // row tiles of this block
+    // one thread per output row: fold the row's unit results in slab order
     if (p.epi.kind) {
-      // one thread per pair: rows (lr, lr + 8) of a tile
-      for (int idx = tid; idx < (n_loc / SL) * 8; idx += PK_WARPS * 32) {
+      // one thread per pair: rows (lr, lr + 8) of a tile (whole rows only: KB == 1)
+      for (int idx = tid; idx < ntl * 8; idx += PK_WARPS * 32) {
         const int tl = idx >> 3, lr = idx & 7;
-        const float* srcp = ures + (size_t)tl * SL * 16 + lr;
+        const float* srcp = ures + (size_t)tl * ks * 16 + lr;
         float sa = 0.f, sb = 0.f;
-        for (int k = 0; k < SL; k++) { sa += srcp[k * 16]; sb += srcp[k * 16 + 8]; }
+        for (int k = 0; k < ks; k++) { sa += srcp[k * 16]; sb += srcp[k * 16 + 8]; }
         emit_pair((tile_b + tl) * 8 + lr, sa, sb);
       }
       return;
     }
-    for (int idx = tid; idx < (n_loc / SL) * 16; idx += PK_WARPS * 32) {
+    const unsigned KB = (unsigned)p.cta_tiles;
+    for (int idx = tid; idx < ntl * 16; idx += PK_WARPS * 32) {
       const int tl = idx >> 4, row = idx & 15;
-      const float* srcp = ures + (size_t)tl * SL * 16 + row;
+      const float* srcp = ures + (size_t)tl * ks * 16 + row;
       float sum = 0.f;
-      for (int k = 0; k < SL; k++) sum += srcp[k * 16];
+      for (int k = 0; k < ks; k++) sum += srcp[k * 16];
       const int n = (tile_b + tl) * 16 + row;
-      if (n < p.N) emit(n, sum);
+      if (KB == 1) {
+        if (n < p.N) emit(n, sum);
+      } else {
+        __stcg(p.partials + ((size_t)kb * p.RT + tile_b + tl) * 16 + row, sum);
+      }
     }
+    if (KB == 1) return;
+    // Slab blocks: the row block's KB partial blocks meet in global memory; the CTA that
+    // arrives last folds them in block order (the same bits whichever CTA that is).
+    __threadfence();
+    __syncthreads();
+    int* flag = (int*)red;
+    if (tid == 0) *flag = (int)atom_add_acq_rel(&p.counters[rb], 1);
+    __syncthreads();
+    if (*flag != (int)KB - 1) return;
+    __threadfence();
+    for (int idx = tid; idx < ntl * 16; idx += PK_WARPS * 32) {
+      const size_t off = (size_t)(tile_b + (idx >> 4)) * 16 + (idx & 15);
+      float sum = 0.f;
+      for (unsigned b0 = 0; b0 < KB; b0 += 8) {
+        float pv[8];
+#pragma unroll
+        for (int k = 0; k < 8; k++)
+          pv[k] = b0 + k < KB ? __ldcg(p.partials + (size_t)(b0 + k) * p.RT * 16 + off) : 0.f;
+#pragma unroll
+        for (int k = 0; k < 8; k++) sum += pv[k];
+      }
+      if ((int)off < p.N) emit((int)off, sum);
+    }
+    if (tid == 0) p.counters[rb] = 0;  // clean for the next launch
     return;
   }
   if (n_units > 0 && s != 0) flush(rt);
 }
 
-static int gemvp_stages(int K) {
+static int gemvp_stages(int slabs) {
   for (int st = 4; st >= 2; st--)
-    if (gemvp_smem_layout(st, K).total <= 227 * 1024) return st;
+    if (gemvp_smem_layout(st, slabs).total <= 227 * 1024) return st;
   return 0;
 }
 
 bool gemv_q4p_supported(long long N, long long K) {
-  return N > 0 && K > 0 && K % 32 == 0 && K <= (1 << 20) && gemvp_stages((int)K) != 0;
+  return N > 0 && K > 0 && K % 32 == 0 && K <= (1 << 20) && gemvp_stages((int)((K + 255) / 256)) != 0;
 }
 
-template <int STAGES, bool PULL>
+template <int STAGES, bool PULL, bool OWN>
 static int gemvp_launch_t(const GemvPParams& p, int ctas, size_t smem, cudaStream_t stream) {
   static bool attr = false;
   if (!attr) {
-    TLB_CUDA(cudaFuncSetAttribute(gemv_q4p_kernel<STAGES, PULL>,
+    TLB_CUDA(cudaFuncSetAttribute(gemv_q4p_kernel<STAGES, PULL, OWN>,
                                   cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
     attr = true;
   }
   LaunchCfg lc(dim3(ctas), dim3(PK_WARPS * 32), smem, stream, pdl_enabled());
-  TLB_CUDA(cudaLaunchKernelEx(&lc.cfg, gemv_q4p_kernel<STAGES, PULL>, p));
+  TLB_CUDA(cudaLaunchKernelEx(&lc.cfg, gemv_q4p_kernel<STAGES, PULL, OWN>, p));
   return TLB_OK;
+}
+template <int STAGES, bool PULL>
+static int gemvp_launch_o(const GemvPParams& p, int ctas, size_t smem, cudaStream_t stream) {
+  return p.cta_tiles ? gemvp_launch_t<STAGES, PULL, true>(p, ctas, smem, stream)
+                     : gemvp_launch_t<STAGES, PULL, false>(p, ctas, smem, stream);
 }
 
 int gemv_q4p_launch(DeviceCtx* c, const void* packed, const float* x, float* y, int N, int K,
@@ -662,7 +726,7 @@ int gemv_q4p_launch(DeviceCtx* c, const void* packed, const float* x, float* y, 
     if (push_comm) return set_error(TLB_ERR_ARG, "gemv_q4p: a pair epilogue cannot push");
     if (N % 16) return set_error(TLB_ERR_ARG, "gemv_q4p: a pair epilogue needs N % 16 == 0");
   }
-  const int stages = gemvp_stages(K);
+  int stages = gemvp_stages((K + 255) / 256);
   if (!stages || K % 32) return set_error(TLB_ERR_UNSUPPORTED, "gemv_q4p: K not supported");
   p.act = act;
   p.delta = delta; p.nw = nw; p.xout = xout; p.eps = eps;
@@ -701,15 +765,47 @@ int gemv_q4p_launch(DeviceCtx* c, const void* packed, const float* x, float* y, 
       ctas = cb;
     }
   }
-  const size_t smem = gemvp_smem_layout(stages, K).total;
-  if (p.act == 3) {
-    if (stages == 4) return gemvp_launch_t<4, true>(p, ctas, smem, stream);
-    if (stages == 3) return gemvp_launch_t<3, true>(p, ctas, smem, stream);
-    return gemvp_launch_t<2, true>(p, ctas, smem, stream);
+  p.slabs = p.SL;
+  if (!p.cta_tiles && p.SL > 2 * PK_WARPS && act <= 1 && !epi) {
+    // Long rows (the down projection): every CTA would turn the whole activation into
+    // digits, 16 slabs per round, before its stream can start.  Slab blocks cut that to one
+    // round at the price of a KB-way fold.  Pick KB by a cost model in ns: a unit is 58 ns of a
+    // CTA's share of the stream, a round of activation prep 600 ns, the fold 300 + 100 KB.
+    const int cb = max_ctas > 0 ? max_ctas : c->sm_count;
+    const int workers = ctas * PK_WARPS;
+    const long long base_cost = (long long)((p.U + workers - 1) / workers) * PK_WARPS * 58 +
+                                (long long)((p.SL + PK_WARPS - 1) / PK_WARPS) * 600;
+    long long best = base_cost;
+    int best_kb = 0;
+    static const int forced = getenv("TLB_GEMV_KB") ? atoi(getenv("TLB_GEMV_KB")) : -1;
+    for (int kb = 2; kb <= 40 && kb <= p.SL && kb <= cb; kb++) {
+      const int rbn = cb / kb < p.RT ? cb / kb : p.RT;
+      const int ksm = (p.SL + kb - 1) / kb, tm = (p.RT + rbn - 1) / rbn;
+      if (ksm * tm > PK_CTA_UNITS) continue;
+      if ((size_t)kb * p.RT * 16 > (size_t)c->gemv_max_workers * 2 * 128) continue;
+      const long long cost = (long long)((ksm * tm + PK_WARPS - 1) / PK_WARPS) * PK_WARPS * 58 +
+                             (long long)((ksm + PK_WARPS - 1) / PK_WARPS) * 600 + 300 + 100 * kb;
+      if (forced == kb) { best = -1; best_kb = kb; }
+      if (cost < best) { best = cost; best_kb = kb; }
+    }
+    if (forced == 0) best_kb = 0;
+    if (best_kb) {
+      const int rbn = cb / best_kb < p.RT ? cb / best_kb : p.RT;
+      p.cta_tiles = best_kb;
+      p.slabs = (p.SL + best_kb - 1) / best_kb;
+      ctas = rbn * best_kb;
+      stages = gemvp_stages(p.slabs);
+    }
   }
-  if (stages == 4) return gemvp_launch_t<4, false>(p, ctas, smem, stream);
-  if (stages == 3) return gemvp_launch_t<3, false>(p, ctas, smem, stream);
-  return gemvp_launch_t<2, false>(p, ctas, smem, stream);
+  const size_t smem = gemvp_smem_layout(stages, p.slabs).total;
+  if (p.act == 3) {
+    if (stages == 4) return gemvp_launch_o<4, true>(p, ctas, smem, stream);
+    if (stages == 3) return gemvp_launch_o<3, true>(p, ctas, smem, stream);
+    return gemvp_launch_o<2, true>(p, ctas, smem, stream);
+  }
+  if (stages == 4) return gemvp_launch_o<4, false>(p, ctas, smem, stream);
+  if (stages == 3) return gemvp_launch_o<3, false>(p, ctas, smem, stream);
+  return gemvp_launch_o<2, false>(p, ctas, smem, stream);
 }
 
 }  // namespace tlb

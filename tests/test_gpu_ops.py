@@ -81,10 +81,13 @@ def test_gemv_cfg1_golden(tl, port, golden):
 
 
 @pytest.mark.parametrize("K,N", [(32, 1), (896, 4864), (3584, 4608), (256, 16), (4864, 896), (18944, 48),
-                                 (1056, 333), (8192, 40)])
+                                 (1056, 333), (8192, 40), (8480, 100), (9472, 1000), (18944, 3584),
+                                 (10240, 5000)])
 def test_gemv_packed_vs_oracle(tl, port, K, N):
     """The decode GEMV on tile-packed weights (padding of N to 16 and K to 256, split
-    row tiles, every ring depth) against the oracle; 1e-4 like the reference-layout GEMV."""
+    row tiles, CTA-owned tiles, slab blocks on rows longer than 32 slabs -- with a ragged
+    last slab and ragged row blocks --, every ring depth) against the oracle; 1e-4 like
+    the reference-layout GEMV."""
     w = synth.normal(60 + K % 7, N, (K, N), std=0.02)
     q = port.to_q4(w)
     x = synth.normal(61, K, (K,))
