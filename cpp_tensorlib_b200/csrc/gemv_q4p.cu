@@ -174,8 +174,9 @@ __device__ __forceinline__ float lds32f(uint32_t a) {
 
 // PULL: the instantiation that can consume a tensor-parallel exchange in its prologue (act 3);
 // kept out of the single-GPU kernel, whose register budget it would eat.
-// OWN: the CTA-owned-block instantiation (p.cta_tiles != 0).
-template <int STAGES, bool PULL, bool OWN>
+// OWN: the CTA-owned-block instantiation (p.cta_tiles != 0).  EPI: the pair epilogue
+// (p.epi.kind) as a compile-time value, so the plain projections carry no rope code.
+template <int STAGES, bool PULL, bool OWN, int EPI>
 __global__ void __launch_bounds__(PK_WARPS * 32, 1) gemv_q4p_kernel(GemvPParams p) {
   extern __shared__ unsigned char smem_raw[];
   unsigned char* base = (unsigned char*)(((uintptr_t)smem_raw + 127) & ~(uintptr_t)127);
@@ -450,7 +451,7 @@ __global__ void __launch_bounds__(PK_WARPS * 32, 1) gemv_q4p_kernel(GemvPParams 
   auto emit_pair = [&](int pi, float a, float b) {
     a = a * p.alpha + p.beta;
     b = b * p.alpha + p.beta;
-    if (p.epi.kind == 1) {
+    if (EPI == 1) {
       // tl_swiglu (kernels/tensorlib_cuda.cu:185-192): silu(gate) * up, same expression
       p.epi.out[pi] = (a / (1.0f + expf(-a))) * b;
       return;
@@ -507,7 +508,7 @@ __global__ void __launch_bounds__(PK_WARPS * 32, 1) gemv_q4p_kernel(GemvPParams 
     const int r0 = rt * 16;
     if (complete) {
       if (t == 0) {
-        if (p.epi.kind) {
+        if (EPI) {
           emit_pair(rt * 8 + g, v0, v1);
         } else {
           if (r0 + g < p.N) emit(r0 + g, v0);
@@ -546,9 +547,9 @@ __global__ void __launch_bounds__(PK_WARPS * 32, 1) gemv_q4p_kernel(GemvPParams 
 #pragma unroll
         for (int k = 0; k < 16; k++) s += pv[k];
       }
-      if (!p.epi.kind && r0 + lane < p.N) emit(r0 + lane, s);
+      if (!EPI && r0 + lane < p.N) emit(r0 + lane, s);
     }
-    if (p.epi.kind) {
+    if (EPI) {
       const float s2 = __shfl_down_sync(0xffffffffu, s, 8);   // row lane + 8 of the tile
       if (lane < 8) emit_pair(rt * 8 + lane, s, s2);
     }
@@ -630,7 +631,7 @@ __global__ void __launch_bounds__(PK_WARPS * 32, 1) gemv_q4p_kernel(GemvPParams 
     __syncthreads();
     const int ntl = n_loc / ks;   // row tiles of this block
     // one thread per output row: fold the row's unit results in slab order
-    if (p.epi.kind) {
+    if (EPI) {
       // one thread per pair: rows (lr, lr + 8) of a tile (whole rows only: KB == 1)
       for (int idx = tid; idx < ntl * 8; idx += PK_WARPS * 32) {
         const int tl = idx >> 3, lr = idx & 7;
@@ -693,22 +694,28 @@ bool gemv_q4p_supported(long long N, long long K) {
   return N > 0 && K > 0 && K % 32 == 0 && K <= (1 << 20) && gemvp_stages((int)((K + 255) / 256)) != 0;
 }
 
-template <int STAGES, bool PULL, bool OWN>
+template <int STAGES, bool PULL, bool OWN, int EPI>
 static int gemvp_launch_t(const GemvPParams& p, int ctas, size_t smem, cudaStream_t stream) {
   static bool attr = false;
   if (!attr) {
-    TLB_CUDA(cudaFuncSetAttribute(gemv_q4p_kernel<STAGES, PULL, OWN>,
+    TLB_CUDA(cudaFuncSetAttribute(gemv_q4p_kernel<STAGES, PULL, OWN, EPI>,
                                   cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
     attr = true;
   }
   LaunchCfg lc(dim3(ctas), dim3(PK_WARPS * 32), smem, stream, pdl_enabled());
-  TLB_CUDA(cudaLaunchKernelEx(&lc.cfg, gemv_q4p_kernel<STAGES, PULL, OWN>, p));
+  TLB_CUDA(cudaLaunchKernelEx(&lc.cfg, gemv_q4p_kernel<STAGES, PULL, OWN, EPI>, p));
   return TLB_OK;
+}
+template <int STAGES, bool PULL, bool OWN>
+static int gemvp_launch_e(const GemvPParams& p, int ctas, size_t smem, cudaStream_t stream) {
+  if (p.epi.kind == 0) return gemvp_launch_t<STAGES, PULL, OWN, 0>(p, ctas, smem, stream);
+  if (p.epi.kind == 1) return gemvp_launch_t<STAGES, PULL, OWN, 1>(p, ctas, smem, stream);
+  return gemvp_launch_t<STAGES, PULL, OWN, 2>(p, ctas, smem, stream);
 }
 template <int STAGES, bool PULL>
 static int gemvp_launch_o(const GemvPParams& p, int ctas, size_t smem, cudaStream_t stream) {
-  return p.cta_tiles ? gemvp_launch_t<STAGES, PULL, true>(p, ctas, smem, stream)
-                     : gemvp_launch_t<STAGES, PULL, false>(p, ctas, smem, stream);
+  if (p.cta_tiles) return gemvp_launch_e<STAGES, PULL, true>(p, ctas, smem, stream);
+  return gemvp_launch_e<STAGES, PULL, false>(p, ctas, smem, stream);
 }
 
 int gemv_q4p_launch(DeviceCtx* c, const void* packed, const float* x, float* y, int N, int K,
@@ -777,7 +784,6 @@ int gemv_q4p_launch(DeviceCtx* c, const void* packed, const float* x, float* y, 
                                 (long long)((p.SL + PK_WARPS - 1) / PK_WARPS) * 600;
     long long best = base_cost;
     int best_kb = 0;
-    static const int forced = getenv("TLB_GEMV_KB") ? atoi(getenv("TLB_GEMV_KB")) : -1;
     for (int kb = 2; kb <= 40 && kb <= p.SL && kb <= cb; kb++) {
       const int rbn = cb / kb < p.RT ? cb / kb : p.RT;
       const int ksm = (p.SL + kb - 1) / kb, tm = (p.RT + rbn - 1) / rbn;
@@ -785,10 +791,8 @@ int gemv_q4p_launch(DeviceCtx* c, const void* packed, const float* x, float* y, 
       if ((size_t)kb * p.RT * 16 > (size_t)c->gemv_max_workers * 2 * 128) continue;
       const long long cost = (long long)((ksm * tm + PK_WARPS - 1) / PK_WARPS) * PK_WARPS * 58 +
                              (long long)((ksm + PK_WARPS - 1) / PK_WARPS) * 600 + 300 + 100 * kb;
-      if (forced == kb) { best = -1; best_kb = kb; }
       if (cost < best) { best = cost; best_kb = kb; }
     }
-    if (forced == 0) best_kb = 0;
     if (best_kb) {
       const int rbn = cb / best_kb < p.RT ? cb / best_kb : p.RT;
       p.cta_tiles = best_kb;
