@@ -307,7 +307,7 @@ __global__ void __launch_bounds__(PK_WARPS * 32, 1) gemv_q4p_kernel(GemvPParams 
   };
   // (slab indices are local to the CTA's block [s_b, s_b + ks); the whole row unless KB > 1)
   for (int job0 = warp; job0 < ks || job0 == warp; job0 += PK_WARPS * PB) {
-    float vv[PB][8], uu[PB][8];
+    float vv[PB][8], uu[PB][8], ww[PB][8];
 #pragma unroll
     for (int b = 0; b < PB; b++) {
       const int sl = job0 + b * PK_WARPS;
@@ -331,6 +331,8 @@ __global__ void __launch_bounds__(PK_WARPS * 32, 1) gemv_q4p_kernel(GemvPParams 
       load8(p.x + k0, vv[b]);
       if (p.act == 1) load8(p.x + p.K + k0, uu[b]);
       if (p.act == 2) load8(p.delta + k0, uu[b]);
+      // the norm weights travel with the activation: no load left behind the block barrier
+      if (normed) load8(p.nw + k0, ww[b]);
       if constexpr (PULL) {
         if (p.act == 3) pull8(k0, uu[b], on);
       }
@@ -381,7 +383,7 @@ __global__ void __launch_bounds__(PK_WARPS * 32, 1) gemv_q4p_kernel(GemvPParams 
           const float sv = v[i] + uu[b][i];
           const bool in = k0 + i < p.K;
           if (in && blockIdx.x == 0) p.xout[k0 + i] = sv;
-          v[i] = in ? sv * nrm_inv * p.nw[k0 + i] : 0.f;
+          v[i] = in ? sv * nrm_inv * ww[b][i] : 0.f;
         }
       }
       float mx = 0.f;
@@ -755,6 +757,7 @@ int gemv_q4p_launch(DeviceCtx* c, const void* packed, const float* x, float* y, 
   p.U = (unsigned)p.RT * (unsigned)p.SL;
   bool vec = ((uintptr_t)x & 15) == 0 && (K % 4) == 0;
   if (act == 2) vec = vec && ((uintptr_t)delta & 15) == 0;
+  if (act == 2 || act == 3) vec = vec && ((uintptr_t)nw & 15) == 0;
   p.x_vec_ok = vec ? 1 : 0;
   if (p.RT > c->gemv_max_tiles)
     return set_error(TLB_ERR_UNSUPPORTED, "gemv_q4p: N exceeds the fix-up counter capacity");
