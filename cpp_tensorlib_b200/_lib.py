@@ -19,6 +19,7 @@ SIGNATURES = {
     "tlb_last_error": (C.c_char_p, []),
     "tlb_version": (ci, []),
     "tlb_device_status": (ci, [C.POINTER(ci), ci]),
+    "tlb_set_wait_limit_cycles": (ci, [i64]),
     "tlb_set_pdl": (ci, [ci]),
     "tlb_alloc": (ci, [i64, C.POINTER(vp)]),
     "tlb_free": (ci, [vp]),
@@ -81,6 +82,7 @@ SIGNATURES = {
     "tlb_decoder_last_token": (ci, [vp, C.POINTER(C.c_int32), vp]),
     "tlb_decoder_ipc_export": (ci, [vp, vp]),
     "tlb_decoder_ipc_open": (ci, [vp, vp]),
+    "tlb_decoder_loopback_peers": (ci, [vp]),
 }
 
 

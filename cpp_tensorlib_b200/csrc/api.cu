@@ -37,7 +37,7 @@ int launch_swiglu(const float*, float*, int, int, cudaStream_t);
 int launch_rope(const float*, const float*, float*, int, int, int, unsigned, const unsigned*,
                 float, cudaStream_t);
 int launch_kv_append(void*, void*, const float*, const float*, unsigned, const unsigned*, long long,
-                     int, int, int, cudaStream_t);
+                     int, int, int, int*, cudaStream_t);
 int launch_incr_u32(unsigned*, cudaStream_t);
 int launch_argmax(DeviceCtx*, const float*, int, int*, int*, cudaStream_t);
 int launch_to_q4(const float*, int, int, unsigned char*, cudaStream_t);
@@ -107,6 +107,10 @@ static int create_ctx(int dev, DeviceCtx** out) {
   TLB_CUDA(cudaMemset(c->argmax_cell, 0, 4 * sizeof(unsigned long long)));
   TLB_CUDA(cudaMalloc(&c->status, ST_WORDS * sizeof(int)));
   TLB_CUDA(cudaMemset(c->status, 0, ST_WORDS * sizeof(int)));
+  {
+    const long long limit = WAIT_LIMIT_DEFAULT;
+    TLB_CUDA(cudaMemcpy(&c->status[ST_WAIT_LIMIT], &limit, sizeof(limit), cudaMemcpyHostToDevice));
+  }
   TLB_CUDA(cudaMallocHost(&c->status_host, ST_WORDS * sizeof(int)));
   TLB_CUDA(cudaDeviceSynchronize());
   *out = c;
@@ -128,6 +132,16 @@ int get_ctx(DeviceCtx** out) {
   g_ctx[dev] = c;
   *out = c;
   return TLB_OK;
+}
+
+// The context of the current device if one was created already; never creates (and so
+// never allocates).
+DeviceCtx* find_ctx() {
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess) return nullptr;
+  std::lock_guard<std::mutex> lk(g_mu);
+  auto it = g_ctx.find(dev);
+  return it == g_ctx.end() ? nullptr : it->second;
 }
 
 static inline cudaStream_t S(void* s) { return reinterpret_cast<cudaStream_t>(s); }
@@ -171,8 +185,31 @@ int tlb_device_status(int* out2, int clear) {
     out2[0] = c->status_host[ST_WAIT_TIMEOUT];
     out2[1] = c->status_host[ST_WAIT_WHERE];
   }
-  if (clear) TLB_CUDA(cudaMemset(c->status, 0, ST_WORDS * sizeof(int)));
-  return c->status_host[ST_WAIT_TIMEOUT] ? TLB_ERR_DEVICE_WAIT : TLB_OK;
+  const bool timed_out = c->status_host[ST_WAIT_TIMEOUT] != 0;
+  const bool overflow = c->status_host[ST_KV_OVERFLOW] != 0;
+  if (clear) {
+    // the wait limit (words 2..3) survives a clear
+    TLB_CUDA(cudaMemset(c->status, 0, 2 * sizeof(int)));
+    TLB_CUDA(cudaMemset(&c->status[ST_KV_OVERFLOW], 0, sizeof(int)));
+    if (timed_out) {
+      // a kernel that gave up may have left its fix-up tickets half counted
+      TLB_CUDA(cudaMemset(c->gemv_counters, 0, (size_t)c->gemv_max_tiles * sizeof(int)));
+      TLB_CUDA(cudaMemset(c->attn_counters, 0, c->attn_max_counters * sizeof(int)));
+      TLB_CUDA(cudaMemset(c->argmax_cell, 0, 4 * sizeof(unsigned long long)));
+    }
+  }
+  if (timed_out) return set_error(TLB_ERR_DEVICE_WAIT, "a bounded device-side wait expired (where = " +
+                                                           std::to_string(c->status_host[ST_WAIT_WHERE]) + ")");
+  if (overflow) return set_error(TLB_ERR_STATE, "a kernel was asked to touch a KV-cache row beyond the cache's capacity and skipped it");
+  return TLB_OK;
+}
+int tlb_set_wait_limit_cycles(int64_t cycles) {
+  TLB_REQUIRE(cycles > 0, "tlb_set_wait_limit_cycles: the limit must be positive");
+  CTX(c);
+  const long long limit = cycles;
+  TLB_CUDA(cudaDeviceSynchronize());
+  TLB_CUDA(cudaMemcpy(&c->status[ST_WAIT_LIMIT], &limit, sizeof(limit), cudaMemcpyHostToDevice));
+  return TLB_OK;
 }
 
 // Undocumented diagnostic hook: device buffer of [ctas][8] u64 that the GEMV fills
@@ -324,6 +361,9 @@ static int attn_decode_any(const float* q, const void* K, const void* V, float* 
   TLB_REQUIRE(q && K && V && out, "tlb_attn_decode: null pointer");
   TLB_REQUIRE(ctx >= 1 && ctx <= kv_max, "tlb_attn_decode: need 1 <= ctx <= kv_max");
   TLB_REQUIRE(n_kv > 0 && n_kv <= 1024, "tlb_attn_decode: n_kv out of range");
+  TLB_REQUIRE(n_q > 0 && n_q <= (1 << 24) && n_q % n_kv == 0,
+              "tlb_attn_decode: need 0 < n_q <= 2^24 and n_q % n_kv == 0");
+  TLB_REQUIRE(kv_max <= (1ll << 30) && (D == 64 || D == 128), "tlb_attn_decode: kv_max / D out of range");
   CTX(c);
   size_t need = attn_partials_bytes((int)n_q, (int)n_kv, ctx, (int)D, c->sm_count);
   if (need > c->attn_scratch_bytes) {
@@ -360,6 +400,9 @@ static int attn_decode_dpos_any(const float* q, const void* K, const void* V, fl
                                 void* partials, void* stream, int kv_bf16) {
   TLB_REQUIRE(q && K && V && out && d_pos && partials, "tlb_attn_decode_dpos: null pointer");
   TLB_REQUIRE(n_kv > 0 && n_kv <= 64, "tlb_attn_decode_dpos: n_kv must be 1..64");
+  TLB_REQUIRE(n_q > 0 && n_q <= (1 << 24) && n_q % n_kv == 0,
+              "tlb_attn_decode_dpos: need 0 < n_q <= 2^24 and n_q % n_kv == 0");
+  TLB_REQUIRE(kv_max >= 1 && kv_max <= (1ll << 30), "tlb_attn_decode_dpos: kv_max out of range");
   TLB_REQUIRE(((uintptr_t)partials & 15) == 0, "tlb_attn_decode_dpos: partials must be 16-byte aligned");
   CTX(c);
   return attn_decode_launch(c, q, K, V, out, (int)n_q, (int)n_kv, 0, kv_max, (int)D, scale,
@@ -409,7 +452,8 @@ int tlb_kv_append(float* Kc, float* Vc, const float* k_new, const float* v_new, 
   TLB_REQUIRE(Kc && Vc && k_new && v_new, "tlb_kv_append: null pointer");
   TLB_REQUIRE(pos >= 0 && pos < kv_max, "tlb_kv_append: pos outside the cache");
   TLB_REQUIRE(D > 0 && D <= 1024 && n_kv > 0, "tlb_kv_append: bad shape");
-  return launch_kv_append(Kc, Vc, k_new, v_new, (unsigned)pos, nullptr, kv_max, (int)n_kv, (int)D, 0,
+  CTX(c);
+  return launch_kv_append(Kc, Vc, k_new, v_new, (unsigned)pos, nullptr, kv_max, (int)n_kv, (int)D, 0, c->status,
                           S(stream));
 }
 int tlb_kv_append_bf16(void* Kc, void* Vc, const float* k_new, const float* v_new, int64_t pos,
@@ -417,22 +461,27 @@ int tlb_kv_append_bf16(void* Kc, void* Vc, const float* k_new, const float* v_ne
   TLB_REQUIRE(Kc && Vc && k_new && v_new, "tlb_kv_append_bf16: null pointer");
   TLB_REQUIRE(pos >= 0 && pos < kv_max, "tlb_kv_append_bf16: pos outside the cache");
   TLB_REQUIRE(D > 0 && D <= 1024 && n_kv > 0, "tlb_kv_append_bf16: bad shape");
-  return launch_kv_append(Kc, Vc, k_new, v_new, (unsigned)pos, nullptr, kv_max, (int)n_kv, (int)D, 1,
+  CTX(c);
+  return launch_kv_append(Kc, Vc, k_new, v_new, (unsigned)pos, nullptr, kv_max, (int)n_kv, (int)D, 1, c->status,
                           S(stream));
 }
 int tlb_kv_append_dpos(float* Kc, float* Vc, const float* k_new, const float* v_new,
                        const void* d_pos, int64_t kv_max, int64_t n_kv, int64_t D, void* stream) {
   TLB_REQUIRE(Kc && Vc && k_new && v_new && d_pos, "tlb_kv_append_dpos: null pointer");
   TLB_REQUIRE(D > 0 && D <= 1024 && n_kv > 0, "tlb_kv_append_dpos: bad shape");
+  CTX(c);
   return launch_kv_append(Kc, Vc, k_new, v_new, 0u, (const unsigned*)d_pos, kv_max, (int)n_kv,
-                          (int)D, 0, S(stream));
+                          (int)D, 0, c->status,
+                          S(stream));
 }
 int tlb_kv_append_dpos_bf16(void* Kc, void* Vc, const float* k_new, const float* v_new,
                             const void* d_pos, int64_t kv_max, int64_t n_kv, int64_t D, void* stream) {
   TLB_REQUIRE(Kc && Vc && k_new && v_new && d_pos, "tlb_kv_append_dpos_bf16: null pointer");
   TLB_REQUIRE(D > 0 && D <= 1024 && n_kv > 0, "tlb_kv_append_dpos_bf16: bad shape");
+  CTX(c);
   return launch_kv_append(Kc, Vc, k_new, v_new, 0u, (const unsigned*)d_pos, kv_max, (int)n_kv,
-                          (int)D, 1, S(stream));
+                          (int)D, 1, c->status,
+                          S(stream));
 }
 int tlb_incr_u32(void* d_pos, void* stream) {
   TLB_REQUIRE(d_pos, "tlb_incr_u32: null pointer");

@@ -45,6 +45,7 @@ struct AttnParams {
   int ctx;
   int n_q, n_kv, grp;
   long long kv_stride;  // kv_max * D
+  int kv_rows;          // kv_max: a device-resident position at or beyond it is refused
   float scale;
   int s_cap;     // partial slots per head (= launched splits)
   int sm2;       // CTA target of the grid (attn_target): split count = target / kv heads
@@ -145,6 +146,15 @@ __global__ void __launch_bounds__(32 * LPK, ((HW >= 4 || LPK > 8) ? 1 : 2))
   __syncthreads();
 
   const int ctx = p.d_pos ? (int)(*p.d_pos) + 1 : p.ctx;
+  if (p.d_pos && (ctx > p.kv_rows || ctx < 1)) {
+    // The position ran past the cache (the host checks this before it launches; this is the
+    // second line of defence for graphs replayed without the host's bookkeeping): read
+    // nothing, leave the tickets untouched, tell the host through the status block.
+    pdl_wait();
+    pdl_launch_dependents();
+    if (p.status && tid == 0) atomicExch(&p.status[ST_KV_OVERFLOW], 1);
+    return;
+  }
   const int chunk = attn_chunk(p.n_kv, ctx, p.sm2);
   const int s_live = (ctx + chunk - 1) / chunk;
   const bool dead = sp >= s_live;  // capacity-sized grid: splits past the live count do nothing
@@ -456,11 +466,10 @@ size_t attn_partials_bytes(int n_q, int n_kv, long long kv_max, int D, int sm_co
 template <int D, int HW, int LPK, bool BF>
 static int launch_b(const AttnParams& p, int splits, cudaStream_t stream) {
   size_t smem = attn_smem_bytes<D, HW, LPK, BF>(p.grp);
-  static bool attr = false;
-  if (!attr) {
-    TLB_CUDA(cudaFuncSetAttribute(attn_decode_kernel<D, HW, LPK, BF>,
-                                  cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
-    attr = true;
+  static std::atomic<unsigned long long> attr_done{0};
+  {
+    const int rc_attr = ensure_dynamic_smem(attn_decode_kernel<D, HW, LPK, BF>, 200 * 1024, attr_done);
+    if (rc_attr) return rc_attr;
   }
   LaunchCfg lc(dim3(splits, p.n_kv), dim3(32 * LPK), smem, stream, pdl_enabled());
   TLB_CUDA(cudaLaunchKernelEx(&lc.cfg, attn_decode_kernel<D, HW, LPK, BF>, p));
@@ -479,7 +488,10 @@ int attn_decode_launch(DeviceCtx* c, const float* q, const void* K, const void* 
                        const unsigned* d_pos, float* partials, int* counters,
                        cudaStream_t stream, int early_kv, int kv_bf16) {
   if (D != 64 && D != 128) return set_error(TLB_ERR_UNSUPPORTED, "attn_decode: D must be 64 or 128");
-  if (n_kv <= 0 || n_q % n_kv != 0) return set_error(TLB_ERR_ARG, "attn_decode: n_q % n_kv != 0");
+  if (n_kv <= 0 || n_q <= 0 || n_q % n_kv != 0)
+    return set_error(TLB_ERR_ARG, "attn_decode: need n_q > 0, n_kv > 0 and n_q % n_kv == 0");
+  if (kv_max <= 0 || kv_max > (1ll << 30) || kv_max * D > (1ll << 40))
+    return set_error(TLB_ERR_ARG, "attn_decode: kv_max out of range");
   const int grp = n_q / n_kv;
   if (grp > 32) return set_error(TLB_ERR_UNSUPPORTED, "attn_decode: GQA group > 32");
   if (((uintptr_t)K & 15) || ((uintptr_t)V & 15) || ((uintptr_t)q & 15) || ((uintptr_t)out & 15))
@@ -487,7 +499,7 @@ int attn_decode_launch(DeviceCtx* c, const float* q, const void* K, const void* 
   AttnParams p;
   p.q = q; p.K = K; p.V = V; p.out = out; p.partials = partials; p.counters = counters;
   p.d_pos = d_pos; p.ctx = ctx; p.n_q = n_q; p.n_kv = n_kv; p.grp = grp;
-  p.kv_stride = kv_max * D; p.scale = scale; p.sm2 = attn_target(grp, c->sm_count); p.status = c->status; p.dbg = g_attn_dbg; p.early_kv = early_kv;
+  p.kv_stride = kv_max * D; p.kv_rows = (int)kv_max; p.scale = scale; p.sm2 = attn_target(grp, c->sm_count); p.status = c->status; p.dbg = g_attn_dbg; p.early_kv = early_kv;
   const int basis = d_pos ? (int)kv_max : ctx;
   const int splits = d_pos ? attn_splits_wanted(n_kv, basis, p.sm2)
                            : (ctx + attn_chunk(n_kv, ctx, p.sm2) - 1) / attn_chunk(n_kv, ctx, p.sm2);
@@ -565,6 +577,9 @@ extern "C" int tlb_attn_decode_noalloc(const float* q, const float* K, const flo
   TLB_REQUIRE(q && K && V && out, "tlb_attn_decode_noalloc: null pointer");
   TLB_REQUIRE(ctx >= 1 && ctx <= kv_max, "tlb_attn_decode_noalloc: need 1 <= ctx <= kv_max");
   TLB_REQUIRE(n_kv > 0 && n_kv <= 64, "tlb_attn_decode_noalloc: n_kv must be 1..64");
+  TLB_REQUIRE(n_q > 0 && n_q <= (1 << 24) && n_q % n_kv == 0,
+              "tlb_attn_decode_noalloc: need 0 < n_q <= 2^24 and n_q % n_kv == 0");
+  TLB_REQUIRE(kv_max <= (1ll << 30), "tlb_attn_decode_noalloc: kv_max out of range");
   TLB_REQUIRE(D == 64 || D == 128, "tlb_attn_decode_noalloc: D must be 64 or 128");
   int dev = 0;
   TLB_CUDA(cudaGetDevice(&dev));
@@ -582,9 +597,13 @@ extern "C" int tlb_attn_decode_noalloc(const float* q, const float* K, const flo
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
   // The array keeps whatever the previous call left: the counters must start at zero.
   TLB_CUDA(cudaMemsetAsync(nd->ptr, 0, NOALLOC_COUNTER_BYTES, s));
-  DeviceCtx local;  // only the SM count is read; no status block (bounded waits still return)
+  // Only the SM count and the status block are read.  The status block is the library's
+  // per-device one when some other call created it already (then an expired wait shows up
+  // in tlb_device_status); this call never creates it, because that would allocate.
+  DeviceCtx local;
   local.sm_count = nd->sm_count;
-  local.status = nullptr;
+  const DeviceCtx* existing = find_ctx();
+  local.status = existing ? existing->status : nullptr;
   return attn_decode_launch(&local, q, K, V, out, (int)n_q, (int)n_kv, (int)ctx, kv_max, (int)D,
                             scale, nullptr, (float*)((unsigned char*)nd->ptr + NOALLOC_COUNTER_BYTES),
                             (int*)nd->ptr, s, 0, 0);

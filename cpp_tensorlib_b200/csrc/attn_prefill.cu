@@ -212,11 +212,10 @@ static int launch_attn_prefill_t(DeviceCtx* c, const float* q, const void* K, co
   long long kv_stride = kv_max * D;
   const size_t smem = 4 * (size_t)PF_KT * D * (BF ? 2 : 4) + 64 + 128;
   LaunchCfg lc(dim3((T + PF_QT - 1) / PF_QT, n_q), dim3(PF_THREADS), smem, s, pdl_enabled());
-  static bool attr = false;
-  if (!attr) {
-    TLB_CUDA(cudaFuncSetAttribute(attn_prefill_kernel<D, BF>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                  100 * 1024));
-    attr = true;
+  static std::atomic<unsigned long long> attr_done{0};
+  {
+    const int rc_attr = ensure_dynamic_smem(attn_prefill_kernel<D, BF>, 100 * 1024, attr_done);
+    if (rc_attr) return rc_attr;
   }
   TLB_CUDA(cudaLaunchKernelEx(&lc.cfg, attn_prefill_kernel<D, BF>, q, K, V, out, T, kv_stride, group, scale,
                               pos0, c->status));

@@ -5,9 +5,13 @@
 // consumer so the transfer overlaps the producer's compute tile by tile:
 //   * the row-parallel GEMV stores every finished output element straight into the
 //     staging buffer of EVERY rank (its own included) as an 8-byte packet
-//     {value bits, sequence number + 1}.  An aligned 8-byte store arrives whole, so
-//     the packet validates itself: no fence, no separate flag, no completion
-//     counter -- the exchange costs one NVLink store latency after the last tile;
+//     {value bits, sequence number + 1}, written and read as ONE 64-bit access
+//     (st / ld .relaxed.sys.b64): a naturally aligned 64-bit scalar access is
+//     single-copy atomic in the PTX memory model (a two-element vector access is
+//     not -- it is modelled as two scalar accesses in unspecified order), so a
+//     reader sees the old packet or the new one, never a mix, and the packet
+//     validates itself: no fence, no separate flag, no completion counter -- the
+//     exchange costs one NVLink store latency after the last tile;
 //   * the following residual-add + RMSNorm kernel polls (bounded) each packet until
 //     its tag matches, sums the partials in rank order -- every rank adds the same
 //     numbers in the same order, so the replicated residual streams stay
@@ -39,28 +43,30 @@ struct CommDev {
 __device__ __forceinline__ unsigned comm_seq(const CommDev& c) {
   return *(volatile unsigned*)c.seq * (unsigned)c.E + (unsigned)c.k;
 }
+// packet = (tag << 32) | value bits, little endian: .x = value, .y = tag
 __device__ __forceinline__ void st_packet_sys(uint2* p, float v, unsigned tag) {
-  asm volatile("st.relaxed.sys.global.v2.u32 [%0], {%1, %2};" ::"l"(p), "r"(__float_as_uint(v)),
-               "r"(tag)
-               : "memory");
+  const unsigned long long w = ((unsigned long long)tag << 32) | (unsigned long long)__float_as_uint(v);
+  asm volatile("st.relaxed.sys.global.b64 [%0], %1;" ::"l"(p), "l"(w) : "memory");
 }
 __device__ __forceinline__ uint2 ld_packet_sys(const uint2* p) {
-  uint2 v;
-  asm volatile("ld.relaxed.sys.global.v2.u32 {%0, %1}, [%2];" : "=r"(v.x), "=r"(v.y) : "l"(p) : "memory");
-  return v;
+  unsigned long long w;
+  asm volatile("ld.relaxed.sys.global.b64 %0, [%1];" : "=l"(w) : "l"(p) : "memory");
+  return make_uint2((unsigned)(w & 0xffffffffull), (unsigned)(w >> 32));
 }
-// Poll a packet until its tag matches, at most ~1 s; on timeout the status block
-// is set, later waits give up at once, and the (stale) payload is returned.
+// Poll a packet until its tag matches, at most the wait limit of the status block (about
+// one second by default); on timeout the status block is set, later waits give up at
+// once, and the (stale) payload is returned.
 __device__ __forceinline__ uint2 wait_packet_bounded(const uint2* p, unsigned tag, int* status,
                                                      int where) {
   uint2 v = ld_packet_sys(p);
   if (v.y == tag) return v;
   const long long t0 = clock64();
+  const long long limit = wait_limit(status);
   while (true) {
     v = ld_packet_sys(p);
     if (v.y == tag) return v;
     if (status && *(volatile int*)&status[ST_WAIT_TIMEOUT]) return v;
-    if (clock64() - t0 > 2000000000ll) {
+    if (clock64() - t0 > limit) {
       if (status) {
         atomicExch(&status[ST_WAIT_TIMEOUT], 1);
         atomicExch(&status[ST_WAIT_WHERE], where);

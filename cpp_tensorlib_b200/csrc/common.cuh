@@ -7,6 +7,7 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include <atomic>
 #include <string>
 
 #include "../../include/tlb200.h"
@@ -15,7 +16,11 @@ namespace tlb {
 
 // status codes (TLB_OK, TLB_ERR_*) come from the public C header
 // Device status word indices (written by kernels whose bounded waits expire).
-enum : int { ST_WAIT_TIMEOUT = 0, ST_WAIT_WHERE = 1, ST_WORDS = 8 };
+// Words 2..3 hold the wait limit in clock64 ticks as one 64-bit value (set by the host,
+// read by a kernel only after a first unsuccessful poll); word 4 is set when a kernel
+// refused to touch a cache row at or beyond the cache's capacity.
+enum : int { ST_WAIT_TIMEOUT = 0, ST_WAIT_WHERE = 1, ST_WAIT_LIMIT = 2, ST_KV_OVERFLOW = 4, ST_WORDS = 8 };
+constexpr long long WAIT_LIMIT_DEFAULT = 2000000000ll;  // about one second at ~2 GHz
 
 int set_error(int code, const std::string& msg);
 int cuda_fail(cudaError_t e, const char* what);
@@ -62,6 +67,7 @@ struct DeviceCtx {
 };
 
 int get_ctx(DeviceCtx** out);  // context of the current device (created on first use)
+DeviceCtx* find_ctx();         // the same if it exists already, else NULL; allocates nothing
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
                                   const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
                                   const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
@@ -102,16 +108,24 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
       : "memory");
   return ok != 0;
 }
-// Bounded wait: gives up after about one second (clock64 at ~2 GHz), records where
+// The limit of every bounded wait, in clock64 ticks: the value the host stored in the
+// status block (tlb_set_wait_limit_cycles), about one second when there is no block.
+__device__ __forceinline__ long long wait_limit(const int* status) {
+  if (!status) return WAIT_LIMIT_DEFAULT;
+  const long long v = *(const volatile long long*)&status[ST_WAIT_LIMIT];
+  return v > 0 ? v : WAIT_LIMIT_DEFAULT;
+}
+// Bounded wait: gives up after the limit (about one second by default), records where
 // in the status block and returns false; the caller must then skip the work that
 // depended on it.
 __device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, uint32_t parity, int* status,
                                                   int where) {
   if (mbar_try_wait(bar, parity)) return true;
   const long long t0 = clock64();
+  const long long limit = wait_limit(status);
   while (true) {
     if (mbar_try_wait(bar, parity)) return true;
-    if (clock64() - t0 > 2000000000ll) break;
+    if (clock64() - t0 > limit) break;
   }
   if (status) {
     atomicExch(&status[ST_WAIT_TIMEOUT], 1);
@@ -182,5 +196,19 @@ struct LaunchCfg {
 };
 
 bool pdl_enabled();  // process-wide switch (tlb_set_pdl)
+
+// cudaFuncAttributeMaxDynamicSharedMemorySize is a per-device attribute of a kernel:
+// set it the first time the kernel is launched on each device of the process.  `done`
+// is one bit per device ordinal, owned by the caller (one per kernel instantiation).
+template <typename Kernel>
+int ensure_dynamic_smem(Kernel kernel, int bytes, std::atomic<unsigned long long>& done) {
+  int dev = 0;
+  TLB_CUDA(cudaGetDevice(&dev));
+  const bool tracked = dev >= 0 && dev < 64;
+  if (tracked && ((done.load(std::memory_order_acquire) >> dev) & 1ull)) return TLB_OK;
+  TLB_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes));
+  if (tracked) done.fetch_or(1ull << dev, std::memory_order_release);
+  return TLB_OK;
+}
 
 }  // namespace tlb

@@ -17,6 +17,7 @@
 // their local argmax keys.  Each rank is one process on one GPU.
 #include <cstdlib>
 #include <cstring>
+#include <string>
 #include <vector>
 
 #include "comm.cuh"
@@ -60,7 +61,7 @@ int launch_add_rmsnorm_ar(const float*, const float*, float*, float*, int, float
 int launch_swiglu(const float*, float*, int, int, cudaStream_t);
 int launch_incr_u32(unsigned*, cudaStream_t);
 int launch_qkv_post(float*, const float*, const float*, const float*, float*, float*, int, int,
-                    int, const unsigned*, long long, float, cudaStream_t);
+                    int, const unsigned*, long long, float, int*, cudaStream_t);
 int launch_embed_gather(const float*, const int*, float*, int, float2*, const unsigned*, int, float,
                         const float*, float*, float, cudaStream_t);
 int launch_argmax(DeviceCtx*, const float*, int, int*, int*, cudaStream_t);
@@ -108,13 +109,35 @@ struct Decoder {
   void* peer_stage_base[TP_MAX] = {};
   void* peer_flags_base[TP_MAX] = {};
   bool peers_open = false;
+  void* sink[TP_MAX] = {};          // loopback drill: stand-ins for peers that never answer
   // batched prompt pass: row-batched scratch for chunks of up to PF_CHUNK tokens
   float* pf = nullptr;
   int* pf_ids = nullptr;
   // graph
   cudaGraphExec_t graph = nullptr;
   long long launches_per_token = 0;
+  // Host mirror of the device-resident position (captured_decoder::cur_pos of the reference,
+  // bench/cuda/qwen_model.h:877-885): every entry point that advances the sequence checks it
+  // against the cache capacity before anything is launched.
+  long long host_pos = 0;
+  long long vocab_total = 0;   // rows of the embedding table (0: unknown, ids are only checked >= 0)
 };
+
+// The reference's feed() returns false when cur_pos >= max_ctx (bench/cuda/qwen_model.h:879);
+// here the refusal is an argument error and nothing is launched.
+static int room_for(Decoder* d, long long n, const char* who) {
+  if (d->host_pos + n > d->max_ctx)
+    return set_error(TLB_ERR_ARG, std::string(who) + ": position " + std::to_string(d->host_pos) + " + " +
+                                      std::to_string(n) + " token(s) exceeds the cache capacity " +
+                                      std::to_string(d->max_ctx));
+  return TLB_OK;
+}
+static int token_ok(Decoder* d, long long token, const char* who) {
+  if (token < 0 || (d->vocab_total > 0 && token >= d->vocab_total))
+    return set_error(TLB_ERR_ARG, std::string(who) + ": token id " + std::to_string(token) +
+                                      " outside the embedding table");
+  return TLB_OK;
+}
 
 static int set_linear(Linear& L, const void* q4, int K, int N, int pair_h = 0) {
   L.q4 = q4;
@@ -171,7 +194,8 @@ static PairEpi qkv_epilogue(const Decoder* d, const DecLayer& L) {
   PairEpi e;
   e.kind = 2; e.H = d->hd / 2; e.out = d->qkv; e.Kc = L.Kc; e.Vc = L.Vc;
   e.bq = L.bq; e.bk = L.bk; e.bv = L.bv; e.n_q = d->n_q; e.n_kv = d->n_kv; e.D = d->hd;
-  e.d_pos = d->d_pos; e.kv_stride = (long long)d->max_ctx * d->hd; e.base = d->rope_base;
+  e.d_pos = d->d_pos; e.kv_stride = (long long)d->max_ctx * d->hd; e.kv_rows = d->max_ctx;
+  e.base = d->rope_base;
   e.rope_cs = d->rope_cs;
   return e;
 }
@@ -241,7 +265,7 @@ static int forward(Decoder* d, cudaStream_t s) {
       }
       if (!pq)
         RUN(launch_qkv_post(d->qkv, L.bq, L.bk, L.bv, L.Kc, L.Vc, d->n_q, d->n_kv, d->hd, d->d_pos,
-                            d->max_ctx, d->rope_base, s));
+                            d->max_ctx, d->rope_base, c->status, s));
       RUN(attn_decode_launch(c, d->qkv, L.Kc, L.Vc, d->att, d->n_q, d->n_kv, 0, d->max_ctx, d->hd,
                              d->scale, d->d_pos, (float*)((char*)d->attn_partials + 256),
                              (int*)d->attn_partials, s, 1, 0));
@@ -278,7 +302,7 @@ static int forward(Decoder* d, cudaStream_t s) {
     RUN(run_linear(c, L.wqkv, d->hb, d->qkv, s, nullptr, 0, nullptr, 0.f, pq));
     if (!pq)
       RUN(launch_qkv_post(d->qkv, L.bq, L.bk, L.bv, L.Kc, L.Vc, d->n_q, d->n_kv, d->hd, d->d_pos,
-                          d->max_ctx, d->rope_base, s));
+                          d->max_ctx, d->rope_base, c->status, s));
     RUN(attn_decode_launch(c, d->qkv, L.Kc, L.Vc, d->att, d->n_q, d->n_kv, 0, d->max_ctx, d->hd,
                            d->scale, d->d_pos, (float*)((char*)d->attn_partials + 256),
                            (int*)d->attn_partials, s, 1, 0));
@@ -334,6 +358,9 @@ int tlb_decoder_create(const int64_t* cfg, int n_cfg, float eps, float rope_base
   d->hidden = (int)cfg[0]; d->n_layers = (int)cfg[1]; d->n_q = (int)cfg[2]; d->n_kv = (int)cfg[3];
   d->hd = (int)cfg[4]; d->ff = (int)cfg[5]; d->vocab = (int)cfg[6]; d->max_ctx = (int)cfg[7];
   d->tp_rank = (int)cfg[8]; d->tp_size = (int)cfg[9]; d->vocab_offset = (unsigned)cfg[10];
+  // cfg[11] (optional): rows of the embedding table; without it a single-GPU decoder knows it
+  // from its own vocabulary, a tensor-parallel shard does not
+  d->vocab_total = n_cfg >= 12 ? cfg[11] : (d->tp_size == 1 ? d->vocab : 0);
   d->eps = eps; d->rope_base = rope_base; d->scale = 1.0f / sqrtf((float)d->hd);
   TLB_REQUIRE(d->hd == 64 || d->hd == 128, "tlb_decoder_create: head_dim must be 64 or 128");
   TLB_REQUIRE(d->n_kv > 0 && d->n_q % d->n_kv == 0 && d->n_kv <= 64, "tlb_decoder_create: bad head counts");
@@ -405,6 +432,7 @@ int tlb_decoder_destroy(void* h) {
   float* bufs[] = {d->x, d->xb, d->t1, d->hb, d->qkv, d->att, d->t0, d->gu, d->mb, d->logits};
   for (float* b : bufs) cudaFree(b);
   cudaFree(d->stage_local);
+  for (void* sk : d->sink) cudaFree(sk);
   cudaFree(d->rope_cs);
   cudaFree(d->pf); cudaFree(d->pf_ids);
   cudaFree(d->attn_partials); cudaFree(d->d_pos); cudaFree(d->d_tok); cudaFree(d->flags_local);
@@ -475,11 +503,16 @@ int tlb_decoder_set_pos(void* h, int64_t pos, void* stream) {
   d->h_tok[8] = (int)pos;
   TLB_CUDA(cudaMemcpyAsync(d->d_pos, &d->h_tok[8], 4, cudaMemcpyHostToDevice, (cudaStream_t)stream));
   TLB_CUDA(cudaStreamSynchronize((cudaStream_t)stream));
+  d->host_pos = pos;
   return TLB_OK;
 }
 int tlb_decoder_set_token(void* h, int64_t token, void* stream) {
   auto* d = (Decoder*)h;
-  TLB_REQUIRE(d && token >= 0, "tlb_decoder_set_token: bad token");
+  TLB_REQUIRE(d, "tlb_decoder_set_token: null decoder");
+  {
+    const int rc = token_ok(d, token, "tlb_decoder_set_token");
+    if (rc) return rc;
+  }
   d->h_tok[0] = (int)token;
   TLB_CUDA(cudaMemcpyAsync(d->d_tok, d->h_tok, 4, cudaMemcpyHostToDevice, (cudaStream_t)stream));
   TLB_CUDA(cudaStreamSynchronize((cudaStream_t)stream));
@@ -491,7 +524,11 @@ int tlb_decoder_set_token(void* h, int64_t token, void* stream) {
 int tlb_decoder_forward(void* h, void* stream) {
   auto* d = (Decoder*)h;
   TLB_REQUIRE(d, "tlb_decoder_forward: null decoder");
-  return forward(d, (cudaStream_t)stream);
+  int rc = room_for(d, 1, "tlb_decoder_forward");
+  if (rc) return rc;
+  rc = forward(d, (cudaStream_t)stream);
+  if (!rc) d->host_pos++;
+  return rc;
 }
 int64_t tlb_decoder_launches_per_token(void* h) {
   auto* d = (Decoder*)h;
@@ -524,7 +561,13 @@ int tlb_decoder_capture(void* h) {
 int tlb_decoder_run(void* h, int64_t n, void* stream) {
   auto* d = (Decoder*)h;
   TLB_REQUIRE(d && d->graph, "tlb_decoder_run: capture the decoder first");
-  for (int64_t i = 0; i < n; i++) TLB_CUDA(cudaGraphLaunch(d->graph, (cudaStream_t)stream));
+  TLB_REQUIRE(n >= 0, "tlb_decoder_run: negative token count");
+  const int rc = room_for(d, n, "tlb_decoder_run");
+  if (rc) return rc;
+  for (int64_t i = 0; i < n; i++) {
+    TLB_CUDA(cudaGraphLaunch(d->graph, (cudaStream_t)stream));
+    d->host_pos++;
+  }
   return TLB_OK;
 }
 
@@ -535,6 +578,11 @@ int tlb_decoder_step(void* h, const int32_t* token_in, int32_t* token_out, void*
   auto* d = (Decoder*)h;
   TLB_REQUIRE(d && token_out, "tlb_decoder_step: bad arguments");
   cudaStream_t s = (cudaStream_t)stream;
+  {
+    int rc = room_for(d, 1, "tlb_decoder_step");
+    if (!rc && token_in && *token_in >= 0) rc = token_ok(d, *token_in, "tlb_decoder_step");
+    if (rc) return rc;
+  }
   if (token_in && *token_in >= 0) {
     d->h_tok[0] = *token_in;
     TLB_CUDA(cudaMemcpyAsync(d->d_tok, d->h_tok, 4, cudaMemcpyHostToDevice, s));
@@ -544,6 +592,7 @@ int tlb_decoder_step(void* h, const int32_t* token_in, int32_t* token_out, void*
     int rc = forward(d, s);
     if (rc) return rc;
   }
+  d->host_pos++;
   TLB_CUDA(cudaMemcpyAsync(d->h_out, d->d_tok_out, 4, cudaMemcpyDeviceToHost, s));
   TLB_CUDA(cudaStreamSynchronize(s));
   *token_out = d->h_out[0];
@@ -574,8 +623,10 @@ int tlb_decoder_prefill(void* h, const int32_t* tokens, int64_t T, int32_t* next
   TLB_CUDA(cudaStreamSynchronize(s));
   if ((long long)pos0 + T > d->max_ctx)
     return set_error(TLB_ERR_ARG, "tlb_decoder_prefill: the prompt does not fit the cache");
-  for (int64_t i = 0; i < T; i++)
-    if (tokens[i] < 0) return set_error(TLB_ERR_ARG, "tlb_decoder_prefill: negative token id");
+  for (int64_t i = 0; i < T; i++) {
+    rc = token_ok(d, tokens[i], "tlb_decoder_prefill");
+    if (rc) return rc;
+  }
   // row-batched scratch, carved from one allocation
   const size_t n_emb = (size_t)CH * E, n_qkv = (size_t)CH * QKV, n_att = (size_t)CH * NQ * D,
                n_gu = (size_t)CH * 2 * FF, n_mb = (size_t)CH * FF;
@@ -645,6 +696,7 @@ int tlb_decoder_prefill(void* h, const int32_t* tokens, int64_t T, int32_t* next
   TLB_CUDA(cudaMemcpyAsync(d->d_pos, &d->h_tok[1], 4, cudaMemcpyHostToDevice, s));
   TLB_CUDA(cudaMemcpyAsync(d->h_out, d->d_tok_out, 4, cudaMemcpyDeviceToHost, s));
   TLB_CUDA(cudaStreamSynchronize(s));
+  d->host_pos = (long long)newpos;
   if (next_token) *next_token = d->h_out[0];
   return TLB_OK;
 }
@@ -684,6 +736,26 @@ int tlb_decoder_ipc_open(void* h, const void* records) {
     d->comm.stage[r] = (uint2*)d->peer_stage_base[r];
   }
   d->peers_open = true;
+  return TLB_OK;
+}
+
+// Fault drill on ONE GPU: wire a tensor-parallel rank to peers that never answer.  Every other
+// rank's staging pointer is aimed at a private, zeroed sink of the right size in this GPU's own
+// memory, so the rank's pushes land somewhere harmless and nobody ever writes the packets it
+// polls for: its next exchange runs into the bounded wait, the kernels return, and
+// tlb_device_status reports TLB_ERR_DEVICE_WAIT.  Nothing faults or hangs.
+int tlb_decoder_loopback_peers(void* h) {
+  auto* d = (Decoder*)h;
+  TLB_REQUIRE(d, "tlb_decoder_loopback_peers: null decoder");
+  if (d->peers_open) return set_error(TLB_ERR_STATE, "tlb_decoder_loopback_peers: real peers are open already");
+  const size_t sb = (size_t)2 * d->tp_size * d->comm.slot_floats * sizeof(uint2);
+  for (int r = 0; r < d->tp_size; r++) {
+    if (r == d->tp_rank) continue;
+    if (!d->sink[r]) TLB_CUDA(cudaMalloc(&d->sink[r], sb));
+    TLB_CUDA(cudaMemset(d->sink[r], 0, sb));
+    d->comm.stage[r] = (uint2*)d->sink[r];
+  }
+  TLB_CUDA(cudaDeviceSynchronize());
   return TLB_OK;
 }
 

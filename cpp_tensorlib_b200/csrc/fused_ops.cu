@@ -114,12 +114,16 @@ __global__ void rope_kernel(const float* x, const float* __restrict__ bias, floa
 __global__ void kv_append_kernel(void* __restrict__ Kc, void* __restrict__ Vc,
                                  const float* __restrict__ k, const float* __restrict__ v,
                                  unsigned pos, const unsigned* __restrict__ d_pos,
-                                 long long kv_stride, int D, int bf) {
+                                 long long kv_stride, int D, int bf, int* status) {
   pdl_wait();
   pdl_launch_dependents();
   const unsigned p0 = d_pos ? *d_pos : pos;
   const int h = blockIdx.x, d = threadIdx.x;
   if (d >= D) return;
+  if ((long long)p0 * D >= kv_stride) {   // row beyond the cache: refuse, tell the host
+    if (status && d == 0) atomicExch(&status[ST_KV_OVERFLOW], 1);
+    return;
+  }
   const size_t dst = (size_t)h * kv_stride + (size_t)p0 * D + d;
   if (bf) {
     ((__nv_bfloat16*)Kc)[dst] = __float2bfloat16_rn(k[h * D + d]);
@@ -146,12 +150,16 @@ __global__ void qkv_post_kernel(float* qkv, const float* __restrict__ bq,
                                 const float* __restrict__ bk, const float* __restrict__ bv,
                                 float* __restrict__ Kc, float* __restrict__ Vc, int n_q, int n_kv,
                                 int D, const unsigned* __restrict__ d_pos, long long kv_stride,
-                                float base) {
+                                float base, int* status) {
   pdl_wait();
   pdl_launch_dependents();
   const int b = blockIdx.x, j = threadIdx.x, half = D >> 1;
   if (j >= half) return;
   const unsigned pos = *d_pos;
+  if ((long long)pos * D >= kv_stride) {   // the cache is full: refuse, tell the host
+    if (status && j == 0) atomicExch(&status[ST_KV_OVERFLOW], 1);
+    return;
+  }
   if (b < n_q) {
     rope_pair(qkv, bq, qkv, (size_t)b * D, j, half, D, pos, base);
   } else if (b < n_q + n_kv) {
@@ -458,10 +466,11 @@ int launch_rope(const float* x, const float* bias, float* out, int rows, int T, 
   return TLB_OK;
 }
 int launch_kv_append(void* Kc, void* Vc, const float* k, const float* v, unsigned pos,
-                     const unsigned* d_pos, long long kv_max, int n_kv, int D, int bf, cudaStream_t s) {
+                     const unsigned* d_pos, long long kv_max, int n_kv, int D, int bf, int* status,
+                     cudaStream_t s) {
   LaunchCfg lc(dim3(n_kv), dim3(D), 0, s, pdl_enabled());
   long long kv_stride = kv_max * D;
-  TLB_CUDA(cudaLaunchKernelEx(&lc.cfg, kv_append_kernel, Kc, Vc, k, v, pos, d_pos, kv_stride, D, bf));
+  TLB_CUDA(cudaLaunchKernelEx(&lc.cfg, kv_append_kernel, Kc, Vc, k, v, pos, d_pos, kv_stride, D, bf, status));
   return TLB_OK;
 }
 int launch_incr_u32(unsigned* p, cudaStream_t s) {
@@ -471,11 +480,11 @@ int launch_incr_u32(unsigned* p, cudaStream_t s) {
 }
 int launch_qkv_post(float* qkv, const float* bq, const float* bk, const float* bv, float* Kc,
                     float* Vc, int n_q, int n_kv, int D, const unsigned* d_pos, long long kv_max,
-                    float base, cudaStream_t s) {
+                    float base, int* status, cudaStream_t s) {
   LaunchCfg lc(dim3(n_q + 2 * n_kv), dim3(D / 2), 0, s, pdl_enabled());
   long long kv_stride = kv_max * D;
   TLB_CUDA(cudaLaunchKernelEx(&lc.cfg, qkv_post_kernel, qkv, bq, bk, bv, Kc, Vc, n_q, n_kv, D,
-                              d_pos, kv_stride, base));
+                              d_pos, kv_stride, base, status));
   return TLB_OK;
 }
 int launch_embed_gather(const float* embed, const int* d_tok, float* x, int n, float2* rope_cs,

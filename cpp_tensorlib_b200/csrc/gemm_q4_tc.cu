@@ -335,11 +335,10 @@ int gemm_q4_tc_launch(DeviceCtx* c, const float* x, long long ldx, int M, const 
             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
       return set_error(TLB_ERR_CUDA, "gemm_q4_tc: tensor map (scales) encode failed");
   }
-  static bool attr = false;
-  if (!attr) {
-    TLB_CUDA(cudaFuncSetAttribute(gemm_q4_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                  227 * 1024));
-    attr = true;
+  static std::atomic<unsigned long long> attr_done{0};
+  {
+    const int rc_attr = ensure_dynamic_smem(gemm_q4_tc_kernel, 227 * 1024, attr_done);
+    if (rc_attr) return rc_attr;
   }
   for (int m0 = 0; m0 < M; m0 += TC_MT_MAX) {
     int Mt = M - m0 < TC_MT_MAX ? M - m0 : TC_MT_MAX;

@@ -65,10 +65,10 @@ int launch_gemv_bf16_row(DeviceCtx* c, const float* a, const void* W, float* y, 
                          cudaStream_t s) {
   const size_t smem = (size_t)K * sizeof(float);
   if (smem > 200 * 1024) return set_error(TLB_ERR_UNSUPPORTED, "gemv_bf16_row: K too large for the activation stage");
-  static bool attr = false;
-  if (!attr) {
-    TLB_CUDA(cudaFuncSetAttribute(gemv_bf16_row_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
-    attr = true;
+  static std::atomic<unsigned long long> attr_done{0};
+  {
+    const int rc_attr = ensure_dynamic_smem(gemv_bf16_row_kernel, 200 * 1024, attr_done);
+    if (rc_attr) return rc_attr;
   }
   int ctas = c->sm_count * 4;
   const int need = (N + GB_WARPS - 1) / GB_WARPS;

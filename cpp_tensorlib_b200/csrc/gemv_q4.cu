@@ -541,11 +541,10 @@ bool gemv_q4_tma_eligible(const void* qw, const void* scales, int N, int K, int 
 template <int NT, int WARPS, int STAGES, bool M1>
 static int gemv_launch_t(const CUtensorMap& tmW, const CUtensorMap& tmS, const GemvParams& p,
                          int ctas, size_t smem, cudaStream_t stream) {
-  static bool attr = false;
-  if (!attr) {
-    TLB_CUDA(cudaFuncSetAttribute(gemv_q4_mma_kernel<NT, WARPS, STAGES, M1>,
-                                  cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
-    attr = true;
+  static std::atomic<unsigned long long> attr_done{0};
+  {
+    const int rc_attr = ensure_dynamic_smem(gemv_q4_mma_kernel<NT, WARPS, STAGES, M1>, 227 * 1024, attr_done);
+    if (rc_attr) return rc_attr;
   }
   LaunchCfg lc(dim3(ctas), dim3(WARPS * 32), smem, stream, pdl_enabled());
   TLB_CUDA(cudaLaunchKernelEx(&lc.cfg, gemv_q4_mma_kernel<NT, WARPS, STAGES, M1>, tmW, tmS, p));

@@ -464,6 +464,12 @@ __global__ void __launch_bounds__(PK_WARPS * 32, 1) gemv_q4p_kernel(GemvPParams 
     const int half = p.epi.D >> 1, D = p.epi.D;
     const int h = pi / half, j = pi - h * half;
     const unsigned pos = *p.epi.d_pos;
+    if (pos >= (unsigned)p.epi.kv_rows) {
+      // the cache is full: write nothing (the attention that follows refuses the position
+      // too) and tell the host through the status block
+      if (p.status) atomicExch(&p.status[ST_KV_OVERFLOW], 1);
+      return;
+    }
     if (h >= p.epi.n_q + p.epi.n_kv) {
       const int kh = h - p.epi.n_q - p.epi.n_kv;
       if (p.epi.bv) { a += p.epi.bv[kh * D + j]; b += p.epi.bv[kh * D + j + half]; }
@@ -698,11 +704,10 @@ bool gemv_q4p_supported(long long N, long long K) {
 
 template <int STAGES, bool PULL, bool OWN, int EPI>
 static int gemvp_launch_t(const GemvPParams& p, int ctas, size_t smem, cudaStream_t stream) {
-  static bool attr = false;
-  if (!attr) {
-    TLB_CUDA(cudaFuncSetAttribute(gemv_q4p_kernel<STAGES, PULL, OWN, EPI>,
-                                  cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024));
-    attr = true;
+  static std::atomic<unsigned long long> attr_done{0};
+  {
+    const int rc_attr = ensure_dynamic_smem(gemv_q4p_kernel<STAGES, PULL, OWN, EPI>, 227 * 1024, attr_done);
+    if (rc_attr) return rc_attr;
   }
   LaunchCfg lc(dim3(ctas), dim3(PK_WARPS * 32), smem, stream, pdl_enabled());
   TLB_CUDA(cudaLaunchKernelEx(&lc.cfg, gemv_q4p_kernel<STAGES, PULL, OWN, EPI>, p));

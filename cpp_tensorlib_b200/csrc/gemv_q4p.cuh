@@ -19,6 +19,7 @@ struct PairEpi {
   int n_q = 0, n_kv = 0, D = 0;
   const unsigned* d_pos = nullptr;
   long long kv_stride = 0;
+  int kv_rows = 0;               // capacity of the caches in rows: a position at or beyond it is refused
   float base = 0.f;
   const float2* rope_cs = nullptr;  // optional [D/2] (cos, sin) of position *d_pos
 };

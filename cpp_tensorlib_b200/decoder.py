@@ -8,11 +8,12 @@ run_layers_ :673-740, captured_decoder :791-905); the reference is single-device
 so the shard plan and the exchange wiring have no counterpart there.
 """
 import ctypes as C
+import time
 
 import numpy as np
 import torch
 
-from ._lib import check, lib
+from ._lib import TlbError, check, lib
 from .cuda import Q4Weight, q4_bytes, to_q4
 
 LINEAR = dict(wqkv=0, wo=1, wgu=2, wd=3, lm_head=4)
@@ -126,6 +127,25 @@ def shard_vector(name, v, cfg, plan):
     return v
 
 
+def host_barrier(store, name, rank, world, timeout_s=60.0, poll_s=0.01):
+    """Arrival check of the tensor-parallel ranks on the HOST, before anything that would make
+    their GPUs wait for one another is launched: every rank posts a key in the c10d store and
+    polls for the others'.  A rank that died, hung or never started is reported by the ranks
+    that did arrive as a ``TlbError`` naming it, after `timeout_s`, instead of a device-side
+    spin on a peer that will never write.  (The device-side waits are bounded too; this check
+    keeps them from being reached.)"""
+    store.set(f"{name}/{rank}", b"1")
+    deadline = time.monotonic() + timeout_s
+    while True:
+        missing = [r for r in range(world) if not store.check([f"{name}/{r}"])]
+        if not missing:
+            return
+        if time.monotonic() > deadline:
+            raise TlbError(f"host barrier '{name}': rank(s) {missing} of {world} did not arrive "
+                           f"within {timeout_s:.1f} s")
+        time.sleep(poll_s)
+
+
 class Q4Decoder:
     """Handle on the native decoder.  Weights are device tensors kept alive here
     (the native side borrows their pointers)."""
@@ -134,11 +154,11 @@ class Q4Decoder:
         self.cfg, self.max_ctx, self.tp_rank, self.tp_size = dict(cfg), max_ctx, tp_rank, tp_size
         self.plan = shard_plan(cfg, tp_size, tp_rank)
         p = self.plan
-        arr = (C.c_int64 * 11)(cfg["hidden"], cfg["layers"], p["n_q"], p["n_kv"], cfg["hd"],
+        arr = (C.c_int64 * 12)(cfg["hidden"], cfg["layers"], p["n_q"], p["n_kv"], cfg["hd"],
                                p["ff_local"], p["vocab_local"], max_ctx, tp_rank, tp_size,
-                               p["vocab"][0])
+                               p["vocab"][0], cfg["vocab"])
         self.h = C.c_void_p()
-        check(lib().tlb_decoder_create(arr, 11, cfg["eps"], cfg["rope_base"], C.byref(self.h)))
+        check(lib().tlb_decoder_create(arr, 12, cfg["eps"], cfg["rope_base"], C.byref(self.h)))
         self._keep = {}
         self.captured = False
 
@@ -192,12 +212,16 @@ class Q4Decoder:
         return _as_tensor(p.value, (self.plan["vocab_local"],))
 
     # ---- tensor-parallel wiring ------------------------------------------------
-    def connect(self, group=None):
+    def connect(self, group=None, store=None, timeout_s=60.0):
         """Exchange the ranks' 128-byte records over torch.distributed and open the
-        peers' exchange buffers."""
+        peers' exchange buffers.  With a c10d `store` the ranks first meet in a host
+        barrier with a timeout (`host_barrier`), so a missing rank is an error here and
+        not a hang in the collective."""
         if self.tp_size == 1:
             return
         import torch.distributed as dist
+        if store is not None:
+            host_barrier(store, "tlb_connect", self.tp_rank, self.tp_size, timeout_s)
         rec = (C.c_ubyte * 128)()
         check(lib().tlb_decoder_ipc_export(self.h, rec))
         mine = torch.tensor(list(bytes(rec)), dtype=torch.uint8, device="cuda")

@@ -41,6 +41,10 @@ int tlb_version(void);
 /* Bounded device-side waits record a timeout here instead of hanging:
  * out[0] = 1 when any wait expired since the last clear, out[1] = where. */
 int tlb_device_status(int* out2, int clear);
+/* The limit of those waits in GPU clock ticks (clock64) for the current device;
+ * default 2e9, about one second.  No counterpart in the reference, whose kernels never
+ * wait on one another.  Synchronises the device. */
+int tlb_set_wait_limit_cycles(int64_t cycles);
 int tlb_set_pdl(int enabled);               /* programmatic dependent launch on/off (default on) */
 
 int tlb_alloc(int64_t bytes, void** dptr);  /* cu.h:586-603 alloc */
@@ -185,7 +189,12 @@ int tlb_graph_destroy(void* graph_exec);    /* graph_destroy */
  * (run_layers_) and qm:791-905 (captured_decoder) with every linear in the q4
  * layout, plus the tensor-parallel path the reference does not have.
  * cfg[0..10] = hidden, n_layers, n_q, n_kv, head_dim, ff, vocab, max_ctx (sizes
- * local to the rank, hidden global), tp_rank, tp_size, vocab_offset. */
+ * local to the rank, hidden global), tp_rank, tp_size, vocab_offset; optional cfg[11] =
+ * rows of the embedding table (token ids are checked against it).
+ * Capacity: set_pos / forward / run / step / prefill keep a host mirror of the position and
+ * refuse (TLB_ERR_ARG, nothing launched) to advance past max_ctx, as captured_decoder::feed
+ * does (qm:877-885).  A graph replayed behind the library's back is caught on the device:
+ * the append epilogue and the attention skip the row and tlb_device_status reports it. */
 int tlb_decoder_create(const int64_t* cfg, int n_cfg, float eps, float rope_base, void** out);
 int tlb_decoder_destroy(void* dec);
 /* which: 0 wqkv 1 wo 2 wgu 3 wd 4 lm_head; q4 = device pointer, borrowed (qm:85-153). */
@@ -212,6 +221,10 @@ int tlb_decoder_prefill(void* dec, const int32_t* tokens, int64_t T, int32_t* ne
  * channel, and every rank opens the others' exchange buffers. */
 int tlb_decoder_ipc_export(void* dec, void* record128);
 int tlb_decoder_ipc_open(void* dec, const void* records);
+/* Fault drill on one GPU (no counterpart in the reference): aim every peer's staging pointer
+ * at a private sink nobody writes, so the rank's next exchange runs into its bounded wait
+ * and tlb_device_status reports TLB_ERR_DEVICE_WAIT; nothing faults or hangs. */
+int tlb_decoder_loopback_peers(void* dec);
 
 #ifdef __cplusplus
 }

@@ -141,6 +141,86 @@ def test_seven_billion_shape_one_layer_prefilled(port):
     d.close(); o.close()
 
 
+def big_weights(cfg, seed):
+    """Random-init weights of a full-width decoder from numpy's Philox stream (the counter-based
+    generator of synth.py needs minutes for the 1.5 G values of a 7B-shape vocabulary); the same
+    arrays feed the oracle and the GPU, so only determinism inside one process matters."""
+    rng = np.random.Generator(np.random.Philox(seed))
+    E, HD, NQ, NKV, FF, V = cfg["hidden"], cfg["hd"], cfg["n_q"], cfg["n_kv"], cfg["ff"], cfg["vocab"]
+    f = lambda *shape: rng.standard_normal(shape, dtype=np.float32) * np.float32(0.02)
+    w = {"embed": f(V, E), "onorm": 1 + f(E), "lm_head": f(E, V), "layers": []}
+    for _ in range(cfg["layers"]):
+        w["layers"].append(dict(wqkv=f(E, (NQ + 2 * NKV) * HD), wo=f(NQ * HD, E), wgu=f(E, 2 * FF), wd=f(FF, E),
+                                bq=f(NQ * HD), bk=f(NKV * HD), bv=f(NKV * HD), an=1 + f(E), fn=1 + f(E)))
+    return w, rng
+
+
+def test_seven_billion_shape_two_layers_full_vocabulary(port):
+    """BASELINE config 5's shape with 2 of its 28 layers and the FULL 152064-row vocabulary and
+    embedding table, both caches pre-filled to ctx 4096 with N(0,1): 10 greedy steps at
+    positions 4096.. against the oracle -- logits within rtol/atol 1e-3 and identical ids at every
+    step, then the same ids again from the device-resident feedback loop (one graph replay per
+    token, the path the benchmark times)."""
+    cfg = dict(cases.QWEN7, layers=2)
+    wts, rng = big_weights(cfg, 4)
+    d, _ = make(cfg, 4, 4200, wts)
+    o = port_decoder(port, cfg, wts, 4200)
+    for l in range(2):
+        K = rng.standard_normal((4, 4096, 128), dtype=np.float32)
+        V = rng.standard_normal((4, 4096, 128), dtype=np.float32)
+        d.fill_kv(l, torch.from_numpy(K).cuda(), torch.from_numpy(V).cuda())
+        o.fill_kv(l, K, V)
+    d.set_pos(4096)
+    d.capture()
+    tok, ids = 7, []
+    for i in range(10):
+        nxt = d.step(tok)
+        want, lg = o.step(tok, 4096 + i)
+        assert np.allclose(d.logits().cpu().numpy(), lg, rtol=1e-3, atol=1e-3), i
+        assert nxt == want, i
+        ids.append(nxt)
+        tok = nxt
+    d.set_pos(4096)
+    d.set_token(7)
+    d.run(10)
+    assert d.last_token() == ids[-1]
+    d.close(); o.close()
+
+
+def test_decoder_refuses_to_run_past_its_cache():
+    """The capacity guard (captured_decoder::feed returns false at cur_pos >= max_ctx,
+    bench/cuda/qwen_model.h:877-885): a step, a run or a prompt that would move the position past
+    max_ctx is refused on the host before anything is launched, and so is a token id outside the
+    embedding table.  Nothing here overruns the cache on the device."""
+    from cpp_tensorlib_b200 import TlbError, lib
+    cfg = cases.TINY64
+    d, _ = make(cfg, 22, 16)
+    d.set_pos(14)
+    d.capture()
+    t = d.step(5)                      # position 14 -> 15
+    t = d.step(t)                      # position 15 -> 16 == capacity: the cache is full now
+    with pytest.raises(TlbError, match="capacity"):
+        d.step(t)
+    with pytest.raises(TlbError, match="capacity"):
+        d.run(1)
+    with pytest.raises(TlbError, match="capacity"):
+        d.forward()
+    d.set_pos(10)
+    with pytest.raises(TlbError, match="capacity"):
+        d.run(7)                       # 10 + 7 > 16: refused as a whole, nothing launched
+    d.run(6)
+    with pytest.raises(TlbError, match="embedding"):
+        d.set_pos(0); d.step(cfg["vocab"])
+    with pytest.raises(TlbError, match="embedding"):
+        d.set_token(cfg["vocab"] + 5)
+    with pytest.raises(TlbError):
+        d.set_pos(0); d.prefill([1] * 17)
+    torch.cuda.synchronize()
+    st = (__import__("ctypes").c_int * 2)()
+    assert lib().tlb_device_status(st, 0) == 0     # the device never saw an out-of-range position
+    d.close()
+
+
 def test_decoder_argument_errors():
     from cpp_tensorlib_b200 import TlbError
     from cpp_tensorlib_b200.decoder import Q4Decoder
@@ -185,3 +265,43 @@ def test_batched_prefill_matches_token_by_token(cfg, seed, T):
         t2 = d2.step(t2); b.append(t2)
     assert a == b
     d1.close(); d2.close()
+
+
+def test_bounded_device_wait_expires_and_the_device_stays_usable(port):
+    """Failure detection without a GPU fault: a tensor-parallel rank whose peers never answer.
+    The rank (tp_size 2, rank 0) is wired to a sink nobody writes (tlb_decoder_loopback_peers),
+    the wait limit is shortened to about a millisecond, and one token is decoded: the exchange
+    consumer's poll of rank 1's packets runs out, every kernel returns, the status block reports
+    TLB_ERR_DEVICE_WAIT with where = 301 (300 + the silent rank).  After the status is cleared a
+    healthy launch gives the oracle's numbers: the context survived."""
+    import ctypes as C
+    import time
+    from cpp_tensorlib_b200 import check, lib
+    from cpp_tensorlib_b200 import cuda as tl
+    from cpp_tensorlib_b200.decoder import Q4Decoder
+    cfg = dict(hidden=512, layers=2, n_q=8, n_kv=2, hd=64, ff=1024, vocab=320, eps=1e-6, rope_base=1e6)
+    wts = cases.decoder_weights(cfg, 55)
+    d = Q4Decoder(cfg, 64, 0, 2)
+    d.load(wts)
+    check(lib().tlb_decoder_loopback_peers(d.h))
+    st = (C.c_int * 2)()
+    assert lib().tlb_device_status(st, 1) == 0
+    check(lib().tlb_set_wait_limit_cycles(2_000_000))          # ~1 ms at ~2 GHz
+    try:
+        d.set_pos(0)
+        t0 = time.perf_counter()
+        d.step(5)                                              # returns; its result is meaningless
+        torch.cuda.synchronize()
+        assert time.perf_counter() - t0 < 5.0
+        rc = lib().tlb_device_status(st, 1)
+        assert rc == 4, rc                                     # TLB_ERR_DEVICE_WAIT
+        assert st[0] == 1 and st[1] == 301, list(st)
+        assert b"wait expired" in lib().tlb_last_error()
+    finally:
+        check(lib().tlb_set_wait_limit_cycles(2_000_000_000))
+        d.close()
+    assert lib().tlb_device_status(st, 0) == 0                 # cleared
+    W, x = cases.cfg1()
+    wq = tl.to_q4(torch.from_numpy(W).cuda())
+    y = tl.gemv_q4p(torch.from_numpy(x).cuda().reshape(-1), tl.Q4Packed(wq)).cpu().numpy()
+    assert np.allclose(y, port.gemm_q4(x, port.to_q4(W), 4864)[0], rtol=1e-4, atol=1e-4)

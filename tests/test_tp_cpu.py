@@ -121,3 +121,57 @@ def test_two_gloo_ranks_agree_with_unsharded(port):
     got = q.get(timeout=120)
     [p.join(60) for p in procs]
     assert got == want
+
+
+def test_host_barrier_reports_the_missing_rank():
+    """Failure detection on the host (no GPU involved): the ranks that arrive learn, after the
+    timeout, which rank did not, instead of launching kernels that would wait for it."""
+    import threading
+    from cpp_tensorlib_b200 import TlbError
+    store = dist.HashStore()
+    with pytest.raises(TlbError, match=r"rank\(s\) \[1\] of 2"):
+        dec.host_barrier(store, "lonely", 0, 2, timeout_s=0.3)
+    # everybody arrives: both return
+    errs = []
+
+    def arrive(r):
+        try:
+            dec.host_barrier(store, "full", r, 3, timeout_s=20.0)
+        except Exception as e:  # pragma: no cover - reported below
+            errs.append(e)
+    ts = [threading.Thread(target=arrive, args=(r,)) for r in range(3)]
+    [t.start() for t in ts]
+    [t.join(30) for t in ts]
+    assert not errs
+
+
+def _barrier_worker(rank, world, prt, q):
+    from datetime import timedelta
+    store = dist.TCPStore("127.0.0.1", prt, world, is_master=(rank == 0), timeout=timedelta(seconds=30))
+    dist.init_process_group("gloo", store=store, rank=rank, world_size=world)
+    dist.barrier()                       # both ranks are alive here
+    if rank == 1:
+        # the rank fails on the host between steps: it raises and never reaches the next exchange
+        q.put(("rank1", "left"))
+        q.close(); q.join_thread()
+        os._exit(0)
+    try:
+        dec.host_barrier(store, "step2", rank, world, timeout_s=1.0)
+        q.put(("rank0", "no error"))
+    except Exception as e:
+        q.put(("rank0", str(e)))
+    q.close(); q.join_thread()
+    os._exit(0)
+
+
+def test_gloo_rank_that_leaves_is_detected_by_the_host_barrier():
+    import socket
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    s = socket.socket(); s.bind(("127.0.0.1", 0)); prt = s.getsockname()[1]; s.close()
+    procs = [ctx.Process(target=_barrier_worker, args=(r, 2, prt, q)) for r in range(2)]
+    [p.start() for p in procs]
+    got = dict(q.get(timeout=120) for _ in range(2))
+    [p.join(60) for p in procs]
+    assert got["rank1"] == "left"
+    assert "rank(s) [1] of 2 did not arrive" in got["rank0"], got
