@@ -30,6 +30,13 @@ QWEN7 = dict(hidden=3584, layers=28, n_q=28, n_kv=4, hd=128, ff=18944, vocab=152
              rope_base=1e6)
 CTX0 = 4096
 SEED = 4
+# DRAM read+write bytes per algorithmic byte of the int4 GEMV, from ncu captures of single
+# launches (profiles/gemv_q4p_gate_up_7b.md: 1.036 on the 85 MB gate|up matrix).  It is a
+# constant taken from those captures and applied to the whole sweep by bytes, not a
+# per-run measurement.
+TRAFFIC_FACTOR = 1.036
+TRAFFIC_NOTE = ("assumed: dram read+write of one ncu capture of the gate|up shape (1.036 x algorithmic) "
+                "applied to the sweep by bytes")
 
 
 def measured_peaks():
@@ -57,7 +64,7 @@ def token_bytes(cfg, ctx):
 
 
 class ClockSampler:
-    """nvidia-smi clocks / throttle reasons sampled every 200 ms during the timed region."""
+    """nvidia-smi clocks / throttle reasons sampled every 50 ms during the timed region."""
     Q = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,"
          "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
          "clocks_event_reasons.sw_power_cap")
@@ -68,7 +75,7 @@ class ClockSampler:
     def __enter__(self):
         try:
             self.proc = subprocess.Popen(["nvidia-smi", "-i", str(self.index), "--query-gpu=" + self.Q,
-                                          "--format=csv,noheader,nounits", "-lms", "200"],
+                                          "--format=csv,noheader,nounits", "-lms", "50"],
                                          stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             self.t = threading.Thread(target=self._read, daemon=True)
             self.t.start()
@@ -159,64 +166,110 @@ def gemv_sweep(cfg, dec, reps):
     return nbytes, e0.elapsed_time(e1) / reps, len(ws)
 
 
-def cpu_sample(cfg, steps, all_threads_note):
+def cpu_sample(cfg, steps, warmup, note, layers=1):
     """The reference's own CPU code (compiled from its headers into oracle/_ref) --
-    or the C restatement when that was never built -- on a bounded sample: ONE of
-    the model's layers at the 7B shape, cache pre-filled to ctx 4096, `steps`
-    tokens.  Tokens/s of the full model is extrapolated by parameter count."""
+    or the C restatement when that was never built -- on a bounded sample: `layers`
+    of the model's layers at the 7B shape (+ a 1024-row lm_head), cache pre-filled to
+    ctx 4096.  One sample step = one token through that slice.  Returns the measured
+    per-step seconds and what is needed to extrapolate to the full model."""
     import numpy as np
     import oracle
     ref = oracle.load_ref()
-    one = dict(cfg, layers=1, vocab=1024)
+    one = dict(cfg, layers=layers, vocab=1024)
     rng = np.random.default_rng(SEED)
     f = lambda *s: (rng.standard_normal(s, dtype=np.float32) * 0.02)
     sh = linear_shapes(one)
+    total = CTX0 + steps + warmup + 1
     if ref is not None:
-        d, kind, cores = oracle.RefDecoder(ref, one, CTX0 + steps + 1), "reference", ref.threads()
+        d, kind, cores = oracle.RefDecoder(ref, one, total), "reference", ref.threads()
         lin = lambda w: w
     else:
         port = oracle.load_port()
-        d, kind, cores = oracle.PortDecoder(port, one, CTX0 + steps + 1), "port", os.cpu_count()
+        d, kind, cores = oracle.PortDecoder(port, one, total), "port", os.cpu_count()
         lin = port.to_q4
     d.set_embed(f(one["vocab"], one["hidden"]))
     d.set_vector(0, 5, 1 + f(one["hidden"]))
     d.set_linear(0, 4, lin(f(*sh["lm_head"])))
-    for i, n in enumerate(("wqkv", "wo", "wgu", "wd")):
-        d.set_linear(0, i, lin(f(*sh[n])))
     HD = one["hd"]
-    for i, n in ((0, one["hidden"]), (1, one["hidden"]), (2, one["n_q"] * HD), (3, one["n_kv"] * HD), (4, one["n_kv"] * HD)):
-        d.set_vector(0, i, (1 if i < 2 else 0) + f(n))
-    d.fill_kv(0, rng.standard_normal((one["n_kv"], CTX0, HD), dtype=np.float32),
-              rng.standard_normal((one["n_kv"], CTX0, HD), dtype=np.float32))
+    for l in range(layers):
+        for i, n in enumerate(("wqkv", "wo", "wgu", "wd")):
+            d.set_linear(l, i, lin(f(*sh[n])))
+        for i, n in ((0, one["hidden"]), (1, one["hidden"]), (2, one["n_q"] * HD), (3, one["n_kv"] * HD), (4, one["n_kv"] * HD)):
+            d.set_vector(l, i, (1 if i < 2 else 0) + f(n))
+        d.fill_kv(l, rng.standard_normal((one["n_kv"], CTX0, HD), dtype=np.float32),
+                  rng.standard_normal((one["n_kv"], CTX0, HD), dtype=np.float32))
     tok, times = 1, []
-    for s in range(steps):
+    for s in range(warmup + steps):
         t0 = time.perf_counter()
         tok, _ = d.step(tok, CTX0 + s, want_logits=False)
         times.append(time.perf_counter() - t0)
     d.close()
     _, _, params = token_bytes(cfg, CTX0)
-    sample_params = sum(a * b for a, b in sh.values())
-    t_layer = min(times)
-    tps = 1.0 / (t_layer * params / sample_params)
-    return dict(value=tps, unit="tokens/s", cores=cores, kind=kind,
-                sample=f"1 of {cfg['layers']} layers (+1024-row lm_head) at the 7B shape, ctx 4096, "
-                       f"{steps} tokens, min {t_layer * 1e3:.0f} ms/token-layer, extrapolated by parameter count "
-                       f"({params / sample_params:.1f}x); {all_threads_note}"), [t * params / sample_params for t in times]
+    sample_params = layers * sum(sh[n][0] * sh[n][1] for n in ("wqkv", "wo", "wgu", "wd")) + \
+        sh["lm_head"][0] * sh["lm_head"][1]
+    return dict(times=times[warmup:], factor=params / sample_params, kind=kind, cores=cores,
+                what=f"{layers} of {cfg['layers']} layers (+1024-row lm_head) at the 7B shape, ctx 4096; {note}")
+
+
+def cpu_baseline_block(cfg, steps, warmup, note):
+    r = cpu_sample(cfg, steps, warmup, note)
+    t = min(r["times"])
+    return dict(value=1.0 / (t * r["factor"]), unit="tokens/s", cores=r["cores"], kind=r["kind"],
+                sample=f"{r['what']}; {steps} sample tokens, min {t * 1e3:.0f} ms per sample token, "
+                       f"extrapolated to the model by parameter count ({r['factor']:.1f}x)")
+
+
+def gpu_reference_rows(quick):
+    """The reference's OWN CUDA kernels (its PTX JIT-compiled for this GPU, reached through its
+    own headers: oracle/_ref/ref_gpu_bench) on the BASELINE shapes: microseconds and GB/s per
+    launch, HBM-cold.  None where the binary was never built."""
+    exe = os.path.join(ROOT, "oracle", "_ref", "ref_gpu_bench")
+    if not os.path.exists(exe):
+        return None
+    try:
+        r = subprocess.run([exe] + (["--quick"] if quick else []), capture_output=True, text=True, timeout=600)
+    except Exception as e:
+        return dict(error=str(e))
+    rows = []
+    for l in r.stdout.splitlines():
+        if l.startswith("{"):
+            try:
+                rows.append(json.loads(l))
+            except ValueError:
+                pass
+    return dict(rows=rows, what="reference kernels (tl_gemv_q4, tl_attn_decode_split + tl_attn_combine) "
+                                "JIT-compiled from the reference's PTX on this GPU, one CUDA graph of rotating "
+                                "operand copies per shape, wall clock / launches, median of 7")
 
 
 def run_reference(args, rank):
+    """Reference arm: the reference's own CPU implementation of the path on this box's host
+    cores.  A step is ONE token through a bounded slice of the workload (1 of the 28 layers
+    at the 7B shape + a 1024-row lm_head, cache at ctx 4096); exactly --steps of them are
+    timed after --warmup untimed ones.  `ms_per_step` is that MEASURED sample step; `value`
+    is the full-model tokens/s extrapolated from it by parameter count, and says so."""
     if rank != 0:
         return
-    steps = max(1, min(args.steps, 6))
-    base, per_tok = cpu_sample(QWEN7, steps + min(args.warmup, 1),
-                               "pool = hardware_concurrency threads, but the M=1 SGEMM and the "
-                               "attention/dequant loops of the reference are single-threaded")
-    ms = statistics.mean(per_tok[-steps:]) * 1e3
-    line = dict(impl="reference", metric="7B-shape int4 decode tok/s", value=1e3 / ms, unit="tokens/s",
-                n_gpus=args.gpus, steps=steps, warmup=min(args.warmup, 1), ms_per_step=ms,
+    note = ("pool = hardware_concurrency threads, but the M=1 SGEMM and the attention / dequant loops "
+            "of the reference are single-threaded")
+    K, W = max(1, args.steps), max(0, args.warmup)
+    r = cpu_sample(QWEN7, K, W, note)
+    ms = statistics.mean(r["times"]) * 1e3
+    value = 1e3 / (ms * r["factor"])
+    # is the cost per layer linear?  Two layers, three tokens.
+    r2 = cpu_sample(QWEN7, 3, 1, note, layers=2)
+    base = dict(value=value, unit="tokens/s", cores=r["cores"], kind=r["kind"],
+                sample=f"{r['what']}; {K} sample tokens timed after {W} warm-up, mean {ms:.0f} ms per sample token")
+    line = dict(impl="reference", metric="7B-shape int4 decode tok/s", value=value, unit="tokens/s",
+                n_gpus=args.gpus, steps=K, warmup=W, ms_per_step=ms,
                 higher_is_better=True, scaling="strong", vs_baseline=None, dtype="f32 compute on int4 weights",
                 data="synthetic", config=config_block(args.gpus), cpu_baseline=base,
-                e2e=dict(value=1e3 / ms, unit="tokens/s", h2d_bytes_per_step=0, d2h_bytes_per_step=0))
+                extrapolated_from=r["what"], factor=r["factor"],
+                ms_per_token_full_model_extrapolated=ms * r["factor"],
+                linearity_check=dict(one_layer_ms=min(r["times"]) * 1e3, two_layer_ms=min(r2["times"]) * 1e3,
+                                     note="sample token through 1 and through 2 layers (+ the same 1024-row lm_head)"),
+                e2e=dict(value=value, unit="tokens/s", h2d_bytes_per_step=0, d2h_bytes_per_step=0),
+                gpu_reference=gpu_reference_rows(quick=False))
     print(json.dumps(line), flush=True)
 
 
@@ -231,7 +284,7 @@ def config_block(n):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=64)
+    ap.add_argument("--steps", type=int, default=128)
     ap.add_argument("--warmup", type=int, default=8)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--layers", type=int, default=0, help="diagnostic: fewer layers (line is marked invalid)")
@@ -256,7 +309,7 @@ def main():
     if args.layers:
         cfg["layers"] = args.layers
     K, W = args.steps, max(3, args.warmup)
-    max_ctx = CTX0 + max(128, K + W) + 8
+    max_ctx = CTX0 + max(128, K + W) + 8      # every region restarts at ctx 4096
     dec = build_decoder(cfg, max_ctx, rank, world, CTX0)
     dec.connect()
     if args.prefill:
@@ -286,22 +339,32 @@ def main():
             dist.barrier()
         torch.cuda.synchronize()
 
-    # ---- device-resident greedy decoding: W warm-up tokens, then exactly K timed
+    # ---- device-resident greedy decoding: W warm-up tokens, then REPEATS timed regions of
+    # exactly K tokens each (every region restarts at ctx 4096 from token 1, so all regions
+    # do the same work; each is bracketed by barrier + synchronize on both sides and timed
+    # with CUDA events on the launching stream, max over ranks).  The line reports the
+    # median region; min and max are given beside it so that a change of 1-2 % can be told
+    # from noise.
+    REPEATS = 5
     barrier()
     dec.run(W)
     barrier()
-    dec.set_pos(CTX0)
-    barrier()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    region_ms = []
     with ClockSampler(local) as clk:
-        e0.record()
-        dec.run(K)
-        e1.record()
-        barrier()
-    ms = torch.tensor([e0.elapsed_time(e1)], device="cuda")
-    if world > 1:
-        dist.all_reduce(ms, op=dist.ReduceOp.MAX)
-    ms_total = float(ms.item())
+        for _ in range(REPEATS):
+            dec.set_pos(CTX0)
+            dec.set_token(1)
+            barrier()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            dec.run(K)
+            e1.record()
+            barrier()
+            ms = torch.tensor([e0.elapsed_time(e1)], device="cuda")
+            if world > 1:
+                dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+            region_ms.append(float(ms.item()))
+    ms_total = statistics.median(region_ms)
     last = dec.last_token()
 
     # ---- end to end through the host-buffer call: id H2D, graph, id D2H, per token
@@ -312,14 +375,18 @@ def main():
     dec.set_pos(CTX0)
     barrier()
     t0 = time.perf_counter()
-    tok = 1
+    tok, ids = 1, []
     for _ in range(K):
         tok = dec.step(tok)
+        ids.append(tok)
     torch.cuda.synchronize()
     e2e_s = torch.tensor([time.perf_counter() - t0], device="cuda")
     if world > 1:
         dist.all_reduce(e2e_s, op=dist.ReduceOp.MAX)
     e2e_tps = K / float(e2e_s.item())
+    import hashlib
+    import struct
+    ids_sha = hashlib.sha256(struct.pack(f"<{len(ids)}i", *ids)).hexdigest()[:16]
 
     # ---- roofline of the dominant kernel (per rank: its own shards)
     peak, peak_src = measured_peaks()
@@ -332,35 +399,43 @@ def main():
     st = (__import__("ctypes").c_int * 2)()
     status = lib().tlb_device_status(st, 0)
     launches = dec.launches_per_token() * K
+    dec.close()
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
     if rank == 0:
         line = dict(metric="7B-shape int4 decode tok/s", value=K / (ms_total * 1e-3), unit="tokens/s",
                     n_gpus=world, steps=K, warmup=W, ms_per_step=ms_total / K, higher_is_better=True,
                     scaling="strong", vs_baseline=None, dtype="f32 compute on int4 weights",
                     data="synthetic", config=config_block(world), clocks=clk.summary(),
+                    repeats=dict(n=REPEATS, statistic="median", ms_per_step_min=min(region_ms) / K,
+                                 ms_per_step_max=max(region_ms) / K),
                     e2e=dict(value=e2e_tps, unit="tokens/s", h2d_bytes_per_step=4, d2h_bytes_per_step=4),
                     gpu_launches=launches,
                     roofline=dict(bound="hbm", achieved=achieved, peak=peak, unit="GB/s", frac=achieved / peak,
-                                  traffic=gbytes * 1.036, peak_source=peak_src, kernel="gemv_q4p_kernel",
-                                  traffic_note="dram read+write of the ncu capture of the gate|up shape "
-                                               "(1.036 x algorithmic, profiles/gemv_q4p_gate_up_7b.md) scaled "
-                                               "to the sweep by bytes",
+                                  traffic=gbytes * TRAFFIC_FACTOR, peak_source=peak_src, kernel="gemv_q4p_kernel",
+                                  traffic_factor_assumed=TRAFFIC_FACTOR, traffic_note=TRAFFIC_NOTE,
                                   what=f"{glaunch} int4 GEMV launches of one token ({gbytes / 1e9:.2f} GB algorithmic), "
                                        f"{gms:.3f} ms per pass, CUDA events"),
                     token_roofline=dict(bound="hbm", achieved=tok_ach, peak=peak, frac=tok_ach / peak, unit="GB/s",
                                         bytes_per_token_per_gpu=tok_bytes),
-                    last_token=last, device_status=int(status))
+                    last_token=last, decoded_ids_sha=ids_sha, decoded_ids_head=ids[:8], device_status=int(status))
+        # The line is only a measurement if the decode was right: the device-resident loop and
+        # the host-buffer loop start from the same token and position, so they must end on the
+        # same token, and no bounded wait may have expired.
+        if ids[-1] != last:
+            line["invalid"] = f"device-resident loop ended on token {last}, host-buffer loop on {ids[-1]}"
+        elif status != 0:
+            line["invalid"] = f"device status {int(status)} (where = {st[1]})"
         if args.layers:
             line["invalid"] = "diagnostic run with fewer layers than the named config"
-        if not args.no_cpu_baseline:
+        # CPU baseline: at N = 1 only, after the GPU work is done and the process group is gone
+        if world == 1 and not args.no_cpu_baseline:
             try:
-                line["cpu_baseline"], _ = cpu_sample(QWEN7, 2, "M=1 path of the reference is single-threaded")
+                line["cpu_baseline"] = cpu_baseline_block(QWEN7, 3, 1, "M=1 path of the reference is single-threaded")
             except Exception as e:  # the checker is optional at run time; say so instead of dying
                 line["cpu_baseline"] = dict(value=None, unit="tokens/s", cores=0, kind="unavailable", sample=str(e))
         print(json.dumps(line), flush=True)
-    dec.close()
-    if world > 1:
-        dist.barrier()
-        dist.destroy_process_group()
 
 
 if __name__ == "__main__":

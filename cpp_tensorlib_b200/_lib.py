@@ -42,6 +42,7 @@ SIGNATURES = {
     "tlb_rmsnorm": (ci, [vp, vp, vp, i64, f32, i64, vp]),
     "tlb_rmsnorm_res": (ci, [vp, vp, vp, vp, vp, i64, f32, i64, vp]),
     "tlb_swiglu": (ci, [vp, vp, i64, i64, vp]),
+    "tlb_swiglu_split": (ci, [vp, i64, vp, i64, vp, i64, i64, vp]),
     "tlb_rope": (ci, [vp, vp, i64, i64, i64, i64, f32, vp, vp]),
     "tlb_rope_dpos": (ci, [vp, vp, i64, i64, i64, vp, f32, vp, vp]),
     "tlb_kv_append": (ci, [vp, vp, vp, vp, i64, i64, i64, i64, vp]),

@@ -34,6 +34,7 @@ int launch_rmsnorm(const float*, const float*, float*, int, float, int, cudaStre
 int launch_add_rmsnorm(const float*, const float*, const float*, float*, float*, int, float, int,
                        cudaStream_t);
 int launch_swiglu(const float*, float*, int, int, cudaStream_t);
+int launch_swiglu_split(const float*, long long, const float*, long long, float*, int, int, cudaStream_t);
 int launch_rope(const float*, const float*, float*, int, int, int, unsigned, const unsigned*,
                 float, cudaStream_t);
 int launch_kv_append(void*, void*, const float*, const float*, unsigned, const unsigned*, long long,
@@ -433,6 +434,12 @@ int tlb_rmsnorm_res(const float* x, const float* delta, const float* w, float* x
 int tlb_swiglu(const float* gu, float* out, int64_t ff, int64_t rows, void* stream) {
   TLB_REQUIRE(gu && out && ff > 0 && rows > 0, "tlb_swiglu: bad arguments");
   return launch_swiglu(gu, out, (int)ff, (int)rows, S(stream));
+}
+int tlb_swiglu_split(const float* gate, int64_t ldg, const float* up, int64_t ldu, float* out, int64_t ff,
+                     int64_t rows, void* stream) {
+  TLB_REQUIRE(gate && up && out && ff > 0 && rows > 0 && rows <= 65535 && ldg >= ff && ldu >= ff,
+              "tlb_swiglu_split: bad arguments");
+  return launch_swiglu_split(gate, ldg, up, ldu, out, (int)ff, (int)rows, S(stream));
 }
 int tlb_rope(const float* x, float* out, int64_t rows, int64_t T, int64_t D, int64_t pos,
              float base, const float* bias, void* stream) {

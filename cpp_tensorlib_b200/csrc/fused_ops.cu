@@ -62,15 +62,18 @@ __global__ void add_rmsnorm_kernel(const float* a, const float* __restrict__ b,
     hout[base + i] = xout[base + i] * inv * w[i];
 }
 
-// out[r,f] = silu(gu[r,f]) * gu[r,ff+f]   -- kernels/tensorlib_cuda.cu:185-192
-__global__ void swiglu_kernel(const float* __restrict__ gu, float* __restrict__ out, int ff) {
+// out[r,f] = silu(g[r,f]) * u[r,f]   -- kernels/tensorlib_cuda.cu:185-192; gate and up rows
+// each with their own row stride (the fused [rows, 2 ff] buffer is g = gu, u = gu + ff,
+// both strides 2 ff)
+__global__ void swiglu_kernel(const float* __restrict__ gate, long long ldg,
+                              const float* __restrict__ up, long long ldu, float* __restrict__ out,
+                              int ff) {
   pdl_wait();
   pdl_launch_dependents();
   const int f = blockIdx.x * blockDim.x + threadIdx.x;
   if (f >= ff) return;
-  const size_t src = (size_t)blockIdx.y * 2u * ff + f;
-  const float g = gu[src];
-  out[(size_t)blockIdx.y * ff + f] = (g / (1.0f + expf(-g))) * gu[src + ff];
+  const float g = gate[(size_t)blockIdx.y * ldg + f];
+  out[(size_t)blockIdx.y * ff + f] = (g / (1.0f + expf(-g))) * up[(size_t)blockIdx.y * ldu + f];
 }
 
 // Half-split RoPE with an optional fused bias -- kernels/tensorlib_cuda.cu:1360-1395
@@ -454,10 +457,14 @@ int launch_add_rmsnorm(const float* a, const float* b, const float* w, float* xo
   TLB_CUDA(cudaLaunchKernelEx(&lc.cfg, add_rmsnorm_kernel, a, b, w, xout, hout, n, eps));
   return TLB_OK;
 }
-int launch_swiglu(const float* gu, float* out, int ff, int rows, cudaStream_t s) {
+int launch_swiglu_split(const float* g, long long ldg, const float* u, long long ldu, float* out, int ff,
+                        int rows, cudaStream_t s) {
   LaunchCfg lc(dim3((ff + 255) / 256, rows), dim3(256), 0, s, pdl_enabled());
-  TLB_CUDA(cudaLaunchKernelEx(&lc.cfg, swiglu_kernel, gu, out, ff));
+  TLB_CUDA(cudaLaunchKernelEx(&lc.cfg, swiglu_kernel, g, ldg, u, ldu, out, ff));
   return TLB_OK;
+}
+int launch_swiglu(const float* gu, float* out, int ff, int rows, cudaStream_t s) {
+  return launch_swiglu_split(gu, 2ll * ff, gu + ff, 2ll * ff, out, ff, rows, s);
 }
 int launch_rope(const float* x, const float* bias, float* out, int rows, int T, int D,
                 unsigned pos, const unsigned* d_pos, float base, cudaStream_t s) {

@@ -69,6 +69,9 @@ struct backend {
   int (*rmsnorm_res)(const float*, const float*, const float*, float*, float*, int64_t, float,
                      int64_t, void*) = nullptr;
   int (*swiglu)(const float*, float*, int64_t, int64_t, void*) = nullptr;
+  int (*swiglu_split)(const float*, int64_t, const float*, int64_t, float*, int64_t, int64_t, void*) = nullptr;
+  int (*gemm_q4)(const float*, int64_t, int64_t, const void*, const float*, float*, int64_t, int64_t,
+                 int64_t, float, float, void*) = nullptr;
   int (*rope)(const float*, float*, int64_t, int64_t, int64_t, int64_t, float, const float*, void*) = nullptr;
   int (*rope_dpos)(const float*, float*, int64_t, int64_t, int64_t, const void*, float, const float*,
                    void*) = nullptr;
@@ -194,7 +197,8 @@ struct backend {
               bind(merge_heads, "tlb_merge_heads") && bind(kv_fill, "tlb_kv_fill") &&
               bind(attn_prefill, "tlb_attn_prefill") && bind(capture_begin, "tlb_capture_begin") &&
               bind(capture_end, "tlb_capture_end") && bind(graph_launch, "tlb_graph_launch") &&
-              bind(graph_destroy, "tlb_graph_destroy");
+              bind(graph_destroy, "tlb_graph_destroy") && bind(swiglu_split, "tlb_swiglu_split") &&
+              bind(gemm_q4, "tlb_gemm_q4");
     if (!ok || device_count() <= 0) return;
     ready = init(0) == 0;
   }

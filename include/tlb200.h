@@ -137,6 +137,10 @@ int tlb_rmsnorm(const float* x, const float* w, float* out, int64_t n, float eps
 int tlb_rmsnorm_res(const float* x, const float* delta, const float* w, float* xout, float* hout,
                     int64_t n, float eps, int64_t rows, void* stream); /* cu.h:1233-1252 */
 int tlb_swiglu(const float* gu, float* out, int64_t ff, int64_t rows, void* stream); /* cu.h:1306-1319 */
+/* arr:2435-2439 array::swiglu(gate, up) = silu(gate) * up on two separate [rows, ff] operands with
+ * row strides ldg / ldu (the lazy graph's composition; tlb_swiglu is the fused-buffer form). */
+int tlb_swiglu_split(const float* gate, int64_t ldg, const float* up, int64_t ldu, float* out,
+                     int64_t ff, int64_t rows, void* stream);
 int tlb_rope(const float* x, float* out, int64_t rows, int64_t T, int64_t D, int64_t pos,
              float base, const float* bias, void* stream);       /* cu.h:1205-1222 */
 int tlb_rope_dpos(const float* x, float* out, int64_t rows, int64_t T, int64_t D,

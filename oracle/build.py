@@ -59,6 +59,7 @@ REFERENCE_CHECKS = {
     "ref_check_llm_block": ["bench/shared/check/check_llm_block.cpp"],
     "ref_check_attn64": ["bench/cuda/check/check_attn64.cpp"],
     "ref_bench_q4_gemv": ["bench/cuda/speed/bench_q4_gemv.cpp"],
+    "ref_bench_attn_decode": ["bench/cuda/speed/bench_attn_decode.cpp"],
 }
 
 
@@ -79,14 +80,54 @@ def build_reference_checks(force=False):
             procs.append(subprocess.Popen(
                 ["g++", "-std=c++17", "-O2", "-DTENSORLIB_CUDA", "-I", seam, "-I", inc,
                  "-I", os.path.join(REF_DIR, "test")] + paths + ["-o", out, "-ldl", "-lpthread"]))
+    # this repository's own check of the runtime-hook executor (include/tlb200_executor.h),
+    # a consumer of the reference's public tl::array API built in its TL_RUNTIME_HOOKS mode
+    exe = os.path.join(out_dir, "check_executor")
+    src = os.path.join(HERE, "..", "tests", "cpp", "check_executor.cpp")
+    built.append(exe)
+    if force or _stale(exe, [src, os.path.join(seam, "tlb200_executor.h")] + deps):
+        procs.append(subprocess.Popen(
+            ["g++", "-std=c++17", "-O2", "-DTENSORLIB_CUDA", "-DTL_RUNTIME_HOOKS", "-I", seam, "-I", inc,
+             src, "-o", exe, "-ldl", "-lpthread"]))
     for p in procs:
         if p.wait():
             raise RuntimeError("compiling a reference check against the seam headers failed")
     return built
 
 
+def build_reference_gpu(force=False):
+    """The reference's OWN CUDA backend, for timing its kernels on the same GPU: its kernel
+    source compiled to PTX the way its CMakeLists does (``nvcc -arch=sm_80 -ptx``; the driver
+    JIT-compiles that PTX for the device it finds), the PTX turned into the byte-list include
+    its ``include/cuda.h`` embeds (what ``cmake/bin2c.cmake`` writes: ``0x..,`` per byte and a
+    closing ``0x00``), and ``ref_gpu_bench.cpp`` -- a small timing driver over the reference's
+    public ``tl::cuda::`` facade -- compiled against the REFERENCE's headers, not this
+    repository's seam.  Outputs only under ``oracle/_ref/``; nothing is copied."""
+    inc = os.path.join(REF_DIR, "include")
+    cu = os.path.join(REF_DIR, "kernels", "tensorlib_cuda.cu")
+    out_dir = os.path.join(HERE, "_ref")
+    out = os.path.join(out_dir, "ref_gpu_bench")
+    if not (os.path.isfile(os.path.join(inc, "tensorlib.h")) and os.path.isfile(cu)):
+        return out if os.path.exists(out) else None
+    src = os.path.join(HERE, "ref_gpu_bench.cpp")
+    if force or _stale(out, [src, cu]):
+        gen = os.path.join(out_dir, "gen")
+        os.makedirs(gen, exist_ok=True)
+        ptx = os.path.join(gen, "tensorlib_cuda.ptx")
+        nvcc = os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc")
+        subprocess.check_call([nvcc, "-arch=sm_80", "-ptx", "-Wno-deprecated-gpu-targets", cu, "-o", ptx])
+        with open(ptx, "rb") as f:
+            data = f.read()
+        with open(os.path.join(gen, "tensorlib_cuda_ptx.inc"), "w") as f:
+            f.write("".join("0x%02x," % b for b in data) + " 0x00\n")
+        subprocess.check_call(["g++", "-std=c++17", "-O2", "-DTENSORLIB_CUDA", "-I", gen, "-I", inc,
+                               src, "-o", out, "-ldl", "-lpthread"])
+    return out
+
+
 def build_all(force=False):
-    return build_port(force), build_reference(force), build_reference_checks(force)
+    return (build_port(force), build_reference(force), build_reference_checks(force),
+            build_reference_gpu(force))
 
 
 if __name__ == "__main__":

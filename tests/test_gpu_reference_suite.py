@@ -59,3 +59,47 @@ def test_reference_q4_gemv_bench_correctness():
             ("qkv_proj", "attn_out", "ffn_gate_up", "ffn_down", "lm_head")]
     assert len(rows) == 5, out[-2000:]
     assert all(float(r[-1]) < 1e-4 for r in rows), rows
+
+
+def test_reference_attn_decode_bench_correctness_sections():
+    """bench/cuda/speed/bench_attn_decode.cpp through the seam: the f32-vs-CPU maxrel column of
+    its llama-shape table (:100-133; the bf16 run's error is the cache's rounding, ~1e-3), and
+    the three 1e-4 correctness sections at D=128, 32 q / 8 kv heads -- the cache grown token by
+    token across the split boundary (:197-298), the batched prefill at T=500 (:324-398) and the
+    decode step that continues it (:400-453)."""
+    rc, out = run("ref_bench_attn_decode", timeout=900)
+    assert "no CUDA device" not in out, "the backend did not come up"
+    assert rc == 0 and "FAIL" not in out, out[-3000:]
+    want = ("grew to", "prefill T=", "decode step at pos=")
+    for w in want:
+        lines = [l for l in out.splitlines() if w in l]
+        assert lines and all(" OK" in l for l in lines), (w, out[-3000:])
+
+
+def test_reference_own_cuda_kernels_run_on_this_gpu():
+    """oracle/_ref/ref_gpu_bench: the reference's OWN kernels (its PTX JIT-compiled by the driver
+    for this GPU, reached through its own include/cuda.h, none of this repository's code on the
+    path) on the BASELINE shapes.  Here only their sanity column is asserted (each kernel's
+    result against a double-precision host loop); the timings are what bench.py's reference
+    arm reports beside this build's."""
+    import json
+    exe = os.path.join(REF, "ref_gpu_bench")
+    if not os.path.exists(exe):
+        pytest.skip("ref_gpu_bench not built (needs the reference tree and nvcc at build time)")
+    r = subprocess.run([exe, "--quick"], capture_output=True, text=True, timeout=600)
+    rows = [json.loads(l) for l in r.stdout.splitlines() if l.startswith("{")]
+    assert r.returncode == 0 and rows and "error" not in rows[0], r.stdout[-2000:] + r.stderr[-2000:]
+    assert {x["name"] for x in rows} >= {"cfg1", "7b_qkv", "7b_o", "7b_gate_up", "7b_down", "cfg2_ctx4096"}
+    for x in rows:
+        assert x["us"] > 0 and x["maxrel"] < 1e-3, x
+
+
+def test_runtime_hook_executor_keeps_the_hot_path_on_the_device():
+    """tests/cpp/check_executor.cpp: the executor installed through the reference's runtime hooks
+    (include/array.h:190-195, 2525-2532) evaluates BASELINE config 4 -- X.dot(Wq) * 0.5f + 1.0f at
+    M in {1, 8, 64, 512} -- as one int4 launch per dot with the epilogue in the kernel and no host
+    dequantisation, recognises the RMSNorm / SwiGLU compositions (array.h:2429-2439), and matches
+    the reference's CPU evaluation (1e-4 / 1e-5)."""
+    rc, out = run("check_executor", timeout=900)
+    assert "no CUDA device" not in out, "the backend did not come up"
+    assert rc == 0 and "ALL OK" in out, out[-3000:]
