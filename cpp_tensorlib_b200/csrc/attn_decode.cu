@@ -26,55 +26,11 @@
 #include <mutex>
 #include <string>
 
-#include "attn_common.cuh"
+#include "attn_split.cuh"
 
 namespace tlb {
 
-// Diagnostics: when set, every launch records per-CTA phase timestamps there.
 unsigned long long* g_attn_dbg = nullptr;
-constexpr int AT_TK = 32;  // keys per tile
-
-struct AttnParams {
-  const float* q;
-  const void* K;   // f32 or bf16 cache (template parameter BF of the kernel)
-  const void* V;
-  float* out;
-  float* partials;     // [n_q][S_cap][D+4]  (acc[D], m, l, pad, pad)
-  int* counters;       // [n_kv], zero between launches
-  const unsigned* d_pos;  // nullptr: use ctx
-  int ctx;
-  int n_q, n_kv, grp;
-  long long kv_stride;  // kv_max * D
-  int kv_rows;          // kv_max: a device-resident position at or beyond it is refused
-  float scale;
-  int s_cap;     // partial slots per head (= launched splits)
-  int sm2;       // CTA target of the grid (attn_target): split count = target / kv heads
-  int* status;
-  int early_kv;  // cache rows below ctx-1 and *d_pos are older than the preceding kernel:
-                 // their tiles may be requested before the grid dependency resolves
-  unsigned long long* dbg;
-};
-
-// CTAs the grid should have: one per SM for wide groups (4 heads per warp: one CTA fits an
-// SM), two per SM otherwise.
-__host__ __device__ inline int attn_target(int grp, int sm_count) {
-  return grp >= 3 ? sm_count : 2 * sm_count;
-}
-// Number of splits wanted for a context length (monotone non-decreasing in ctx).
-__host__ __device__ inline int attn_splits_wanted(int n_kv, int ctx, int sm2) {
-  int s = sm2 / (n_kv > 0 ? n_kv : 1);
-  int cap = (ctx + 63) / 64;     // never less than 64 keys (2 tiles) per split
-  if (s > cap) s = cap;
-  if (s > 96) s = 96;  // the merge keeps (m, l) of at most 3 splits per lane
-  return s < 1 ? 1 : s;
-}
-// Keys per split: ceil(ctx / wanted) rounded up to a whole tile.
-__host__ __device__ inline int attn_chunk(int n_kv, int ctx, int sm2) {
-  int s = attn_splits_wanted(n_kv, ctx, sm2);
-  int chunk = (ctx + s - 1) / s;
-  chunk = (chunk + AT_TK - 1) / AT_TK * AT_TK;
-  return chunk < AT_TK ? AT_TK : chunk;
-}
 
 // Warps across heads: ceil(grp / HW) rounded up to a divisor of the warp count.
 __host__ __device__ inline int attn_hs(int grp, int HW, int warps) {
@@ -481,6 +437,9 @@ static int launch_t(const AttnParams& p, int splits, cudaStream_t stream, bool b
   return launch_b<D, HW, LPK, false>(p, splits, stream);
 }
 
+bool attn_decode_mma_eligible(int grp, int D, int n_kv, long long kv_max, int kv_bf16);
+int attn_decode_mma_launch(const AttnParams& p, int D, int splits, cudaStream_t stream);
+
 // ctx >= 1 and d_pos == nullptr: host-position variant.  d_pos != nullptr: the
 // context is *d_pos + 1 and the grid is sized from kv_max.
 int attn_decode_launch(DeviceCtx* c, const float* q, const void* K, const void* V, float* out,
@@ -504,6 +463,11 @@ int attn_decode_launch(DeviceCtx* c, const float* q, const void* K, const void* 
   const int splits = d_pos ? attn_splits_wanted(n_kv, basis, p.sm2)
                            : (ctx + attn_chunk(n_kv, ctx, p.sm2) - 1) / attn_chunk(n_kv, ctx, p.sm2);
   p.s_cap = d_pos ? splits : attn_splits_wanted(n_kv, basis, p.sm2);
+  // GQA groups of 3..8 heads on an f32 cache: the tensor-core form (attn_decode_mma.cu).
+  // TLB_ATTN_MMA=0 keeps the CUDA-core form (a diagnostic switch for A/B timing).
+  static const bool mma_on = !(getenv("TLB_ATTN_MMA") && atoi(getenv("TLB_ATTN_MMA")) == 0);
+  if (mma_on && attn_decode_mma_eligible(grp, D, n_kv, kv_max, kv_bf16))
+    return attn_decode_mma_launch(p, D, splits, stream);
   // heads per warp: the smallest of {1,2,4} such that ceil(grp/HW) divides 8
   int HW = grp == 1 ? 1 : (grp == 2 ? 2 : 4);
   if (D == 128) {

@@ -59,6 +59,7 @@ int launch_add_rmsnorm(const float*, const float*, const float*, float*, float*,
 int launch_add_rmsnorm_ar(const float*, const float*, float*, float*, int, float, const CommDev&,
                           int*, cudaStream_t);
 int launch_swiglu(const float*, float*, int, int, cudaStream_t);
+int launch_ar_sum(float*, int, const CommDev&, int*, cudaStream_t);
 int launch_incr_u32(unsigned*, cudaStream_t);
 int launch_qkv_post(float*, const float*, const float*, const float*, float*, float*, int, int,
                     int, const unsigned*, long long, float, int*, cudaStream_t);
@@ -235,19 +236,24 @@ static int forward(Decoder* d, cudaStream_t s) {
     c2.E = EX;
     return c2;
   };
-  // TLB_TP_PULL_MAX: largest rank count whose exchanges are consumed inside the next
-  // projection's prologue.  Default 1 = never: measured on 2 GPUs the 148 CTAs' system-scope
-  // polls cost what the two saved kernels per layer cost (582 vs 589 tok/s).
+  // How a tensor-parallel exchange is consumed.  Default: a small multi-CTA kernel sums the
+  // ranks' packets into a local vector (ar_sum_kernel) and the next projection's ordinary fused
+  // add+norm prologue reads that vector -- one short extra launch per exchange, no system-scope
+  // polling from 148 CTAs.  TLB_TP_PULL_MAX = largest rank count whose exchanges are instead
+  // consumed inside the next projection's prologue (it polls the packets itself: two kernels
+  // fewer per layer, measured slower on 2 GPUs, 582 vs 589 tok/s); TLB_TP_SUM=0 selects the
+  // older single-CTA add+norm consumer (add_rmsnorm_ar_kernel).
   const char* pm = getenv("TLB_TP_PULL_MAX");
   const int pull_max = pm ? atoi(pm) : 1;
-  if (all_tma && (!tp || d->tp_size <= pull_max)) {
+  const char* ts = getenv("TLB_TP_SUM");
+  const bool tp_sum = !(ts && atoi(ts) == 0);
+  const bool pull = tp && d->tp_size <= pull_max;
+  if (all_tma && (!tp || pull || tp_sum)) {
     // Both residual adds and norms of a layer run inside the following projection's
-    // activation prep (5 launches per layer).  Tensor parallel (opt-in, see above): that
-    // prologue is also the exchange's consumer -- it polls the ranks' partial vectors from
-    // this rank's staging and sums them in rank order -- so the row-parallel projection's
-    // push and the next projection are the only kernels of an all-reduce.  The residual
-    // ping-pongs between two buffers because every CTA of the projection reads it while
-    // one CTA writes the new sum.
+    // activation prep (5 launches per layer, + one packet-sum launch per exchange when tensor
+    // parallel).  The residual ping-pongs between two buffers because every CTA of the
+    // projection reads it while one CTA writes the new sum.
+    const bool sum = tp && !pull;
     float* x = d->x;
     float* xalt = d->xb;
     for (int l = 0; l < d->n_layers; l++) {
@@ -259,7 +265,7 @@ static int forward(Decoder* d, cudaStream_t s) {
       if (l == 0) {
         RUN(run_linear(c, L.wqkv, d->hb, d->qkv, s, nullptr, 0, nullptr, 0.f, pq));
       } else {
-        NormIn nm{tp ? nullptr : d->t1, L.an, xalt, tp ? &c_prev : nullptr};
+        NormIn nm{pull ? nullptr : d->t1, L.an, xalt, pull ? &c_prev : nullptr};
         RUN(run_linear(c, L.wqkv, x, d->qkv, s, nullptr, 0, &nm, d->eps, pq));
         float* t = x; x = xalt; xalt = t;
       }
@@ -270,7 +276,8 @@ static int forward(Decoder* d, cudaStream_t s) {
                              d->scale, d->d_pos, (float*)((char*)d->attn_partials + 256),
                              (int*)d->attn_partials, s, 1, 0));
       RUN(run_linear(c, L.wo, d->att, tp ? nullptr : d->t0, s, tp ? &c_wo : nullptr));
-      NormIn nf{tp ? nullptr : d->t0, L.fn, xalt, tp ? &c_wo : nullptr};
+      if (sum) RUN(launch_ar_sum(d->t0, E, c_wo, c->status, s));
+      NormIn nf{pull ? nullptr : d->t0, L.fn, xalt, pull ? &c_wo : nullptr};
       RUN(run_linear(c, L.wgu, x, d->gu, s, nullptr, 0, &nf, d->eps, pg));
       { float* t = x; x = xalt; xalt = t; }
       if (pg) {
@@ -278,9 +285,10 @@ static int forward(Decoder* d, cudaStream_t s) {
       } else {
         RUN(run_linear(c, L.wd, d->gu, tp ? nullptr : d->t1, s, tp ? &c_wd : nullptr, 1));
       }
+      if (sum) RUN(launch_ar_sum(d->t1, E, c_wd, c->status, s));
     }
     const CommDev c_last = cm(2 * d->n_layers - 1);
-    NormIn no{tp ? nullptr : d->t1, d->onorm, xalt, tp ? &c_last : nullptr};
+    NormIn no{pull ? nullptr : d->t1, d->onorm, xalt, pull ? &c_last : nullptr};
     RUN(run_linear(c, d->lm_head, x, d->logits, s, nullptr, 0, &no, d->eps));
     if (tp) {
       RUN(launch_argmax_tp(c, d->logits, d->vocab, d->vocab_offset, cm(2 * d->n_layers), d->d_tok,

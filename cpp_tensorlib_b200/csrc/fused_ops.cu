@@ -374,6 +374,34 @@ __global__ void add_rmsnorm_ar_kernel(const float* a, const float* __restrict__ 
   for (int i = threadIdx.x; i < n; i += blockDim.x) hout[i] = xout[i] * inv * w[i];
 }
 
+// out[i] = sum_r partial_r[i]: only the reduction of an exchange, spread over many CTAs so that
+// every poll of every rank's packet is in flight at once (one thread per element, tp loads
+// each).  The sum lands in this GPU's own memory; the residual add and the norm are then the
+// ordinary fused prologue of the next projection, which reads a plain local vector instead of
+// polling system-scope packets from every SM.  Partials are added in rank order, so all ranks
+// compute identical bits.
+__global__ void ar_sum_kernel(float* __restrict__ out, int n, CommDev comm, int* status) {
+  pdl_wait();
+  pdl_launch_dependents();
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n) return;
+  const unsigned seq = comm_seq(comm);
+  const uint2* st = comm.stage[comm.rank] + (size_t)(seq & 1u) * comm.size * comm.slot_floats + i;
+  uint2 pk[TP_MAX];
+#pragma unroll
+  for (int r = 0; r < TP_MAX; r++)
+    if (r < comm.size) pk[r] = ld_packet_sys(st + (size_t)r * comm.slot_floats);
+  float d = 0.f;
+#pragma unroll
+  for (int r = 0; r < TP_MAX; r++)
+    if (r < comm.size) {
+      if (pk[r].y != seq + 1u)
+        pk[r] = wait_packet_bounded(st + (size_t)r * comm.slot_floats, seq + 1u, status, 300 + r);
+      d += __uint_as_float(pk[r].x);
+    }
+  out[i] = d;
+}
+
 // Vocabulary-parallel argmax: each rank reduces its logits shard to a packed key
 // (ordered float bits, inverted GLOBAL index), the last block pushes the key to
 // every rank as two tagged packets, and argmax_finish_kernel takes the maximum.
@@ -534,6 +562,12 @@ int launch_add_rmsnorm_ar(const float* a, const float* w, float* xout, float* ho
                           float eps, const CommDev& comm, int* status, cudaStream_t s) {
   LaunchCfg lc(dim3(1), dim3(row_threads(n)), 0, s, pdl_enabled());
   TLB_CUDA(cudaLaunchKernelEx(&lc.cfg, add_rmsnorm_ar_kernel, a, w, xout, hout, n, eps, comm, status));
+  return TLB_OK;
+}
+int launch_ar_sum(float* out, int n, const CommDev& comm, int* status, cudaStream_t s) {
+  const int threads = 128;
+  LaunchCfg lc(dim3((n + threads - 1) / threads), dim3(threads), 0, s, pdl_enabled());
+  TLB_CUDA(cudaLaunchKernelEx(&lc.cfg, ar_sum_kernel, out, n, comm, status));
   return TLB_OK;
 }
 int launch_argmax_tp(DeviceCtx* c, const float* in, int n, unsigned vocab_offset,

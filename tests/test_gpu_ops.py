@@ -297,6 +297,9 @@ def test_attn_cfg2_headline_sizes_vs_oracle(tl, port, ctx):
     (14, 2, 64, 2048, [1, 2, 31, 32, 33, 127, 128, 129, 255, 256, 257, 1000, 2047, 2048]),
     (32, 8, 128, 600, [1, 5, 63, 64, 65, 300, 511, 600]),
     (28, 4, 128, 4224, [1, 4096, 4097, 4224]),
+    (28, 4, 128, 16384, [9000, 16384]),       # GQA tensor-core form: more tiles per CTA than ring slots
+    (14, 2, 64, 40000, [33000, 39999]),       # the same at head_dim 64, ragged last tile
+    (24, 8, 128, 1100, [1100]), (10, 2, 64, 700, [1, 17, 699]), (8, 1, 128, 400, [400]),   # groups 3, 5, 8
     (4, 4, 128, 300, [7, 300]), (6, 2, 64, 300, [299]), (12, 1, 64, 160, [160]), (40, 2, 64, 96, [96])])
 def test_attn_gqa_prefix_sweep(tl, port, n_q, n_kv, D, kv_max, ctxs):
     """GQA groups 1/3/4/7/12/20, both head dims, contexts straddling every tile and

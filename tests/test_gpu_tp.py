@@ -12,12 +12,14 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 
 
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
-@pytest.mark.parametrize("pull_max", ["1", "4"])
-def test_two_rank_decoder_matches_oracle(pull_max):
-    """Two ranks on two GPUs against the oracle, with the exchange consumed by its own
-    add+rmsnorm kernel (pull_max 1, the default) and inside the next projection's
-    prologue (pull_max 4)."""
-    env = dict(os.environ, NCCL_NVLS_ENABLE="0", TLB_TP_PULL_MAX=pull_max)
+@pytest.mark.parametrize("mode", ["sum", "pull", "single_cta"])
+def test_two_rank_decoder_matches_oracle(mode):
+    """Two ranks on two GPUs against the oracle, with the exchange consumed by the multi-CTA
+    packet sum + the next projection's fused add+norm (the default), inside the next
+    projection's prologue (TLB_TP_PULL_MAX=4), and by the older single-CTA add+norm kernel
+    (TLB_TP_SUM=0)."""
+    extra = {"sum": {}, "pull": {"TLB_TP_PULL_MAX": "4"}, "single_cta": {"TLB_TP_SUM": "0"}}[mode]
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0", **extra)
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2",
            "--master-addr", "127.0.0.1", "--master-port", "29611", os.path.join(HERE, "tp_worker.py")]
     r = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=600)
