@@ -29,7 +29,7 @@ size_t attn_partials_bytes(int n_q, int n_kv, long long kv_max, int D, int sm_co
 int attn_decode_launch(DeviceCtx* c, const float* q, const void* K, const void* V, float* out,
                        int n_q, int n_kv, int ctx, long long kv_max, int D, float scale,
                        const unsigned* d_pos, float* partials, int* counters, cudaStream_t stream,
-                       int early_kv, int kv_bf16);
+                       int early_kv, int kv_bf16, const GvStream* prefetch = nullptr);
 int launch_rmsnorm(const float*, const float*, float*, int, float, int, cudaStream_t);
 int launch_add_rmsnorm(const float*, const float*, const float*, float*, float*, int, float, int,
                        cudaStream_t);

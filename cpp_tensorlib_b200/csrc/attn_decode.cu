@@ -445,7 +445,7 @@ int attn_decode_mma_launch(const AttnParams& p, int D, int splits, cudaStream_t 
 int attn_decode_launch(DeviceCtx* c, const float* q, const void* K, const void* V, float* out,
                        int n_q, int n_kv, int ctx, long long kv_max, int D, float scale,
                        const unsigned* d_pos, float* partials, int* counters,
-                       cudaStream_t stream, int early_kv, int kv_bf16) {
+                       cudaStream_t stream, int early_kv, int kv_bf16, const GvStream* prefetch) {
   if (D != 64 && D != 128) return set_error(TLB_ERR_UNSUPPORTED, "attn_decode: D must be 64 or 128");
   if (n_kv <= 0 || n_q <= 0 || n_q % n_kv != 0)
     return set_error(TLB_ERR_ARG, "attn_decode: need n_q > 0, n_kv > 0 and n_q % n_kv == 0");
@@ -570,5 +570,5 @@ extern "C" int tlb_attn_decode_noalloc(const float* q, const float* K, const flo
   local.status = existing ? existing->status : nullptr;
   return attn_decode_launch(&local, q, K, V, out, (int)n_q, (int)n_kv, (int)ctx, kv_max, (int)D,
                             scale, nullptr, (float*)((unsigned char*)nd->ptr + NOALLOC_COUNTER_BYTES),
-                            (int*)nd->ptr, s, 0, 0);
+                            (int*)nd->ptr, s, 0, 0, nullptr);
 }

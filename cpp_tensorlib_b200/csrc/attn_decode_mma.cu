@@ -189,6 +189,12 @@ __global__ void __launch_bounds__(MmaCfg<D>::THREADS, 1)
       issue(i);
     }
   }
+  // every tile of this CTA is requested: ask the L2 for the head of the next kernel's weights
+  if (warp == W && p.pf.wp) {
+    __syncwarp();
+    const unsigned me = blockIdx.y * gridDim.x + blockIdx.x, step = gridDim.x * gridDim.y;
+    for (unsigned nc = me; nc < (unsigned)p.pf.grid; nc += step) gv_prefetch_head(p.pf, nc, lane);
+  }
 
   float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.f, l1 = 0.f;   // heads 2t, 2t+1
   float acc[2 * SEGS][4];

@@ -6,6 +6,7 @@
 #pragma once
 
 #include "attn_common.cuh"
+#include "gemv_q4p.cuh"
 
 namespace tlb {
 
@@ -32,6 +33,7 @@ struct AttnParams {
   int early_kv;  // cache rows below ctx-1 and *d_pos are older than the preceding kernel:
                  // their tiles may be requested before the grid dependency resolves
   unsigned long long* dbg;
+  GvStream pf;   // head of the next kernel's weight stream to request from the L2 (wp == NULL: none)
 };
 
 // CTAs the grid should have: one per SM for wide groups (4 heads per warp: one CTA fits an

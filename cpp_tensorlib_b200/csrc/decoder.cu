@@ -42,7 +42,7 @@ size_t attn_partials_bytes(int n_q, int n_kv, long long kv_max, int D, int sm_co
 int attn_decode_launch(DeviceCtx* c, const float* q, const void* K, const void* V, float* out,
                        int n_q, int n_kv, int ctx, long long kv_max, int D, float scale,
                        const unsigned* d_pos, float* partials, int* counters, cudaStream_t stream,
-                       int early_kv, int kv_bf16);
+                       int early_kv, int kv_bf16, const GvStream* prefetch = nullptr);
 int launch_rmsnorm(const float*, const float*, float*, int, float, int, cudaStream_t);
 int launch_embed_rows(const float*, const int*, float*, int, int, cudaStream_t);
 int launch_rope(const float*, const float*, float*, int, int, int, unsigned, const unsigned*, float,
@@ -167,16 +167,29 @@ struct NormIn {
   const CommDev* pull = nullptr;
 };
 
+// What the decode launch of linear L will stream first (for the kernel in front of it to
+// prefetch); `normed`: launched with the fused add+norm prologue.  Off unless TLB_PREFETCH=1:
+// measured on the 7B decode the L2 prefetch of the next kernel's first ring fill LOSES 7 %
+// (646 against 693 tokens/s) -- the prefetch competes with the demand copies of the warps that
+// are still streaming, and what it brings in is not where the next launch's time goes.
+static GvStream stream_of(DeviceCtx* c, const Linear& L, bool normed) {
+  GvStream g;
+  static const bool on = getenv("TLB_PREFETCH") && atoi(getenv("TLB_PREFETCH")) == 1;
+  if (!on || !L.packed || (normed && (L.K + 255) / 256 > 32)) return g;
+  if (gemv_q4p_stream_of(c, L.packed, L.N, L.K, normed ? 2 : 0, L.pair_h > 0, 0, &g)) g = GvStream();
+  return g;
+}
+
 static int run_linear(DeviceCtx* c, const Linear& L, const float* x, float* y, cudaStream_t s,
                       const CommDev* push, int act = 0, const NormIn* nm = nullptr, float eps = 0.f,
-                      const PairEpi* epi = nullptr) {
+                      const PairEpi* epi = nullptr, const GvStream* next = nullptr) {
   if (!L.q4) return set_error(TLB_ERR_STATE, "decoder: a linear weight was never set");
   if ((epi != nullptr) != (L.pair_h > 0))
     return set_error(TLB_ERR_STATE, "decoder: pair-packed weight and epilogue do not match");
   if (L.packed && !(nm && (L.K + 255) / 256 > 32))
     return gemv_q4p_launch(c, L.packed, x, y, L.N, L.K, 1.0f, 0.0f, s, 0, push, nm ? 2 : act,
                            nm ? nm->delta : nullptr, nm ? nm->w : nullptr, nm ? nm->xout : nullptr, eps,
-                           epi, nm ? nm->pull : nullptr);
+                           epi, nm ? nm->pull : nullptr, next);
   if (epi) return set_error(TLB_ERR_STATE, "decoder: pair epilogue without a packed weight");
   if (nm && nm->pull) return set_error(TLB_ERR_STATE, "decoder: fused exchange without a packed weight");
   if (L.tma && nm)
@@ -262,6 +275,11 @@ static int forward(Decoder* d, cudaStream_t s) {
       const PairEpi* pq = L.wqkv.pair_h > 0 ? &eq : nullptr;
       const PairEpi* pg = L.wgu.pair_h > 0 ? &eg : nullptr;
       const CommDev c_prev = cm(2 * l - 1), c_wo = cm(2 * l), c_wd = cm(2 * l + 1);
+      // each weight-streaming kernel asks the L2 for the head of the next one's stream
+      const GvStream s_wo = stream_of(c, L.wo, false), s_gu = stream_of(c, L.wgu, true),
+                     s_wd = stream_of(c, L.wd, false),
+                     s_nx = l + 1 < d->n_layers ? stream_of(c, d->layers[l + 1].wqkv, true)
+                                                : stream_of(c, d->lm_head, true);
       if (l == 0) {
         RUN(run_linear(c, L.wqkv, d->hb, d->qkv, s, nullptr, 0, nullptr, 0.f, pq));
       } else {
@@ -274,22 +292,28 @@ static int forward(Decoder* d, cudaStream_t s) {
                             d->max_ctx, d->rope_base, c->status, s));
       RUN(attn_decode_launch(c, d->qkv, L.Kc, L.Vc, d->att, d->n_q, d->n_kv, 0, d->max_ctx, d->hd,
                              d->scale, d->d_pos, (float*)((char*)d->attn_partials + 256),
-                             (int*)d->attn_partials, s, 1, 0));
-      RUN(run_linear(c, L.wo, d->att, tp ? nullptr : d->t0, s, tp ? &c_wo : nullptr));
+                             (int*)d->attn_partials, s, 1, 0, &s_wo));
+      RUN(run_linear(c, L.wo, d->att, tp ? nullptr : d->t0, s, tp ? &c_wo : nullptr, 0, nullptr, 0.f, nullptr,
+                     &s_gu));
       if (sum) RUN(launch_ar_sum(d->t0, E, c_wo, c->status, s));
       NormIn nf{pull ? nullptr : d->t0, L.fn, xalt, pull ? &c_wo : nullptr};
-      RUN(run_linear(c, L.wgu, x, d->gu, s, nullptr, 0, &nf, d->eps, pg));
+      RUN(run_linear(c, L.wgu, x, d->gu, s, nullptr, 0, &nf, d->eps, pg, &s_wd));
       { float* t = x; x = xalt; xalt = t; }
       if (pg) {
-        RUN(run_linear(c, L.wd, d->mb, tp ? nullptr : d->t1, s, tp ? &c_wd : nullptr, 0));
+        RUN(run_linear(c, L.wd, d->mb, tp ? nullptr : d->t1, s, tp ? &c_wd : nullptr, 0, nullptr, 0.f, nullptr,
+                       &s_nx));
       } else {
-        RUN(run_linear(c, L.wd, d->gu, tp ? nullptr : d->t1, s, tp ? &c_wd : nullptr, 1));
+        RUN(run_linear(c, L.wd, d->gu, tp ? nullptr : d->t1, s, tp ? &c_wd : nullptr, 1, nullptr, 0.f, nullptr,
+                       &s_nx));
       }
       if (sum) RUN(launch_ar_sum(d->t1, E, c_wd, c->status, s));
     }
     const CommDev c_last = cm(2 * d->n_layers - 1);
     NormIn no{pull ? nullptr : d->t1, d->onorm, xalt, pull ? &c_last : nullptr};
-    RUN(run_linear(c, d->lm_head, x, d->logits, s, nullptr, 0, &no, d->eps));
+    // the next token starts with layer 0's QKV projection (plain prologue: its norm is done
+    // by the embedding gather)
+    const GvStream s_q0 = stream_of(c, d->layers[0].wqkv, false);
+    RUN(run_linear(c, d->lm_head, x, d->logits, s, nullptr, 0, &no, d->eps, nullptr, &s_q0));
     if (tp) {
       RUN(launch_argmax_tp(c, d->logits, d->vocab, d->vocab_offset, cm(2 * d->n_layers), d->d_tok,
                            d->d_tok_out, s));

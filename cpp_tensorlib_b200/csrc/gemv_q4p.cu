@@ -126,6 +126,7 @@ struct GemvPParams {
                     // of a row block are folded by the last CTA to arrive
   int slabs;        // activation slabs a CTA holds in shared memory (SL, or the largest slab block)
   CommDev comm;
+  GvStream pf;      // what the next weight-streaming kernel reads first (wp == NULL: nothing)
 };
 
 struct GemvPSmem {
@@ -635,6 +636,12 @@ __global__ void __launch_bounds__(PK_WARPS * 32, 1) gemv_q4p_kernel(GemvPParams 
       rt++;
     }
   }
+  // This warp's stream has run dry: ask the L2 for the head of the next kernel's weights.
+  if (p.pf.wp) {
+    for (unsigned nc = blockIdx.x + gridDim.x * (unsigned)warp; nc < (unsigned)p.pf.grid;
+         nc += gridDim.x * PK_WARPS)
+      gv_prefetch_head(p.pf, nc, lane);
+  }
   if (own) {
     __syncthreads();
     const int ntl = n_loc / ks;   // row tiles of this block
@@ -725,12 +732,89 @@ static int gemvp_launch_o(const GemvPParams& p, int ctas, size_t smem, cudaStrea
   return gemvp_launch_e<STAGES, PULL, false>(p, ctas, smem, stream);
 }
 
+struct GemvPlan {
+  int ctas = 0, cta_tiles = 0, slabs = 0, stages = 0;
+};
+// Grid, ownership mode and ring depth of a launch (the decisions, without the launch).
+static int gemvp_plan(DeviceCtx* c, int N, int K, int act, bool has_epi, int max_ctas, GemvPlan* out) {
+  GemvPlan pl;
+  pl.stages = gemvp_stages((K + 255) / 256);
+  if (!pl.stages || K % 32) return set_error(TLB_ERR_UNSUPPORTED, "gemv_q4p: K not supported");
+  const int RT = (N + 15) / 16, SL = (K + 255) / 256;
+  const unsigned U = (unsigned)RT * (unsigned)SL;
+  if (RT > c->gemv_max_tiles)
+    return set_error(TLB_ERR_UNSUPPORTED, "gemv_q4p: N exceeds the fix-up counter capacity");
+  int ctas = max_ctas > 0 ? max_ctas : c->sm_count;
+  const int need = (int)((U + PK_WARPS - 1) / PK_WARPS);
+  if (ctas > need) ctas = need;
+  if (ctas * PK_WARPS > c->gemv_max_workers) ctas = c->gemv_max_workers / PK_WARPS;
+  {
+    // CTA-owned row tiles when that leaves every CTA at most about two units per warp
+    int cb = max_ctas > 0 ? max_ctas : c->sm_count;
+    if (cb > RT) cb = RT;
+    const int tiles_max = (RT + cb - 1) / cb;
+    if (tiles_max * SL <= PK_CTA_UNITS && tiles_max * SL <= 2 * PK_WARPS + PK_WARPS / 2) {
+      pl.cta_tiles = 1;
+      ctas = cb;
+    }
+  }
+  pl.slabs = SL;
+  if (!pl.cta_tiles && SL > 2 * PK_WARPS && act <= 1 && !has_epi) {
+    // Long rows (the down projection): every CTA would turn the whole activation into
+    // digits, 16 slabs per round, before its stream can start.  Slab blocks cut that to one
+    // round at the price of a KB-way fold.  Pick KB by a cost model in ns: a unit is 58 ns of a
+    // CTA's share of the stream, a round of activation prep 600 ns, the fold 300 + 100 KB.
+    const int cb = max_ctas > 0 ? max_ctas : c->sm_count;
+    const int workers = ctas * PK_WARPS;
+    const long long base_cost = (long long)((U + workers - 1) / workers) * PK_WARPS * 58 +
+                                (long long)((SL + PK_WARPS - 1) / PK_WARPS) * 600;
+    long long best = base_cost;
+    int best_kb = 0;
+    for (int kb = 2; kb <= 40 && kb <= SL && kb <= cb; kb++) {
+      const int rbn = cb / kb < RT ? cb / kb : RT;
+      const int ksm = (SL + kb - 1) / kb, tm = (RT + rbn - 1) / rbn;
+      if (ksm * tm > PK_CTA_UNITS) continue;
+      if ((size_t)kb * RT * 16 > (size_t)c->gemv_max_workers * 2 * 128) continue;
+      const long long cost = (long long)((ksm * tm + PK_WARPS - 1) / PK_WARPS) * PK_WARPS * 58 +
+                             (long long)((ksm + PK_WARPS - 1) / PK_WARPS) * 600 + 300 + 100 * kb;
+      if (cost < best) { best = cost; best_kb = kb; }
+    }
+    if (best_kb) {
+      const int rbn = cb / best_kb < RT ? cb / best_kb : RT;
+      pl.cta_tiles = best_kb;
+      pl.slabs = (SL + best_kb - 1) / best_kb;
+      ctas = rbn * best_kb;
+      pl.stages = gemvp_stages(pl.slabs);
+    }
+  }
+  pl.ctas = ctas;
+  *out = pl;
+  return TLB_OK;
+}
+
+int gemv_q4p_stream_of(DeviceCtx* c, const void* packed, int N, int K, int act, bool has_epi, int max_ctas,
+                       GvStream* out) {
+  GemvPlan pl;
+  const int rc = gemvp_plan(c, N, K, act, has_epi, max_ctas, &pl);
+  if (rc) return rc;
+  out->wp = (const unsigned char*)packed;
+  out->RT = (N + 15) / 16;
+  out->SL = (K + 255) / 256;
+  out->U = (unsigned)out->RT * (unsigned)out->SL;
+  out->KB = pl.cta_tiles;
+  out->grid = pl.ctas;
+  out->stages = pl.stages;
+  return TLB_OK;
+}
+
 int gemv_q4p_launch(DeviceCtx* c, const void* packed, const float* x, float* y, int N, int K,
                     float alpha, float beta, cudaStream_t stream, int max_ctas,
                     const CommDev* push_comm, int act, const float* delta, const float* nw,
-                    float* xout, float eps, const PairEpi* epi, const CommDev* pull_comm) {
+                    float* xout, float eps, const PairEpi* epi, const CommDev* pull_comm,
+                    const GvStream* prefetch) {
   GemvPParams p;
   memset(&p, 0, sizeof(p));
+  if (prefetch) p.pf = *prefetch;
   if (pull_comm) {
     if (push_comm) return set_error(TLB_ERR_ARG, "gemv_q4p: a launch pulls or pushes, not both");
     act = 3;
@@ -740,8 +824,11 @@ int gemv_q4p_launch(DeviceCtx* c, const void* packed, const float* x, float* y, 
     if (push_comm) return set_error(TLB_ERR_ARG, "gemv_q4p: a pair epilogue cannot push");
     if (N % 16) return set_error(TLB_ERR_ARG, "gemv_q4p: a pair epilogue needs N % 16 == 0");
   }
-  int stages = gemvp_stages((K + 255) / 256);
-  if (!stages || K % 32) return set_error(TLB_ERR_UNSUPPORTED, "gemv_q4p: K not supported");
+  GemvPlan pl;
+  {
+    const int rc = gemvp_plan(c, N, K, act, epi != nullptr, max_ctas, &pl);
+    if (rc) return rc;
+  }
   p.act = act;
   p.delta = delta; p.nw = nw; p.xout = xout; p.eps = eps;
   if (act == 2 && (!delta || !nw || !xout))
@@ -764,51 +851,9 @@ int gemv_q4p_launch(DeviceCtx* c, const void* packed, const float* x, float* y, 
   if (act == 2) vec = vec && ((uintptr_t)delta & 15) == 0;
   if (act == 2 || act == 3) vec = vec && ((uintptr_t)nw & 15) == 0;
   p.x_vec_ok = vec ? 1 : 0;
-  if (p.RT > c->gemv_max_tiles)
-    return set_error(TLB_ERR_UNSUPPORTED, "gemv_q4p: N exceeds the fix-up counter capacity");
-  int ctas = max_ctas > 0 ? max_ctas : c->sm_count;
-  const int need = (int)((p.U + PK_WARPS - 1) / PK_WARPS);
-  if (ctas > need) ctas = need;
-  if (ctas * PK_WARPS > c->gemv_max_workers) ctas = c->gemv_max_workers / PK_WARPS;
-  {
-    // CTA-owned row tiles when that leaves every CTA at most about two units per warp
-    int cb = max_ctas > 0 ? max_ctas : c->sm_count;
-    if (cb > p.RT) cb = p.RT;
-    const int tiles_max = (p.RT + cb - 1) / cb;
-    if (tiles_max * p.SL <= PK_CTA_UNITS && tiles_max * p.SL <= 2 * PK_WARPS + PK_WARPS / 2) {
-      p.cta_tiles = 1;
-      ctas = cb;
-    }
-  }
-  p.slabs = p.SL;
-  if (!p.cta_tiles && p.SL > 2 * PK_WARPS && act <= 1 && !epi) {
-    // Long rows (the down projection): every CTA would turn the whole activation into
-    // digits, 16 slabs per round, before its stream can start.  Slab blocks cut that to one
-    // round at the price of a KB-way fold.  Pick KB by a cost model in ns: a unit is 58 ns of a
-    // CTA's share of the stream, a round of activation prep 600 ns, the fold 300 + 100 KB.
-    const int cb = max_ctas > 0 ? max_ctas : c->sm_count;
-    const int workers = ctas * PK_WARPS;
-    const long long base_cost = (long long)((p.U + workers - 1) / workers) * PK_WARPS * 58 +
-                                (long long)((p.SL + PK_WARPS - 1) / PK_WARPS) * 600;
-    long long best = base_cost;
-    int best_kb = 0;
-    for (int kb = 2; kb <= 40 && kb <= p.SL && kb <= cb; kb++) {
-      const int rbn = cb / kb < p.RT ? cb / kb : p.RT;
-      const int ksm = (p.SL + kb - 1) / kb, tm = (p.RT + rbn - 1) / rbn;
-      if (ksm * tm > PK_CTA_UNITS) continue;
-      if ((size_t)kb * p.RT * 16 > (size_t)c->gemv_max_workers * 2 * 128) continue;
-      const long long cost = (long long)((ksm * tm + PK_WARPS - 1) / PK_WARPS) * PK_WARPS * 58 +
-                             (long long)((ksm + PK_WARPS - 1) / PK_WARPS) * 600 + 300 + 100 * kb;
-      if (cost < best) { best = cost; best_kb = kb; }
-    }
-    if (best_kb) {
-      const int rbn = cb / best_kb < p.RT ? cb / best_kb : p.RT;
-      p.cta_tiles = best_kb;
-      p.slabs = (p.SL + best_kb - 1) / best_kb;
-      ctas = rbn * best_kb;
-      stages = gemvp_stages(p.slabs);
-    }
-  }
+  p.cta_tiles = pl.cta_tiles;
+  p.slabs = pl.slabs;
+  const int ctas = pl.ctas, stages = pl.stages;
   const size_t smem = gemvp_smem_layout(stages, p.slabs).total;
   if (p.act == 3) {
     if (stages == 4) return gemvp_launch_o<4, true>(p, ctas, smem, stream);
