@@ -235,7 +235,9 @@ __global__ void __launch_bounds__(MmaCfg<D>::THREADS, 1)
           __syncwarp();
         }
         // ---- S^T = K_blk . Q^T ----
-        float s[4] = {0.f, 0.f, 0.f, 0.f};
+        // three accumulators, one per term of the split product: three independent MMA chains
+        // of KSTEPS instead of one of 3 KSTEPS (the chain's latency is what a block costs)
+        float s[4] = {0.f, 0.f, 0.f, 0.f}, s_hl[4] = {0.f, 0.f, 0.f, 0.f}, s_lh[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
         for (int ks = 0; ks < KSTEPS; ks++) {
           const uint32_t c0 = (uint32_t)((ks & 3) * 2) << 4;
@@ -249,9 +251,11 @@ __global__ void __launch_bounds__(MmaCfg<D>::THREADS, 1)
           split_tf32(k2, h2, e2);
           split_tf32(k3, h3, e3);
           mma_tf32(s, h0, h1, h2, h3, qf.x, qf.y);
-          mma_tf32(s, h0, h1, h2, h3, qf.z, qf.w);
-          mma_tf32(s, e0, e1, e2, e3, qf.x, qf.y);
+          mma_tf32(s_hl, h0, h1, h2, h3, qf.z, qf.w);
+          mma_tf32(s_lh, e0, e1, e2, e3, qf.x, qf.y);
         }
+#pragma unroll
+        for (int i = 0; i < 4; i++) s[i] += s_hl[i] + s_lh[i];
         // s[0], s[1]: key g, heads 2t, 2t+1;  s[2], s[3]: key g + 8
         if (g >= valid) s[0] = s[1] = -INFINITY;
         if (g + 8 >= valid) s[2] = s[3] = -INFINITY;

@@ -24,3 +24,18 @@ def test_two_rank_decoder_matches_oracle(mode):
            "--master-addr", "127.0.0.1", "--master-port", "29611", os.path.join(HERE, "tp_worker.py")]
     r = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=600)
     assert "TP_OK" in r.stdout, r.stdout[-2000:] + r.stderr[-2000:]
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")
+def test_ranks_at_the_7b_shape_match_oracle():
+    """BASELINE config 5's shape (2 of its layers, the full 152064-row vocabulary, caches
+    pre-filled to ctx 4096) sharded over every GPU of the box (2, 4 or 8 ranks): logits shards
+    within 1e-3 of the unsharded oracle and identical greedy ids at every step, from the
+    host-buffer loop and from the device-resident loop."""
+    n = torch.cuda.device_count()
+    world = 8 if n >= 8 else (4 if n >= 4 else 2)
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0", TLB_TP_CFG="7b2")
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={world}",
+           "--master-addr", "127.0.0.1", "--master-port", "29613", os.path.join(HERE, "tp_worker.py")]
+    r = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=1200)
+    assert "TP_OK" in r.stdout, r.stdout[-2000:] + r.stderr[-2000:]
