@@ -56,6 +56,14 @@ SIGNATURES = {
     "tlb_q4p_bytes": (i64, [i64, i64]),
     "tlb_q4_pack": (ci, [vp, i64, i64, vp, vp]),
     "tlb_gemv_q4p": (ci, [vp, vp, vp, i64, i64, f32, f32, vp]),
+    "tlb_binary": (ci, [ci, vp, vp, vp, i64, f32, f32, vp]),
+    "tlb_binary_bcast": (ci, [ci, vp, i64, i64, vp, i64, i64, vp, i64, i64, f32, f32, vp]),
+    "tlb_unary": (ci, [ci, vp, vp, i64, f32, f32, vp]),
+    "tlb_row_op": (ci, [ci, vp, vp, i64, i64, f32, f32, vp]),
+    "tlb_gemm_f32": (ci, [vp, i64, ci, vp, i64, ci, vp, i64, i64, i64, f32, f32, vp]),
+    "tlb_gemm_bf16_nt": (ci, [vp, vp, vp, i64, i64, i64, vp]),
+    "tlb_gemv_f32": (ci, [vp, vp, vp, i64, i64, vp]),
+    "tlb_gemv_bf16": (ci, [vp, vp, vp, i64, i64, vp]),
     "tlb_split_heads": (ci, [vp, vp, vp, i64, i64, i64, i64, i64, vp]),
     "tlb_merge_heads": (ci, [vp, vp, i64, i64, i64, vp]),
     "tlb_kv_fill": (ci, [vp, vp, vp, vp, i64, i64, i64, i64, i64, vp]),

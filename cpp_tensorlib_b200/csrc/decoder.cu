@@ -182,14 +182,16 @@ static GvStream stream_of(DeviceCtx* c, const Linear& L, bool normed) {
 
 static int run_linear(DeviceCtx* c, const Linear& L, const float* x, float* y, cudaStream_t s,
                       const CommDev* push, int act = 0, const NormIn* nm = nullptr, float eps = 0.f,
-                      const PairEpi* epi = nullptr, const GvStream* next = nullptr) {
+                      const PairEpi* epi = nullptr, const GvStream* next = nullptr, float* push_sum = nullptr,
+                      int push_sum_n = 0) {
   if (!L.q4) return set_error(TLB_ERR_STATE, "decoder: a linear weight was never set");
   if ((epi != nullptr) != (L.pair_h > 0))
     return set_error(TLB_ERR_STATE, "decoder: pair-packed weight and epilogue do not match");
   if (L.packed && !(nm && (L.K + 255) / 256 > 32))
     return gemv_q4p_launch(c, L.packed, x, y, L.N, L.K, 1.0f, 0.0f, s, 0, push, nm ? 2 : act,
                            nm ? nm->delta : nullptr, nm ? nm->w : nullptr, nm ? nm->xout : nullptr, eps,
-                           epi, nm ? nm->pull : nullptr, next);
+                           epi, nm ? nm->pull : nullptr, next, push_sum, push_sum_n);
+  if (push_sum) return set_error(TLB_ERR_STATE, "decoder: the fused exchange sum needs a packed weight");
   if (epi) return set_error(TLB_ERR_STATE, "decoder: pair epilogue without a packed weight");
   if (nm && nm->pull) return set_error(TLB_ERR_STATE, "decoder: fused exchange without a packed weight");
   if (L.tma && nm)
@@ -249,24 +251,27 @@ static int forward(Decoder* d, cudaStream_t s) {
     c2.E = EX;
     return c2;
   };
-  // How a tensor-parallel exchange is consumed.  Default: a small multi-CTA kernel sums the
-  // ranks' packets into a local vector (ar_sum_kernel) and the next projection's ordinary fused
-  // add+norm prologue reads that vector -- one short extra launch per exchange, no system-scope
-  // polling from 148 CTAs.  TLB_TP_PULL_MAX = largest rank count whose exchanges are instead
+  // How a tensor-parallel exchange is consumed.  Default (TLB_TP_SUM=2): the CTA of the pushing
+  // projection that finishes last sums the ranks' packets into a local vector (gemv_sum_tail)
+  // and the next projection's ordinary fused add+norm prologue reads that vector -- the
+  // all-reduce has no kernel of its own.  TLB_TP_SUM=1: the same sum as a small multi-CTA kernel
+  // (ar_sum_kernel), one short extra launch per exchange.  TLB_TP_PULL_MAX = largest rank count whose exchanges are instead
   // consumed inside the next projection's prologue (it polls the packets itself: two kernels
   // fewer per layer, measured slower on 2 GPUs, 582 vs 589 tok/s); TLB_TP_SUM=0 selects the
   // older single-CTA add+norm consumer (add_rmsnorm_ar_kernel).
   const char* pm = getenv("TLB_TP_PULL_MAX");
   const int pull_max = pm ? atoi(pm) : 1;
   const char* ts = getenv("TLB_TP_SUM");
-  const bool tp_sum = !(ts && atoi(ts) == 0);
+  const int tp_sum_mode = ts ? atoi(ts) : 2;   // 2: sum in the pushing kernel's tail; 1: ar_sum_kernel
+  const bool tp_sum = tp_sum_mode != 0;
   const bool pull = tp && d->tp_size <= pull_max;
   if (all_tma && (!tp || pull || tp_sum)) {
     // Both residual adds and norms of a layer run inside the following projection's
     // activation prep (5 launches per layer, + one packet-sum launch per exchange when tensor
     // parallel).  The residual ping-pongs between two buffers because every CTA of the
     // projection reads it while one CTA writes the new sum.
-    const bool sum = tp && !pull;
+    const bool sum = tp && !pull && tp_sum_mode == 1;      // separate packet-sum kernel
+    const bool tail = tp && !pull && tp_sum_mode != 1;     // the pushing kernel's last CTA sums
     float* x = d->x;
     float* xalt = d->xb;
     for (int l = 0; l < d->n_layers; l++) {
@@ -294,17 +299,17 @@ static int forward(Decoder* d, cudaStream_t s) {
                              d->scale, d->d_pos, (float*)((char*)d->attn_partials + 256),
                              (int*)d->attn_partials, s, 1, 0, &s_wo));
       RUN(run_linear(c, L.wo, d->att, tp ? nullptr : d->t0, s, tp ? &c_wo : nullptr, 0, nullptr, 0.f, nullptr,
-                     &s_gu));
+                     &s_gu, tail ? d->t0 : nullptr, E));
       if (sum) RUN(launch_ar_sum(d->t0, E, c_wo, c->status, s));
       NormIn nf{pull ? nullptr : d->t0, L.fn, xalt, pull ? &c_wo : nullptr};
       RUN(run_linear(c, L.wgu, x, d->gu, s, nullptr, 0, &nf, d->eps, pg, &s_wd));
       { float* t = x; x = xalt; xalt = t; }
       if (pg) {
         RUN(run_linear(c, L.wd, d->mb, tp ? nullptr : d->t1, s, tp ? &c_wd : nullptr, 0, nullptr, 0.f, nullptr,
-                       &s_nx));
+                       &s_nx, tail ? d->t1 : nullptr, E));
       } else {
         RUN(run_linear(c, L.wd, d->gu, tp ? nullptr : d->t1, s, tp ? &c_wd : nullptr, 1, nullptr, 0.f, nullptr,
-                       &s_nx));
+                       &s_nx, tail ? d->t1 : nullptr, E));
       }
       if (sum) RUN(launch_ar_sum(d->t1, E, c_wd, c->status, s));
     }

@@ -127,6 +127,12 @@ struct GemvPParams {
   int slabs;        // activation slabs a CTA holds in shared memory (SL, or the largest slab block)
   CommDev comm;
   GvStream pf;      // what the next weight-streaming kernel reads first (wp == NULL: nothing)
+  // push mode only: the CTA that finishes last also REDUCES the exchange -- it polls every
+  // rank's packets of this exchange in this rank's staging and leaves their sum (rank order)
+  // in sum_out[0..sum_n), so the all-reduce needs no kernel of its own
+  float* sum_out;
+  int sum_n;
+  int* sum_ticket;
 };
 
 struct GemvPSmem {
@@ -171,6 +177,47 @@ __device__ __forceinline__ float lds32f(uint32_t a) {
   float v;
   asm volatile("ld.shared.f32 %0, [%1];" : "=f"(v) : "r"(a) : "memory");
   return v;
+}
+
+// Tail of a pushing launch (tensor parallel): a ticket elects the CTA that finishes last; it
+// polls the packets all ranks pushed for this exchange (bounded), adds them in rank order --
+// every rank computes the same bits -- and writes the sum to local memory, where the next
+// projection's fused add+norm prologue reads it as an ordinary vector.  Kept out of line so
+// its registers do not count against the streaming loop.
+__device__ __noinline__ void gemv_sum_tail(const CommDev& comm, unsigned seq, float* out, int n, int* ticket,
+                                           int* status, int* flag) {
+  __syncthreads();                       // every thread's pushes are issued
+  if (threadIdx.x == 0) *flag = (int)atom_add_acq_rel(ticket, 1);
+  __syncthreads();
+  if (*flag != (int)gridDim.x - 1) return;
+  const uint2* st = comm.stage[comm.rank] + (size_t)(seq & 1u) * comm.size * comm.slot_floats;
+  const unsigned tag = seq + 1u;
+  constexpr int J = 4;                   // elements per thread with all their polls in flight
+  for (int i0 = threadIdx.x; i0 < n; i0 += blockDim.x * J) {
+    uint2 pk[J][TP_MAX];
+#pragma unroll
+    for (int j = 0; j < J; j++) {
+      const int i = i0 + j * blockDim.x;
+#pragma unroll
+      for (int r = 0; r < TP_MAX; r++)
+        if (r < comm.size && i < n) pk[j][r] = ld_packet_sys(st + (size_t)r * comm.slot_floats + i);
+    }
+#pragma unroll
+    for (int j = 0; j < J; j++) {
+      const int i = i0 + j * blockDim.x;
+      if (i >= n) continue;
+      float d = 0.f;
+#pragma unroll
+      for (int r = 0; r < TP_MAX; r++)
+        if (r < comm.size) {
+          if (pk[j][r].y != tag)
+            pk[j][r] = wait_packet_bounded(st + (size_t)r * comm.slot_floats + i, tag, status, 300 + r);
+          d += __uint_as_float(pk[j][r].x);
+        }
+      out[i] = d;
+    }
+  }
+  if (threadIdx.x == 0) *ticket = 0;     // clean for the next launch
 }
 
 // PULL: the instantiation that can consume a tensor-parallel exchange in its prologue (act 3);
@@ -670,7 +717,10 @@ __global__ void __launch_bounds__(PK_WARPS * 32, 1) gemv_q4p_kernel(GemvPParams 
         __stcg(p.partials + ((size_t)kb * p.RT + tile_b + tl) * 16 + row, sum);
       }
     }
-    if (KB == 1) return;
+    if (KB == 1) {
+      if (p.sum_out) gemv_sum_tail(p.comm, ar_seq, p.sum_out, p.sum_n, p.sum_ticket, p.status, (int*)red);
+      return;
+    }
     // Slab blocks: the row block's KB partial blocks meet in global memory; the CTA that
     // arrives last folds them in block order (the same bits whichever CTA that is).
     __threadfence();
@@ -678,7 +728,10 @@ __global__ void __launch_bounds__(PK_WARPS * 32, 1) gemv_q4p_kernel(GemvPParams 
     int* flag = (int*)red;
     if (tid == 0) *flag = (int)atom_add_acq_rel(&p.counters[rb], 1);
     __syncthreads();
-    if (*flag != (int)KB - 1) return;
+    if (*flag != (int)KB - 1) {
+      if (p.sum_out) gemv_sum_tail(p.comm, ar_seq, p.sum_out, p.sum_n, p.sum_ticket, p.status, (int*)red);
+      return;
+    }
     __threadfence();
     for (int idx = tid; idx < ntl * 16; idx += PK_WARPS * 32) {
       const size_t off = (size_t)(tile_b + (idx >> 4)) * 16 + (idx & 15);
@@ -694,9 +747,11 @@ __global__ void __launch_bounds__(PK_WARPS * 32, 1) gemv_q4p_kernel(GemvPParams 
       if ((int)off < p.N) emit((int)off, sum);
     }
     if (tid == 0) p.counters[rb] = 0;  // clean for the next launch
+    if (p.sum_out) gemv_sum_tail(p.comm, ar_seq, p.sum_out, p.sum_n, p.sum_ticket, p.status, (int*)red);
     return;
   }
   if (n_units > 0 && s != 0) flush(rt);
+  if (p.sum_out) gemv_sum_tail(p.comm, ar_seq, p.sum_out, p.sum_n, p.sum_ticket, p.status, (int*)red);
 }
 
 static int gemvp_stages(int slabs) {
@@ -811,10 +866,17 @@ int gemv_q4p_launch(DeviceCtx* c, const void* packed, const float* x, float* y, 
                     float alpha, float beta, cudaStream_t stream, int max_ctas,
                     const CommDev* push_comm, int act, const float* delta, const float* nw,
                     float* xout, float eps, const PairEpi* epi, const CommDev* pull_comm,
-                    const GvStream* prefetch) {
+                    const GvStream* prefetch, float* push_sum_out, int push_sum_n) {
   GemvPParams p;
   memset(&p, 0, sizeof(p));
   if (prefetch) p.pf = *prefetch;
+  if (push_sum_out) {
+    if (!push_comm || push_sum_n > push_comm->slot_floats)
+      return set_error(TLB_ERR_ARG, "gemv_q4p: the fused exchange sum needs a pushing launch and n within the staging slot");
+    p.sum_out = push_sum_out;
+    p.sum_n = push_sum_n;
+    p.sum_ticket = c->gemv_counters + c->gemv_max_tiles;   // one word behind the row-tile tickets
+  }
   if (pull_comm) {
     if (push_comm) return set_error(TLB_ERR_ARG, "gemv_q4p: a launch pulls or pushes, not both");
     act = 3;

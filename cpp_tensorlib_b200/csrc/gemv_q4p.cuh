@@ -46,7 +46,7 @@ int gemv_q4p_launch(DeviceCtx* c, const void* packed, const float* x, float* y, 
                     float alpha, float beta, cudaStream_t stream, int max_ctas,
                     const CommDev* push_comm, int act, const float* delta, const float* nw,
                     float* xout, float eps, const PairEpi* epi, const CommDev* pull_comm,
-                    const GvStream* prefetch = nullptr);
+                    const GvStream* prefetch = nullptr, float* push_sum_out = nullptr, int push_sum_n = 0);
 // The walk a launch with these arguments would take (same decisions as gemv_q4p_launch).
 int gemv_q4p_stream_of(DeviceCtx* c, const void* packed, int N, int K, int act, bool has_epi, int max_ctas,
                        GvStream* out);

@@ -10,11 +10,12 @@
 //
 // Scope: the quantized-decode path -- gemv_q4, attn_decode(+_dpos), rope(+_dpos),
 // rmsnorm, rmsnorm_res, swiglu, argmax, kv_append(+_dpos), kv_cache (f32 or bf16), incr_u32, graph
-// capture, the host/device mirror (alloc / release / sync_to_host / upload).  Ops
-// outside that path (elementwise, f32 GEMM, row reductions, f32/bf16 GEMV) decline with `false`, which the reference evaluator answers with its
-// own CPU code -- the same contract its stub backend uses.  A hot-path op that the
-// library refuses is NOT declined: it throws, because silently computing a decode
-// op on the CPU is exactly what this backend exists to prevent.
+// capture, the host/device mirror (alloc / release / sync_to_host / upload) -- and the rest of
+// the evaluator's GPU surface (elementwise and broadcast binaries, unary ops, row reductions and
+// softmax, f32 GEMM, f32 / bf16 GEMVs and the bf16 prefill GEMM), so a graph evaluated under
+// tl::use_gpu() stays on the device between hot ops.  An op the library refuses is NOT
+// declined: it throws, because silently computing a decode op on the CPU is exactly what
+// this backend exists to prevent.
 #pragma once
 
 #include <dlfcn.h>
@@ -99,6 +100,16 @@ struct backend {
   int (*kv_fill)(float*, float*, const float*, const float*, int64_t, int64_t, int64_t, int64_t, int64_t, void*) = nullptr;
   int (*attn_prefill)(const float*, const float*, const float*, float*, int64_t, int64_t, int64_t, int64_t,
                       int64_t, float, int64_t, void*) = nullptr;
+  int (*binary_)(int, const float*, const float*, float*, int64_t, float, float, void*) = nullptr;
+  int (*binary_bcast_)(int, const float*, int64_t, int64_t, const float*, int64_t, int64_t, float*, int64_t,
+                       int64_t, float, float, void*) = nullptr;
+  int (*unary_)(int, const float*, float*, int64_t, float, float, void*) = nullptr;
+  int (*row_op_)(int, const float*, float*, int64_t, int64_t, float, float, void*) = nullptr;
+  int (*gemm_f32_)(const float*, int64_t, int, const float*, int64_t, int, float*, int64_t, int64_t, int64_t,
+                   float, float, void*) = nullptr;
+  int (*gemm_bf16_nt_)(const float*, const void*, float*, int64_t, int64_t, int64_t, void*) = nullptr;
+  int (*gemv_f32_)(const float*, const float*, float*, int64_t, int64_t, void*) = nullptr;
+  int (*gemv_bf16_)(const float*, const void*, float*, int64_t, int64_t, void*) = nullptr;
   int (*capture_begin)(void**) = nullptr;
   int (*capture_end)(void**) = nullptr;
   int (*graph_launch)(void*, void*) = nullptr;
@@ -198,7 +209,10 @@ struct backend {
               bind(attn_prefill, "tlb_attn_prefill") && bind(capture_begin, "tlb_capture_begin") &&
               bind(capture_end, "tlb_capture_end") && bind(graph_launch, "tlb_graph_launch") &&
               bind(graph_destroy, "tlb_graph_destroy") && bind(swiglu_split, "tlb_swiglu_split") &&
-              bind(gemm_q4, "tlb_gemm_q4");
+              bind(gemm_q4, "tlb_gemm_q4") && bind(binary_, "tlb_binary") &&
+              bind(binary_bcast_, "tlb_binary_bcast") && bind(unary_, "tlb_unary") && bind(row_op_, "tlb_row_op") &&
+              bind(gemm_f32_, "tlb_gemm_f32") && bind(gemm_bf16_nt_, "tlb_gemm_bf16_nt") &&
+              bind(gemv_f32_, "tlb_gemv_f32") && bind(gemv_bf16_, "tlb_gemv_bf16");
     if (!ok || device_count() <= 0) return;
     ready = init(0) == 0;
   }
@@ -319,17 +333,99 @@ inline void upload_u32(void* native, unsigned val) {
   t->where = detail::backend::BOTH;
 }
 
-// ---- ops outside the quantized-decode path: declined (the evaluator runs its own
-// CPU code for them, as with the reference's stub backend) ----
-inline bool binary(kop, void*, int64_t, void*, int64_t, void*, int64_t, int64_t, float, float) { return false; }
-inline bool binary_bcast(kop, void*, int64_t, int64_t, int64_t, void*, int64_t, int64_t, int64_t,
-                         void*, int64_t, int64_t, int64_t, float, float) { return false; }
-inline bool unary(kop, void*, int64_t, void*, int64_t, int64_t, float, float) { return false; }
-inline bool gemm(void*, int64_t, int64_t, bool, void*, int64_t, int64_t, bool, void*, int64_t,
-                 int64_t, int64_t, int64_t, float, float) { return false; }
-inline bool row_op(kop, void*, int64_t, void*, int64_t, int64_t, int64_t, float, float) { return false; }
-inline bool gemv_f32(void*, void*, void*, int64_t, int64_t) { return false; }
-inline bool gemv_bf16(void*, void*, void*, int64_t, int64_t) { return false; }
+// ---- the rest of the evaluator's surface (reference cuda.h:640-742, 1409-1503): on the device
+// too, so a graph evaluated under tl::use_gpu() does not bounce to the host between hot ops.
+// Offsets are in BYTES (reference array.h:1480-1482 passes offset_ * 4). ----
+namespace detail {
+inline const float* at(void* p, int64_t byte_off) {
+  return reinterpret_cast<const float*>(static_cast<const char*>(p) + byte_off);
+}
+inline float* at_w(void* p, int64_t byte_off) { return reinterpret_cast<float*>(static_cast<char*>(p) + byte_off); }
+inline int bin_code(kop op) {
+  switch (op) {
+    case kop::add: case kop::badd: return 0;
+    case kop::sub: case kop::bsub: return 1;
+    case kop::mul: case kop::bmul: return 2;
+    case kop::div: case kop::bdiv: return 3;
+    case kop::pow_: case kop::bpow: return 4;
+    default: return -1;
+  }
+}
+inline int una_code(kop op) {
+  switch (op) {
+    case kop::exp_: return 0;
+    case kop::log_: return 1;
+    case kop::sqrt_: return 2;
+    case kop::sigmoid: return 3;
+    case kop::relu: return 4;
+    case kop::affine: return 5;
+    default: return -1;
+  }
+}
+}  // namespace detail
+
+inline bool binary(kop op, void* a, int64_t ao, void* b_, int64_t bo, void* out, int64_t oo, int64_t n,
+                   float scale, float offset) {
+  auto& b = detail::backend::get();
+  const int code = detail::bin_code(op);
+  if (!b.ready || code < 0) return false;
+  b.reads(a); b.reads(b_); b.writes(out);
+  b.must(b.binary_(code, detail::at(a, ao), detail::at(b_, bo), detail::at_w(out, oo), n, scale, offset, b.stream),
+         "binary");
+  return true;
+}
+inline bool binary_bcast(kop op, void* a, int64_t ao, int64_t ars, int64_t acs, void* b_, int64_t bo, int64_t brs,
+                         int64_t bcs, void* out, int64_t oo, int64_t rows, int64_t cols, float scale,
+                         float offset) {
+  auto& b = detail::backend::get();
+  const int code = detail::bin_code(op);
+  if (!b.ready || code < 0) return false;
+  b.reads(a); b.reads(b_); b.writes(out);
+  b.must(b.binary_bcast_(code, detail::at(a, ao), ars, acs, detail::at(b_, bo), brs, bcs, detail::at_w(out, oo),
+                         rows, cols, scale, offset, b.stream), "binary_bcast");
+  return true;
+}
+inline bool unary(kop op, void* a, int64_t ao, void* out, int64_t oo, int64_t n, float scale, float offset) {
+  auto& b = detail::backend::get();
+  const int code = detail::una_code(op);
+  if (!b.ready || code < 0) return false;
+  b.reads(a); b.writes(out);
+  b.must(b.unary_(code, detail::at(a, ao), detail::at_w(out, oo), n, scale, offset, b.stream), "unary");
+  return true;
+}
+inline bool gemm(void* a, int64_t ao, int64_t lda, bool ta, void* b_, int64_t bo, int64_t ldb, bool tb,
+                 void* out, int64_t oo, int64_t m, int64_t n, int64_t k, float scale, float offset) {
+  auto& b = detail::backend::get();
+  if (!b.ready) return false;
+  b.reads(a); b.reads(b_); b.writes(out);
+  b.must(b.gemm_f32_(detail::at(a, ao), lda, ta ? 1 : 0, detail::at(b_, bo), ldb, tb ? 1 : 0,
+                     detail::at_w(out, oo), m, n, k, scale, offset, b.stream), "gemm");
+  return true;
+}
+inline bool row_op(kop op, void* in, int64_t io, void* out, int64_t oo, int64_t rows, int64_t cols, float scale,
+                   float offset) {
+  auto& b = detail::backend::get();
+  const int code = op == kop::softmax ? 0 : (op == kop::row_sum ? 1 : (op == kop::row_max ? 2 : -1));
+  if (!b.ready || code < 0 || cols <= 0) return false;
+  b.reads(in); b.writes(out);
+  b.must(b.row_op_(code, detail::at(in, io), detail::at_w(out, oo), rows, cols, scale, offset, b.stream), "row_op");
+  return true;
+}
+// decode GEMV on [K,N] weights (reference cuda.h:719-742)
+inline bool gemv_f32(void* a, void* B, void* y, int64_t n, int64_t k) {
+  auto& b = detail::backend::get();
+  if (!b.ready || n <= 0 || k <= 0) return false;
+  b.reads(a); b.reads(B); b.writes(y);
+  b.must(b.gemv_f32_(detail::f(a), detail::f(B), detail::fw(y), n, k, b.stream), "gemv_f32");
+  return true;
+}
+inline bool gemv_bf16(void* a, void* B, void* y, int64_t n, int64_t k) {
+  auto& b = detail::backend::get();
+  if (!b.ready || n <= 0 || k <= 0) return false;
+  b.reads(a); b.reads(B); b.writes(y);
+  b.must(b.gemv_bf16_(detail::f(a), B, detail::fw(y), n, k, b.stream), "gemv_bf16");
+  return true;
+}
 // bf16 row-major weights [N][K] (reference cuda.h:770-785): the decode projection of the
 // reference's bf16-weight models
 inline bool gemv_bf16_row(void* a, void* B, void* y, int64_t n, int64_t k) {
@@ -339,7 +435,14 @@ inline bool gemv_bf16_row(void* a, void* B, void* y, int64_t n, int64_t k) {
   b.must(b.gemv_bf16_row_(detail::f(a), B, detail::fw(y), n, k, b.stream), "gemv_bf16_row");
   return true;
 }
-inline bool gemm_bf16_nt(void*, void*, void*, int64_t, int64_t, int64_t) { return false; }
+// weight-native prefill GEMM on bf16 [N,K] weights (reference cuda.h:790-841)
+inline bool gemm_bf16_nt(void* A, void* W, void* C, int64_t M, int64_t N, int64_t K) {
+  auto& b = detail::backend::get();
+  if (!b.ready || M <= 0 || N <= 0 || K <= 0) return false;
+  b.reads(A); b.reads(W); b.writes(C);
+  b.must(b.gemm_bf16_nt_(detail::f(A), W, detail::fw(C), M, N, K, b.stream), "gemm_bf16_nt");
+  return true;
+}
 
 // ---- the quantized-decode path ----
 inline bool gemv_q4(void* a, void* qw, void* scales, void* y, int64_t N, int64_t K, int64_t group) {

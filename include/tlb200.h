@@ -162,6 +162,49 @@ int tlb_argmax(const float* in, int64_t n, int64_t* out_idx, void* stream);
 /* Asynchronous form: the int32 index is written to d_out (device), no sync. */
 int tlb_argmax_dev(const float* in, int64_t n, void* d_out, void* stream);
 
+/* ---- the rest of the evaluator's GPU surface (elementwise, broadcast, row ops, f32 GEMM,
+ * [K,N]-layout GEMVs, bf16 prefill GEMM).  Every kernel computes out = expr * scale + offset
+ * like the reference's (.cu:25-82). ---- */
+#define TLB_OP_ADD 0
+#define TLB_OP_SUB 1
+#define TLB_OP_MUL 2
+#define TLB_OP_DIV 3
+#define TLB_OP_POW 4   /* the reference declines pow on CUDA (cu.h:642); here it runs on the device */
+#define TLB_UOP_EXP 0
+#define TLB_UOP_LOG 1
+#define TLB_UOP_SQRT 2
+#define TLB_UOP_SIGMOID 3
+#define TLB_UOP_RELU 4
+#define TLB_UOP_AFFINE 5
+#define TLB_ROW_SOFTMAX 0
+#define TLB_ROW_SUM 1
+#define TLB_ROW_MAX 2
+/* cu.h:640-655 cuda::binary / .cu:25-36: out[i] = (a[i] OP b[i]) * scale + offset */
+int tlb_binary(int op, const float* a, const float* b, float* out, int64_t n, float scale, float offset,
+               void* stream);
+/* cu.h:658-662 cuda::binary_bcast (declined by the reference's CUDA backend; arr:1487-1506 gives
+ * the contract): out[r,c] = (a[r*a_rs + c*a_cs] OP b[r*b_rs + c*b_cs]) * scale + offset,
+ * strides in elements, 0 for a broadcast axis */
+int tlb_binary_bcast(int op, const float* a, int64_t a_rs, int64_t a_cs, const float* b, int64_t b_rs,
+                     int64_t b_cs, float* out, int64_t rows, int64_t cols, float scale, float offset,
+                     void* stream);
+/* cu.h:664-675 cuda::unary / .cu:38-51 */
+int tlb_unary(int op, const float* a, float* out, int64_t n, float scale, float offset, void* stream);
+/* cu.h:1487-1503 cuda::row_op / .cu:53-82, 222-258: softmax writes rows x cols (scale / offset
+ * ignored), row_sum / row_max one value per row */
+int tlb_row_op(int op, const float* in, float* out, int64_t rows, int64_t cols, float scale, float offset,
+               void* stream);
+/* cu.h:1409-1483 cuda::gemm / .cu:262-421: C[m,n] = (A . B) * scale + offset, C contiguous,
+ * A(i,k) = ta ? A[k*lda+i] : A[i*lda+k], B(k,j) = tb ? B[j*ldb+k] : B[k*ldb+j] */
+int tlb_gemm_f32(const float* a, int64_t lda, int ta, const float* b, int64_t ldb, int tb, float* out,
+                 int64_t m, int64_t n, int64_t k, float scale, float offset, void* stream);
+/* cu.h:790-841 cuda::gemm_bf16_nt / .cu:474-595: C[M,N] = A[M,K] . W^T, W bf16 row-major [N,K] */
+int tlb_gemm_bf16_nt(const float* a, const void* w, float* c, int64_t M, int64_t N, int64_t K, void* stream);
+/* cu.h:719-742 cuda::gemv_f32 / gemv_bf16, .cu:611-682: y[n] = sum_k a[k] * B[k*n_cols + n],
+ * B row-major [K,N] f32 or bf16 */
+int tlb_gemv_f32(const float* a, const float* B, float* y, int64_t n, int64_t k, void* stream);
+int tlb_gemv_bf16(const float* a, const void* B, float* y, int64_t n, int64_t k, void* stream);
+
 /* ---- batched prefill (the "next" row: prompt chunks instead of token-by-token) ---- */
 /* cu.h:848-864 split_heads: [T, ld] token-major (column block at `off`) -> [H, T, D], + bias[H*D] */
 int tlb_split_heads(const float* src, const float* bias, float* dst, int64_t T, int64_t ld,
