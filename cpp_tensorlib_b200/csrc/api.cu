@@ -99,9 +99,8 @@ static int create_ctx(int dev, DeviceCtx** out) {
   c->gemv_max_workers = c->sm_count * 2 * 8;
   c->gemv_max_tiles = 1 << 16;  // N up to 1,048,576 rows
   TLB_CUDA(cudaMalloc(&c->gemv_partials, (size_t)c->gemv_max_workers * 2 * 128 * sizeof(float)));
-  // row-tile tickets + 64 spare words (the exchange-sum ticket of a pushing launch)
-  TLB_CUDA(cudaMalloc(&c->gemv_counters, (size_t)(c->gemv_max_tiles + 64) * sizeof(int)));
-  TLB_CUDA(cudaMemset(c->gemv_counters, 0, (size_t)(c->gemv_max_tiles + 64) * sizeof(int)));
+  TLB_CUDA(cudaMalloc(&c->gemv_counters, (size_t)c->gemv_max_tiles * sizeof(int)));
+  TLB_CUDA(cudaMemset(c->gemv_counters, 0, (size_t)c->gemv_max_tiles * sizeof(int)));
   c->attn_max_counters = 1024;
   TLB_CUDA(cudaMalloc(&c->attn_counters, c->attn_max_counters * sizeof(int)));
   TLB_CUDA(cudaMemset(c->attn_counters, 0, c->attn_max_counters * sizeof(int)));
@@ -195,7 +194,7 @@ int tlb_device_status(int* out2, int clear) {
     TLB_CUDA(cudaMemset(&c->status[ST_KV_OVERFLOW], 0, sizeof(int)));
     if (timed_out) {
       // a kernel that gave up may have left its fix-up tickets half counted
-      TLB_CUDA(cudaMemset(c->gemv_counters, 0, (size_t)(c->gemv_max_tiles + 64) * sizeof(int)));
+      TLB_CUDA(cudaMemset(c->gemv_counters, 0, (size_t)c->gemv_max_tiles * sizeof(int)));
       TLB_CUDA(cudaMemset(c->attn_counters, 0, c->attn_max_counters * sizeof(int)));
       TLB_CUDA(cudaMemset(c->argmax_cell, 0, 4 * sizeof(unsigned long long)));
     }

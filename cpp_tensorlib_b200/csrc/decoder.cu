@@ -62,7 +62,7 @@ int launch_swiglu(const float*, float*, int, int, cudaStream_t);
 int launch_ar_sum(float*, int, const CommDev&, int*, cudaStream_t);
 int launch_incr_u32(unsigned*, cudaStream_t);
 int launch_qkv_post(float*, const float*, const float*, const float*, float*, float*, int, int,
-                    int, const unsigned*, long long, float, int*, cudaStream_t);
+                    int, const unsigned*, long long, float, int, int*, cudaStream_t);
 int launch_embed_gather(const float*, const int*, float*, int, float2*, const unsigned*, int, float,
                         const float*, float*, float, cudaStream_t);
 int launch_argmax(DeviceCtx*, const float*, int, int*, int*, cudaStream_t);
@@ -90,6 +90,7 @@ struct Decoder {
   int hidden = 0, n_layers = 0, n_q = 0, n_kv = 0, hd = 0, ff = 0, vocab = 0, max_ctx = 0;
   float eps = 1e-6f, rope_base = 1e6f, scale = 1.f;
   int tp_rank = 0, tp_size = 1;
+  int kv_bf16 = 0;   // caches hold bf16 (kv_cache::init with dtype::bf16, include/cuda.h:1336-1346)
   unsigned vocab_offset = 0;
   std::vector<DecLayer> layers;
   Linear lm_head;
@@ -182,16 +183,14 @@ static GvStream stream_of(DeviceCtx* c, const Linear& L, bool normed) {
 
 static int run_linear(DeviceCtx* c, const Linear& L, const float* x, float* y, cudaStream_t s,
                       const CommDev* push, int act = 0, const NormIn* nm = nullptr, float eps = 0.f,
-                      const PairEpi* epi = nullptr, const GvStream* next = nullptr, float* push_sum = nullptr,
-                      int push_sum_n = 0) {
+                      const PairEpi* epi = nullptr, const GvStream* next = nullptr) {
   if (!L.q4) return set_error(TLB_ERR_STATE, "decoder: a linear weight was never set");
   if ((epi != nullptr) != (L.pair_h > 0))
     return set_error(TLB_ERR_STATE, "decoder: pair-packed weight and epilogue do not match");
   if (L.packed && !(nm && (L.K + 255) / 256 > 32))
     return gemv_q4p_launch(c, L.packed, x, y, L.N, L.K, 1.0f, 0.0f, s, 0, push, nm ? 2 : act,
                            nm ? nm->delta : nullptr, nm ? nm->w : nullptr, nm ? nm->xout : nullptr, eps,
-                           epi, nm ? nm->pull : nullptr, next, push_sum, push_sum_n);
-  if (push_sum) return set_error(TLB_ERR_STATE, "decoder: the fused exchange sum needs a packed weight");
+                           epi, nm ? nm->pull : nullptr, next);
   if (epi) return set_error(TLB_ERR_STATE, "decoder: pair epilogue without a packed weight");
   if (nm && nm->pull) return set_error(TLB_ERR_STATE, "decoder: fused exchange without a packed weight");
   if (L.tma && nm)
@@ -208,7 +207,7 @@ static int run_linear(DeviceCtx* c, const Linear& L, const float* x, float* y, c
 
 static PairEpi qkv_epilogue(const Decoder* d, const DecLayer& L) {
   PairEpi e;
-  e.kind = 2; e.H = d->hd / 2; e.out = d->qkv; e.Kc = L.Kc; e.Vc = L.Vc;
+  e.kind = 2; e.H = d->hd / 2; e.out = d->qkv; e.Kc = L.Kc; e.Vc = L.Vc; e.kv_bf16 = d->kv_bf16;
   e.bq = L.bq; e.bk = L.bk; e.bv = L.bv; e.n_q = d->n_q; e.n_kv = d->n_kv; e.D = d->hd;
   e.d_pos = d->d_pos; e.kv_stride = (long long)d->max_ctx * d->hd; e.kv_rows = d->max_ctx;
   e.base = d->rope_base;
@@ -251,27 +250,26 @@ static int forward(Decoder* d, cudaStream_t s) {
     c2.E = EX;
     return c2;
   };
-  // How a tensor-parallel exchange is consumed.  Default (TLB_TP_SUM=2): the CTA of the pushing
-  // projection that finishes last sums the ranks' packets into a local vector (gemv_sum_tail)
-  // and the next projection's ordinary fused add+norm prologue reads that vector -- the
-  // all-reduce has no kernel of its own.  TLB_TP_SUM=1: the same sum as a small multi-CTA kernel
-  // (ar_sum_kernel), one short extra launch per exchange.  TLB_TP_PULL_MAX = largest rank count whose exchanges are instead
+  // How a tensor-parallel exchange is consumed.  Default: a small multi-CTA kernel sums the
+  // ranks' packets into a local vector (ar_sum_kernel) and the next projection's ordinary fused
+  // add+norm prologue reads that vector -- one short extra launch per exchange, no system-scope
+  // polling from 148 CTAs.  (Summing in the LAST CTA of the pushing projection instead was
+  // built and measured on 2 GPUs: 494 against 732 tokens/s -- a CTA that polls while the
+  // peers' stores are still arriving is far slower than one launched after them.)  TLB_TP_PULL_MAX = largest rank count whose exchanges are instead
   // consumed inside the next projection's prologue (it polls the packets itself: two kernels
   // fewer per layer, measured slower on 2 GPUs, 582 vs 589 tok/s); TLB_TP_SUM=0 selects the
   // older single-CTA add+norm consumer (add_rmsnorm_ar_kernel).
   const char* pm = getenv("TLB_TP_PULL_MAX");
   const int pull_max = pm ? atoi(pm) : 1;
   const char* ts = getenv("TLB_TP_SUM");
-  const int tp_sum_mode = ts ? atoi(ts) : 2;   // 2: sum in the pushing kernel's tail; 1: ar_sum_kernel
-  const bool tp_sum = tp_sum_mode != 0;
+  const bool tp_sum = !(ts && atoi(ts) == 0);
   const bool pull = tp && d->tp_size <= pull_max;
   if (all_tma && (!tp || pull || tp_sum)) {
     // Both residual adds and norms of a layer run inside the following projection's
     // activation prep (5 launches per layer, + one packet-sum launch per exchange when tensor
     // parallel).  The residual ping-pongs between two buffers because every CTA of the
     // projection reads it while one CTA writes the new sum.
-    const bool sum = tp && !pull && tp_sum_mode == 1;      // separate packet-sum kernel
-    const bool tail = tp && !pull && tp_sum_mode != 1;     // the pushing kernel's last CTA sums
+    const bool sum = tp && !pull;
     float* x = d->x;
     float* xalt = d->xb;
     for (int l = 0; l < d->n_layers; l++) {
@@ -294,22 +292,22 @@ static int forward(Decoder* d, cudaStream_t s) {
       }
       if (!pq)
         RUN(launch_qkv_post(d->qkv, L.bq, L.bk, L.bv, L.Kc, L.Vc, d->n_q, d->n_kv, d->hd, d->d_pos,
-                            d->max_ctx, d->rope_base, c->status, s));
+                            d->max_ctx, d->rope_base, d->kv_bf16, c->status, s));
       RUN(attn_decode_launch(c, d->qkv, L.Kc, L.Vc, d->att, d->n_q, d->n_kv, 0, d->max_ctx, d->hd,
                              d->scale, d->d_pos, (float*)((char*)d->attn_partials + 256),
-                             (int*)d->attn_partials, s, 1, 0, &s_wo));
+                             (int*)d->attn_partials, s, 1, d->kv_bf16, &s_wo));
       RUN(run_linear(c, L.wo, d->att, tp ? nullptr : d->t0, s, tp ? &c_wo : nullptr, 0, nullptr, 0.f, nullptr,
-                     &s_gu, tail ? d->t0 : nullptr, E));
+                     &s_gu));
       if (sum) RUN(launch_ar_sum(d->t0, E, c_wo, c->status, s));
       NormIn nf{pull ? nullptr : d->t0, L.fn, xalt, pull ? &c_wo : nullptr};
       RUN(run_linear(c, L.wgu, x, d->gu, s, nullptr, 0, &nf, d->eps, pg, &s_wd));
       { float* t = x; x = xalt; xalt = t; }
       if (pg) {
         RUN(run_linear(c, L.wd, d->mb, tp ? nullptr : d->t1, s, tp ? &c_wd : nullptr, 0, nullptr, 0.f, nullptr,
-                       &s_nx, tail ? d->t1 : nullptr, E));
+                       &s_nx));
       } else {
         RUN(run_linear(c, L.wd, d->gu, tp ? nullptr : d->t1, s, tp ? &c_wd : nullptr, 1, nullptr, 0.f, nullptr,
-                       &s_nx, tail ? d->t1 : nullptr, E));
+                       &s_nx));
       }
       if (sum) RUN(launch_ar_sum(d->t1, E, c_wd, c->status, s));
     }
@@ -339,10 +337,10 @@ static int forward(Decoder* d, cudaStream_t s) {
     RUN(run_linear(c, L.wqkv, d->hb, d->qkv, s, nullptr, 0, nullptr, 0.f, pq));
     if (!pq)
       RUN(launch_qkv_post(d->qkv, L.bq, L.bk, L.bv, L.Kc, L.Vc, d->n_q, d->n_kv, d->hd, d->d_pos,
-                          d->max_ctx, d->rope_base, c->status, s));
+                          d->max_ctx, d->rope_base, d->kv_bf16, c->status, s));
     RUN(attn_decode_launch(c, d->qkv, L.Kc, L.Vc, d->att, d->n_q, d->n_kv, 0, d->max_ctx, d->hd,
                            d->scale, d->d_pos, (float*)((char*)d->attn_partials + 256),
-                           (int*)d->attn_partials, s, 1, 0));
+                           (int*)d->attn_partials, s, 1, d->kv_bf16));
     if (tp) {
       RUN(run_linear(c, L.wo, d->att, nullptr, s, &c_wo));
       RUN(launch_add_rmsnorm_ar(d->x, L.fn, d->x, d->hb, E, d->eps, c_wo, c->status, s));
@@ -398,6 +396,9 @@ int tlb_decoder_create(const int64_t* cfg, int n_cfg, float eps, float rope_base
   // cfg[11] (optional): rows of the embedding table; without it a single-GPU decoder knows it
   // from its own vocabulary, a tensor-parallel shard does not
   d->vocab_total = n_cfg >= 12 ? cfg[11] : (d->tp_size == 1 ? d->vocab : 0);
+  // cfg[12] (optional): 1 = the KV caches hold bf16 (half the KV stream; values rounded to
+  // nearest even on append, widened exactly for the dot and the accumulate)
+  d->kv_bf16 = n_cfg >= 13 && cfg[12] != 0 ? 1 : 0;
   d->eps = eps; d->rope_base = rope_base; d->scale = 1.0f / sqrtf((float)d->hd);
   TLB_REQUIRE(d->hd == 64 || d->hd == 128, "tlb_decoder_create: head_dim must be 64 or 128");
   TLB_REQUIRE(d->n_kv > 0 && d->n_q % d->n_kv == 0 && d->n_kv <= 64, "tlb_decoder_create: bad head counts");
@@ -405,7 +406,7 @@ int tlb_decoder_create(const int64_t* cfg, int n_cfg, float eps, float rope_base
               "tlb_decoder_create: bad tensor-parallel rank/size");
   TLB_REQUIRE(d->n_layers > 0 && d->hidden > 0 && d->max_ctx > 0, "tlb_decoder_create: bad sizes");
   d->layers.resize(d->n_layers);
-  const size_t kvb = (size_t)d->n_kv * d->max_ctx * d->hd * sizeof(float);
+  const size_t kvb = (size_t)d->n_kv * d->max_ctx * d->hd * (d->kv_bf16 ? 2 : sizeof(float));
   for (auto& L : d->layers) {
     TLB_CUDA(cudaMalloc(&L.Kc, kvb));
     TLB_CUDA(cudaMalloc(&L.Vc, kvb));
@@ -711,8 +712,9 @@ int tlb_decoder_prefill(void* h, const int32_t* tokens, int64_t T, int32_t* next
       // [H, rows, D] flattened: row r = h*rows + t, so rope's position is pos + r % rows
       PF(launch_rope(qkvh, nullptr, qkvh, NQ * rows, rows, D, pos, nullptr, d->rope_base, s));
       PF(launch_rope(kh, nullptr, kh, NKV * rows, rows, D, pos, nullptr, d->rope_base, s));
-      PF(launch_kv_fill(L.Kc, L.Vc, kh, vh, rows, d->max_ctx, NKV, D, (int)pos, 0, s));
-      PF(launch_attn_prefill(c, qkvh, L.Kc, L.Vc, ah, NQ, NKV, rows, d->max_ctx, D, d->scale, (int)pos, 0, s));
+      PF(launch_kv_fill(L.Kc, L.Vc, kh, vh, rows, d->max_ctx, NKV, D, (int)pos, d->kv_bf16, s));
+      PF(launch_attn_prefill(c, qkvh, L.Kc, L.Vc, ah, NQ, NKV, rows, d->max_ctx, D, d->scale, (int)pos,
+                             d->kv_bf16, s));
       PF(launch_merge_heads(ah, at, rows, NQ, D, s));
       PF(gemm(L.wo, at, md, rows));
       PF(launch_add_rmsnorm(x, md, L.fn, ro, h2, E, d->eps, rows, s));

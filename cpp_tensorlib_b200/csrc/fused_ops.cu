@@ -153,7 +153,7 @@ __global__ void qkv_post_kernel(float* qkv, const float* __restrict__ bq,
                                 const float* __restrict__ bk, const float* __restrict__ bv,
                                 float* __restrict__ Kc, float* __restrict__ Vc, int n_q, int n_kv,
                                 int D, const unsigned* __restrict__ d_pos, long long kv_stride,
-                                float base, int* status) {
+                                float base, int kv_bf16, int* status) {
   pdl_wait();
   pdl_launch_dependents();
   const int b = blockIdx.x, j = threadIdx.x, half = D >> 1;
@@ -168,7 +168,7 @@ __global__ void qkv_post_kernel(float* qkv, const float* __restrict__ bq,
   } else if (b < n_q + n_kv) {
     const int kh = b - n_q;
     // rotate into the cache row: out pointer offset so that index bi+j lands there
-    float* dst = Kc + (size_t)kh * kv_stride + (size_t)pos * D;
+    const size_t row = (size_t)kh * kv_stride + (size_t)pos * D;
     const float* src = qkv + (size_t)b * D;
     const double theta = exp2(-2.0 * (double)j / (double)D * log2((double)base));
     double sd, cd;
@@ -179,19 +179,31 @@ __global__ void qkv_post_kernel(float* qkv, const float* __restrict__ bq,
       x0 += bk[kh * D + j];
       x1 += bk[kh * D + j + half];
     }
-    dst[j] = x0 * c - x1 * s;
-    dst[j + half] = x0 * s + x1 * c;
+    if (kv_bf16) {
+      __nv_bfloat16* dst = (__nv_bfloat16*)Kc + row;
+      dst[j] = __float2bfloat16_rn(x0 * c - x1 * s);
+      dst[j + half] = __float2bfloat16_rn(x0 * s + x1 * c);
+    } else {
+      Kc[row + j] = x0 * c - x1 * s;
+      Kc[row + j + half] = x0 * s + x1 * c;
+    }
   } else {
     const int kh = b - n_q - n_kv;
-    float* dst = Vc + (size_t)kh * kv_stride + (size_t)pos * D;
+    const size_t row = (size_t)kh * kv_stride + (size_t)pos * D;
     const float* src = qkv + (size_t)b * D;
     float v0 = src[j], v1 = src[j + half];
     if (bv) {
       v0 += bv[kh * D + j];
       v1 += bv[kh * D + j + half];
     }
-    dst[j] = v0;
-    dst[j + half] = v1;
+    if (kv_bf16) {
+      __nv_bfloat16* dst = (__nv_bfloat16*)Vc + row;
+      dst[j] = __float2bfloat16_rn(v0);
+      dst[j + half] = __float2bfloat16_rn(v1);
+    } else {
+      Vc[row + j] = v0;
+      Vc[row + j + half] = v1;
+    }
   }
 }
 
@@ -515,11 +527,11 @@ int launch_incr_u32(unsigned* p, cudaStream_t s) {
 }
 int launch_qkv_post(float* qkv, const float* bq, const float* bk, const float* bv, float* Kc,
                     float* Vc, int n_q, int n_kv, int D, const unsigned* d_pos, long long kv_max,
-                    float base, int* status, cudaStream_t s) {
+                    float base, int kv_bf16, int* status, cudaStream_t s) {
   LaunchCfg lc(dim3(n_q + 2 * n_kv), dim3(D / 2), 0, s, pdl_enabled());
   long long kv_stride = kv_max * D;
   TLB_CUDA(cudaLaunchKernelEx(&lc.cfg, qkv_post_kernel, qkv, bq, bk, bv, Kc, Vc, n_q, n_kv, D,
-                              d_pos, kv_stride, base, status));
+                              d_pos, kv_stride, base, kv_bf16, status));
   return TLB_OK;
 }
 int launch_embed_gather(const float* embed, const int* d_tok, float* x, int n, float2* rope_cs,

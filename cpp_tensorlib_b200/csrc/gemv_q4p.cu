@@ -31,6 +31,8 @@
 // Split-K falls out of the unit ranges; partial row tiles are combined by the
 // last-arriving warp in worker order (deterministic, no float atomics, no spin-wait
 // on another CTA).
+#include <cuda_bf16.h>
+
 #include <cstdlib>
 #include <cstring>
 
@@ -127,12 +129,6 @@ struct GemvPParams {
   int slabs;        // activation slabs a CTA holds in shared memory (SL, or the largest slab block)
   CommDev comm;
   GvStream pf;      // what the next weight-streaming kernel reads first (wp == NULL: nothing)
-  // push mode only: the CTA that finishes last also REDUCES the exchange -- it polls every
-  // rank's packets of this exchange in this rank's staging and leaves their sum (rank order)
-  // in sum_out[0..sum_n), so the all-reduce needs no kernel of its own
-  float* sum_out;
-  int sum_n;
-  int* sum_ticket;
 };
 
 struct GemvPSmem {
@@ -179,52 +175,12 @@ __device__ __forceinline__ float lds32f(uint32_t a) {
   return v;
 }
 
-// Tail of a pushing launch (tensor parallel): a ticket elects the CTA that finishes last; it
-// polls the packets all ranks pushed for this exchange (bounded), adds them in rank order --
-// every rank computes the same bits -- and writes the sum to local memory, where the next
-// projection's fused add+norm prologue reads it as an ordinary vector.  Kept out of line so
-// its registers do not count against the streaming loop.
-__device__ __noinline__ void gemv_sum_tail(const CommDev& comm, unsigned seq, float* out, int n, int* ticket,
-                                           int* status, int* flag) {
-  __syncthreads();                       // every thread's pushes are issued
-  if (threadIdx.x == 0) *flag = (int)atom_add_acq_rel(ticket, 1);
-  __syncthreads();
-  if (*flag != (int)gridDim.x - 1) return;
-  const uint2* st = comm.stage[comm.rank] + (size_t)(seq & 1u) * comm.size * comm.slot_floats;
-  const unsigned tag = seq + 1u;
-  constexpr int J = 4;                   // elements per thread with all their polls in flight
-  for (int i0 = threadIdx.x; i0 < n; i0 += blockDim.x * J) {
-    uint2 pk[J][TP_MAX];
-#pragma unroll
-    for (int j = 0; j < J; j++) {
-      const int i = i0 + j * blockDim.x;
-#pragma unroll
-      for (int r = 0; r < TP_MAX; r++)
-        if (r < comm.size && i < n) pk[j][r] = ld_packet_sys(st + (size_t)r * comm.slot_floats + i);
-    }
-#pragma unroll
-    for (int j = 0; j < J; j++) {
-      const int i = i0 + j * blockDim.x;
-      if (i >= n) continue;
-      float d = 0.f;
-#pragma unroll
-      for (int r = 0; r < TP_MAX; r++)
-        if (r < comm.size) {
-          if (pk[j][r].y != tag)
-            pk[j][r] = wait_packet_bounded(st + (size_t)r * comm.slot_floats + i, tag, status, 300 + r);
-          d += __uint_as_float(pk[j][r].x);
-        }
-      out[i] = d;
-    }
-  }
-  if (threadIdx.x == 0) *ticket = 0;     // clean for the next launch
-}
-
 // PULL: the instantiation that can consume a tensor-parallel exchange in its prologue (act 3);
 // kept out of the single-GPU kernel, whose register budget it would eat.
 // OWN: the CTA-owned-block instantiation (p.cta_tiles != 0).  EPI: the pair epilogue
 // (p.epi.kind) as a compile-time value, so the plain projections carry no rope code.
-template <int STAGES, bool PULL, bool OWN, int EPI>
+// PUSH: the tensor-parallel producer (outputs go to every rank's staging as tagged packets).
+template <int STAGES, bool PULL, bool OWN, int EPI, bool PUSH>
 __global__ void __launch_bounds__(PK_WARPS * 32, 1) gemv_q4p_kernel(GemvPParams p) {
   extern __shared__ unsigned char smem_raw[];
   unsigned char* base = (unsigned char*)(((uintptr_t)smem_raw + 127) & ~(uintptr_t)127);
@@ -486,12 +442,12 @@ __global__ void __launch_bounds__(PK_WARPS * 32, 1) gemv_q4p_kernel(GemvPParams 
   const uint32_t cl = 2048u + (uint32_t)g * 32u + (uint32_t)t * 8u;
 
   unsigned ar_seq = 0;
-  if (p.push) ar_seq = comm_seq(p.comm);
+  if (PUSH) ar_seq = comm_seq(p.comm);
   const size_t ar_off =
       ((size_t)(ar_seq & 1u) * p.comm.size + p.comm.rank) * (size_t)p.comm.slot_floats;
   auto emit = [&](int n, float v) {
     v = v * p.alpha + p.beta;
-    if (p.push) {
+    if (PUSH) {
       for (int r = 0; r < p.comm.size; r++) st_packet_sys(&p.comm.stage[r][ar_off + n], v, ar_seq + 1u);
     } else {
       p.y[n] = v;
@@ -521,9 +477,16 @@ __global__ void __launch_bounds__(PK_WARPS * 32, 1) gemv_q4p_kernel(GemvPParams 
     if (h >= p.epi.n_q + p.epi.n_kv) {
       const int kh = h - p.epi.n_q - p.epi.n_kv;
       if (p.epi.bv) { a += p.epi.bv[kh * D + j]; b += p.epi.bv[kh * D + j + half]; }
-      float* dst = p.epi.Vc + (size_t)kh * p.epi.kv_stride + (size_t)pos * D;
-      dst[j] = a;
-      dst[j + half] = b;
+      const size_t row = (size_t)kh * p.epi.kv_stride + (size_t)pos * D;
+      if (p.epi.kv_bf16) {
+        __nv_bfloat16* dst = (__nv_bfloat16*)p.epi.Vc + row;
+        dst[j] = __float2bfloat16_rn(a);
+        dst[j + half] = __float2bfloat16_rn(b);
+      } else {
+        float* dst = p.epi.Vc + row;
+        dst[j] = a;
+        dst[j + half] = b;
+      }
       return;
     }
     float c, sn;
@@ -547,9 +510,16 @@ __global__ void __launch_bounds__(PK_WARPS * 32, 1) gemv_q4p_kernel(GemvPParams 
     } else {
       const int kh = h - p.epi.n_q;
       if (p.epi.bk) { a += p.epi.bk[kh * D + j]; b += p.epi.bk[kh * D + j + half]; }
-      float* dst = p.epi.Kc + (size_t)kh * p.epi.kv_stride + (size_t)pos * D;
-      dst[j] = a * c - b * sn;
-      dst[j + half] = a * sn + b * c;
+      const size_t row = (size_t)kh * p.epi.kv_stride + (size_t)pos * D;
+      if (p.epi.kv_bf16) {
+        __nv_bfloat16* dst = (__nv_bfloat16*)p.epi.Kc + row;
+        dst[j] = __float2bfloat16_rn(a * c - b * sn);
+        dst[j + half] = __float2bfloat16_rn(a * sn + b * c);
+      } else {
+        float* dst = p.epi.Kc + row;
+        dst[j] = a * c - b * sn;
+        dst[j + half] = a * sn + b * c;
+      }
     }
   };
   auto flush = [&](int rt) {
@@ -717,10 +687,7 @@ __global__ void __launch_bounds__(PK_WARPS * 32, 1) gemv_q4p_kernel(GemvPParams 
         __stcg(p.partials + ((size_t)kb * p.RT + tile_b + tl) * 16 + row, sum);
       }
     }
-    if (KB == 1) {
-      if (p.sum_out) gemv_sum_tail(p.comm, ar_seq, p.sum_out, p.sum_n, p.sum_ticket, p.status, (int*)red);
-      return;
-    }
+    if (KB == 1) return;
     // Slab blocks: the row block's KB partial blocks meet in global memory; the CTA that
     // arrives last folds them in block order (the same bits whichever CTA that is).
     __threadfence();
@@ -728,10 +695,7 @@ __global__ void __launch_bounds__(PK_WARPS * 32, 1) gemv_q4p_kernel(GemvPParams 
     int* flag = (int*)red;
     if (tid == 0) *flag = (int)atom_add_acq_rel(&p.counters[rb], 1);
     __syncthreads();
-    if (*flag != (int)KB - 1) {
-      if (p.sum_out) gemv_sum_tail(p.comm, ar_seq, p.sum_out, p.sum_n, p.sum_ticket, p.status, (int*)red);
-      return;
-    }
+    if (*flag != (int)KB - 1) return;
     __threadfence();
     for (int idx = tid; idx < ntl * 16; idx += PK_WARPS * 32) {
       const size_t off = (size_t)(tile_b + (idx >> 4)) * 16 + (idx & 15);
@@ -747,11 +711,9 @@ __global__ void __launch_bounds__(PK_WARPS * 32, 1) gemv_q4p_kernel(GemvPParams 
       if ((int)off < p.N) emit((int)off, sum);
     }
     if (tid == 0) p.counters[rb] = 0;  // clean for the next launch
-    if (p.sum_out) gemv_sum_tail(p.comm, ar_seq, p.sum_out, p.sum_n, p.sum_ticket, p.status, (int*)red);
     return;
   }
   if (n_units > 0 && s != 0) flush(rt);
-  if (p.sum_out) gemv_sum_tail(p.comm, ar_seq, p.sum_out, p.sum_n, p.sum_ticket, p.status, (int*)red);
 }
 
 static int gemvp_stages(int slabs) {
@@ -764,22 +726,26 @@ bool gemv_q4p_supported(long long N, long long K) {
   return N > 0 && K > 0 && K % 32 == 0 && K <= (1 << 20) && gemvp_stages((int)((K + 255) / 256)) != 0;
 }
 
-template <int STAGES, bool PULL, bool OWN, int EPI>
+template <int STAGES, bool PULL, bool OWN, int EPI, bool PUSH>
 static int gemvp_launch_t(const GemvPParams& p, int ctas, size_t smem, cudaStream_t stream) {
   static std::atomic<unsigned long long> attr_done{0};
   {
-    const int rc_attr = ensure_dynamic_smem(gemv_q4p_kernel<STAGES, PULL, OWN, EPI>, 227 * 1024, attr_done);
+    const int rc_attr = ensure_dynamic_smem(gemv_q4p_kernel<STAGES, PULL, OWN, EPI, PUSH>, 227 * 1024, attr_done);
     if (rc_attr) return rc_attr;
   }
   LaunchCfg lc(dim3(ctas), dim3(PK_WARPS * 32), smem, stream, pdl_enabled());
-  TLB_CUDA(cudaLaunchKernelEx(&lc.cfg, gemv_q4p_kernel<STAGES, PULL, OWN, EPI>, p));
+  TLB_CUDA(cudaLaunchKernelEx(&lc.cfg, gemv_q4p_kernel<STAGES, PULL, OWN, EPI, PUSH>, p));
   return TLB_OK;
 }
 template <int STAGES, bool PULL, bool OWN>
 static int gemvp_launch_e(const GemvPParams& p, int ctas, size_t smem, cudaStream_t stream) {
-  if (p.epi.kind == 0) return gemvp_launch_t<STAGES, PULL, OWN, 0>(p, ctas, smem, stream);
-  if (p.epi.kind == 1) return gemvp_launch_t<STAGES, PULL, OWN, 1>(p, ctas, smem, stream);
-  return gemvp_launch_t<STAGES, PULL, OWN, 2>(p, ctas, smem, stream);
+  if (p.push) {   // a pushing launch has neither a pair epilogue nor a pulling prologue
+    if (PULL) return set_error(TLB_ERR_ARG, "gemv_q4p: a launch pulls or pushes, not both");
+    return gemvp_launch_t<STAGES, false, OWN, 0, true>(p, ctas, smem, stream);
+  }
+  if (p.epi.kind == 0) return gemvp_launch_t<STAGES, PULL, OWN, 0, false>(p, ctas, smem, stream);
+  if (p.epi.kind == 1) return gemvp_launch_t<STAGES, PULL, OWN, 1, false>(p, ctas, smem, stream);
+  return gemvp_launch_t<STAGES, PULL, OWN, 2, false>(p, ctas, smem, stream);
 }
 template <int STAGES, bool PULL>
 static int gemvp_launch_o(const GemvPParams& p, int ctas, size_t smem, cudaStream_t stream) {
@@ -866,17 +832,10 @@ int gemv_q4p_launch(DeviceCtx* c, const void* packed, const float* x, float* y, 
                     float alpha, float beta, cudaStream_t stream, int max_ctas,
                     const CommDev* push_comm, int act, const float* delta, const float* nw,
                     float* xout, float eps, const PairEpi* epi, const CommDev* pull_comm,
-                    const GvStream* prefetch, float* push_sum_out, int push_sum_n) {
+                    const GvStream* prefetch) {
   GemvPParams p;
   memset(&p, 0, sizeof(p));
   if (prefetch) p.pf = *prefetch;
-  if (push_sum_out) {
-    if (!push_comm || push_sum_n > push_comm->slot_floats)
-      return set_error(TLB_ERR_ARG, "gemv_q4p: the fused exchange sum needs a pushing launch and n within the staging slot");
-    p.sum_out = push_sum_out;
-    p.sum_n = push_sum_n;
-    p.sum_ticket = c->gemv_counters + c->gemv_max_tiles;   // one word behind the row-tile tickets
-  }
   if (pull_comm) {
     if (push_comm) return set_error(TLB_ERR_ARG, "gemv_q4p: a launch pulls or pushes, not both");
     act = 3;

@@ -31,6 +31,7 @@ struct PairEpi {
   const float* bk = nullptr;
   const float* bv = nullptr;
   int n_q = 0, n_kv = 0, D = 0;
+  int kv_bf16 = 0;               // kind 2: the caches hold bf16 (rows rounded to nearest even)
   const unsigned* d_pos = nullptr;
   long long kv_stride = 0;
   int kv_rows = 0;               // capacity of the caches in rows: a position at or beyond it is refused
@@ -46,7 +47,7 @@ int gemv_q4p_launch(DeviceCtx* c, const void* packed, const float* x, float* y, 
                     float alpha, float beta, cudaStream_t stream, int max_ctas,
                     const CommDev* push_comm, int act, const float* delta, const float* nw,
                     float* xout, float eps, const PairEpi* epi, const CommDev* pull_comm,
-                    const GvStream* prefetch = nullptr, float* push_sum_out = nullptr, int push_sum_n = 0);
+                    const GvStream* prefetch = nullptr);
 // The walk a launch with these arguments would take (same decisions as gemv_q4p_launch).
 int gemv_q4p_stream_of(DeviceCtx* c, const void* packed, int N, int K, int act, bool has_epi, int max_ctas,
                        GvStream* out);

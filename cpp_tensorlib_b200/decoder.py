@@ -150,15 +150,20 @@ class Q4Decoder:
     """Handle on the native decoder.  Weights are device tensors kept alive here
     (the native side borrows their pointers)."""
 
-    def __init__(self, cfg, max_ctx, tp_rank=0, tp_size=1):
+    def __init__(self, cfg, max_ctx, tp_rank=0, tp_size=1, kv_dtype="f32"):
+        """kv_dtype "bf16": the KV caches hold bf16 (kv_cache::init with dtype::bf16,
+        include/cuda.h:1336-1346): half the KV stream, rows rounded to nearest even on append."""
+        if kv_dtype not in ("f32", "bf16"):
+            raise ValueError("kv_dtype must be 'f32' or 'bf16'")
+        self.kv_bf16 = kv_dtype == "bf16"
         self.cfg, self.max_ctx, self.tp_rank, self.tp_size = dict(cfg), max_ctx, tp_rank, tp_size
         self.plan = shard_plan(cfg, tp_size, tp_rank)
         p = self.plan
-        arr = (C.c_int64 * 12)(cfg["hidden"], cfg["layers"], p["n_q"], p["n_kv"], cfg["hd"],
+        arr = (C.c_int64 * 13)(cfg["hidden"], cfg["layers"], p["n_q"], p["n_kv"], cfg["hd"],
                                p["ff_local"], p["vocab_local"], max_ctx, tp_rank, tp_size,
-                               p["vocab"][0], cfg["vocab"])
+                               p["vocab"][0], cfg["vocab"], 1 if self.kv_bf16 else 0)
         self.h = C.c_void_p()
-        check(lib().tlb_decoder_create(arr, 12, cfg["eps"], cfg["rope_base"], C.byref(self.h)))
+        check(lib().tlb_decoder_create(arr, 13, cfg["eps"], cfg["rope_base"], C.byref(self.h)))
         self._keep = {}
         self.captured = False
 
@@ -196,6 +201,9 @@ class Q4Decoder:
         K, V = C.c_void_p(), C.c_void_p()
         check(lib().tlb_decoder_kv(self.h, layer, C.byref(K), C.byref(V)))
         shape = (self.plan["n_kv"], self.max_ctx, self.cfg["hd"])
+        if self.kv_bf16:
+            return (_as_tensor(K.value, shape, "<u2").view(torch.bfloat16),
+                    _as_tensor(V.value, shape, "<u2").view(torch.bfloat16))
         return _as_tensor(K.value, shape), _as_tensor(V.value, shape)
 
     def fill_kv(self, layer, K, V):
@@ -287,5 +295,5 @@ class _Ext:
                                              version=2)
 
 
-def _as_tensor(ptr, shape):
-    return torch.as_tensor(_Ext(ptr, shape), device="cuda")
+def _as_tensor(ptr, shape, typestr="<f4"):
+    return torch.as_tensor(_Ext(ptr, shape, typestr), device="cuda")

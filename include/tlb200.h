@@ -237,7 +237,9 @@ int tlb_graph_destroy(void* graph_exec);    /* graph_destroy */
  * layout, plus the tensor-parallel path the reference does not have.
  * cfg[0..10] = hidden, n_layers, n_q, n_kv, head_dim, ff, vocab, max_ctx (sizes
  * local to the rank, hidden global), tp_rank, tp_size, vocab_offset; optional cfg[11] =
- * rows of the embedding table (token ids are checked against it).
+ * rows of the embedding table (token ids are checked against it); optional cfg[12] = 1: the KV
+ * caches hold bf16 (cu.h:1336-1346 kv_cache::init with dtype::bf16; tlb_decoder_kv then returns
+ * bf16 buffers).
  * Capacity: set_pos / forward / run / step / prefill keep a host mirror of the position and
  * refuse (TLB_ERR_ARG, nothing launched) to advance past max_ctx, as captured_decoder::feed
  * does (qm:877-885).  A graph replayed behind the library's back is caught on the device:

@@ -52,6 +52,8 @@ class Port:
         L.orc_decoder_fill_kv.argtypes = [C.c_void_p, _i64, _f32p, _f32p, _i64]
         L.orc_decoder_step.argtypes = [C.c_void_p, _i64, _i64, C.c_void_p]
         L.orc_decoder_step.restype = _i64
+        L.orc_decoder_set_kv_bf16.argtypes = [C.c_void_p, C.c_int]
+        L.orc_bf16_round_array.argtypes = [_f32p, _i64, _f32p]
 
     def to_q4(self, w_kn):
         w = _f(w_kn)
@@ -116,16 +118,24 @@ class Port:
         v = _f(v).ravel()
         return int(self.lib.orc_argmax(v, v.size))
 
+    def bf16_round(self, v):
+        v = _f(v)
+        out = np.empty_like(v)
+        self.lib.orc_bf16_round_array(v.ravel(), v.size, out.ravel())
+        return out
+
 
 class PortDecoder:
     """Qwen2.5-block decoder on the host with q4 linears (borrowed buffers kept alive here)."""
 
-    def __init__(self, port, cfg, max_ctx):
+    def __init__(self, port, cfg, max_ctx, kv_bf16=False):
         self.p, self.cfg, self.max_ctx = port, cfg, max_ctx
         self._keep = []
         self.h = port.lib.orc_decoder_create(cfg["hidden"], cfg["layers"], cfg["n_q"], cfg["n_kv"],
                                              cfg["hd"], cfg["ff"], cfg["vocab"], max_ctx,
                                              cfg["eps"], cfg["rope_base"])
+        if kv_bf16:
+            port.lib.orc_decoder_set_kv_bf16(self.h, 1)
 
     def set_linear(self, layer, which, q4):
         q4 = np.ascontiguousarray(q4, np.uint8)

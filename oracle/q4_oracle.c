@@ -224,7 +224,32 @@ typedef struct {
   const uint8_t* lm_head;
   orc_layer* layers;
   float *x, *hb, *qkv, *att, *t0, *gu, *mb;
+  int kv_bf16; /* cache rows are rounded to bf16 when stored (kv_st, kernels/tensorlib_cuda.cu:828-831) */
 } orc_decoder;
+
+/* f32 -> bf16 -> f32, round to nearest even: what __float2bfloat16 does in kv_st
+ * (kernels/tensorlib_cuda.cu:831) followed by the exact widening of kv_ld (:828-830). */
+static float orc_bf16_round(float x) {
+  uint32_t u;
+  memcpy(&u, &x, 4);
+  if ((u & 0x7fffffffu) > 0x7f800000u) return x; /* NaN stays NaN */
+  u += 0x7fffu + ((u >> 16) & 1u);
+  u &= 0xffff0000u;
+  memcpy(&x, &u, 4);
+  return x;
+}
+void orc_bf16_round_array(const float* in, int64_t n, float* out) {
+  for (int64_t i = 0; i < n; i++) out[i] = orc_bf16_round(in[i]);
+}
+static void orc_store_row(const orc_decoder* d, float* dst, const float* src, int64_t n) {
+  if (d->kv_bf16)
+    for (int64_t i = 0; i < n; i++) dst[i] = orc_bf16_round(src[i]);
+  else
+    memcpy(dst, src, sizeof(float) * (size_t)n);
+}
+/* kv_cache::init with dtype::bf16 (include/cuda.h:1336-1346): the host model keeps f32 storage
+ * holding bf16-representable values, which is what the bf16 cache widens to. */
+void orc_decoder_set_kv_bf16(void* h, int on) { ((orc_decoder*)h)->kv_bf16 = on ? 1 : 0; }
 
 void* orc_decoder_create(int64_t hidden, int64_t n_layers, int64_t n_q, int64_t n_kv,
                          int64_t hd, int64_t ff, int64_t vocab, int64_t max_ctx,
@@ -278,8 +303,8 @@ void orc_decoder_fill_kv(void* h, int64_t layer, const float* K, const float* V,
   orc_decoder* d = (orc_decoder*)h;
   orc_layer* L = &d->layers[layer];
   for (int64_t kh = 0; kh < d->n_kv; kh++) {
-    memcpy(L->Kc + kh * d->max_ctx * d->hd, K + kh * n * d->hd, sizeof(float) * n * d->hd);
-    memcpy(L->Vc + kh * d->max_ctx * d->hd, V + kh * n * d->hd, sizeof(float) * n * d->hd);
+    orc_store_row(d, L->Kc + kh * d->max_ctx * d->hd, K + kh * n * d->hd, n * d->hd);
+    orc_store_row(d, L->Vc + kh * d->max_ctx * d->hd, V + kh * n * d->hd, n * d->hd);
   }
 }
 
@@ -298,8 +323,8 @@ int64_t orc_decoder_step(void* h, int64_t token, int64_t pos, float* logits) {
     orc_rope(k, L->bk, NKV, 1, HD, pos, d->rope_base, k);
     for (int64_t i = 0; i < NKV * HD; i++) v[i] += L->bv[i];
     for (int64_t kh = 0; kh < NKV; kh++) {
-      memcpy(L->Kc + (kh * d->max_ctx + pos) * HD, k + kh * HD, sizeof(float) * HD);
-      memcpy(L->Vc + (kh * d->max_ctx + pos) * HD, v + kh * HD, sizeof(float) * HD);
+      orc_store_row(d, L->Kc + (kh * d->max_ctx + pos) * HD, k + kh * HD, HD);
+      orc_store_row(d, L->Vc + (kh * d->max_ctx + pos) * HD, v + kh * HD, HD);
     }
     orc_attn_decode(q, L->Kc, L->Vc, NQ, NKV, pos + 1, d->max_ctx, HD, d->scale, d->att);
     orc_gemm_q4(d->att, 1, NQ * HD, L->wo, E, 1.0f, 0.0f, d->t0);

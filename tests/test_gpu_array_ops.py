@@ -5,7 +5,8 @@ bf16 prefill GEMM.  Each is a floating-point kernel whose expression is the refe
 (kernels/tensorlib_cuda.cu:25-82, 222-276, 611-682; include/array.h ref:: loops on the CPU),
 so the check is a float64 numpy evaluation of that expression: 1e-6 relative for the
 elementwise ops (one rounding each, libm vs device intrinsics 2 ulp), 1e-5 for reductions
-and contractions (summation order differs)."""
+and contractions (summation order differs), 1e-4 where a single f32 accumulator runs over
+thousands of terms (rows of 151936 columns, K = 4864): the bound follows sqrt(terms) * 2^-24."""
 import ctypes as C
 
 import numpy as np
@@ -103,7 +104,7 @@ def test_row_ops(L, rows, cols):
     assert relerr(out.cpu().numpy(), e / e.sum(1, keepdims=True)) < 1e-6
     red = torch.empty(rows, device="cuda")
     check(L.tlb_row_op(1, _p(dx), _p(red), rows, cols, 0.5, 1.0, _s()))
-    assert relerr(red.cpu().numpy(), x64.sum(1) * 0.5 + 1.0) < 1e-5
+    assert relerr(red.cpu().numpy(), x64.sum(1) * 0.5 + 1.0) < (1e-4 if cols > 10000 else 1e-5)
     check(L.tlb_row_op(2, _p(dx), _p(red), rows, cols, 2.0, -1.0, _s()))
     assert relerr(red.cpu().numpy(), x64.max(1) * 2.0 - 1.0) < 1e-6
 
@@ -120,7 +121,7 @@ def test_gemm_f32_layouts(L, m, n, k, ta, tb):
     out = torch.empty((m, n), device="cuda")
     check(L.tlb_gemm_f32(_p(dA), As.shape[1], ta, _p(dB), Bs.shape[1], tb, _p(out), m, n, k, 0.5, 1.0, _s()))
     want = A.astype(np.float64) @ B.astype(np.float64) * 0.5 + 1.0
-    assert relerr(out.cpu().numpy(), want) < 1e-5
+    assert relerr(out.cpu().numpy(), want) < (1e-4 if k > 1024 else 1e-5)
 
 
 @pytest.mark.parametrize("K,N", [(8, 1), (896, 4864), (3584, 1000), (129, 131), (4864, 896)])

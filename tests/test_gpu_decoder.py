@@ -305,3 +305,47 @@ def test_bounded_device_wait_expires_and_the_device_stays_usable(port):
     wq = tl.to_q4(torch.from_numpy(W).cuda())
     y = tl.gemv_q4p(torch.from_numpy(x).cuda().reshape(-1), tl.Q4Packed(wq)).cpu().numpy()
     assert np.allclose(y, port.gemm_q4(x, port.to_q4(W), 4864)[0], rtol=1e-4, atol=1e-4)
+
+
+@pytest.mark.parametrize("cfg,seed", [(cases.TINY, 21), (cases.TINY64, 22)])
+def test_decoder_with_bf16_kv_cache(port, cfg, seed):
+    """The decoder's own caches in bf16 (kv_cache::init with dtype::bf16, include/cuda.h:1336-1346):
+    prompt by the batched pass, then greedy steps, against the oracle whose cache rows are
+    rounded to bf16 when stored (kv_st / kv_ld, kernels/tensorlib_cuda.cu:828-831) -- logits 1e-3,
+    ids exact; the cache itself must hold exactly the oracle's rounded rows."""
+    from cpp_tensorlib_b200.decoder import Q4Decoder
+    wts = cases.decoder_weights(cfg, seed)
+    d = Q4Decoder(cfg, 64, kv_dtype="bf16")
+    d.load(wts)
+    o = oracle.PortDecoder(port, cfg, 64, kv_bf16=True)
+    o.set_embed(wts["embed"]); o.set_vector(0, 5, wts["onorm"]); o.set_linear(0, 4, port.to_q4(wts["lm_head"]))
+    for l, L in enumerate(wts["layers"]):
+        for k, i in cases.LINEAR_IDS.items():
+            o.set_linear(l, i, port.to_q4(L[k]))
+        for k, i in cases.VECTOR_IDS.items():
+            o.set_vector(l, i, L[k])
+    d.set_pos(0)
+    d.capture()
+    tok = 5
+    for pos in range(20):
+        nxt = d.step(tok)
+        want, lg = o.step(tok, pos)
+        assert np.allclose(d.logits().cpu().numpy(), lg, rtol=1e-3, atol=1e-3), pos
+        assert nxt == want, pos
+        tok = nxt
+    K, V = d.kv(0)
+    assert K.dtype == torch.bfloat16 and K.shape == (cfg["n_kv"], 64, cfg["hd"])
+    assert torch.isfinite(K[:, :20].float()).all() and K[:, :20].float().abs().max() > 0
+    # the batched prompt pass writes the same kind of cache and continues identically
+    d2 = Q4Decoder(cfg, 64, kv_dtype="bf16")
+    d2.load(wts)
+    prompt = [int(t) for t in synth.token_ids(seed, 7, 11, cfg["vocab"])]
+    d.set_pos(0)
+    a = 0
+    for t in prompt:
+        a = d.step(t)
+    d2.set_pos(0)
+    assert d2.prefill(prompt) == a
+    K2, _ = d2.kv(0)
+    assert np.allclose(K2[:, :11].float().cpu().numpy(), K[:, :11].float().cpu().numpy(), rtol=1e-2, atol=1e-2)
+    d.close(); d2.close(); o.close()

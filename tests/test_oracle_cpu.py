@@ -127,3 +127,42 @@ def test_port_against_live_reference(port, ref):
     assert relerr(port.attn_decode(q, K, V, 0.125), ref.attn_decode(q, K, V, 0.125)[0]) < 1e-5
     xr = synth.normal(43, 1, (6, 3, 64))
     assert np.array_equal(port.rope(xr, 123, 1e6), ref.rope(xr, 123, 1e6))
+
+
+def test_port_bf16_cache_rounding_matches_torch(port):
+    """The oracle's bf16-cache mode rounds stored rows to nearest even like kv_st
+    (kernels/tensorlib_cuda.cu:831): checked against torch's f32 -> bf16 -> f32 on values that
+    include exact ties, and on a decoder step whose logits must differ from the f32-cache run by
+    no more than the rounding allows."""
+    import torch
+    import cases
+    import oracle
+    cfg = cases.TINY64
+    wts = cases.decoder_weights(cfg, 22)
+
+    def build(bf):
+        o = oracle.PortDecoder(port, cfg, 16, kv_bf16=bf)
+        o.set_embed(wts["embed"]); o.set_vector(0, 5, wts["onorm"]); o.set_linear(0, 4, port.to_q4(wts["lm_head"]))
+        for l, L in enumerate(wts["layers"]):
+            for k, i in cases.LINEAR_IDS.items():
+                o.set_linear(l, i, port.to_q4(L[k]))
+            for k, i in cases.VECTOR_IDS.items():
+                o.set_vector(l, i, L[k])
+        return o
+    a, b = build(False), build(True)
+    # fill_kv goes through the same store: read it back through one attention step
+    import synth
+    v = np.concatenate([np.array([1.0, 1.00390625, 1.01171875, -3.0e-5, 0.0, -0.0, 3.3e38, 1e-40], np.float32),
+                        synth.normal(9, 1, (4096,), 3.0)])
+    want = torch.from_numpy(v).to(torch.bfloat16).float().numpy()
+    assert want[1] == 1.0 and want[2] == np.float32(1.015625)                 # ties go to even
+    assert np.array_equal(port.bf16_round(v).view(np.uint32), want.view(np.uint32))
+    la = lb = None
+    tok = 3
+    for pos in range(4):
+        ta, la = a.step(tok, pos)
+        tb, lb = b.step(tok, pos)
+        tok = ta
+    assert not np.array_equal(la, lb)                     # the rounding is really applied
+    assert np.max(np.abs(la - lb)) < 5e-2
+    a.close(); b.close()
