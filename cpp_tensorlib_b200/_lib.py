@@ -8,7 +8,8 @@ import ctypes as C
 import os
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(_HERE, "libtlb200.so")
+# TLB200_LIB names another build of the library (the C++ seam honours the same variable)
+LIB_PATH = os.environ.get("TLB200_LIB") or os.path.join(_HERE, "libtlb200.so")
 
 i64, f32, vp, ci = C.c_int64, C.c_float, C.c_void_p, C.c_int
 

@@ -1,5 +1,6 @@
 // extern "C" surface (declared in include/tlb200.h), the per-device context and
 // error plumbing.  Host code only; kernels live in the sibling .cu files.
+#include <cstdlib>
 #include <map>
 #include <mutex>
 #include <string>
@@ -25,6 +26,11 @@ bool gemm_q4_tc_eligible(const void* qw, const void* scales, int N, int K, int M
 int gemm_q4_tc_launch(DeviceCtx* c, const float* x, long long ldx, int M, const void* qw,
                       const float* scales, float* y, long long ldy, int N, int K, float alpha,
                       float beta, float* xsplit, cudaStream_t stream);
+bool gemm_q4_tc2_eligible(const void* qw, const void* scales, int N, int K, int M);
+size_t gemm_q4_tc2_scratch_bytes(int M, int K);
+int gemm_q4_tc2_launch(DeviceCtx* c, const float* x, long long ldx, int M, const void* qw, const float* scales,
+                       float* y, long long ldy, int N, int K, float alpha, float beta, void* scratch,
+                       cudaStream_t stream);
 size_t attn_partials_bytes(int n_q, int n_kv, long long kv_max, int D, int sm_count);
 int attn_decode_launch(DeviceCtx* c, const float* q, const void* K, const void* V, float* out,
                        int n_q, int n_kv, int ctx, long long kv_max, int D, float scale,
@@ -283,7 +289,23 @@ int tlb_gemm_q4(const float* x, int64_t M, int64_t ldx, const void* qw, const fl
   TLB_REQUIRE(ldx >= K && ldy >= N, "tlb_gemm_q4: row strides shorter than the rows");
   if (M == 0 || N == 0) return TLB_OK;
   CTX(c);
-  // Many rows: tensor-core path (tcgen05, TMEM accumulator, exact tf32 hi/lo splits).
+  // Many rows: tensor-core path (tcgen05, TMEM accumulators).  Default: integer weights x two
+  // fp16 activation planes, group scales applied outside the tensor core (gemm_q4_tc2.cu);
+  // TLB_GEMM_TC=1 selects the earlier formulation with scaled tf32 hi/lo operands.
+  static const bool tc_old = getenv("TLB_GEMM_TC") && atoi(getenv("TLB_GEMM_TC")) == 1;
+  if (!tc_old && gemm_q4_tc2_eligible(qw, scales, (int)N, (int)K, (int)M)) {
+    const size_t need = gemm_q4_tc2_scratch_bytes((int)M, (int)K);
+    if (need > c->xsplit_bytes) {
+      TLB_CUDA(cudaDeviceSynchronize());
+      if (c->xsplit) TLB_CUDA(cudaFree(c->xsplit));
+      c->xsplit = nullptr;
+      c->xsplit_bytes = 0;
+      TLB_CUDA(cudaMalloc(&c->xsplit, need));
+      c->xsplit_bytes = need;
+    }
+    return gemm_q4_tc2_launch(c, x, ldx, (int)M, qw, scales, y, ldy, (int)N, (int)K, alpha, beta, c->xsplit,
+                              S(stream));
+  }
   if (gemm_q4_tc_eligible(qw, scales, (int)N, (int)K, (int)M)) {
     const size_t need = (size_t)2 * M * K * sizeof(float);
     if (need > c->xsplit_bytes) {

@@ -10,8 +10,11 @@
 // row (q fragment, running max / sum / accumulator in registers), the four row
 // groups of a warp share each key row, K/V tiles of 32 keys arrive by bulk copy into
 // a two-stage ring.  f32 throughout (the parity bar is 1e-4 against a double CPU
-// reference); correctness-first -- a tensor-core version is future work.
+// reference).  This CUDA-core form serves bf16 caches; f32 caches take the tensor-core form in
+// attn_prefill_mma.cu.
 #include <cuda_bf16.h>
+
+#include <cstdlib>
 
 #include "attn_common.cuh"
 
@@ -221,9 +224,18 @@ static int launch_attn_prefill_t(DeviceCtx* c, const float* q, const void* K, co
                               pos0, c->status));
   return TLB_OK;
 }
+bool attn_prefill_mma_eligible(int D, int n_kv, long long kv_max, int bf);
+int attn_prefill_mma_launch(DeviceCtx* c, const float* q, const void* K, const void* V, float* out, int n_q,
+                            int n_kv, int T, long long kv_max, int D, float scale, int pos0, cudaStream_t s);
+
 int launch_attn_prefill(DeviceCtx* c, const float* q, const void* K, const void* V, float* out,
                         int n_q, int n_kv, int T, long long kv_max, int D, float scale, int pos0,
                         int bf, cudaStream_t s) {
+  // f32 caches: the tensor-core form (attn_prefill_mma.cu); TLB_PREFILL_MMA=0 keeps the CUDA-core
+  // form below (a diagnostic switch for A/B timing), which also serves bf16 caches
+  static const bool mma_on = !(getenv("TLB_PREFILL_MMA") && atoi(getenv("TLB_PREFILL_MMA")) == 0);
+  if (mma_on && attn_prefill_mma_eligible(D, n_kv, kv_max, bf))
+    return attn_prefill_mma_launch(c, q, K, V, out, n_q, n_kv, T, kv_max, D, scale, pos0, s);
   if (D == 128)
     return bf ? launch_attn_prefill_t<128, true>(c, q, K, V, out, n_q, n_kv, T, kv_max, scale, pos0, s)
               : launch_attn_prefill_t<128, false>(c, q, K, V, out, n_q, n_kv, T, kv_max, scale, pos0, s);

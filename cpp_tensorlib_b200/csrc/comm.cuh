@@ -61,11 +61,16 @@ __device__ __forceinline__ uint2 wait_packet_bounded(const uint2* p, unsigned ta
   uint2 v = ld_packet_sys(p);
   if (v.y == tag) return v;
   const long long t0 = clock64();
-  const long long limit = wait_limit(status);
-  while (true) {
+  // the status block is a second L2 round trip: look at it (the limit, another waiter's
+  // timeout) once in 32 polls, so that the common case costs one load per poll
+  long long limit = 1ll << 62;
+  for (unsigned spin = 1;; spin++) {
     v = ld_packet_sys(p);
     if (v.y == tag) return v;
-    if (status && *(volatile int*)&status[ST_WAIT_TIMEOUT]) return v;
+    if ((spin & 31u) == 0) {
+      limit = wait_limit(status);
+      if (status && *(volatile int*)&status[ST_WAIT_TIMEOUT]) return v;
+    }
     if (clock64() - t0 > limit) {
       if (status) {
         atomicExch(&status[ST_WAIT_TIMEOUT], 1);

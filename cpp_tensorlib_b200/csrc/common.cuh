@@ -122,6 +122,11 @@ __device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, uint32_t parity
                                                   int where) {
   if (mbar_try_wait(bar, parity)) return true;
   const long long t0 = clock64();
+  // the first microseconds poll without touching memory: the limit lives in the status block
+  // (a load that goes to L2) and a wait that reads it up front pays that round trip every time
+  // it does not succeed at once -- several hundred ns per pipeline hand-off
+  while (clock64() - t0 < 8192)
+    if (mbar_try_wait(bar, parity)) return true;
   const long long limit = wait_limit(status);
   while (true) {
     if (mbar_try_wait(bar, parity)) return true;

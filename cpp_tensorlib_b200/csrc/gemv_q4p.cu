@@ -42,7 +42,15 @@
 namespace tlb {
 
 constexpr int PK_UNIT = 2560;
-constexpr int PK_WARPS = 16;
+// Warps per CTA and CTAs per SM: 16 x 1 (one CTA owns the SM's shared memory), or 8 x 2 when
+// built with -DTLB_PK_WARPS=8 (two half-size CTAs per SM, so that a CTA of the NEXT kernel can
+// become resident, and request its weights, as soon as ONE of the two exits).
+#ifndef TLB_PK_WARPS
+#define TLB_PK_WARPS 16
+#endif
+constexpr int PK_WARPS = TLB_PK_WARPS;
+constexpr int PK_CTAS_PER_SM = 16 / PK_WARPS;
+static_assert(PK_WARPS == 16 || PK_WARPS == 8, "16 warps x 1 CTA or 8 warps x 2 CTAs per SM");
 constexpr int PK_CTA_UNITS = 144; // most units one CTA may own in the CTA-owned modes
 
 long long q4p_bytes(long long N, long long K) {
@@ -181,7 +189,7 @@ __device__ __forceinline__ float lds32f(uint32_t a) {
 // (p.epi.kind) as a compile-time value, so the plain projections carry no rope code.
 // PUSH: the tensor-parallel producer (outputs go to every rank's staging as tagged packets).
 template <int STAGES, bool PULL, bool OWN, int EPI, bool PUSH>
-__global__ void __launch_bounds__(PK_WARPS * 32, 1) gemv_q4p_kernel(GemvPParams p) {
+__global__ void __launch_bounds__(PK_WARPS * 32, PK_CTAS_PER_SM) gemv_q4p_kernel(GemvPParams p) {
   extern __shared__ unsigned char smem_raw[];
   unsigned char* base = (unsigned char*)(((uintptr_t)smem_raw + 127) & ~(uintptr_t)127);
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -718,12 +726,15 @@ __global__ void __launch_bounds__(PK_WARPS * 32, 1) gemv_q4p_kernel(GemvPParams 
 
 static int gemvp_stages(int slabs) {
   for (int st = 4; st >= 2; st--)
-    if (gemvp_smem_layout(st, slabs).total <= 227 * 1024) return st;
+    if (gemvp_smem_layout(st, slabs).total <= (size_t)(227 * 1024 / PK_CTAS_PER_SM) - (PK_CTAS_PER_SM > 1 ? 1024 : 0)) return st;
   return 0;
 }
 
 bool gemv_q4p_supported(long long N, long long K) {
-  return N > 0 && K > 0 && K % 32 == 0 && K <= (1 << 20) && gemvp_stages((int)((K + 255) / 256)) != 0;
+  if (!(N > 0 && K > 0 && K % 32 == 0 && K <= (1 << 20))) return false;
+  const int SL = (int)((K + 255) / 256);
+  // whole rows in shared memory, or slab blocks of at most 2 x PK_WARPS slabs
+  return gemvp_stages(SL) != 0 || (SL > 2 * PK_WARPS && gemvp_stages(2 * PK_WARPS) != 0);
 }
 
 template <int STAGES, bool PULL, bool OWN, int EPI, bool PUSH>
@@ -759,19 +770,20 @@ struct GemvPlan {
 // Grid, ownership mode and ring depth of a launch (the decisions, without the launch).
 static int gemvp_plan(DeviceCtx* c, int N, int K, int act, bool has_epi, int max_ctas, GemvPlan* out) {
   GemvPlan pl;
-  pl.stages = gemvp_stages((K + 255) / 256);
-  if (!pl.stages || K % 32) return set_error(TLB_ERR_UNSUPPORTED, "gemv_q4p: K not supported");
+  if (K % 32) return set_error(TLB_ERR_UNSUPPORTED, "gemv_q4p: K not supported");
   const int RT = (N + 15) / 16, SL = (K + 255) / 256;
+  const bool whole_rows_fit = gemvp_stages(SL) != 0;   // else only slab blocks can run this K
   const unsigned U = (unsigned)RT * (unsigned)SL;
   if (RT > c->gemv_max_tiles)
     return set_error(TLB_ERR_UNSUPPORTED, "gemv_q4p: N exceeds the fix-up counter capacity");
-  int ctas = max_ctas > 0 ? max_ctas : c->sm_count;
+  const int slots = c->sm_count * PK_CTAS_PER_SM;   // CTAs resident at once
+  int ctas = max_ctas > 0 ? max_ctas : slots;
   const int need = (int)((U + PK_WARPS - 1) / PK_WARPS);
   if (ctas > need) ctas = need;
   if (ctas * PK_WARPS > c->gemv_max_workers) ctas = c->gemv_max_workers / PK_WARPS;
   {
     // CTA-owned row tiles when that leaves every CTA at most about two units per warp
-    int cb = max_ctas > 0 ? max_ctas : c->sm_count;
+    int cb = max_ctas > 0 ? max_ctas : slots;
     if (cb > RT) cb = RT;
     const int tiles_max = (RT + cb - 1) / cb;
     if (tiles_max * SL <= PK_CTA_UNITS && tiles_max * SL <= 2 * PK_WARPS + PK_WARPS / 2) {
@@ -785,16 +797,16 @@ static int gemvp_plan(DeviceCtx* c, int N, int K, int act, bool has_epi, int max
     // digits, 16 slabs per round, before its stream can start.  Slab blocks cut that to one
     // round at the price of a KB-way fold.  Pick KB by a cost model in ns: a unit is 58 ns of a
     // CTA's share of the stream, a round of activation prep 600 ns, the fold 300 + 100 KB.
-    const int cb = max_ctas > 0 ? max_ctas : c->sm_count;
+    const int cb = max_ctas > 0 ? max_ctas : slots;
     const int workers = ctas * PK_WARPS;
     const long long base_cost = (long long)((U + workers - 1) / workers) * PK_WARPS * 58 +
                                 (long long)((SL + PK_WARPS - 1) / PK_WARPS) * 600;
-    long long best = base_cost;
+    long long best = whole_rows_fit ? base_cost : (1ll << 60);
     int best_kb = 0;
     for (int kb = 2; kb <= 40 && kb <= SL && kb <= cb; kb++) {
       const int rbn = cb / kb < RT ? cb / kb : RT;
       const int ksm = (SL + kb - 1) / kb, tm = (RT + rbn - 1) / rbn;
-      if (ksm * tm > PK_CTA_UNITS) continue;
+      if (ksm * tm > PK_CTA_UNITS || gemvp_stages(ksm) == 0) continue;
       if ((size_t)kb * RT * 16 > (size_t)c->gemv_max_workers * 2 * 128) continue;
       const long long cost = (long long)((ksm * tm + PK_WARPS - 1) / PK_WARPS) * PK_WARPS * 58 +
                              (long long)((ksm + PK_WARPS - 1) / PK_WARPS) * 600 + 300 + 100 * kb;
@@ -805,9 +817,10 @@ static int gemvp_plan(DeviceCtx* c, int N, int K, int act, bool has_epi, int max
       pl.cta_tiles = best_kb;
       pl.slabs = (SL + best_kb - 1) / best_kb;
       ctas = rbn * best_kb;
-      pl.stages = gemvp_stages(pl.slabs);
     }
   }
+  pl.stages = gemvp_stages(pl.slabs);
+  if (!pl.stages) return set_error(TLB_ERR_UNSUPPORTED, "gemv_q4p: K too large for the activation fragments");
   pl.ctas = ctas;
   *out = pl;
   return TLB_OK;

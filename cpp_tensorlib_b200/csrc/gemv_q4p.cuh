@@ -60,7 +60,11 @@ __device__ __forceinline__ void l2_prefetch(const void* ptr, unsigned bytes) {
 // describes and request what that warp (unit-range mode) or that CTA (owned-block mode)
 // streams first.  The address arithmetic mirrors gemv_q4p_kernel.
 __device__ __forceinline__ void gv_prefetch_head(const GvStream& n, unsigned cta, int lane) {
+#ifdef TLB_PK_WARPS
+  constexpr unsigned UNIT = 2560, WARPS = TLB_PK_WARPS;
+#else
   constexpr unsigned UNIT = 2560, WARPS = 16;
+#endif
   if (lane >= (int)WARPS || cta >= (unsigned)n.grid) return;
   if (n.KB == 0) {
     const unsigned Wall = (unsigned)n.grid * WARPS, Wtot = Wall < n.U ? Wall : n.U;
