@@ -107,6 +107,8 @@ static int create_ctx(int dev, DeviceCtx** out) {
   TLB_CUDA(cudaMalloc(&c->gemv_partials, (size_t)c->gemv_max_workers * 2 * 128 * sizeof(float)));
   TLB_CUDA(cudaMalloc(&c->gemv_counters, (size_t)c->gemv_max_tiles * sizeof(int)));
   TLB_CUDA(cudaMemset(c->gemv_counters, 0, (size_t)c->gemv_max_tiles * sizeof(int)));
+  TLB_CUDA(cudaMalloc(&c->chain_cell, 64));
+  TLB_CUDA(cudaMemset(c->chain_cell, 0, 64));
   c->attn_max_counters = 1024;
   TLB_CUDA(cudaMalloc(&c->attn_counters, c->attn_max_counters * sizeof(int)));
   TLB_CUDA(cudaMemset(c->attn_counters, 0, c->attn_max_counters * sizeof(int)));
@@ -202,6 +204,7 @@ int tlb_device_status(int* out2, int clear) {
       // a kernel that gave up may have left its fix-up tickets half counted
       TLB_CUDA(cudaMemset(c->gemv_counters, 0, (size_t)c->gemv_max_tiles * sizeof(int)));
       TLB_CUDA(cudaMemset(c->attn_counters, 0, c->attn_max_counters * sizeof(int)));
+      TLB_CUDA(cudaMemset(c->chain_cell, 0, 64));
       TLB_CUDA(cudaMemset(c->argmax_cell, 0, 4 * sizeof(unsigned long long)));
     }
   }

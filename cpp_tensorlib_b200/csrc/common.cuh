@@ -49,6 +49,7 @@ struct DeviceCtx {
   float* gemv_partials = nullptr;  // [max_workers][2][16*8]
   int* gemv_counters = nullptr;    // [max_row_tiles], zero between launches
   int gemv_max_workers = 0, gemv_max_tiles = 0;
+  unsigned long long* chain_cell = nullptr;   // arrival counter of the GEMV chains' phase barrier
   // attention split-KV partials for the host-ctx entry point (grown on demand)
   float* attn_scratch = nullptr;
   size_t attn_scratch_bytes = 0;
@@ -146,6 +147,22 @@ __device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* tm, in
       "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, "
       "%3}], [%4];" ::"r"(smem_u32(dst)),
       "l"(tm), "r"(x), "r"(y), "r"(smem_u32(bar))
+      : "memory");
+}
+// L2 policy for data that is read once per pass (weight streams): evict it first, so that what
+// is re-read every launch -- the kernels' own instructions above all, then activations and
+// scratch -- stays in the L2 instead of being pushed out by gigabytes of weights.
+__device__ __forceinline__ uint64_t l2_evict_first_policy() {
+  uint64_t pol;
+  asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(pol));
+  return pol;
+}
+__device__ __forceinline__ void bulk_load_1d_hint(void* dst, const void* src, uint32_t bytes, uint64_t* bar,
+                                                  uint64_t policy) {
+  asm volatile(
+      "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint [%0], [%1], %2, [%3], %4;" ::"r"(
+          smem_u32(dst)),
+      "l"(src), "r"(bytes), "r"(smem_u32(bar)), "l"(policy)
       : "memory");
 }
 // 1-D bulk copy global -> shared (16-byte aligned addresses and size).

@@ -115,6 +115,7 @@ struct Decoder {
   // batched prompt pass: row-batched scratch for chunks of up to PF_CHUNK tokens
   float* pf = nullptr;
   int* pf_ids = nullptr;
+  int pf_rows = 0;          // rows the prefill scratch was sized for
   // graph
   cudaGraphExec_t graph = nullptr;
   long long launches_per_token = 0;
@@ -272,6 +273,17 @@ static int forward(Decoder* d, cudaStream_t s) {
     const bool sum = tp && !pull;
     float* x = d->x;
     float* xalt = d->xb;
+    // Single GPU: the four projections between two attention calls (o, gate|up, down, the
+    // next layer's qkv or the lm_head) run as the phases of ONE persistent launch whose
+    // weight ring streams across the phase boundaries.  Opt-in (TLB_CHAIN=1): measured on the
+    // 7B shape it is SLOWER than one launch each (575 - 600 against 685 tokens/s), because
+    // what a projection costs beyond its stream is the activation prep and the fold of the
+    // partial sums -- about 800 instructions per warp of mostly serial code -- and a phase
+    // pays those plus the barrier (1.5 us), where a launch of its own pays them plus 1.3 us.
+    const char* ch = getenv("TLB_CHAIN");
+    const bool chain = !tp && ch && atoi(ch) == 1;
+    bool qkv_done = false;   // this layer's qkv ran as the last phase of the chain before it
+    bool head_done = false;
     for (int l = 0; l < d->n_layers; l++) {
       DecLayer& L = d->layers[l];
       const PairEpi eq = qkv_epilogue(d, L), eg = swiglu_epilogue(d);
@@ -283,7 +295,9 @@ static int forward(Decoder* d, cudaStream_t s) {
                      s_wd = stream_of(c, L.wd, false),
                      s_nx = l + 1 < d->n_layers ? stream_of(c, d->layers[l + 1].wqkv, true)
                                                 : stream_of(c, d->lm_head, true);
-      if (l == 0) {
+      if (qkv_done) {
+        qkv_done = false;
+      } else if (l == 0) {
         RUN(run_linear(c, L.wqkv, d->hb, d->qkv, s, nullptr, 0, nullptr, 0.f, pq));
       } else {
         NormIn nm{pull ? nullptr : d->t1, L.an, xalt, pull ? &c_prev : nullptr};
@@ -296,6 +310,33 @@ static int forward(Decoder* d, cudaStream_t s) {
       RUN(attn_decode_launch(c, d->qkv, L.Kc, L.Vc, d->att, d->n_q, d->n_kv, 0, d->max_ctx, d->hd,
                              d->scale, d->d_pos, (float*)((char*)d->attn_partials + 256),
                              (int*)d->attn_partials, s, 1, d->kv_bf16, &s_wo));
+      if (chain && pg && (E + 255) / 256 <= 32) {
+        const bool last = l + 1 == d->n_layers;
+        const Linear& nx = last ? d->lm_head : d->layers[l + 1].wqkv;
+        PairEpi eqn;
+        if (!last) eqn = qkv_epilogue(d, d->layers[l + 1]);
+        const bool nx_pair = nx.pair_h > 0;
+        if (last ? !nx_pair : nx_pair) {
+          GvPhase ph[4];
+          ph[0].packed = L.wo.packed; ph[0].x = d->att; ph[0].y = d->t0; ph[0].N = L.wo.N; ph[0].K = L.wo.K;
+          ph[1].packed = L.wgu.packed; ph[1].x = x; ph[1].y = d->gu; ph[1].N = L.wgu.N; ph[1].K = L.wgu.K;
+          ph[1].act = 2; ph[1].delta = d->t0; ph[1].nw = L.fn; ph[1].xout = xalt; ph[1].eps = d->eps; ph[1].epi = pg;
+          ph[2].packed = L.wd.packed; ph[2].x = d->mb; ph[2].y = d->t1; ph[2].N = L.wd.N; ph[2].K = L.wd.K;
+          // after gate|up the residual lives in xalt: the fourth phase reads it and writes x
+          ph[3].packed = nx.packed; ph[3].x = xalt; ph[3].y = last ? d->logits : d->qkv; ph[3].N = nx.N; ph[3].K = nx.K;
+          ph[3].act = 2; ph[3].delta = d->t1; ph[3].nw = last ? d->onorm : d->layers[l + 1].an; ph[3].xout = x;
+          ph[3].eps = d->eps; ph[3].epi = last ? nullptr : &eqn;
+          bool fused = false;
+          rc = gemv_q4p_chain_launch(c, ph, 4, s, &fused);
+          if (rc) return rc;
+          if (fused) {
+            n++;
+            // two swaps (gate|up, then the fourth phase): x is the residual again
+            if (last) head_done = true; else qkv_done = true;
+            continue;
+          }
+        }
+      }
       RUN(run_linear(c, L.wo, d->att, tp ? nullptr : d->t0, s, tp ? &c_wo : nullptr, 0, nullptr, 0.f, nullptr,
                      &s_gu));
       if (sum) RUN(launch_ar_sum(d->t0, E, c_wo, c->status, s));
@@ -316,7 +357,7 @@ static int forward(Decoder* d, cudaStream_t s) {
     // the next token starts with layer 0's QKV projection (plain prologue: its norm is done
     // by the embedding gather)
     const GvStream s_q0 = stream_of(c, d->layers[0].wqkv, false);
-    RUN(run_linear(c, d->lm_head, x, d->logits, s, nullptr, 0, &no, d->eps, nullptr, &s_q0));
+    if (!head_done) RUN(run_linear(c, d->lm_head, x, d->logits, s, nullptr, 0, &no, d->eps, nullptr, &s_q0));
     if (tp) {
       RUN(launch_argmax_tp(c, d->logits, d->vocab, d->vocab_offset, cm(2 * d->n_layers), d->d_tok,
                            d->d_tok_out, s));
@@ -639,7 +680,7 @@ int tlb_decoder_step(void* h, const int32_t* token_in, int32_t* token_out, void*
 // ---- batched prompt pass (bench/cuda/qwen_model.h:357-442 prefill_chunk_ / prefill_batched):
 // the same forward as the decode step with one row per prompt token -- every projection is a
 // GEMM on the int4 weights (tensor cores for more than 8 rows), attention is one tiled causal
-// pass over the cache -- in chunks of up to 256 tokens starting at the decoder's current
+// pass over the cache -- in chunks of up to 1024 tokens starting at the decoder's current
 // position.  Leaves the caches and the position at pos + T, the greedy next token in the
 // device-resident token cell (so tlb_decoder_run continues from there) and in *next_token.
 // Single GPU; the weights are read in the reference layout the caller handed to
@@ -653,7 +694,9 @@ int tlb_decoder_prefill(void* h, const int32_t* tokens, int64_t T, int32_t* next
   int rc = get_ctx(&c);
   if (rc) return rc;
   cudaStream_t s = (cudaStream_t)stream;
-  constexpr int CH = 256;
+  // rows per pass: enough CTAs for the narrow (hidden-wide) projections; TLB_PREFILL_CHUNK overrides
+  int CH = 1024;
+  if (const char* e = getenv("TLB_PREFILL_CHUNK")) CH = atoi(e) < 16 ? 16 : (atoi(e) > 8192 ? 8192 : atoi(e));
   const int E = d->hidden, D = d->hd, NQ = d->n_q, NKV = d->n_kv, FF = d->ff;
   const int QKV = (NQ + 2 * NKV) * D;
   unsigned pos0 = 0;
@@ -669,9 +712,17 @@ int tlb_decoder_prefill(void* h, const int32_t* tokens, int64_t T, int32_t* next
   const size_t n_emb = (size_t)CH * E, n_qkv = (size_t)CH * QKV, n_att = (size_t)CH * NQ * D,
                n_gu = (size_t)CH * 2 * FF, n_mb = (size_t)CH * FF;
   const size_t total = 5 * n_emb /* res0 res1 h h2 md */ + 2 * n_qkv + 2 * n_att + n_gu + n_mb;
+  if (d->pf && d->pf_rows < CH) {
+    TLB_CUDA(cudaStreamSynchronize(s));
+    TLB_CUDA(cudaFree(d->pf));
+    TLB_CUDA(cudaFree(d->pf_ids));
+    d->pf = nullptr;
+    d->pf_ids = nullptr;
+  }
   if (!d->pf) {
     TLB_CUDA(cudaMalloc(&d->pf, total * sizeof(float)));
     TLB_CUDA(cudaMalloc(&d->pf_ids, CH * sizeof(int)));
+    d->pf_rows = CH;
   }
   float* p = d->pf;
   float* res[2] = {p, p + n_emb};

@@ -307,6 +307,10 @@ __global__ void __launch_bounds__(T2_THREADS, 1)
       if (!mbar_wait_bounded(&bars[T2_D_FULL + buf], (gi / T2_NBUF) & 1, p.status, 630)) { ok = false; break; }
       t2_fence_after();
       const uint32_t taddr = tmem + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(buf * MT + c_lo);
+      // 32 columns per read; the accumulator goes back to the issuers as soon as the last
+      // read has landed, before its FMAs.  (Measured and dropped: fma.rn.f32x2 pairs -- the
+      // register pairing costs more than the halved FMA count saves, 200 vs 170 us at M = 512 --
+      // and 16-column reads in flight under the previous 16 columns' FMAs.)
       constexpr int BATCH = HC < 32 ? HC : 32;
 #pragma unroll
       for (int c0 = 0; c0 < HC; c0 += BATCH) {
@@ -314,14 +318,16 @@ __global__ void __launch_bounds__(T2_THREADS, 1)
 #pragma unroll
         for (int b = 0; b < BATCH / 16; b++) t2_ld16_issue(taddr + (uint32_t)(c0 + 16 * b), v[b]);
         t2_wait_ld();
+        if (c0 + BATCH >= HC) {
+          t2_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&bars[T2_D_EMPTY + buf]);
+        }
 #pragma unroll
         for (int b = 0; b < BATCH / 16; b++)
 #pragma unroll
           for (int i = 0; i < 16; i++) acc[c0 + 16 * b + i] = fmaf(sc, __uint_as_float(v[b][i]), acc[c0 + 16 * b + i]);
       }
-      t2_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(&bars[T2_D_EMPTY + buf]);
     }
     if (ok && n < p.N) {
 #pragma unroll
@@ -349,8 +355,17 @@ __global__ void split_f16_kernel(const float* __restrict__ x, long long ldx, int
   pdl_launch_dependents();
   const int m = blockIdx.x;
   const float* row = x + (long long)m * ldx;
+  const bool vec = ((uintptr_t)row & 15) == 0;   // K % 8 == 0 always; 16-byte rows take the float4 path
   float mx = 0.f;
-  for (int k = threadIdx.x; k < K; k += blockDim.x) mx = fmaxf(mx, fabsf(row[k]));
+  if (vec) {
+    const float4* row4 = (const float4*)row;
+    for (int i = threadIdx.x; i < K / 4; i += blockDim.x) {
+      const float4 a = __ldg(row4 + i);
+      mx = fmaxf(fmaxf(mx, fmaxf(fabsf(a.x), fabsf(a.y))), fmaxf(fabsf(a.z), fabsf(a.w)));
+    }
+  } else {
+    for (int k = threadIdx.x; k < K; k += blockDim.x) mx = fmaxf(mx, fabsf(row[k]));
+  }
   mx = warp_max(mx);
   if ((threadIdx.x & 31) == 0) sm[threadIdx.x >> 5] = mx;
   __syncthreads();
@@ -365,6 +380,26 @@ __global__ void split_f16_kernel(const float* __restrict__ x, long long ldx, int
   }
   const float s = ldexpf(1.0f, -e);
   if (threadIdx.x == 0) rowscale[m] = ldexpf(1.0f, e);
+  if (vec) {
+    const float4* row4 = (const float4*)row;
+    uint4* o1 = (uint4*)(x1 + (size_t)m * K);
+    uint4* o2 = (uint4*)(x2 + (size_t)m * K);
+    for (int i = threadIdx.x; i < K / 8; i += blockDim.x) {
+      const float4 a = __ldg(row4 + 2 * i), b = __ldg(row4 + 2 * i + 1);
+      const float f[8] = {a.x * s, b.x * s, a.y * s, b.y * s, a.z * s, b.z * s, a.w * s, b.w * s};   // k 0,4,1,5,2,6,3,7
+      unsigned w1[4], w2[4];
+#pragma unroll
+      for (int j = 0; j < 4; j++) {
+        const __half ha = __float2half_rn(f[2 * j]), hb = __float2half_rn(f[2 * j + 1]);
+        const __half la = __float2half_rn(f[2 * j] - __half2float(ha)), lb = __float2half_rn(f[2 * j + 1] - __half2float(hb));
+        w1[j] = (unsigned)__half_as_ushort(ha) | ((unsigned)__half_as_ushort(hb) << 16);
+        w2[j] = (unsigned)__half_as_ushort(la) | ((unsigned)__half_as_ushort(lb) << 16);
+      }
+      o1[i] = make_uint4(w1[0], w1[1], w1[2], w1[3]);
+      o2[i] = make_uint4(w2[0], w2[1], w2[2], w2[3]);
+    }
+    return;
+  }
   for (int k = threadIdx.x; k < K; k += blockDim.x) {
     const float v = row[k] * s;
     const __half h1 = __float2half_rn(v);

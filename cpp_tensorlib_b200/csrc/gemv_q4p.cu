@@ -51,6 +51,9 @@ constexpr int PK_UNIT = 2560;
 constexpr int PK_WARPS = TLB_PK_WARPS;
 constexpr int PK_CTAS_PER_SM = 16 / PK_WARPS;
 static_assert(PK_WARPS == 16 || PK_WARPS == 8, "16 warps x 1 CTA or 8 warps x 2 CTAs per SM");
+// dynamic shared memory a CTA may ask for: the 227 KB of an SM less the kernels' static part
+// (the warps' producer cursors, the chain's epoch)
+constexpr int PK_DYN_SMEM_MAX = 224 * 1024;
 constexpr int PK_CTA_UNITS = 144; // most units one CTA may own in the CTA-owned modes
 
 long long q4p_bytes(long long N, long long K) {
@@ -135,6 +138,12 @@ struct GemvPParams {
                     // a CTA prepares only its own slabs of the activation; the KB partial blocks
                     // of a row block are folded by the last CTA to arrive
   int slabs;        // activation slabs a CTA holds in shared memory (SL, or the largest slab block)
+  int grid;         // CTAs that work on this launch / phase (a chain's grid can be larger)
+  // the splits of units over warps (unit ranges) or of row tiles / slabs over CTAs (owned
+  // blocks), divided out on the host: a run-time division is two dozen instructions of a
+  // prologue that runs from a cold instruction cache
+  unsigned Wtot, RB;
+  GvSplit sp, ct, cs;
   CommDev comm;
   GvStream pf;      // what the next weight-streaming kernel reads first (wp == NULL: nothing)
 };
@@ -183,15 +192,141 @@ __device__ __forceinline__ float lds32f(uint32_t a) {
   return v;
 }
 
+#ifdef GV_PROF
+__device__ long long gv_prof[160][20];
+__device__ __forceinline__ long long gv_now() { long long t; asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t)); return t; }
+__device__ int gv_gate;
+__device__ int gv_sel;   // standalone launches: record the matrix with this many rows
+#define GV_MARK(i) do { if (threadIdx.x == 0 && *(volatile int*)&gv_gate) gv_prof[blockIdx.x][i] = gv_now(); } while (0)
+#else
+#define GV_MARK(i) do { } while (0)
+#endif
+// One warp's share of a launch (or of one phase of a chain): which units it streams and how
+// they map to (row tile, slab).
+struct GvWarp {
+  bool idle;
+  unsigned u0, u1, wid, kb, rb;
+  GvSplit sp;
+  int n_units, tile_b, n_loc, s_b, ks, rt, s;
+};
+__device__ __forceinline__ void gv_warp_setup(const GemvPParams& p, int warp, GvWarp& w) {
+  const int SL = p.SL;
+  const unsigned grid = (unsigned)p.grid;
+  const bool in_grid = blockIdx.x < grid;
+  // Never more workers than units, so every worker's range is non-empty and the
+  // contributors of a row tile are exactly the owners of its first..last unit.
+  const unsigned Wtot = p.Wtot;
+  w.wid = blockIdx.x * PK_WARPS + warp;
+  w.idle = !in_grid || w.wid >= Wtot;
+  w.sp = p.sp;
+  w.u0 = w.idle ? 0u : gv_start(w.wid, w.sp);
+  w.u1 = w.idle ? 0u : gv_start(w.wid + 1, w.sp);
+  w.n_units = (int)(w.u1 - w.u0);
+  // Small matrices (about two row tiles per CTA or fewer): a CTA owns whole row tiles,
+  // its warps take the tiles' units round-robin and the 16-row results meet in shared
+  // memory -- no partials in global memory, no ticket, no last-arriver chain.
+  w.tile_b = 0; w.n_loc = 0;
+  w.s_b = 0; w.ks = SL;      // the slabs this CTA prepares and indexes locally: [s_b, s_b + ks)
+  w.rt = 0; w.s = 0;         // row tile and (local) slab of the unit being consumed
+  w.kb = 0; w.rb = 0;
+  if (p.cta_tiles) {
+    if (!in_grid) {
+      w.n_units = 0;
+      return;
+    }
+    const unsigned KB = (unsigned)p.cta_tiles;
+    w.rb = KB == 1 ? blockIdx.x : blockIdx.x / KB;
+    w.kb = blockIdx.x - w.rb * KB;
+    const GvSplit ct = p.ct, cs = p.cs;
+    w.tile_b = (int)gv_start(w.rb, ct);
+    w.s_b = (int)gv_start(w.kb, cs);
+    w.ks = (int)gv_start(w.kb + 1, cs) - w.s_b;
+    w.n_loc = ((int)gv_start(w.rb + 1, ct) - w.tile_b) * w.ks;
+    w.n_units = warp < w.n_loc ? (w.n_loc - warp + PK_WARPS - 1) / PK_WARPS : 0;
+    // the block's units in (tile, slab) order, dealt round-robin: this warp starts at `warp`
+    w.rt = w.tile_b + warp / w.ks;
+    w.s = warp % w.ks;
+    w.u0 = (unsigned)(w.rt * SL + w.s_b + w.s);
+  } else {
+    w.rt = (int)(w.u0 / (unsigned)SL);
+    w.s = (int)(w.u0 - (unsigned)w.rt * SL);
+  }
+}
+
+// A warp's ring of weight units lives across the phases of a chain: the producer cursor says
+// where its next unit comes from (and moves on to the next phase's range when this one's is
+// issued), the ring state which slot is filled / consumed next.  Weights depend on nothing, so
+// the ring is refilled for the next phase while this one's results still travel.
+struct GvCursor {
+  const unsigned char* src;
+  int isl, ks, SL, left, own, ph;
+};
+struct GvRing {
+  int istage, inflight, st;
+  unsigned parity;
+  bool dead;   // a wait ran out: consume nothing more
+  uint64_t policy;   // L2 evict-first: a weight byte is read once per token
+};
+__device__ __forceinline__ void gv_cursor_from(GvCursor& c, const GemvPParams& p, const GvWarp& w) {
+  c.src = p.wp + (size_t)w.u0 * PK_UNIT;
+  c.isl = w.s;
+  c.ks = w.ks;
+  c.SL = p.SL;
+  c.left = w.n_units;
+  c.own = p.cta_tiles != 0;
+}
+__device__ __forceinline__ void gv_cursor_set(GvCursor& c, const GemvPParams& p, int warp) {
+  GvWarp w;
+  gv_warp_setup(p, warp, w);
+  gv_cursor_from(c, p, w);
+}
+// Fill the ring up to `limit` units in flight, walking on into later phases.
+// `table`: this warp's cursors of all phases (shared memory; NULL for a single launch).
+template <int STAGES>
+__device__ __forceinline__ void gv_top_up(GvRing& r, GvCursor& c, const GvCursor* table, int nph,
+                                          unsigned char* myR, uint64_t* mybar, int lane, int limit) {
+  while (r.inflight < limit) {
+    while (c.left == 0 && c.ph + 1 < nph) {
+      const int ph = c.ph + 1;
+      c = table[ph];
+      c.ph = ph;
+    }
+    if (c.left == 0) return;
+    // lane 0 issues one 2560-byte bulk copy per unit
+    if (lane == 0) {
+      mbar_expect_tx(&mybar[r.istage], PK_UNIT);
+      bulk_load_1d_hint(myR + r.istage * PK_UNIT, c.src, PK_UNIT, &mybar[r.istage], r.policy);
+    }
+    if (c.own) {
+      // PK_WARPS units further on in the block; past the block's slabs the next tile's begin
+      c.isl += PK_WARPS;
+      c.src += (size_t)PK_WARPS * PK_UNIT;
+      while (c.isl >= c.ks) {
+        c.isl -= c.ks;
+        c.src += (size_t)(c.SL - c.ks) * PK_UNIT;
+      }
+    } else {
+      c.src += PK_UNIT;
+    }
+    c.left--;
+    r.inflight++;
+    if (++r.istage == STAGES) r.istage = 0;
+  }
+}
+
 // PULL: the instantiation that can consume a tensor-parallel exchange in its prologue (act 3);
 // kept out of the single-GPU kernel, whose register budget it would eat.
 // OWN: the CTA-owned-block instantiation (p.cta_tiles != 0).  EPI: the pair epilogue
 // (p.epi.kind) as a compile-time value, so the plain projections carry no rope code.
 // PUSH: the tensor-parallel producer (outputs go to every rank's staging as tagged packets).
-template <int STAGES, bool PULL, bool OWN, int EPI, bool PUSH>
-__global__ void __launch_bounds__(PK_WARPS * 32, PK_CTAS_PER_SM) gemv_q4p_kernel(GemvPParams p) {
-  extern __shared__ unsigned char smem_raw[];
-  unsigned char* base = (unsigned char*)(((uintptr_t)smem_raw + 127) & ~(uintptr_t)127);
+// The work of one launch, or of one phase `phi` of a chain of `nph` (phases[phi] == p).
+// OWN_T / EPI_T = -1: read from the parameters at run time -- ONE instantiation for every
+// single-GPU projection of a decoder, so that its code stays in the instruction cache from one
+// launch to the next (four instantiations per layer do not fit, and their prologues then run
+// at the speed of instruction fetches from the L2).
+template <int STAGES, bool PULL, int OWN_T, int EPI_T, bool PUSH>
+__device__ __forceinline__ void gemv_q4p_body(const GemvPParams& p, const GvCursor* table, int nph, int phi,
+                                              GvRing& ring, GvCursor& cur, unsigned char* base) {
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int g = lane >> 2, t = lane & 3;
   const int SL = p.SL;
@@ -204,85 +339,50 @@ __global__ void __launch_bounds__(PK_WARPS * 32, PK_CTAS_PER_SM) gemv_q4p_kernel
   unsigned char* myR = base + L.ring + (size_t)warp * STAGES * PK_UNIT;
   uint64_t* mybar = bars + warp * STAGES;
 
-  // Never more workers than units, so every worker's range is non-empty and the
-  // contributors of a row tile are exactly the owners of its first..last unit.
-  const unsigned Wall = gridDim.x * PK_WARPS;
-  const unsigned Wtot = Wall < p.U ? Wall : p.U;
-  const unsigned wid = blockIdx.x * PK_WARPS + warp;
-  const bool idle = wid >= Wtot;
-  const GvSplit sp = {p.U / Wtot, p.U % Wtot};
-  unsigned u0 = idle ? 0u : gv_start(wid, sp);
-  const unsigned u1 = idle ? 0u : gv_start(wid + 1, sp);
-  int n_units = (int)(u1 - u0);
-  // Small matrices (about two row tiles per CTA or fewer): a CTA owns whole row tiles,
-  // its warps take the tiles' units round-robin and the 16-row results meet in shared
-  // memory -- no partials in global memory, no ticket, no last-arriver chain.
-  constexpr bool own = OWN;
-  int tile_b = 0, n_loc = 0;
-  int s_b = 0, ks = SL;      // the slabs this CTA prepares and indexes locally: [s_b, s_b + ks)
-  int rt = 0, s = 0;         // row tile and (local) slab of the unit being consumed
-  unsigned kb = 0, rb = 0;
-  if (own) {
-    const unsigned KB = (unsigned)p.cta_tiles, RB = gridDim.x / KB;
-    rb = blockIdx.x / KB;
-    kb = blockIdx.x - rb * KB;
-    const GvSplit ct = {(unsigned)p.RT / RB, (unsigned)p.RT % RB};
-    const GvSplit cs = {(unsigned)SL / KB, (unsigned)SL % KB};
-    tile_b = (int)gv_start(rb, ct);
-    s_b = (int)gv_start(kb, cs);
-    ks = (int)gv_start(kb + 1, cs) - s_b;
-    n_loc = ((int)gv_start(rb + 1, ct) - tile_b) * ks;
-    n_units = warp < n_loc ? (n_loc - warp + PK_WARPS - 1) / PK_WARPS : 0;
-    // the block's units in (tile, slab) order, dealt round-robin: this warp starts at `warp`
-    rt = tile_b + warp / ks;
-    s = warp % ks;
-    u0 = (unsigned)(rt * SL + s_b + s);
-  } else {
-    rt = (int)(u0 / (unsigned)SL);
-    s = (int)(u0 - (unsigned)rt * SL);
-  }
+  GvWarp ws;
+  gv_warp_setup(p, warp, ws);
+  if (nph == 1) gv_cursor_from(cur, p, ws);   // a single launch: the one setup serves the producer too
+  const unsigned wid = ws.wid, u0 = ws.u0, u1 = ws.u1, kb = ws.kb, rb = ws.rb;
+  const GvSplit sp = ws.sp;
+  const int n_units = ring.dead ? 0 : ws.n_units;
+  const bool own = OWN_T < 0 ? (p.cta_tiles != 0) : (OWN_T != 0);
+  const int EPI = EPI_T < 0 ? p.epi.kind : EPI_T;
+  const int tile_b = ws.tile_b, n_loc = ws.n_loc, s_b = ws.s_b, ks = ws.ks;
+  int rt = ws.rt, s = ws.s;
   float* ures = (float*)(base + L.ures);
 
-  if (lane == 0) {
-    for (int s = 0; s < STAGES; s++) mbar_init(&mybar[s], 1);
-    mbar_fence_init();
-  }
-  __syncwarp();
-
-  // producer: lane 0 issues one 2560-byte bulk copy per unit, the warp's units are
-  // consecutive in memory
-  const unsigned char* src = p.wp + (size_t)u0 * PK_UNIT;
-  int istage = 0, isl = s;
-  auto issue_next = [&]() {
-    if (lane == 0) {
-      mbar_expect_tx(&mybar[istage], PK_UNIT);
-      bulk_load_1d(myR + istage * PK_UNIT, src, PK_UNIT, &mybar[istage]);
-    }
-    if (own) {
-      // PK_WARPS units further on in the block; past the block's slabs the next tile's begin
-      isl += PK_WARPS;
-      src += (size_t)PK_WARPS * PK_UNIT;
-      while (isl >= ks) {
-        isl -= ks;
-        src += (size_t)(SL - ks) * PK_UNIT;
-      }
-    } else {
-      src += PK_UNIT;
-    }
-    if (++istage == STAGES) istage = 0;
-  };
+  auto top_up = [&](int limit) { gv_top_up<STAGES>(ring, cur, table, nph, myR, mybar, lane, limit); };
   // Weights do not depend on the previous kernel: the first stage streams before the
   // wait.  The other stages are issued right after the activation loads below, so
-  // those small loads are not queued behind the weight traffic.
-  const int pre_total = n_units < STAGES ? n_units : STAGES;
-  if (pre_total > 0) issue_next();
-
-  pdl_wait();  // activations and the fix-up scratch are valid from here
+  // those small loads are not queued behind the weight traffic.  (Later phases of a chain
+  // find their ring filled by the phase before.)
+  if (phi == 0) {
+    top_up(1);
+    // While the kernel in front still runs: touch what the prep will read, so that the
+    // address translations (and for the norm weights, which nobody writes, the data) are
+    // there when the wait returns.  A prefetch of a line the previous kernel is still
+    // writing is harmless: the L2 is where its stores land.
+    {
+      const int k0 = (s_b + warp) * 256 + lane * 8;
+      if (warp < ks && k0 < p.K) {
+        asm volatile("prefetch.global.L2 [%0];" ::"l"(p.x + k0));
+        if (p.act == 1) asm volatile("prefetch.global.L2 [%0];" ::"l"(p.x + p.K + k0));
+        if (p.act == 2) {
+          asm volatile("prefetch.global.L2 [%0];" ::"l"(p.delta + k0));
+          asm volatile("prefetch.global.L2 [%0];" ::"l"(p.nw + k0));
+        }
+      }
+    }
+    pdl_wait();  // activations and the fix-up scratch are valid from here
+  }
+#ifdef GV_PROF
+  const bool sel = nph == 1 && gv_sel == p.N;
+  if (sel && threadIdx.x == 0) gv_prof[blockIdx.x][1] = gv_now();
+#endif
 
   // ---- activation prep.  One warp per slab of 256 k, four slabs in flight per warp.
   // Lane l covers x[256*slab + 8*l .. +8) = group jj = l/4, quad slot tt = l%4.
   float nrm_inv = 1.f;
-  constexpr int PB = 2;
   const bool normed = p.act == 2 || (PULL && p.act == 3);
   unsigned pull_seq = 0;
   if (PULL && p.act == 3) pull_seq = comm_seq(p.comm);
@@ -318,126 +418,182 @@ __global__ void __launch_bounds__(PK_WARPS * 32, PK_CTAS_PER_SM) gemv_q4p_kernel
     }
   };
   // (slab indices are local to the CTA's block [s_b, s_b + ks); the whole row unless KB > 1)
-  for (int job0 = warp; job0 < ks || job0 == warp; job0 += PK_WARPS * PB) {
-    float vv[PB][8], uu[PB][8], ww[PB][8];
-#pragma unroll
-    for (int b = 0; b < PB; b++) {
-      const int sl = job0 + b * PK_WARPS;
-      const int k0 = (s_b + sl) * 256 + lane * 8;
-      const bool on = sl < ks && k0 < p.K;   // K % 32 == 0: a lane's 8 values are all in or all out
-      auto load8 = [&](const float* s8, float (&o)[8]) {
-        if (on) {
-          if (p.x_vec_ok) {
-            const float4 q0 = *(const float4*)s8, q1 = *(const float4*)(s8 + 4);
-            o[0] = q0.x; o[1] = q0.y; o[2] = q0.z; o[3] = q0.w;
-            o[4] = q1.x; o[5] = q1.y; o[6] = q1.z; o[7] = q1.w;
+  //
+  // This code runs once per launch, straight from a cold instruction cache: what it costs is
+  // its LENGTH (measured: 3 us of a 5 us projection with two unrolled slab batches per warp),
+  // so there is one copy of the load and one of the conversion, in loops that are not unrolled.
+  float xv[8], xu[8], xw[8];   // the slab's activation, its second operand (up / delta), its norm weights
+  auto load_slab = [&](int sl, bool with_w) {
+    const int k0 = (s_b + sl) * 256 + lane * 8;
+    const bool on = sl < ks && k0 < p.K;   // K % 32 == 0: a lane's 8 values are all in or all out
+    auto load8 = [&](const float* s8, float (&o)[8]) {
+      if (on) {
+        if (p.x_vec_ok) {
+          // .cg in a chain: the vector was written by other SMs earlier in this launch.  A
+          // launch of its own reads through the L1 (measured 1 % of a decode step faster).
+          float4 q0, q1;
+          if (nph > 1) {
+            q0 = __ldcg((const float4*)s8);
+            q1 = __ldcg((const float4*)(s8 + 4));
           } else {
-#pragma unroll
-            for (int i = 0; i < 8; i++) o[i] = s8[i];
+            q0 = *(const float4*)s8;
+            q1 = *(const float4*)(s8 + 4);
           }
+          o[0] = q0.x; o[1] = q0.y; o[2] = q0.z; o[3] = q0.w;
+          o[4] = q1.x; o[5] = q1.y; o[6] = q1.z; o[7] = q1.w;
         } else {
 #pragma unroll
-          for (int i = 0; i < 8; i++) o[i] = 0.f;
+          for (int i = 0; i < 8; i++) o[i] = nph > 1 ? __ldcg(s8 + i) : s8[i];
         }
-      };
-      load8(p.x + k0, vv[b]);
-      if (p.act == 1) load8(p.x + p.K + k0, uu[b]);
-      if (p.act == 2) load8(p.delta + k0, uu[b]);
-      // the norm weights travel with the activation: no load left behind the block barrier
-      if (normed) load8(p.nw + k0, ww[b]);
-      if constexpr (PULL) {
-        if (p.act == 3) pull8(k0, uu[b], on);
+      } else {
+#pragma unroll
+        for (int i = 0; i < 8; i++) o[i] = 0.f;
       }
+    };
+    load8(p.x + k0, xv);
+    if (p.act == 1) load8(p.x + p.K + k0, xu);
+    if (p.act == 2) load8(p.delta + k0, xu);
+    // the norm weights travel with the activation: no load left behind the block barrier
+    if (normed && with_w) load8(p.nw + k0, xw);
+    if constexpr (PULL) {
+      if (p.act == 3) pull8(k0, xu, on);
     }
-    if (job0 == warp) {
-      // first batch: its loads are in flight, now queue the rest of the weight ring
-      // (an L2 prefetch of the units behind the ring was tried here and lost 4 us on the
-      // 85 MB gate|up matrix: the demand copies queue behind it)
-      for (int i = 1; i < pre_total; i++) issue_next();
-      if (normed) {
-        // fused residual add + RMSNorm (tl_add_rmsnorm, kernels/tensorlib_cuda.cu:155-179):
-        // every CTA reduces sum((x+delta)^2) itself from the values it just loaded, in
-        // the same order everywhere, so all CTAs agree on the scale.  (The host only
-        // selects this mode when one batch covers the row.)
-        float sq = 0.f;
+  };
+  load_slab(warp, true);
+#ifdef GV_PROF
+  if (sel && threadIdx.x == 0) gv_prof[blockIdx.x][4] = gv_now();
+#endif
+  // The rest of the weight ring is queued only when this warp's activation values have
+  // ARRIVED (first use below): a small load issued behind 160 KB of bulk copies per SM waits
+  // until they have drained -- measured, the prep of a projection took 2 - 4 us that way, the
+  // time the ring fill needs from HBM.  (An L2 prefetch of the units behind the ring was tried
+  // too and lost 4 us on the 85 MB gate|up matrix for the same reason.)
+  if (normed) {
+    // fused residual add + RMSNorm (tl_add_rmsnorm, kernels/tensorlib_cuda.cu:155-179):
+    // every CTA reduces sum((x+delta)^2) itself, slabs in the same order everywhere, so all
+    // CTAs agree on the scale
+    float sq = 0.f;
 #pragma unroll
-        for (int b = 0; b < PB; b++)
-#pragma unroll
-          for (int i = 0; i < 8; i++) {
-            const float sv = vv[b][i] + uu[b][i];
-            sq = fmaf(sv, sv, sq);
-          }
-        sq = warp_sum(sq);
-        if (lane == 0) red[warp] = sq;
-        __syncthreads();
-        float tot = 0.f;
-        for (int w = 0; w < PK_WARPS; w++) tot += red[w];
-        nrm_inv = 1.0f / sqrtf(tot / (float)p.K + p.eps);
-      }
+    for (int i = 0; i < 8; i++) {
+      const float sv = xv[i] + xu[i];
+      sq = fmaf(sv, sv, sq);
     }
+    if (ks > PK_WARPS) {
+      // rows longer than 16 slabs: this warp's further slabs, read once more below
+      float kv[8], ku[8], kw[8];
 #pragma unroll
-    for (int b = 0; b < PB; b++) {
-      const int sl = job0 + b * PK_WARPS;
-      if (sl >= ks) break;  // warp-uniform
-      float v[8];
-#pragma unroll
-      for (int i = 0; i < 8; i++) v[i] = vv[b][i];
-      if (p.act == 1) {
-        // fused SwiGLU (kernels/tensorlib_cuda.cu:185-192 of the reference): the row
-        // holds gate then up; same expression g / (1 + exp(-g)) * u
-#pragma unroll
-        for (int i = 0; i < 8; i++) v[i] = (v[i] / (1.0f + expf(-v[i]))) * uu[b][i];
-      }
-      if (normed) {
-        const int k0 = sl * 256 + lane * 8;   // (the fused norm is never combined with slab blocks)
+      for (int i = 0; i < 8; i++) { kv[i] = xv[i]; ku[i] = xu[i]; kw[i] = xw[i]; }
+#pragma unroll 1
+      for (int sl = warp + PK_WARPS; sl < ks; sl += PK_WARPS) {
+        load_slab(sl, false);
 #pragma unroll
         for (int i = 0; i < 8; i++) {
-          const float sv = v[i] + uu[b][i];
-          const bool in = k0 + i < p.K;
-          if (in && blockIdx.x == 0) p.xout[k0 + i] = sv;
-          v[i] = in ? sv * nrm_inv * ww[b][i] : 0.f;
+          const float sv = xv[i] + xu[i];
+          sq = fmaf(sv, sv, sq);
         }
       }
-      float mx = 0.f;
 #pragma unroll
-      for (int i = 0; i < 8; i++) mx = fmaxf(mx, fabsf(v[i]));
-      mx = warp_max(mx);
-      int e = (int)((__float_as_uint(mx) >> 23) & 0xff) - 126;  // mx < 2^e
-      e = mx > 0.f ? (e < -100 ? -100 : (e > 100 ? 100 : e)) : 0;
-      if (!(mx < 3.0e38f)) e = 100;                              // inf / nan: keep the exponent legal
-      const float s23 = __uint_as_float((unsigned)(127 + 23 - e) << 23);
-      int isum = 0;
-      unsigned hh[8], ll[8];
+      for (int i = 0; i < 8; i++) { xv[i] = kv[i]; xu[i] = ku[i]; xw[i] = kw[i]; }
+    }
+    sq = warp_sum(sq);
+#ifdef GV_PROF
+    if (sel && threadIdx.x == 0) gv_prof[blockIdx.x][5] = gv_now();
+#endif
+    top_up(STAGES);
+    if (lane == 0) red[warp] = sq;
+    __syncthreads();
+    float tot = 0.f;
+#pragma unroll
+    for (int w = 0; w < PK_WARPS; w++) tot += red[w];
+    nrm_inv = 1.0f / sqrtf(tot / (float)p.K + p.eps);
+#ifdef GV_PROF
+    if (sel && threadIdx.x == 0) gv_prof[blockIdx.x][6] = gv_now();
+#endif
+  }
+#pragma unroll 1
+  for (int sl = warp; sl < ks; sl += PK_WARPS) {
+    if (sl != warp) load_slab(sl, true);
+    float v[8];
+#pragma unroll
+    for (int i = 0; i < 8; i++) v[i] = xv[i];
+    if (p.act == 1) {
+      // fused SwiGLU (kernels/tensorlib_cuda.cu:185-192 of the reference): the row
+      // holds gate then up; same expression g / (1 + exp(-g)) * u
+#pragma unroll
+      for (int i = 0; i < 8; i++) v[i] = (v[i] / (1.0f + expf(-v[i]))) * xu[i];
+    }
+    if (normed) {
+      const int k0 = sl * 256 + lane * 8;   // (the fused norm is never combined with slab blocks)
 #pragma unroll
       for (int i = 0; i < 8; i++) {
-        const int X = __float2int_rn(v[i] * s23);                // |X| <= 2^23
-        const int d1 = ((X + 2048) & 4095) - 2048;               // [-2048, 2047]
-        const int d0 = (X - d1) >> 12;                           // [-2048, 2048]
-        isum += X;
-        // the odd nibble of a byte reads as nib * 2^-20: its activation digits carry 2^-4
-        const float f = (i & 1) ? 0.0625f : 1.0f;
-        hh[i] = __half_as_ushort(__float2half_rn((float)d0 * f));
-        ll[i] = __half_as_ushort(__float2half_rn((float)d1 * f));
+        const float sv = v[i] + xu[i];
+        const bool in = k0 + i < p.K;
+        if (in && blockIdx.x == 0) p.xout[k0 + i] = sv;
+        v[i] = in ? sv * nrm_inv * xw[i] : 0.f;
       }
-      isum += __shfl_xor_sync(0xffffffffu, isum, 1);
-      isum += __shfl_xor_sync(0xffffffffu, isum, 2);
-      uint4 fh, fl;
-      fh.x = hh[0] | (hh[4] << 16); fh.y = hh[1] | (hh[5] << 16);
-      fh.z = hh[2] | (hh[6] << 16); fh.w = hh[3] | (hh[7] << 16);
-      fl.x = ll[0] | (ll[4] << 16); fl.y = ll[1] | (ll[5] << 16);
-      fl.z = ll[2] | (ll[6] << 16); fl.w = ll[3] | (ll[7] << 16);
-      const int jj = lane >> 2, tt = lane & 3;
-      Bfrag[((size_t)(sl * 8 + jj) * 2 + 0) * 4 + tt] = fh;
-      Bfrag[((size_t)(sl * 8 + jj) * 2 + 1) * 4 + tt] = fl;
-      // 8 * sum(x_g) in the same fixed point: (8 * isum) * 2^(e-23)
-      if (tt == 0) Qg[sl * 8 + jj] = (float)isum * __uint_as_float((unsigned)(127 + 3 - 23 + e) << 23);
-      // a non-finite activation makes every output of the slab NaN instead of garbage
-      if (lane == 0)
-        Pslab[sl] = (mx < 3.0e38f) ? __uint_as_float((unsigned)(127 + 13 + e) << 23) : __uint_as_float(0x7fc00000u);
     }
+    float mx = 0.f;
+#pragma unroll
+    for (int i = 0; i < 8; i++) mx = fmaxf(mx, fabsf(v[i]));
+    mx = warp_max(mx);
+#ifdef GV_PROF
+    if (sel && threadIdx.x == 0) gv_prof[blockIdx.x][7] = gv_now();
+#endif
+    if (sl == warp) top_up(STAGES);
+    int e = (int)((__float_as_uint(mx) >> 23) & 0xff) - 126;  // mx < 2^e
+    e = mx > 0.f ? (e < -100 ? -100 : (e > 100 ? 100 : e)) : 0;
+    if (!(mx < 3.0e38f)) e = 100;                              // inf / nan: keep the exponent legal
+    const float s23 = __uint_as_float((unsigned)(127 + 23 - e) << 23);
+    // X = rn(v * 2^(23-e)), |X| <= 2^23, as two balanced 12-bit digits X = 4096 d0 + d1 -- without
+    // a float -> int conversion: those run at a sixteenth of the FMA rate, and 40 of them per
+    // lane made this loop a microsecond on every CTA.  d0 = rn(y / 4096) and d1 = rn(y - 4096 d0)
+    // by the add-and-subtract of 1.5 * 2^23 (round to nearest even, like cvt.rni); the
+    // subtraction in between is exact, so 4096 d0 + d1 == rn(y).
+    const float MAGIC = 12582912.0f;
+    float d0f[8], d1f[8], sd0 = 0.f, sd1 = 0.f;
+#pragma unroll
+    for (int i = 0; i < 8; i++) {
+      const float y = v[i] * s23;
+      d0f[i] = fmaf(y, 0.000244140625f, MAGIC) - MAGIC;   // [-2048, 2048]
+      const float r = fmaf(d0f[i], -4096.0f, y);           // exact, |r| <= 2048
+      d1f[i] = (r + MAGIC) - MAGIC;                        // [-2048, 2048]
+      sd0 += d0f[i];                                       // sums of at most 2^16: exact
+      sd1 += d1f[i];
+    }
+    sd0 += __shfl_xor_sync(0xffffffffu, sd0, 1);
+    sd0 += __shfl_xor_sync(0xffffffffu, sd0, 2);
+    sd1 += __shfl_xor_sync(0xffffffffu, sd1, 1);
+    sd1 += __shfl_xor_sync(0xffffffffu, sd1, 2);
+    // the odd nibble of a byte reads as nib * 2^-20: its activation digits carry 2^-4;
+    // element i pairs with i + 4 in one 32-bit word, converted as a pair
+    auto pk = [](float a, float b) {
+      const __half2 h = __floats2half2_rn(a, b);
+      return *reinterpret_cast<const unsigned*>(&h);
+    };
+    uint4 fh, fl;
+    fh.x = pk(d0f[0], d0f[4]);                     fl.x = pk(d1f[0], d1f[4]);
+    fh.y = pk(d0f[1] * 0.0625f, d0f[5] * 0.0625f); fl.y = pk(d1f[1] * 0.0625f, d1f[5] * 0.0625f);
+    fh.z = pk(d0f[2], d0f[6]);                     fl.z = pk(d1f[2], d1f[6]);
+    fh.w = pk(d0f[3] * 0.0625f, d0f[7] * 0.0625f); fl.w = pk(d1f[3] * 0.0625f, d1f[7] * 0.0625f);
+    const int jj = lane >> 2, tt = lane & 3;
+    Bfrag[((size_t)(sl * 8 + jj) * 2 + 0) * 4 + tt] = fh;
+    Bfrag[((size_t)(sl * 8 + jj) * 2 + 1) * 4 + tt] = fl;
+    // 8 * sum(x_g) in the same fixed point: (8 * isum) * 2^(e-23)
+    // (the correctly rounded value of the exact integer sum, what (float)isum gave)
+    if (tt == 0) Qg[sl * 8 + jj] = fmaf(sd0, 4096.0f, sd1) * __uint_as_float((unsigned)(127 + 3 - 23 + e) << 23);
+    // a non-finite activation makes every output of the slab NaN instead of garbage
+    if (lane == 0)
+      Pslab[sl] = (mx < 3.0e38f) ? __uint_as_float((unsigned)(127 + 13 + e) << 23) : __uint_as_float(0x7fc00000u);
   }
+#ifdef GV_PROF
+  if (sel && threadIdx.x == 0) gv_prof[blockIdx.x][8] = gv_now();
+#endif
   __syncthreads();
-  pdl_launch_dependents();
+  if (phi == 0) pdl_launch_dependents();
+  GV_MARK(4 * phi + 2);
+#ifdef GV_PROF
+  if (sel && threadIdx.x == 0) gv_prof[blockIdx.x][2] = gv_now();
+#endif
 
   // ---- streaming loop ------------------------------------------------------
   float acc0 = 0.f, acc1 = 0.f, corr0 = 0.f, corr1 = 0.f;
@@ -474,7 +630,9 @@ __global__ void __launch_bounds__(PK_WARPS * 32, PK_CTAS_PER_SM) gemv_q4p_kernel
     // q <- rope(q + bq), rope(k + bk) and v + bv into cache row *d_pos.  Angle in double,
     // like the CPU reference's trig (the f32 fast path drifts past 1e-3 on the low pairs).
     const int half = p.epi.D >> 1, D = p.epi.D;
-    const int h = pi / half, j = pi - h * half;
+    // (head sizes are powers of two in practice: a shift instead of two dozen instructions)
+    const int h = (half & (half - 1)) == 0 ? pi >> (31 - __clz(half)) : pi / half;
+    const int j = pi - h * half;
     const unsigned pos = *p.epi.d_pos;
     if (pos >= (unsigned)p.epi.kv_rows) {
       // the cache is full: write nothing (the attention that follows refuses the position
@@ -590,14 +748,16 @@ __global__ void __launch_bounds__(PK_WARPS * 32, PK_CTAS_PER_SM) gemv_q4p_kernel
     if (lane == 0) p.counters[rt] = 0;  // leave the counter clean for the next launch
   };
 
-  int st = 0;
-  unsigned phase = 0;
   for (int i = 0; i < n_units; i++) {
+    const int st = ring.st;
     if (own && i > 0) {   // next unit of this warp: PK_WARPS further on
       s += PK_WARPS;
       while (s >= ks) { s -= ks; rt++; }
     }
-    if (!mbar_wait_bounded(&mybar[st], phase, p.status, 100 + st)) break;
+    if (!mbar_wait_bounded(&mybar[st], ring.parity, p.status, 100 + st)) {
+      ring.dead = true;
+      break;
+    }
     const uint32_t ust = ring32 + (uint32_t)st * PK_UNIT;
     const uint32_t wa = ust + wl, sa = ust + sl_, bs = bh32 + (uint32_t)s * 1024u;
     // the 8 group scales of rows g and g+8
@@ -637,8 +797,9 @@ __global__ void __launch_bounds__(PK_WARPS * 32, PK_CTAS_PER_SM) gemv_q4p_kernel
     acc0 = fmaf(P, ua0, acc0);
     acc1 = fmaf(P, ua1, acc1);
     __syncwarp();
-    if (i + STAGES < n_units) issue_next();
-    if (++st == STAGES) { st = 0; phase ^= 1u; }
+    ring.inflight--;
+    top_up(STAGES);   // the slot just freed: this phase's next unit, or the next phase's first
+    if (++ring.st == STAGES) { ring.st = 0; ring.parity ^= 1u; }
     if (own) {
       // this unit's 16 row sums go to the CTA's table, slot = unit index inside the CTA
       float v0 = (t == 0 ? acc0 : 0.f) - corr0, v1 = (t == 0 ? acc1 : 0.f) - corr1;
@@ -661,10 +822,14 @@ __global__ void __launch_bounds__(PK_WARPS * 32, PK_CTAS_PER_SM) gemv_q4p_kernel
       rt++;
     }
   }
+  GV_MARK(4 * phi + 3);
+#ifdef GV_PROF
+  if (sel && threadIdx.x == 0) gv_prof[blockIdx.x][3] = gv_now();
+#endif
   // This warp's stream has run dry: ask the L2 for the head of the next kernel's weights.
   if (p.pf.wp) {
-    for (unsigned nc = blockIdx.x + gridDim.x * (unsigned)warp; nc < (unsigned)p.pf.grid;
-         nc += gridDim.x * PK_WARPS)
+    for (unsigned nc = blockIdx.x + (unsigned)p.grid * (unsigned)warp; nc < (unsigned)p.pf.grid;
+         nc += (unsigned)p.grid * PK_WARPS)
       gv_prefetch_head(p.pf, nc, lane);
   }
   if (own) {
@@ -724,9 +889,221 @@ __global__ void __launch_bounds__(PK_WARPS * 32, PK_CTAS_PER_SM) gemv_q4p_kernel
   if (n_units > 0 && s != 0) flush(rt);
 }
 
+__device__ __forceinline__ unsigned char* gv_ring_init(unsigned char* smem_raw, int stages, GvRing& ring) {
+  unsigned char* base = (unsigned char*)(((uintptr_t)smem_raw + 127) & ~(uintptr_t)127);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  uint64_t* mybar = (uint64_t*)(base + gemvp_smem_layout(stages, 0).bars) + warp * stages;
+  if (lane == 0) {
+    for (int s = 0; s < stages; s++) mbar_init(&mybar[s], 1);
+    mbar_fence_init();
+  }
+  __syncwarp();
+  ring.istage = 0; ring.inflight = 0; ring.st = 0; ring.parity = 0u; ring.dead = false;
+  ring.policy = l2_evict_first_policy();
+  return base;
+}
+
+template <int STAGES, bool PULL, int OWN, int EPI, bool PUSH>
+__global__ void __launch_bounds__(PK_WARPS * 32, PK_CTAS_PER_SM)
+    gemv_q4p_kernel(const __grid_constant__ GemvPParams p) {
+  extern __shared__ unsigned char smem_raw[];
+  GvRing ring;
+  unsigned char* base = gv_ring_init(smem_raw, STAGES, ring);
+#ifdef GV_PROF
+  if (threadIdx.x == 0 && gv_sel == p.N) gv_prof[blockIdx.x][0] = gv_now();
+#endif
+  GvCursor cur;
+  cur.ph = 0;
+  gemv_q4p_body<STAGES, PULL, OWN, EPI, PUSH>(p, nullptr, 1, 0, ring, cur, base);
+#ifdef GV_PROF
+  if (threadIdx.x == 0 && gv_sel == p.N) gv_prof[blockIdx.x][16] = gv_now();
+#endif
+}
+
+// ---- a chain of GEMVs in one launch ------------------------------------------------------
+// The projections between two attention calls of a decoder (o, gate|up, down, the next
+// layer's qkv -- or the lm_head) each need the whole output of the one before, so as separate
+// launches every boundary costs the drain of one kernel and the ramp of the next (about 3 us
+// of an idle HBM each, against 1.3 - 13 us of streaming).  Here they are phases of one
+// persistent launch: between phases the CTAs meet at a counter in global memory (bounded
+// spin), and because a warp's ring of weight units is refilled across the phase boundary
+// (weights depend on nothing), the HBM keeps streaming the next matrix while the last
+// results of this one are folded, the barrier is crossed and the activations are prepared.
+constexpr int GV_CHAIN_MAX = 4;
+constexpr int GV_CHAIN_BARRIERS = GV_CHAIN_MAX - 1;   // arrivals per CTA and launch, always
+struct GvChainParams {
+  GemvPParams ph[GV_CHAIN_MAX];
+  int nph;
+  unsigned long long* cell;   // arrival counter of the device: never reset, += BARRIERS * grid per launch
+};
+
+__device__ __forceinline__ unsigned long long ld_acquire_u64(const unsigned long long* p) {
+  unsigned long long v;
+  asm volatile("ld.acquire.gpu.global.u64 %0, [%1];" : "=l"(v) : "l"(p) : "memory");
+  return v;
+}
+// All CTAs of the launch arrive; nobody leaves before the last has arrived (or the wait limit
+// of the status block runs out: the status block records it and the phase runs on stale data).
+// `epoch` = value of the counter when the launch began, found at the first barrier: no CTA
+// can be past barrier 1 before this one has arrived at it, so the counter then lies in
+// [epoch, epoch + grid).
+__device__ __forceinline__ void gv_grid_barrier(unsigned long long* cell, unsigned long long& epoch, int k,
+                                                int* status) {
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    const unsigned long long per_launch = (unsigned long long)GV_CHAIN_BARRIERS * gridDim.x;
+    if (k == 1) {
+      const unsigned long long c0 = ld_acquire_u64(cell);
+      epoch = c0 - c0 % per_launch;
+    }
+    __threadfence();
+    atomicAdd(cell, 1ull);
+    const unsigned long long target = epoch + (unsigned long long)k * gridDim.x;
+    if (ld_acquire_u64(cell) < target) {
+      const long long t0 = clock64();
+      long long limit = 1ll << 62;
+      for (unsigned spin = 1;; spin++) {
+        if (ld_acquire_u64(cell) >= target) break;
+        if ((spin & 63u) == 0) limit = wait_limit(status);
+        if (clock64() - t0 > limit) {
+          if (status) {
+            atomicExch(&status[ST_WAIT_TIMEOUT], 1);
+            atomicExch(&status[ST_WAIT_WHERE], 700 + k);
+          }
+          break;
+        }
+      }
+    }
+  }
+  __syncthreads();
+}
+
+// A phase's instantiation is chosen at compile time (code 3 * own + epilogue kind), so that its
+// parameters stay immediate operands from the constant bank like in a launch of its own; the
+// host picks the kernel whose codes match the phases' plans.
+template <int STAGES, int CODE>
+__device__ __forceinline__ void gv_chain_phase(const GemvPParams& p, const GvCursor* table, int nph, int phi,
+                                               GvRing& ring, GvCursor& cur, unsigned char* base,
+                                               unsigned long long* cell, unsigned long long& epoch) {
+  if (phi >= nph) return;
+  GV_MARK(4 * phi + 0);
+  if (phi > 0) gv_grid_barrier(cell, epoch, phi, p.status);
+  GV_MARK(4 * phi + 1);
+  if (blockIdx.x < (unsigned)p.grid) {
+    gemv_q4p_body<STAGES, false, (CODE >= 3), CODE % 3, false>(p, table, nph, phi, ring, cur, base);
+  } else if (phi == 0) {
+    pdl_wait();
+    pdl_launch_dependents();
+  }
+  if (phi == nph - 1) GV_MARK(16);
+}
+
+template <int STAGES, int C0, int C1, int C2, int C3>
+__global__ void __launch_bounds__(PK_WARPS * 32, PK_CTAS_PER_SM)
+    gemv_q4p_chain_kernel(const __grid_constant__ GvChainParams cp) {
+  extern __shared__ unsigned char smem_raw[];
+  // every warp's unit range in every phase, worked out once (phase numbers are immediates
+  // here, so the parameters are plain constant-bank operands) and looked up when the ring
+  // moves on to the next phase
+  __shared__ GvCursor curs[PK_WARPS][GV_CHAIN_MAX];
+  __shared__ unsigned long long epoch_s;
+#ifdef GV_PROF
+  if (threadIdx.x == 0) gv_gate = (C3 == 5);   // every CTA writes the same value
+#endif
+  GvRing ring;
+  unsigned char* base = gv_ring_init(smem_raw, STAGES, ring);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int nph = cp.nph;
+  GvCursor cur;
+  cur.ph = 0;
+  gv_cursor_set(cur, cp.ph[0], warp);
+  {
+    GvCursor t;
+    t.ph = 0;
+#pragma unroll
+    for (int i = 1; i < GV_CHAIN_MAX; i++) {
+      if (i < nph) {
+        gv_cursor_set(t, cp.ph[i], warp);
+        if (lane == 0) curs[warp][i] = t;
+      }
+    }
+    __syncwarp();
+  }
+  const GvCursor* table = curs[warp];
+  unsigned long long& epoch = epoch_s;   // thread 0 alone reads and writes it
+  gv_chain_phase<STAGES, C0>(cp.ph[0], table, nph, 0, ring, cur, base, cp.cell, epoch);
+  gv_chain_phase<STAGES, C1>(cp.ph[1], table, nph, 1, ring, cur, base, cp.cell, epoch);
+  gv_chain_phase<STAGES, C2>(cp.ph[2], table, nph, 2, ring, cur, base, cp.cell, epoch);
+  gv_chain_phase<STAGES, C3>(cp.ph[3], table, nph, 3, ring, cur, base, cp.cell, epoch);
+  // every launch adds the same number of arrivals, whatever its length
+  __syncthreads();
+  if (threadIdx.x == 0 && nph - 1 < GV_CHAIN_BARRIERS)
+    atomicAdd(cp.cell, (unsigned long long)(GV_CHAIN_BARRIERS - (nph - 1)) );
+}
+
+// The same chain with ONE copy of the body in a loop over the phases (run-time modes, the
+// phases' parameters in shared memory because kernel parameters cannot be indexed by a
+// run-time phase number): phases after the first run from a warm instruction cache.
+template <int STAGES>
+__global__ void __launch_bounds__(PK_WARPS * 32, PK_CTAS_PER_SM)
+    gemv_q4p_chain_loop_kernel(const __grid_constant__ GvChainParams cp) {
+  extern __shared__ unsigned char smem_raw[];
+  __shared__ GvCursor curs[PK_WARPS][GV_CHAIN_MAX];
+  __shared__ unsigned long long epoch_s;
+  __shared__ __align__(16) GemvPParams sph[GV_CHAIN_MAX];
+#ifdef GV_PROF
+  if (threadIdx.x == 0) gv_gate = cp.ph[3].epi.kind == 2;
+#endif
+  GvRing ring;
+  unsigned char* base = gv_ring_init(smem_raw, STAGES, ring);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int nph = cp.nph;
+  {
+    static_assert(sizeof(GemvPParams) % 4 == 0, "copied word by word");
+    constexpr int W = (int)(sizeof(GemvPParams) / 4);
+    const unsigned* srcw = (const unsigned*)&cp.ph[0];
+    unsigned* dstw = (unsigned*)&sph[0];
+    for (int i = threadIdx.x; i < GV_CHAIN_MAX * W; i += blockDim.x) dstw[i] = srcw[i];
+  }
+  GvCursor cur;
+  cur.ph = 0;
+  gv_cursor_set(cur, cp.ph[0], warp);
+  {
+    GvCursor t;
+    t.ph = 0;
+#pragma unroll
+    for (int i = 1; i < GV_CHAIN_MAX; i++) {
+      if (i < nph) {
+        gv_cursor_set(t, cp.ph[i], warp);
+        if (lane == 0) curs[warp][i] = t;
+      }
+    }
+  }
+  __syncthreads();
+  const GvCursor* table = curs[warp];
+  unsigned long long& epoch = epoch_s;
+#pragma unroll 1
+  for (int phi = 0; phi < nph; phi++) {
+    const GemvPParams& p = sph[phi];
+    GV_MARK(4 * phi + 0);
+    if (phi > 0) gv_grid_barrier(cp.cell, epoch, phi, p.status);
+    GV_MARK(4 * phi + 1);
+    if (blockIdx.x < (unsigned)p.grid) {
+      gemv_q4p_body<STAGES, false, -1, -1, false>(p, table, nph, phi, ring, cur, base);
+    } else if (phi == 0) {
+      pdl_wait();
+      pdl_launch_dependents();
+    }
+  }
+  GV_MARK(16);
+  __syncthreads();
+  if (threadIdx.x == 0 && nph - 1 < GV_CHAIN_BARRIERS)
+    atomicAdd(cp.cell, (unsigned long long)(GV_CHAIN_BARRIERS - (nph - 1)));
+}
+
 static int gemvp_stages(int slabs) {
   for (int st = 4; st >= 2; st--)
-    if (gemvp_smem_layout(st, slabs).total <= (size_t)(227 * 1024 / PK_CTAS_PER_SM) - (PK_CTAS_PER_SM > 1 ? 1024 : 0)) return st;
+    if (gemvp_smem_layout(st, slabs).total <= (size_t)(PK_DYN_SMEM_MAX / PK_CTAS_PER_SM) - (PK_CTAS_PER_SM > 1 ? 1024 : 0)) return st;
   return 0;
 }
 
@@ -737,11 +1114,11 @@ bool gemv_q4p_supported(long long N, long long K) {
   return gemvp_stages(SL) != 0 || (SL > 2 * PK_WARPS && gemvp_stages(2 * PK_WARPS) != 0);
 }
 
-template <int STAGES, bool PULL, bool OWN, int EPI, bool PUSH>
+template <int STAGES, bool PULL, int OWN, int EPI, bool PUSH>
 static int gemvp_launch_t(const GemvPParams& p, int ctas, size_t smem, cudaStream_t stream) {
   static std::atomic<unsigned long long> attr_done{0};
   {
-    const int rc_attr = ensure_dynamic_smem(gemv_q4p_kernel<STAGES, PULL, OWN, EPI, PUSH>, 227 * 1024, attr_done);
+    const int rc_attr = ensure_dynamic_smem(gemv_q4p_kernel<STAGES, PULL, OWN, EPI, PUSH>, PK_DYN_SMEM_MAX, attr_done);
     if (rc_attr) return rc_attr;
   }
   LaunchCfg lc(dim3(ctas), dim3(PK_WARPS * 32), smem, stream, pdl_enabled());
@@ -760,6 +1137,11 @@ static int gemvp_launch_e(const GemvPParams& p, int ctas, size_t smem, cudaStrea
 }
 template <int STAGES, bool PULL>
 static int gemvp_launch_o(const GemvPParams& p, int ctas, size_t smem, cudaStream_t stream) {
+  // TLB_GEMV_UNIFIED=1: the one instantiation with run-time modes for every single-GPU launch
+  // (measured 3 % slower than one instantiation per mode: the instruction cache does not carry
+  // a kernel's code from one launch to the next, so sharing it buys nothing)
+  static const bool unified = getenv("TLB_GEMV_UNIFIED") && atoi(getenv("TLB_GEMV_UNIFIED")) == 1;
+  if (!PULL && !p.push && unified) return gemvp_launch_t<STAGES, false, -1, -1, false>(p, ctas, smem, stream);
   if (p.cta_tiles) return gemvp_launch_e<STAGES, PULL, true>(p, ctas, smem, stream);
   return gemvp_launch_e<STAGES, PULL, false>(p, ctas, smem, stream);
 }
@@ -841,12 +1223,12 @@ int gemv_q4p_stream_of(DeviceCtx* c, const void* packed, int N, int K, int act, 
   return TLB_OK;
 }
 
-int gemv_q4p_launch(DeviceCtx* c, const void* packed, const float* x, float* y, int N, int K,
-                    float alpha, float beta, cudaStream_t stream, int max_ctas,
-                    const CommDev* push_comm, int act, const float* delta, const float* nw,
-                    float* xout, float eps, const PairEpi* epi, const CommDev* pull_comm,
-                    const GvStream* prefetch) {
-  GemvPParams p;
+// Parameters and plan of one launch / phase from the caller's arguments.
+static int gemvp_fill(DeviceCtx* c, const void* packed, const float* x, float* y, int N, int K, float alpha,
+                      float beta, int max_ctas, const CommDev* push_comm, int act, const float* delta,
+                      const float* nw, float* xout, float eps, const PairEpi* epi, const CommDev* pull_comm,
+                      const GvStream* prefetch, GemvPParams* out, GemvPlan* plan) {
+  GemvPParams& p = *out;
   memset(&p, 0, sizeof(p));
   if (prefetch) p.pf = *prefetch;
   if (pull_comm) {
@@ -887,6 +1269,34 @@ int gemv_q4p_launch(DeviceCtx* c, const void* packed, const float* x, float* y, 
   p.x_vec_ok = vec ? 1 : 0;
   p.cta_tiles = pl.cta_tiles;
   p.slabs = pl.slabs;
+  p.grid = pl.ctas;
+  {
+    const unsigned Wall = (unsigned)pl.ctas * PK_WARPS;
+    p.Wtot = Wall < p.U ? Wall : p.U;
+    p.sp = {p.U / p.Wtot, p.U % p.Wtot};
+    if (pl.cta_tiles) {
+      const unsigned KB = (unsigned)pl.cta_tiles;
+      p.RB = (unsigned)pl.ctas / KB;
+      p.ct = {(unsigned)p.RT / p.RB, (unsigned)p.RT % p.RB};
+      p.cs = {(unsigned)p.SL / KB, (unsigned)p.SL % KB};
+    }
+  }
+  *plan = pl;
+  return TLB_OK;
+}
+
+int gemv_q4p_launch(DeviceCtx* c, const void* packed, const float* x, float* y, int N, int K,
+                    float alpha, float beta, cudaStream_t stream, int max_ctas,
+                    const CommDev* push_comm, int act, const float* delta, const float* nw,
+                    float* xout, float eps, const PairEpi* epi, const CommDev* pull_comm,
+                    const GvStream* prefetch) {
+  GemvPParams p;
+  GemvPlan pl;
+  {
+    const int rc = gemvp_fill(c, packed, x, y, N, K, alpha, beta, max_ctas, push_comm, act, delta, nw, xout, eps,
+                              epi, pull_comm, prefetch, &p, &pl);
+    if (rc) return rc;
+  }
   const int ctas = pl.ctas, stages = pl.stages;
   const size_t smem = gemvp_smem_layout(stages, p.slabs).total;
   if (p.act == 3) {
@@ -899,4 +1309,70 @@ int gemv_q4p_launch(DeviceCtx* c, const void* packed, const float* x, float* y, 
   return gemvp_launch_o<2, false>(p, ctas, smem, stream);
 }
 
+// Up to GV_CHAIN_MAX single-GPU GEMVs, each reading what the one before wrote, as one
+// persistent launch of one CTA per SM.  *fused = false (and nothing launched) when the phases
+// cannot share a ring (different ring depths): the caller then launches them one by one.
+int gemv_q4p_chain_launch(DeviceCtx* c, const GvPhase* ph, int nph, cudaStream_t stream, bool* fused) {
+  *fused = false;
+  if (nph < 2 || nph > GV_CHAIN_MAX) return set_error(TLB_ERR_ARG, "gemv_q4p chain: 2 to 4 phases");
+  if (!c->chain_cell) return TLB_OK;
+  GvChainParams cp;
+  memset(&cp, 0, sizeof(cp));
+  size_t smem = 0;
+  for (int i = 0; i < nph; i++) {
+    GemvPlan pl;
+    const int rc = gemvp_fill(c, ph[i].packed, ph[i].x, ph[i].y, ph[i].N, ph[i].K, 1.0f, 0.0f, 0, nullptr, ph[i].act,
+                              ph[i].delta, ph[i].nw, ph[i].xout, ph[i].eps, ph[i].epi, nullptr, nullptr, &cp.ph[i],
+                              &pl);
+    if (rc) return rc;
+    if (pl.stages != 4 || pl.ctas > c->sm_count) return TLB_OK;
+    const size_t need = gemvp_smem_layout(4, cp.ph[i].slabs).total;
+    if (need > smem) smem = need;
+  }
+  cp.nph = nph;
+  cp.cell = c->chain_cell;
+  // the instantiated phase signatures: o, gate|up, down, then the next qkv or the lm_head, for
+  // wide (7B-like: gate|up in unit ranges) and narrow (0.5B-like: gate|up CTA-owned) shapes
+  int code[GV_CHAIN_MAX] = {0, 0, 0, 0};
+  for (int i = 0; i < nph; i++) code[i] = (cp.ph[i].cta_tiles ? 3 : 0) + cp.ph[i].epi.kind;
+  const int sig = nph == 4 ? code[0] * 1000 + code[1] * 100 + code[2] * 10 + code[3] : -1;
+  LaunchCfg lc(dim3(c->sm_count), dim3(PK_WARPS * 32), smem, stream, pdl_enabled());
+#define TLB_CHAIN_CASE(A, B, C, D)                                                                         \
+  case A * 1000 + B * 100 + C * 10 + D: {                                                                  \
+    static std::atomic<unsigned long long> attr_done{0};                                                   \
+    const int rc_attr = ensure_dynamic_smem(gemv_q4p_chain_kernel<4, A, B, C, D>, PK_DYN_SMEM_MAX, attr_done);  \
+    if (rc_attr) return rc_attr;                                                                           \
+    TLB_CUDA(cudaLaunchKernelEx(&lc.cfg, gemv_q4p_chain_kernel<4, A, B, C, D>, cp));                       \
+    break;                                                                                                 \
+  }
+  // every SM gets exactly one CTA (the kernel's shared memory allows no second one), so all
+  // CTAs are resident together and the barrier between phases can complete
+  static const bool looped = getenv("TLB_CHAIN_LOOP") && atoi(getenv("TLB_CHAIN_LOOP")) == 1;
+  if (looped) {
+    static std::atomic<unsigned long long> attr_done{0};
+    const int rc_attr = ensure_dynamic_smem(gemv_q4p_chain_loop_kernel<4>, PK_DYN_SMEM_MAX - 2048, attr_done);
+    if (rc_attr) return rc_attr;
+    TLB_CUDA(cudaLaunchKernelEx(&lc.cfg, gemv_q4p_chain_loop_kernel<4>, cp));
+    *fused = true;
+    return TLB_OK;
+  }
+  switch (sig) {
+    TLB_CHAIN_CASE(3, 1, 3, 5)
+    TLB_CHAIN_CASE(3, 1, 3, 0)
+    TLB_CHAIN_CASE(3, 4, 3, 5)
+    TLB_CHAIN_CASE(3, 4, 3, 0)
+    default:
+      return TLB_OK;   // not fused: the caller launches the phases one by one
+  }
+#undef TLB_CHAIN_CASE
+  *fused = true;
+  return TLB_OK;
+}
+
+#ifdef GV_PROF
+}
+extern "C" int tlb_gv_sel(int n) { return (int)cudaMemcpyToSymbol(tlb::gv_sel, &n, 4); }
+extern "C" int tlb_gv_prof(long long* out) { return (int)cudaMemcpyFromSymbol(out, tlb::gv_prof, 160 * 20 * 8); }
+namespace tlb {
+#endif
 }  // namespace tlb

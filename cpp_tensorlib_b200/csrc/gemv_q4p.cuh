@@ -48,6 +48,20 @@ int gemv_q4p_launch(DeviceCtx* c, const void* packed, const float* x, float* y, 
                     const CommDev* push_comm, int act, const float* delta, const float* nw,
                     float* xout, float eps, const PairEpi* epi, const CommDev* pull_comm,
                     const GvStream* prefetch = nullptr);
+// One phase of a chain: y = W . prep(x) with the optional fused add+norm prologue (act 2) and
+// pair epilogue of gemv_q4p_launch; alpha = 1, beta = 0, single GPU.
+struct GvPhase {
+  const void* packed = nullptr;
+  const float* x = nullptr;
+  float* y = nullptr;
+  int N = 0, K = 0, act = 0;
+  const float* delta = nullptr;
+  const float* nw = nullptr;
+  float* xout = nullptr;
+  float eps = 0.f;
+  const PairEpi* epi = nullptr;
+};
+int gemv_q4p_chain_launch(DeviceCtx* c, const GvPhase* ph, int nph, cudaStream_t stream, bool* fused);
 // The walk a launch with these arguments would take (same decisions as gemv_q4p_launch).
 int gemv_q4p_stream_of(DeviceCtx* c, const void* packed, int N, int K, int act, bool has_epi, int max_ctas,
                        GvStream* out);

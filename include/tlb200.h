@@ -262,7 +262,7 @@ int tlb_decoder_run(void* dec, int64_t n_tokens, void* stream);        /* qm:862
 int tlb_decoder_step(void* dec, const int32_t* token_in, int32_t* token_out, void* stream);
 int tlb_decoder_last_token(void* dec, int32_t* token_out, void* stream);
 /* qm:357-442 prefill_chunk_ / prefill_batched: T prompt tokens (HOST ids) as row-batched GEMMs on
- * the int4 weights + tiled causal attention, in chunks of 256, from the current position; leaves
+ * the int4 weights + tiled causal attention, in chunks of 1024 (TLB_PREFILL_CHUNK overrides), from the current position; leaves
  * position += T and the greedy next token on the device and in *next_token.  Single GPU. */
 int tlb_decoder_prefill(void* dec, const int32_t* tokens, int64_t T, int32_t* next_token, void* stream);
 /* Tensor-parallel wiring (no counterpart in the reference, which is single-device):

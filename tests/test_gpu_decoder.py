@@ -236,11 +236,12 @@ def test_decoder_argument_errors():
 
 @pytest.mark.parametrize("cfg,seed,T", [(cases.TINY, 21, 19), (cases.TINY64, 22, 40),
                                         (dict(cases.QWEN05, layers=2), 2, 300)])
-def test_batched_prefill_matches_token_by_token(cfg, seed, T):
+def test_batched_prefill_matches_token_by_token(cfg, seed, T, monkeypatch):
     """The batched prompt pass (bench/cuda/qwen_model.h:357-442) against the decode loop of
     the same decoder: same greedy token after the prompt, logits and every cache row within
-    1e-3, and identical greedy ids for the tokens decoded after it.  T = 300 spans two
-    chunks of 256 and puts the projections on the tensor-core GEMM."""
+    1e-3, and identical greedy ids for the tokens decoded after it.  T = 300 with the pass
+    limited to 256 rows spans two chunks and puts the projections on the tensor-core GEMM."""
+    monkeypatch.setenv("TLB_PREFILL_CHUNK", "256")
     d1, wts = make(cfg, seed, T + 16)
     d2, _ = make(cfg, seed, T + 16, wts)
     prompt = [int(t) for t in synth.token_ids(seed, 7, T, cfg["vocab"])]
