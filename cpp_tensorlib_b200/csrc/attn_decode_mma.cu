@@ -138,14 +138,19 @@ __global__ void __launch_bounds__(MmaCfg<D>::THREADS, 1)
 
   // ======================= producer: first tiles =======================
   const bool producer = (warp == W && lane == 0);
+  // A long context is read once per token and is far larger than the L2 over the layers of a
+  // model: mark it evict-first, so that the small things every launch re-reads (biases, norm
+  // weights, activations, scratch) stay.  A short one may survive to the next token: leave it.
+  const uint64_t pol = (size_t)p.n_kv * ctx * D * 8 >= ((size_t)8 << 20) ? l2_evict_first_policy()
+                                                                          : l2_evict_normal_policy();
   auto issue = [&](int i) {
     const int st = i % STAGES;
     unsigned char* dst = ring + (size_t)st * C::TILE_BYTES;
     mbar_expect_tx(&full[st], C::TILE_BYTES);
 #pragma unroll
     for (int sg = 0; sg < SEGS; sg++) {
-      tma_load_2d(dst + sg * MM_BOX_BYTES, &tmK, sg * 32, row0 + i * MM_TK, &full[st]);
-      tma_load_2d(dst + (SEGS + sg) * MM_BOX_BYTES, &tmV, sg * 32, row0 + i * MM_TK, &full[st]);
+      tma_load_2d_hint(dst + sg * MM_BOX_BYTES, &tmK, sg * 32, row0 + i * MM_TK, &full[st], pol);
+      tma_load_2d_hint(dst + (SEGS + sg) * MM_BOX_BYTES, &tmV, sg * 32, row0 + i * MM_TK, &full[st], pol);
     }
   };
   const int first = n_tiles < STAGES ? n_tiles : STAGES;

@@ -157,12 +157,26 @@ __device__ __forceinline__ uint64_t l2_evict_first_policy() {
   asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(pol));
   return pol;
 }
+__device__ __forceinline__ uint64_t l2_evict_normal_policy() {
+  uint64_t pol;
+  asm volatile("createpolicy.fractional.L2::evict_normal.b64 %0, 1.0;" : "=l"(pol));
+  return pol;
+}
 __device__ __forceinline__ void bulk_load_1d_hint(void* dst, const void* src, uint32_t bytes, uint64_t* bar,
                                                   uint64_t policy) {
   asm volatile(
       "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint [%0], [%1], %2, [%3], %4;" ::"r"(
           smem_u32(dst)),
       "l"(src), "r"(bytes), "r"(smem_u32(bar)), "l"(policy)
+      : "memory");
+}
+// 2-D tiled TMA load with an L2 policy (see l2_evict_first_policy).
+__device__ __forceinline__ void tma_load_2d_hint(void* dst, const CUtensorMap* tm, int x, int y, uint64_t* bar,
+                                                 uint64_t policy) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint [%0], [%1, {%2, "
+      "%3}], [%4], %5;" ::"r"(smem_u32(dst)),
+      "l"(tm), "r"(x), "r"(y), "r"(smem_u32(bar)), "l"(policy)
       : "memory");
 }
 // 1-D bulk copy global -> shared (16-byte aligned addresses and size).

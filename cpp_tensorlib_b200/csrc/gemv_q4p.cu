@@ -192,15 +192,6 @@ __device__ __forceinline__ float lds32f(uint32_t a) {
   return v;
 }
 
-#ifdef GV_PROF
-__device__ long long gv_prof[160][20];
-__device__ __forceinline__ long long gv_now() { long long t; asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t)); return t; }
-__device__ int gv_gate;
-__device__ int gv_sel;   // standalone launches: record the matrix with this many rows
-#define GV_MARK(i) do { if (threadIdx.x == 0 && *(volatile int*)&gv_gate) gv_prof[blockIdx.x][i] = gv_now(); } while (0)
-#else
-#define GV_MARK(i) do { } while (0)
-#endif
 // One warp's share of a launch (or of one phase of a chain): which units it streams and how
 // they map to (row tile, slab).
 struct GvWarp {
@@ -373,12 +364,22 @@ __device__ __forceinline__ void gemv_q4p_body(const GemvPParams& p, const GvCurs
         }
       }
     }
+    if (EPI == 2 && own && warp == 0 && ks > 0 && lane < n_loc / ks) {
+      // ... and what the epilogue of this CTA's row tiles will read: the biases of the tile's
+      // eight pairs (two runs of 32 bytes), the rotary table entries
+      const int half = p.epi.D >> 1;
+      const int pi = (tile_b + lane) * 8;
+      const int h = pi / half, j = pi - h * half;
+      const float* bias = h < p.epi.n_q ? p.epi.bq : (h < p.epi.n_q + p.epi.n_kv ? p.epi.bk : p.epi.bv);
+      const int hh = h < p.epi.n_q ? h : (h < p.epi.n_q + p.epi.n_kv ? h - p.epi.n_q : h - p.epi.n_q - p.epi.n_kv);
+      if (bias) {
+        asm volatile("prefetch.global.L2 [%0];" ::"l"(bias + hh * p.epi.D + j));
+        asm volatile("prefetch.global.L2 [%0];" ::"l"(bias + hh * p.epi.D + j + half));
+      }
+      if (p.epi.rope_cs) asm volatile("prefetch.global.L2 [%0];" ::"l"(p.epi.rope_cs + j));
+    }
     pdl_wait();  // activations and the fix-up scratch are valid from here
   }
-#ifdef GV_PROF
-  const bool sel = nph == 1 && gv_sel == p.N;
-  if (sel && threadIdx.x == 0) gv_prof[blockIdx.x][1] = gv_now();
-#endif
 
   // ---- activation prep.  One warp per slab of 256 k, four slabs in flight per warp.
   // Lane l covers x[256*slab + 8*l .. +8) = group jj = l/4, quad slot tt = l%4.
@@ -460,9 +461,6 @@ __device__ __forceinline__ void gemv_q4p_body(const GemvPParams& p, const GvCurs
     }
   };
   load_slab(warp, true);
-#ifdef GV_PROF
-  if (sel && threadIdx.x == 0) gv_prof[blockIdx.x][4] = gv_now();
-#endif
   // The rest of the weight ring is queued only when this warp's activation values have
   // ARRIVED (first use below): a small load issued behind 160 KB of bulk copies per SM waits
   // until they have drained -- measured, the prep of a projection took 2 - 4 us that way, the
@@ -496,19 +494,12 @@ __device__ __forceinline__ void gemv_q4p_body(const GemvPParams& p, const GvCurs
       for (int i = 0; i < 8; i++) { xv[i] = kv[i]; xu[i] = ku[i]; xw[i] = kw[i]; }
     }
     sq = warp_sum(sq);
-#ifdef GV_PROF
-    if (sel && threadIdx.x == 0) gv_prof[blockIdx.x][5] = gv_now();
-#endif
     top_up(STAGES);
+    // The scale 1 / rms is a scalar factor of every activation, so it need not be known before
+    // the digits are made: the digits are those of (x + delta) * w, and the factor multiplies
+    // the outputs (with alpha, below).  That takes a block barrier and the serial sum out of
+    // the prep; the warp sums meet at the barrier that ends it.
     if (lane == 0) red[warp] = sq;
-    __syncthreads();
-    float tot = 0.f;
-#pragma unroll
-    for (int w = 0; w < PK_WARPS; w++) tot += red[w];
-    nrm_inv = 1.0f / sqrtf(tot / (float)p.K + p.eps);
-#ifdef GV_PROF
-    if (sel && threadIdx.x == 0) gv_prof[blockIdx.x][6] = gv_now();
-#endif
   }
 #pragma unroll 1
   for (int sl = warp; sl < ks; sl += PK_WARPS) {
@@ -529,16 +520,14 @@ __device__ __forceinline__ void gemv_q4p_body(const GemvPParams& p, const GvCurs
         const float sv = v[i] + xu[i];
         const bool in = k0 + i < p.K;
         if (in && blockIdx.x == 0) p.xout[k0 + i] = sv;
-        v[i] = in ? sv * nrm_inv * xw[i] : 0.f;
+        v[i] = in ? sv * xw[i] : 0.f;
       }
     }
     float mx = 0.f;
 #pragma unroll
     for (int i = 0; i < 8; i++) mx = fmaxf(mx, fabsf(v[i]));
-    mx = warp_max(mx);
-#ifdef GV_PROF
-    if (sel && threadIdx.x == 0) gv_prof[blockIdx.x][7] = gv_now();
-#endif
+    // the maximum over the warp in one instruction: non-negative floats order like their bits
+    mx = __uint_as_float(__reduce_max_sync(0xffffffffu, __float_as_uint(mx)));
     if (sl == warp) top_up(STAGES);
     int e = (int)((__float_as_uint(mx) >> 23) & 0xff) - 126;  // mx < 2^e
     e = mx > 0.f ? (e < -100 ? -100 : (e > 100 ? 100 : e)) : 0;
@@ -585,15 +574,16 @@ __device__ __forceinline__ void gemv_q4p_body(const GemvPParams& p, const GvCurs
     if (lane == 0)
       Pslab[sl] = (mx < 3.0e38f) ? __uint_as_float((unsigned)(127 + 13 + e) << 23) : __uint_as_float(0x7fc00000u);
   }
-#ifdef GV_PROF
-  if (sel && threadIdx.x == 0) gv_prof[blockIdx.x][8] = gv_now();
-#endif
   __syncthreads();
   if (phi == 0) pdl_launch_dependents();
-  GV_MARK(4 * phi + 2);
-#ifdef GV_PROF
-  if (sel && threadIdx.x == 0) gv_prof[blockIdx.x][2] = gv_now();
-#endif
+  if (normed) {
+    // sum of the warp sums in warp order: every warp of every CTA computes the same bits
+    float tot = 0.f;
+#pragma unroll
+    for (int w = 0; w < PK_WARPS; w++) tot += red[w];
+    nrm_inv = 1.0f / sqrtf(tot / (float)p.K + p.eps);
+  }
+  const float alpha_n = p.alpha * nrm_inv;
 
   // ---- streaming loop ------------------------------------------------------
   float acc0 = 0.f, acc1 = 0.f, corr0 = 0.f, corr1 = 0.f;
@@ -610,7 +600,7 @@ __device__ __forceinline__ void gemv_q4p_body(const GemvPParams& p, const GvCurs
   const size_t ar_off =
       ((size_t)(ar_seq & 1u) * p.comm.size + p.comm.rank) * (size_t)p.comm.slot_floats;
   auto emit = [&](int n, float v) {
-    v = v * p.alpha + p.beta;
+    v = v * alpha_n + p.beta;
     if (PUSH) {
       for (int r = 0; r < p.comm.size; r++) st_packet_sys(&p.comm.stage[r][ar_off + n], v, ar_seq + 1u);
     } else {
@@ -619,8 +609,8 @@ __device__ __forceinline__ void gemv_q4p_body(const GemvPParams& p, const GvCurs
   };
   // pair index pi of a pair-packed matrix, a = its first row's sum, b = its second's
   auto emit_pair = [&](int pi, float a, float b) {
-    a = a * p.alpha + p.beta;
-    b = b * p.alpha + p.beta;
+    a = a * alpha_n + p.beta;
+    b = b * alpha_n + p.beta;
     if (EPI == 1) {
       // tl_swiglu (kernels/tensorlib_cuda.cu:185-192): silu(gate) * up, same expression
       p.epi.out[pi] = (a / (1.0f + expf(-a))) * b;
@@ -822,10 +812,6 @@ __device__ __forceinline__ void gemv_q4p_body(const GemvPParams& p, const GvCurs
       rt++;
     }
   }
-  GV_MARK(4 * phi + 3);
-#ifdef GV_PROF
-  if (sel && threadIdx.x == 0) gv_prof[blockIdx.x][3] = gv_now();
-#endif
   // This warp's stream has run dry: ask the L2 for the head of the next kernel's weights.
   if (p.pf.wp) {
     for (unsigned nc = blockIdx.x + (unsigned)p.grid * (unsigned)warp; nc < (unsigned)p.pf.grid;
@@ -909,15 +895,9 @@ __global__ void __launch_bounds__(PK_WARPS * 32, PK_CTAS_PER_SM)
   extern __shared__ unsigned char smem_raw[];
   GvRing ring;
   unsigned char* base = gv_ring_init(smem_raw, STAGES, ring);
-#ifdef GV_PROF
-  if (threadIdx.x == 0 && gv_sel == p.N) gv_prof[blockIdx.x][0] = gv_now();
-#endif
   GvCursor cur;
   cur.ph = 0;
   gemv_q4p_body<STAGES, PULL, OWN, EPI, PUSH>(p, nullptr, 1, 0, ring, cur, base);
-#ifdef GV_PROF
-  if (threadIdx.x == 0 && gv_sel == p.N) gv_prof[blockIdx.x][16] = gv_now();
-#endif
 }
 
 // ---- a chain of GEMVs in one launch ------------------------------------------------------
@@ -986,16 +966,13 @@ __device__ __forceinline__ void gv_chain_phase(const GemvPParams& p, const GvCur
                                                GvRing& ring, GvCursor& cur, unsigned char* base,
                                                unsigned long long* cell, unsigned long long& epoch) {
   if (phi >= nph) return;
-  GV_MARK(4 * phi + 0);
   if (phi > 0) gv_grid_barrier(cell, epoch, phi, p.status);
-  GV_MARK(4 * phi + 1);
   if (blockIdx.x < (unsigned)p.grid) {
     gemv_q4p_body<STAGES, false, (CODE >= 3), CODE % 3, false>(p, table, nph, phi, ring, cur, base);
   } else if (phi == 0) {
     pdl_wait();
     pdl_launch_dependents();
   }
-  if (phi == nph - 1) GV_MARK(16);
 }
 
 template <int STAGES, int C0, int C1, int C2, int C3>
@@ -1007,9 +984,6 @@ __global__ void __launch_bounds__(PK_WARPS * 32, PK_CTAS_PER_SM)
   // moves on to the next phase
   __shared__ GvCursor curs[PK_WARPS][GV_CHAIN_MAX];
   __shared__ unsigned long long epoch_s;
-#ifdef GV_PROF
-  if (threadIdx.x == 0) gv_gate = (C3 == 5);   // every CTA writes the same value
-#endif
   GvRing ring;
   unsigned char* base = gv_ring_init(smem_raw, STAGES, ring);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -1051,9 +1025,6 @@ __global__ void __launch_bounds__(PK_WARPS * 32, PK_CTAS_PER_SM)
   __shared__ GvCursor curs[PK_WARPS][GV_CHAIN_MAX];
   __shared__ unsigned long long epoch_s;
   __shared__ __align__(16) GemvPParams sph[GV_CHAIN_MAX];
-#ifdef GV_PROF
-  if (threadIdx.x == 0) gv_gate = cp.ph[3].epi.kind == 2;
-#endif
   GvRing ring;
   unsigned char* base = gv_ring_init(smem_raw, STAGES, ring);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -1085,9 +1056,7 @@ __global__ void __launch_bounds__(PK_WARPS * 32, PK_CTAS_PER_SM)
 #pragma unroll 1
   for (int phi = 0; phi < nph; phi++) {
     const GemvPParams& p = sph[phi];
-    GV_MARK(4 * phi + 0);
     if (phi > 0) gv_grid_barrier(cp.cell, epoch, phi, p.status);
-    GV_MARK(4 * phi + 1);
     if (blockIdx.x < (unsigned)p.grid) {
       gemv_q4p_body<STAGES, false, -1, -1, false>(p, table, nph, phi, ring, cur, base);
     } else if (phi == 0) {
@@ -1095,7 +1064,6 @@ __global__ void __launch_bounds__(PK_WARPS * 32, PK_CTAS_PER_SM)
       pdl_launch_dependents();
     }
   }
-  GV_MARK(16);
   __syncthreads();
   if (threadIdx.x == 0 && nph - 1 < GV_CHAIN_BARRIERS)
     atomicAdd(cp.cell, (unsigned long long)(GV_CHAIN_BARRIERS - (nph - 1)));
@@ -1369,10 +1337,4 @@ int gemv_q4p_chain_launch(DeviceCtx* c, const GvPhase* ph, int nph, cudaStream_t
   return TLB_OK;
 }
 
-#ifdef GV_PROF
-}
-extern "C" int tlb_gv_sel(int n) { return (int)cudaMemcpyToSymbol(tlb::gv_sel, &n, 4); }
-extern "C" int tlb_gv_prof(long long* out) { return (int)cudaMemcpyFromSymbol(out, tlb::gv_prof, 160 * 20 * 8); }
-namespace tlb {
-#endif
 }  // namespace tlb
