@@ -31,12 +31,13 @@ QWEN7 = dict(hidden=3584, layers=28, n_q=28, n_kv=4, hd=128, ff=18944, vocab=152
 CTX0 = 4096
 SEED = 4
 # DRAM read+write bytes per algorithmic byte of the int4 GEMV, from ncu captures of single
-# launches (profiles/gemv_q4p_gate_up_7b.md: 1.036 on the 85 MB gate|up matrix).  It is a
-# constant taken from those captures and applied to the whole sweep by bytes, not a
-# per-run measurement.
-TRAFFIC_FACTOR = 1.036
-TRAFFIC_NOTE = ("assumed: dram read+write of one ncu capture of the gate|up shape (1.036 x algorithmic) "
-                "applied to the sweep by bytes")
+# launches (profiles/gemv_q4p_gate_up_7b.md, profiles/gemv_q4p_qkv_7b_small_launch.md): 1.036 on
+# the 85 MB gate|up matrix, 1.001 on the down projection, 1.005 on qkv.  Constants taken from
+# those captures and applied to each matrix of the sweep by its bytes (o like qkv, the lm_head
+# like gate|up: same kernel mode), not a per-run measurement.
+TRAFFIC_FACTORS = dict(wgu=1.036, lm_head=1.036, wd=1.001, wqkv=1.005, wo=1.005)
+TRAFFIC_NOTE = ("ncu captures of single launches: dram read+write / algorithmic bytes = 1.036 (gate|up), "
+                "1.001 (down), 1.005 (qkv); o taken as qkv, lm_head as gate|up; applied per matrix by bytes")
 
 
 def measured_peaks():
@@ -135,14 +136,18 @@ def gemv_sweep(cfg, dec, reps):
     """The packed int4 GEMV kernel alone over one token's weight matrices (28 x {qkv, o,
     gate|up, down} + lm_head = 4.42 GB at 7B, HBM-cold because the set is far larger
     than L2), launched back to back eagerly and bracketed by CUDA events on the
-    launching stream.  Returns (bytes per pass, ms per pass, launches per pass)."""
+    launching stream.  Returns (bytes per pass, ms per pass, launches per pass, estimated DRAM
+    traffic per pass)."""
     import torch
     from cpp_tensorlib_b200 import cuda as tlc
     names = ("wqkv", "wo", "wgu", "wd")
-    ws = [dec._keep[(l, n)] for l in range(cfg["layers"]) for n in names] + [dec._keep[(0, "lm_head")]]
+    keys = [(l, n) for l in range(cfg["layers"]) for n in names] + [(0, "lm_head")]
+    ws = [dec._keep[k] for k in keys]
     xs = {w.K: torch.randn(w.K, device="cuda") for w in ws}
     ys = {w.N: torch.empty(w.N, device="cuda") for w in ws}
-    nbytes = sum(w.N * w.K * 0.625 + 4 * w.K + 4 * w.N for w in ws)
+    one = lambda w: w.N * w.K * 0.625 + 4 * w.K + 4 * w.N
+    nbytes = sum(one(w) for w in ws)
+    traffic = sum(one(w) * TRAFFIC_FACTORS[k[1]] for k, w in zip(keys, ws))
     ws = [tlc.Q4Packed(w) for w in ws]          # the layout the decoder's linears stream
     for w in ws:
         tlc.gemv_q4p(xs[w.K], w, y=ys[w.N])
@@ -163,7 +168,7 @@ def gemv_sweep(cfg, dec, reps):
         g.replay()
     e1.record()
     torch.cuda.synchronize()
-    return nbytes, e0.elapsed_time(e1) / reps, len(ws)
+    return nbytes, e0.elapsed_time(e1) / reps, len(ws), traffic
 
 
 def cpu_sample(cfg, steps, warmup, note, layers=1):
@@ -390,7 +395,7 @@ def main():
 
     # ---- roofline of the dominant kernel (per rank: its own shards)
     peak, peak_src = measured_peaks()
-    gbytes, gms, glaunch = gemv_sweep(cfg, dec, 5)
+    gbytes, gms, glaunch, gtraffic = gemv_sweep(cfg, dec, 5)
     wbytes, kvbytes, _ = token_bytes(cfg, CTX0)
     achieved = gbytes / (gms * 1e-3) / 1e9
     tok_bytes = (wbytes + kvbytes) / world
@@ -413,8 +418,8 @@ def main():
                     e2e=dict(value=e2e_tps, unit="tokens/s", h2d_bytes_per_step=4, d2h_bytes_per_step=4),
                     gpu_launches=launches,
                     roofline=dict(bound="hbm", achieved=achieved, peak=peak, unit="GB/s", frac=achieved / peak,
-                                  traffic=gbytes * TRAFFIC_FACTOR, peak_source=peak_src, kernel="gemv_q4p_kernel",
-                                  traffic_factor_assumed=TRAFFIC_FACTOR, traffic_note=TRAFFIC_NOTE,
+                                  traffic=gtraffic, peak_source=peak_src, kernel="gemv_q4p_kernel",
+                                  traffic_factors=TRAFFIC_FACTORS, traffic_note=TRAFFIC_NOTE,
                                   what=f"{glaunch} int4 GEMV launches of one token ({gbytes / 1e9:.2f} GB algorithmic), "
                                        f"{gms:.3f} ms per pass, CUDA events"),
                     token_roofline=dict(bound="hbm", achieved=tok_ach, peak=peak, frac=tok_ach / peak, unit="GB/s",

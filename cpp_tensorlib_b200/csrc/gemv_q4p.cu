@@ -1315,7 +1315,7 @@ int gemv_q4p_chain_launch(DeviceCtx* c, const GvPhase* ph, int nph, cudaStream_t
   }
   // every SM gets exactly one CTA (the kernel's shared memory allows no second one), so all
   // CTAs are resident together and the barrier between phases can complete
-  static const bool looped = getenv("TLB_CHAIN_LOOP") && atoi(getenv("TLB_CHAIN_LOOP")) == 1;
+  const bool looped = getenv("TLB_CHAIN_LOOP") && atoi(getenv("TLB_CHAIN_LOOP")) == 1;
   if (looped) {
     static std::atomic<unsigned long long> attr_done{0};
     const int rc_attr = ensure_dynamic_smem(gemv_q4p_chain_loop_kernel<4>, PK_DYN_SMEM_MAX - 2048, attr_done);

@@ -155,12 +155,15 @@ def big_weights(cfg, seed):
     return w, rng
 
 
-def test_seven_billion_shape_two_layers_full_vocabulary(port):
+def test_seven_billion_shape_two_layers_full_vocabulary(port, monkeypatch):
     """BASELINE config 5's shape with 2 of its 28 layers and the FULL 152064-row vocabulary and
     embedding table, both caches pre-filled to ctx 4096 with N(0,1): 10 greedy steps at
     positions 4096.. against the oracle -- logits within rtol/atol 1e-3 and identical ids at every
     step, then the same ids again from the device-resident feedback loop (one graph replay per
-    token, the path the benchmark times)."""
+    token, the path the benchmark times).  Then the opt-in forms of the same step -- the four
+    projections between two attention calls as ONE persistent launch (TLB_CHAIN=1: one
+    instantiation per phase; TLB_CHAIN_LOOP=1: one body in a loop) -- must decode the same ids
+    and land within 1e-3 of the same logits."""
     cfg = dict(cases.QWEN7, layers=2)
     wts, rng = big_weights(cfg, 4)
     d, _ = make(cfg, 4, 4200, wts)
@@ -184,7 +187,25 @@ def test_seven_billion_shape_two_layers_full_vocabulary(port):
     d.set_token(7)
     d.run(10)
     assert d.last_token() == ids[-1]
-    d.close(); o.close()
+    lg_ref = d.logits().cpu().numpy().copy()
+    kv_ref = [tuple(t.clone() for t in d.kv(l)) for l in range(2)]
+    o.close()
+    for loop in ("0", "1"):
+        monkeypatch.setenv("TLB_CHAIN", "1")
+        monkeypatch.setenv("TLB_CHAIN_LOOP", loop)
+        d2, _ = make(cfg, 4, 4200, wts)
+        for l in range(2):
+            d2.fill_kv(l, kv_ref[l][0][:, :4096].contiguous(), kv_ref[l][1][:, :4096].contiguous())
+        d2.set_pos(4096)
+        d2.capture()
+        tok, got = 7, []
+        for i in range(10):
+            tok = d2.step(tok)
+            got.append(tok)
+        assert got == ids, (loop, got, ids)
+        assert np.allclose(d2.logits().cpu().numpy(), lg_ref, rtol=1e-3, atol=1e-3), loop
+        d2.close()
+    d.close()
 
 
 def test_decoder_refuses_to_run_past_its_cache():
