@@ -111,6 +111,9 @@ __global__ void __launch_bounds__(MmaCfg<D>::THREADS, 1)
   const int g = lane >> 2, t = lane & 3;
   const int kh = blockIdx.y, sp = blockIdx.x;
 
+  // the position is an L2 round trip away and everything below depends on it: ask for it
+  // before the barrier setup, not after
+  const int ctx = p.d_pos ? (int)(*(const volatile unsigned*)p.d_pos) + 1 : p.ctx;
   if (tid == 0) {
     for (int s = 0; s < STAGES; s++) {
       mbar_init(&full[s], 1);
@@ -120,7 +123,6 @@ __global__ void __launch_bounds__(MmaCfg<D>::THREADS, 1)
   }
   __syncthreads();
 
-  const int ctx = p.d_pos ? (int)(*p.d_pos) + 1 : p.ctx;
   if (p.d_pos && (ctx > p.kv_rows || ctx < 1)) {
     // position beyond the cache: read nothing, leave the tickets alone, tell the host
     pdl_wait();
