@@ -392,26 +392,39 @@ __global__ void add_rmsnorm_ar_kernel(const float* a, const float* __restrict__ 
 // ordinary fused prologue of the next projection, which reads a plain local vector instead of
 // polling system-scope packets from every SM.  Partials are added in rank order, so all ranks
 // compute identical bits.
+//
+// With two ranks the kernel does NOT wait for the pushing projection in front of it before it
+// polls: packets validate themselves by their tag, so polling may begin as soon as CTAs of that
+// projection exit, and the dependency wait comes LAST (this kernel's completion must still imply
+// the projection's, whose fix-up counters the next projection reuses; `out` was last read a whole
+// attention block / MLP ago).  Measured: 789 -> 805 tokens/s on 2 GPUs, no change on 4, and on 8
+// GPUs -- where the projection's grid leaves SMs free and the pollers really run beside it and
+// beside the peers' incoming stores -- 1035 -> 996, so from three ranks on the wait comes first.
+// The sequence number (a device-resident counter, stable within a token) is read before the wait
+// either way.
 __global__ void ar_sum_kernel(float* __restrict__ out, int n, CommDev comm, int* status) {
-  pdl_wait();
   pdl_launch_dependents();
-  const int i = blockIdx.x * blockDim.x + threadIdx.x;
-  if (i >= n) return;
   const unsigned seq = comm_seq(comm);
-  const uint2* st = comm.stage[comm.rank] + (size_t)(seq & 1u) * comm.size * comm.slot_floats + i;
-  uint2 pk[TP_MAX];
+  const bool early = comm.size <= 2;
+  if (!early) pdl_wait();
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < n) {
+    const uint2* st = comm.stage[comm.rank] + (size_t)(seq & 1u) * comm.size * comm.slot_floats + i;
+    uint2 pk[TP_MAX];
 #pragma unroll
-  for (int r = 0; r < TP_MAX; r++)
-    if (r < comm.size) pk[r] = ld_packet_sys(st + (size_t)r * comm.slot_floats);
-  float d = 0.f;
+    for (int r = 0; r < TP_MAX; r++)
+      if (r < comm.size) pk[r] = ld_packet_sys(st + (size_t)r * comm.slot_floats);
+    float d = 0.f;
 #pragma unroll
-  for (int r = 0; r < TP_MAX; r++)
-    if (r < comm.size) {
-      if (pk[r].y != seq + 1u)
-        pk[r] = wait_packet_bounded(st + (size_t)r * comm.slot_floats, seq + 1u, status, 300 + r);
-      d += __uint_as_float(pk[r].x);
-    }
-  out[i] = d;
+    for (int r = 0; r < TP_MAX; r++)
+      if (r < comm.size) {
+        if (pk[r].y != seq + 1u)
+          pk[r] = wait_packet_bounded(st + (size_t)r * comm.slot_floats, seq + 1u, status, 300 + r);
+        d += __uint_as_float(pk[r].x);
+      }
+    out[i] = d;
+  }
+  if (early) pdl_wait();
 }
 
 // Vocabulary-parallel argmax: each rank reduces its logits shard to a packed key
@@ -577,6 +590,10 @@ int launch_add_rmsnorm_ar(const float* a, const float* w, float* xout, float* ho
   return TLB_OK;
 }
 int launch_ar_sum(float* out, int n, const CommDev& comm, int* status, cudaStream_t s) {
+  // 128 threads: a CTA of this size does NOT fit into the registers an SM has left beside a
+  // 512-thread GEMV CTA, so the polling starts where that grid leaves SMs free or as its CTAs
+  // exit.  (64-thread CTAs, which fit beside it, were measured: 790 against 805 tokens/s on 2
+  // GPUs -- pollers sharing an SM with the stream cost it more than they save.)
   const int threads = 128;
   LaunchCfg lc(dim3((n + threads - 1) / threads), dim3(threads), 0, s, pdl_enabled());
   TLB_CUDA(cudaLaunchKernelEx(&lc.cfg, ar_sum_kernel, out, n, comm, status));
