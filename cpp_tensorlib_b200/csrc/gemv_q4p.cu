@@ -31,6 +31,13 @@
 // Split-K falls out of the unit ranges; partial row tiles are combined by the
 // last-arriving warp in worker order (deterministic, no float atomics, no spin-wait
 // on another CTA).
+//
+// Structure of this file: the work of a launch is a device function (gemv_q4p_body) over the
+// launch's parameters, a ring state and a producer cursor.  gemv_q4p_kernel calls it once.
+// gemv_q4p_chain_kernel / gemv_q4p_chain_loop_kernel (opt-in) call it once per phase for up to
+// four projections that depend on each other, with a grid-wide arrival counter between the
+// phases -- the one place in the library where CTAs of a launch wait for each other; the
+// wait is bounded and reports through the status block.
 #include <cuda_bf16.h>
 
 #include <cstdlib>
