@@ -206,6 +206,8 @@ def test_seven_billion_shape_two_layers_full_vocabulary(port, monkeypatch):
         assert np.allclose(d2.logits().cpu().numpy(), lg_ref, rtol=1e-3, atol=1e-3), loop
         d2.close()
     d.close()
+    del kv_ref
+    torch.cuda.empty_cache()
 
 
 def test_decoder_refuses_to_run_past_its_cache():
